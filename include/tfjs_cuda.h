@@ -1,0 +1,205 @@
+/*
+ * C ABI of the B200 `cuda` kernel backend for tfjs-core.
+ *
+ * This is the boundary a Node N-API shim (or any FFI: ctypes, cffi) binds.  It follows the
+ * shape of the reference's only native backend ABI, tfjs-backend-wasm/src/lib.cc:57-132
+ * (`register_tensor(id, shape, rank, dtype, ptr)`, `dispose_data(id)`, `add(a_id, b_id,
+ * out_id)`, `dispose()`): tensors are integer ids in a table owned by the library, kernels
+ * take ids.  Unlike the wasm ABI the table lives in an explicit per-device context, storage
+ * is cudaMalloc'd device memory owned by the library, and every call returns a status.
+ *
+ * Each entry point names the KernelBackend method (tfjs-core/src/backends/backend.ts) or
+ * engine call it serves.
+ *
+ * Conventions
+ *  - return 0 on success, a negative tfjs_cuda_status otherwise; never abort, never throw.
+ *  - tfjs_cuda_last_error(ctx) gives the message of the last failure on that context.
+ *  - kernels only enqueue work on the context's stream and return; tensor_read blocks.
+ *  - one context = one device + one stream; calls on one context come from one host
+ *    thread at a time.  Different contexts are independent (one per GPU for batch sharding).
+ *  - zero-sized tensors are legal everywhere and launch nothing.
+ *  - there is no CPU fallback: if no CUDA device is usable, ctx_create fails.
+ */
+#ifndef TFJS_CUDA_H_
+#define TFJS_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tfjs_cuda_ctx tfjs_cuda_ctx;
+typedef struct tfjs_cuda_event tfjs_cuda_event;
+typedef struct tfjs_cuda_graph tfjs_cuda_graph;
+typedef int64_t tfjs_tensor_id; /* 0 is never a valid id; use 0 for "absent" operands */
+
+typedef enum {
+  TFJS_CUDA_OK = 0,
+  TFJS_CUDA_ERR_INVALID_ARG = -1,
+  TFJS_CUDA_ERR_OOM = -2,
+  TFJS_CUDA_ERR_CUDA = -3,
+  TFJS_CUDA_ERR_TIMEOUT = -4,
+  TFJS_CUDA_ERR_UNSUPPORTED = -5,
+  TFJS_CUDA_ERR_NOT_FOUND = -6
+} tfjs_cuda_status;
+
+/* DataType subset the path stores; numbering of tfjs-backend-wasm/src/lib.cc:26-30. */
+typedef enum { TFJS_F32 = 0, TFJS_I32 = 1, TFJS_BOOL = 2 } tfjs_dtype;
+
+/* Activation of fused ops.  linear/relu/prelu are tfjs-core/src/ops/fused_util.ts:20;
+ * CLIP is an extension (relu6 = clip(0, 6), i.e. tf.clipByValue fused into the producer). */
+typedef enum {
+  TFJS_ACT_LINEAR = 0,
+  TFJS_ACT_RELU = 1,
+  TFJS_ACT_PRELU = 2,
+  TFJS_ACT_CLIP = 3
+} tfjs_activation;
+
+/* Contraction arithmetic: TF32 = one tcgen05 pass on tf32-rounded operands (max error
+ * ~1e-3 relative); TF32X3 = three passes on hi/lo splits (fp32-level, ~1e-6). */
+typedef enum { TFJS_MATH_TF32X3 = 0, TFJS_MATH_TF32 = 1 } tfjs_math_mode;
+
+typedef enum { TFJS_BIN_ADD = 0, TFJS_BIN_SUB = 1, TFJS_BIN_MUL = 2, TFJS_BIN_DIV = 3,
+               TFJS_BIN_PRELU = 4, TFJS_BIN_NOT_EQUAL = 5 } tfjs_binary_op;
+typedef enum { TFJS_UN_RELU = 0, TFJS_UN_CLIP = 1, TFJS_UN_EXP = 2, TFJS_UN_LOG = 3,
+               TFJS_UN_INT = 4 } tfjs_unary_op;
+typedef enum { TFJS_RED_SUM = 0, TFJS_RED_MAX = 1, TFJS_RED_ARGMAX = 2 } tfjs_reduce_op;
+
+/* Conv2DInfo, tfjs-core/src/ops/conv_util.ts:43-64, channelsLast (NHWC) only; padInfo is
+ * flattened.  The op layer computes it (computeConv2DInfo :123-182) and passes it down. */
+typedef struct {
+  int32_t batchSize, inHeight, inWidth, inChannels;
+  int32_t outHeight, outWidth, outChannels;
+  int32_t strideHeight, strideWidth;
+  int32_t dilationHeight, dilationWidth;
+  int32_t filterHeight, filterWidth;
+  int32_t effectiveFilterHeight, effectiveFilterWidth;
+  int32_t padTop, padBottom, padLeft, padRight;
+} tfjs_conv2d_info;
+
+/* Fused epilogue: out = act(acc + bias).  bias/prelu are tensor ids or 0.  bias_len and
+ * prelu_len are 1 (scalar) or the output channel count (a vector broadcast along the
+ * inner-most axis); any other broadcast shape is composed by the caller from the linear
+ * op followed by tfjs_cuda_binary, as MathBackendCPU does (backend_cpu.ts:542-555). */
+typedef struct {
+  tfjs_tensor_id bias;
+  int64_t bias_len;
+  int32_t activation; /* tfjs_activation */
+  tfjs_tensor_id prelu;
+  int64_t prelu_len;
+  float clip_lo, clip_hi; /* TFJS_ACT_CLIP only */
+} tfjs_epilogue;
+
+typedef struct {
+  int64_t num_tensors;        /* live entries in the tensor table */
+  int64_t bytes_in_use;       /* device bytes held by live tensors */
+  int64_t bytes_reserved;     /* device bytes obtained from cudaMalloc (live + cached) */
+  int64_t num_buffers_cached; /* free buffers waiting for reuse */
+  int64_t num_device_allocs;  /* cudaMalloc calls so far */
+} tfjs_cuda_mem_stats;
+
+/* ---- context: the backend factory of tf.registerBackend('cuda', factory)
+ *      (tfjs-core/src/engine.ts:220-307) creates one; KernelBackend.dispose() destroys it. */
+int tfjs_cuda_ctx_create(int device_ordinal, tfjs_cuda_ctx** out);
+int tfjs_cuda_ctx_destroy(tfjs_cuda_ctx* ctx);
+const char* tfjs_cuda_last_error(const tfjs_cuda_ctx* ctx);
+/* Flags mirrored from ENV.registerFlag (environment.ts:32-142).  Keys: "math_mode"
+ * (tfjs_math_mode), "use_tensor_cores" (0 forces the CUDA-core kernels), "debug_sync". */
+int tfjs_cuda_ctx_set_option(tfjs_cuda_ctx* ctx, const char* key, double value);
+/* Blocks until all enqueued work is done; TFJS_CUDA_ERR_TIMEOUT after timeout_ms (<0: none). */
+int tfjs_cuda_ctx_sync(tfjs_cuda_ctx* ctx, int timeout_ms);
+/* KernelBackend.memory() (backend.ts:114-116). */
+int tfjs_cuda_ctx_memory(tfjs_cuda_ctx* ctx, tfjs_cuda_mem_stats* out);
+/* KernelBackend.time(f) (backend.ts:92-94): bracket f() with these; *kernel_ms is device
+ * time between them, *num_launches the kernels this library launched in between. */
+int tfjs_cuda_ctx_time_begin(tfjs_cuda_ctx* ctx);
+int tfjs_cuda_ctx_time_end(tfjs_cuda_ctx* ctx, float* kernel_ms, int64_t* num_launches);
+/* Total kernels launched by this context since creation. */
+int64_t tfjs_cuda_ctx_launch_count(const tfjs_cuda_ctx* ctx);
+/* The cudaStream_t of the context (as void*), for callers that time with their own events. */
+void* tfjs_cuda_ctx_stream(tfjs_cuda_ctx* ctx);
+
+/* ---- tensor storage: KernelBackend.register / write / readSync / read / disposeData
+ *      (backend.ts:95-113; CPU backend_cpu.ts:102-129, 199-237). */
+int tfjs_cuda_tensor_register(tfjs_cuda_ctx* ctx, tfjs_tensor_id* out_id, int rank,
+                              const int64_t* shape, int dtype);
+int tfjs_cuda_tensor_write(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, const void* host, size_t nbytes);
+int tfjs_cuda_tensor_read(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, void* host, size_t nbytes);
+/* Non-blocking readback for KernelBackend.read(): the copy into `host` (pinned memory for a
+ * truly asynchronous copy) completes when the event does. */
+int tfjs_cuda_tensor_read_async(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, void* host, size_t nbytes,
+                                tfjs_cuda_event** out_event);
+int tfjs_cuda_event_query(tfjs_cuda_event* ev); /* 1 done, 0 pending, <0 error */
+int tfjs_cuda_event_wait(tfjs_cuda_event* ev, int timeout_ms);
+int tfjs_cuda_event_destroy(tfjs_cuda_event* ev);
+/* Idempotent, like backend_cpu.ts:228-237; unknown ids are ignored. */
+int tfjs_cuda_tensor_dispose(tfjs_cuda_ctx* ctx, tfjs_tensor_id id);
+/* Device pointer and byte size of a tensor's storage (zero-copy interop, benchmarks). */
+int tfjs_cuda_tensor_device_ptr(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, void** ptr, size_t* nbytes);
+/* Pinned host staging memory for write/read_async callers. */
+int tfjs_cuda_host_alloc(void** ptr, size_t nbytes);
+int tfjs_cuda_host_free(void* ptr);
+
+/* Extension: keep a weight tensor as uint8 affine-quantised bytes, w = q*scale + min
+ * (tfjs-core/src/io/io_utils.ts:122-146, manifest field io/types.ts:103-107).  The id can be
+ * passed as the filter / b operand of conv2d and batch_matmul (dequantised in shared memory
+ * inside the GEMM main loop) and of depthwise_conv2d.  tensor_read returns the float32
+ * values decodeWeights would have produced. */
+int tfjs_cuda_tensor_register_quantized(tfjs_cuda_ctx* ctx, tfjs_tensor_id* out_id, int rank,
+                                        const int64_t* shape, const uint8_t* q, double scale,
+                                        double min);
+
+/* ---- contractions.
+ * KernelBackend.batchMatMul / fusedBatchMatMul (backend.ts:128-138; CPU :491-555):
+ * a is [batch, a_d1, a_d2], b is [batch, b_d1, b_d2]; out is [batch, M, N] with
+ * M = transpose_a ? a_d2 : a_d1, N = transpose_b ? b_d1 : b_d2.  epi may be NULL. */
+int tfjs_cuda_batch_matmul(tfjs_cuda_ctx* ctx, tfjs_tensor_id a, tfjs_tensor_id b,
+                           tfjs_tensor_id out, int32_t batch, int32_t a_d1, int32_t a_d2,
+                           int32_t b_d1, int32_t b_d2, int transpose_a, int transpose_b,
+                           const tfjs_epilogue* epi);
+/* KernelBackend.conv2d / fusedConv2d (backend.ts:414-422; CPU :1536-1616). */
+int tfjs_cuda_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id filter,
+                     tfjs_tensor_id out, const tfjs_conv2d_info* info, const tfjs_epilogue* epi);
+
+/* ---- memory-bound kernels.
+ * KernelBackend.depthwiseConv2D (backend.ts:431-434; CPU :1979-2035).  epi != NULL is the
+ * fused extension depthwise + bias + activation; NULL is the reference method. */
+int tfjs_cuda_depthwise_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id filter,
+                               tfjs_tensor_id out, const tfjs_conv2d_info* info,
+                               const tfjs_epilogue* epi);
+/* KernelBackend.avgPool / maxPool (backend.ts:453-462; CPU :2273-2343, 2869-2873). */
+int tfjs_cuda_pool2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id out,
+                     const tfjs_conv2d_info* info, int is_avg);
+/* KernelBackend.add / subtract / multiply / realDivide / prelu / notEqual (backend.ts:164-178,
+ * 329-331; CPU broadcastedBinaryOp :3515-3549).  Shapes follow broadcast_util.ts:58-87; out
+ * must be registered with the broadcast shape. */
+int tfjs_cuda_binary(tfjs_cuda_ctx* ctx, int op, tfjs_tensor_id a, int a_rank,
+                     const int64_t* a_shape, tfjs_tensor_id b, int b_rank, const int64_t* b_shape,
+                     tfjs_tensor_id out);
+/* KernelBackend.relu / clip / exp / log / int (backend.ts:300-346; CPU :1094-1275). */
+int tfjs_cuda_unary(tfjs_cuda_ctx* ctx, int op, tfjs_tensor_id x, tfjs_tensor_id out, float p0,
+                    float p1);
+/* KernelBackend.sum / max / argMax over the inner-most axes (backend.ts:183, 198, 255;
+ * CPU :590-611, 686-712, 906-929): x viewed as [outer, inner]. */
+int tfjs_cuda_reduce_last(tfjs_cuda_ctx* ctx, int op, tfjs_tensor_id x, tfjs_tensor_id out,
+                          int64_t outer, int64_t inner);
+/* Extension: tf.softmax over the last axis as one kernel, with the stage-by-stage float32
+ * rounding of the op-layer chain (ops/softmax.ts:57-63, ops/reduction_ops.ts:56-73). */
+int tfjs_cuda_softmax_last(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id out, int64_t outer,
+                           int64_t inner);
+/* KernelBackend.cast (backend.ts:484-486; backend_util.ts:36-71) where a copy is needed:
+ * converts x's stored dtype to out's dtype (float->int truncates, ->bool is != 0). */
+int tfjs_cuda_cast(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id out);
+
+/* ---- extension: CUDA-graph capture of a sequence of calls on the context. */
+int tfjs_cuda_graph_begin(tfjs_cuda_ctx* ctx);
+int tfjs_cuda_graph_end(tfjs_cuda_ctx* ctx, tfjs_cuda_graph** out);
+int tfjs_cuda_graph_launch(tfjs_cuda_ctx* ctx, tfjs_cuda_graph* graph);
+int tfjs_cuda_graph_destroy(tfjs_cuda_ctx* ctx, tfjs_cuda_graph* graph);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TFJS_CUDA_H_ */

@@ -1,0 +1,317 @@
+"""CUDA kernels against the CPU oracle on seeded inputs (through the op layer and the C ABI).
+
+Bars: memory-bound kernels (depthwise, direct conv, bias/clip/relu, pooling, softmax) follow
+the reference's operation order and must agree to <= 2 ulp (double rounding of the oracle's
+float64 temporaries is the only source of difference); contractions on tensor cores use a
+different summation order, so they are held to the stated tolerances: max relative error
+(floored at 1 % of the tensor's largest magnitude) <= 1e-5 for 3xTF32 and <= 1e-3 for TF32.
+"""
+import numpy as np
+import pytest
+
+import oracle
+from gpu_util import rel_err, tf, ulp_diff  # noqa: F401
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"3xtf32": 1e-5, "tf32": 1e-3}
+
+
+def _rng(seed):
+    return np.random.Generator(np.random.PCG64(seed))
+
+
+# ---- BASELINE config 1: fused matMul 256x1024x1024 + bias + relu, seed 0 ----------------------
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
+def test_config1_fused_matmul(tf, mode):
+    rng = _rng(0)
+    a = rng.uniform(-1, 1, (256, 1024)).astype(np.float32)
+    lim = np.sqrt(6.0 / 2048)
+    b = rng.uniform(-lim, lim, (1024, 1024)).astype(np.float32)
+    bias = rng.normal(0, 0.01, 1024).astype(np.float32)
+    want = oracle.fused_matmul(a[None], b[None], bias=bias, activation="relu")[0]
+    bk = tf.ENGINE.backend
+    bk.setMathMode(mode)
+    try:
+        got = tf.ops.fused_matmul(tf.ops.tensor(a), tf.ops.tensor(b), bias=tf.ops.tensor(bias),
+                                  activation="relu").dataSync().reshape(want.shape)
+    finally:
+        bk.setMathMode("3xtf32")
+    assert rel_err(got, want) <= TOL[mode]
+
+
+# ---- BASELINE config 2: fused conv2d 8x56x56x64 * 3x3x64x64, same, bias, relu, seed 1 ---------
+def test_config2_fused_conv2d(tf):
+    rng = _rng(1)
+    x = rng.uniform(0, 1, (8, 56, 56, 64)).astype(np.float32)
+    w = rng.normal(0, np.sqrt(2.0 / (3 * 3 * 64)), (3, 3, 64, 64)).astype(np.float32)
+    bias = rng.normal(0, 0.01, 64).astype(np.float32)
+    ci = oracle.compute_conv2d_info(x.shape, w.shape, 1, 1, "same")
+    want = oracle.fused_conv2d(x, w, ci, bias=bias, activation="relu")
+    got = tf.ops.fused_conv2d(tf.ops.tensor(x), tf.ops.tensor(w), 1, "same", bias=tf.ops.tensor(bias),
+                              activation="relu").dataSync().reshape(want.shape)
+    assert rel_err(got, want) <= 1e-5
+
+
+# ---- BASELINE config 3: depthwise 8x112x112x32 * 3x3x32x1 s2 same, then bias and relu6, seed 2 -
+@pytest.mark.parametrize("fused", [False, True])
+def test_config3_depthwise_bias_relu6(tf, fused):
+    rng = _rng(2)
+    x = rng.uniform(0, 1, (8, 112, 112, 32)).astype(np.float32)
+    w = rng.normal(0, np.sqrt(2.0 / 9), (3, 3, 32, 1)).astype(np.float32)
+    bias = rng.normal(0, 0.01, 32).astype(np.float32)
+    ci = oracle.compute_conv2d_info(x.shape, w.shape, 2, 1, "same", None, True)
+    want = oracle.unary("clip", oracle.binary("add", oracle.depthwise_conv2d(x, w, ci), bias), 0, 6)
+    xt, wt, bt = tf.ops.tensor(x), tf.ops.tensor(w), tf.ops.tensor(bias)
+    if fused:
+        from tfjs_core_b200 import conv_util
+        dci = conv_util.compute_conv2d_info(x.shape, w.shape, 2, 1, "same", None, True)
+        got = tf.ENGINE.backend.fusedDepthwiseConv2D(xt, wt, dci, bt, "relu6")
+    else:
+        got = tf.ops.clip_by_value(tf.ops.add(tf.ops.depthwise_conv2d(xt, wt, 2, "same"), bt), 0, 6)
+    got = got.dataSync().reshape(want.shape)
+    assert ulp_diff(got, want) <= 2
+
+
+# ---- contraction shapes: tile edges, tails, transposes -----------------------------------------
+@pytest.mark.parametrize("m,k,n", [(130, 68, 72), (1, 32, 8), (127, 4, 1000), (300, 96, 40),
+                                   (128, 32, 64), (513, 260, 264), (64, 1024, 1000)])
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
+def test_matmul_shapes(tf, m, k, n, mode):
+    rng = _rng(m * 7 + k * 3 + n)
+    a = rng.uniform(-1, 1, (1, m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (1, k, n)).astype(np.float32)
+    bias = rng.normal(0, 1, n).astype(np.float32)
+    want = oracle.fused_matmul(a, b, bias=bias, activation=None)
+    bk = tf.ENGINE.backend
+    bk.setMathMode(mode)
+    try:
+        got = tf.ops.fused_matmul(tf.ops.tensor(a), tf.ops.tensor(b), bias=tf.ops.tensor(bias)).dataSync()
+    finally:
+        bk.setMathMode("3xtf32")
+    assert rel_err(got.reshape(want.shape), want) <= TOL[mode]
+
+
+@pytest.mark.parametrize("ta,tb", [(False, True), (True, False), (True, True)])
+def test_matmul_transposes_tensor_core(tf, ta, tb):
+    rng = _rng(11)
+    m, k, n, batch = 96, 64, 48, 3
+    a = rng.uniform(-1, 1, (batch, k, m) if ta else (batch, m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (batch, n, k) if tb else (batch, k, n)).astype(np.float32)
+    want = oracle.batch_matmul(a, b, ta, tb)
+    got = tf.ops.matmul(tf.ops.tensor(a), tf.ops.tensor(b), ta, tb).dataSync().reshape(want.shape)
+    assert rel_err(got, want) <= 1e-5
+
+
+def test_matmul_integer_exact(tf):
+    """Small integers are exact in tf32, so the tensor-core result must equal the oracle's
+    bit for bit whatever the summation order (the idea of tfjs-webgpu/src/matmul_test.ts:58)."""
+    rng = _rng(5)
+    a = rng.integers(0, 10, (1, 260, 132)).astype(np.float32)
+    b = rng.integers(0, 10, (1, 132, 136)).astype(np.float32)
+    want = oracle.batch_matmul(a, b)
+    for mode in ("3xtf32", "tf32"):
+        tf.ENGINE.backend.setMathMode(mode)
+        got = tf.ops.matmul(tf.ops.tensor(a), tf.ops.tensor(b)).dataSync().reshape(want.shape)
+        tf.ENGINE.backend.setMathMode("3xtf32")
+        assert np.array_equal(got, want), mode
+
+
+def test_matmul_zero_sized(tf):
+    # ops/matmul_test.ts:621-642
+    a = tf.ops.tensor(np.zeros((0, 3), np.float32), [0, 3])
+    b = tf.ops.tensor(np.ones((3, 2), np.float32))
+    out = tf.ops.matmul(a, b)
+    assert out.shape == [0, 2] and out.dataSync().size == 0
+
+
+def test_matmul_nan_propagates(tf):
+    a = np.ones((1, 128, 32), np.float32)
+    a[0, 5, 7] = np.nan
+    b = np.ones((1, 32, 16), np.float32)
+    got = tf.ops.matmul(tf.ops.tensor(a), tf.ops.tensor(b)).dataSync().reshape(128, 16)
+    assert np.isnan(got[5]).all() and not np.isnan(np.delete(got, 5, 0)).any()
+
+
+# ---- pointwise conv through the GEMM, with every epilogue -----------------------------------
+@pytest.mark.parametrize("act", ["linear", "relu", "prelu", "relu6"])
+def test_pointwise_conv_epilogues(tf, act):
+    rng = _rng(21)
+    x = rng.uniform(-1, 1, (2, 14, 14, 64)).astype(np.float32)
+    w = rng.uniform(-0.3, 0.3, (1, 1, 64, 128)).astype(np.float32)
+    bias = rng.normal(0, 0.5, 128).astype(np.float32)
+    alpha = rng.uniform(0, 1, 128).astype(np.float32)
+    ci = oracle.compute_conv2d_info(x.shape, w.shape, 1, 1, "same")
+    y = oracle.binary("add", oracle.conv2d(x, w, ci), bias)
+    if act == "relu":
+        want = oracle.unary("relu", y)
+    elif act == "prelu":
+        want = oracle.binary("prelu", y, alpha)
+    elif act == "relu6":
+        want = oracle.unary("clip", y, 0, 6)
+    else:
+        want = y
+    from tfjs_core_b200 import conv_util
+    dci = conv_util.compute_conv2d_info(x.shape, w.shape, 1, 1, "same")
+    got = tf.ENGINE.backend.fusedConv2d(tf.ops.tensor(x), tf.ops.tensor(w), dci, tf.ops.tensor(bias), act,
+                                        tf.ops.tensor(alpha) if act == "prelu" else None)
+    assert rel_err(got.dataSync().reshape(want.shape), want) <= 1e-5
+
+
+# ---- memory-bound kernels: exactness --------------------------------------------------------
+@pytest.mark.parametrize("shape,fshape,stride,pad,dil", [
+    ((2, 9, 11, 8), (3, 3, 8, 1), 1, "same", 1),
+    ((2, 10, 10, 12), (3, 3, 12, 1), 2, "same", 1),
+    ((1, 7, 7, 1024), (3, 3, 1024, 1), 1, "same", 1),
+    ((1, 13, 9, 5), (3, 3, 5, 2), 1, "valid", 1),
+    ((1, 12, 12, 4), (2, 3, 4, 1), 1, "same", 2),
+    ((3, 15, 15, 16), (3, 3, 16, 1), 2, "valid", 1),
+])
+def test_depthwise_shapes(tf, shape, fshape, stride, pad, dil):
+    rng = _rng(sum(shape))
+    x = rng.uniform(-1, 1, shape).astype(np.float32)
+    w = rng.uniform(-1, 1, fshape).astype(np.float32)
+    ci = oracle.compute_conv2d_info(shape, fshape, stride, dil, pad, None, True)
+    want = oracle.depthwise_conv2d(x, w, ci)
+    got = tf.ops.depthwise_conv2d(tf.ops.tensor(x), tf.ops.tensor(w), stride, pad, "NHWC", dil)
+    assert got.shape == list(want.shape)
+    assert ulp_diff(got.dataSync(), want) <= 2
+
+
+@pytest.mark.parametrize("shape,fshape,stride,pad,dil", [
+    ((2, 16, 16, 3), (3, 3, 3, 32), 2, "same", 1),      # stem geometry
+    ((1, 15, 17, 3), (3, 3, 3, 32), 2, "same", 1),      # odd input, conv_util_test.ts:82-99
+    ((1, 9, 9, 5), (3, 3, 5, 7), 1, "valid", 1),
+    ((2, 8, 8, 4), (1, 1, 4, 6), 2, "same", 1),
+    ((1, 10, 10, 2), (2, 2, 2, 3), 1, "same", 2),
+    ((1, 6, 6, 8), (3, 3, 8, 16), 1, 1, 1),
+])
+def test_direct_conv_shapes(tf, shape, fshape, stride, pad, dil):
+    rng = _rng(sum(shape) + 1)
+    x = rng.uniform(-1, 1, shape).astype(np.float32)
+    w = rng.uniform(-1, 1, fshape).astype(np.float32)
+    ci = oracle.compute_conv2d_info(shape, fshape, stride, dil, pad)
+    want = oracle.conv2d(x, w, ci)
+    got = tf.ops.conv2d(tf.ops.tensor(x), tf.ops.tensor(w), stride, pad, "NHWC", dil)
+    assert got.shape == list(want.shape)
+    assert ulp_diff(got.dataSync(), want) <= 2
+
+
+def test_elementwise_and_reductions(tf):
+    rng = _rng(31)
+    x = rng.normal(0, 3, (4, 7, 7, 36)).astype(np.float32)
+    b = rng.normal(0, 1, 36).astype(np.float32)
+    col = rng.normal(0, 1, (4, 1, 7, 1)).astype(np.float32)
+    o = tf.ops
+    xt = o.tensor(x)
+    assert np.array_equal(o.add(xt, o.tensor(b)).dataSync().reshape(x.shape), oracle.binary("add", x, b))
+    assert np.array_equal(o.add(o.tensor(b), xt).dataSync().reshape(x.shape), oracle.binary("add", b, x))
+    for name, fn in (("add", o.add), ("sub", o.sub), ("mul", o.mul), ("div", o.div)):
+        assert np.array_equal(fn(xt, o.tensor(col)).dataSync().reshape(x.shape), oracle.binary(name, x, col)), name
+    assert np.array_equal(o.relu(xt).dataSync().reshape(x.shape), oracle.unary("relu", x))
+    assert np.array_equal(o.clip_by_value(xt, 0, 6).dataSync().reshape(x.shape), oracle.unary("clip", x, 0, 6))
+    assert ulp_diff(o.exp(xt).dataSync(), oracle.unary("exp", x)) <= 1
+    xp = np.abs(x) + 0.1
+    assert ulp_diff(o.log(o.tensor(xp)).dataSync(), oracle.unary("log", xp)) <= 1
+    r = x.reshape(-1, 36)
+    assert ulp_diff(o.sum(o.tensor(r), -1).dataSync(), oracle.sum_last(r)) <= 1
+    assert np.array_equal(o.max(o.tensor(r), -1).dataSync(), oracle.max_last(r))
+    assert np.array_equal(o.arg_max(o.tensor(r), -1).dataSync(), oracle.argmax_last(r))
+
+
+def test_nan_rules(tf):
+    o = tf.ops
+    x = np.array([[np.nan, 1, 2], [1, np.nan, 3], [-np.inf, -np.inf, -np.inf]], np.float32)
+    assert np.array_equal(o.max(o.tensor(x), -1).dataSync(), oracle.max_last(x), equal_nan=True)
+    assert np.array_equal(o.arg_max(o.tensor(x), -1).dataSync(), oracle.argmax_last(x))
+    v = np.array([np.nan, -1, 0, 7], np.float32)
+    assert np.array_equal(o.relu(o.tensor(v)).dataSync(), oracle.unary("relu", v), equal_nan=True)
+    assert np.array_equal(o.clip_by_value(o.tensor(v), 0, 6).dataSync(), oracle.unary("clip", v, 0, 6),
+                          equal_nan=True)
+
+
+def test_softmax_matches_chain_and_oracle(tf):
+    rng = _rng(41)
+    x = rng.normal(0, 4, (64, 1000)).astype(np.float32)
+    want = oracle.softmax_last(x)
+    chain = tf.ops.softmax(tf.ops.tensor(x)).dataSync().reshape(x.shape)
+    fused = tf.ops.fused_softmax(tf.ops.tensor(x)).dataSync().reshape(x.shape)
+    assert ulp_diff(fused, want) <= 2 and ulp_diff(chain, want) <= 2
+    assert ulp_diff(fused, chain) <= 2
+
+
+def test_pooling(tf):
+    rng = _rng(51)
+    x = rng.normal(0, 1, (3, 7, 7, 1024)).astype(np.float32)
+    ci = oracle.compute_pool2d_info(x.shape, [7, 7], 1, 1, "valid")
+    got = tf.ops.avg_pool(tf.ops.tensor(x), [7, 7], 1, "valid").dataSync().reshape(3, 1, 1, 1024)
+    assert np.array_equal(got, oracle.pool(x, ci, "avg"))
+    x2 = rng.normal(0, 1, (2, 9, 8, 6)).astype(np.float32)
+    for kind, op in (("max", tf.ops.max_pool), ("avg", tf.ops.avg_pool)):
+        ci = oracle.compute_pool2d_info(x2.shape, [3, 2], 2, 1, "same")
+        got = op(tf.ops.tensor(x2), [3, 2], 2, "same")
+        assert np.array_equal(got.dataSync().reshape(ci.outShape), oracle.pool(x2, ci, kind)), kind
+
+
+# ---- quantised weights ----------------------------------------------------------------------
+def test_quantized_weights_pointwise_and_depthwise(tf):
+    rng = _rng(61)
+    bk = tf.ENGINE.backend
+    x = rng.uniform(-1, 1, (2, 14, 14, 64)).astype(np.float32)
+    q = rng.integers(0, 256, (1, 1, 64, 96), dtype=np.uint8)
+    scale, mn = 0.0123, -128 * 0.0123
+    w = oracle.dequant_u8(q, scale, mn)
+    ci = oracle.compute_conv2d_info(x.shape, w.shape, 1, 1, "same")
+    want = oracle.conv2d(x, w, ci)
+    wq = bk.registerQuantized(list(q.shape), q, scale, mn)
+    assert np.array_equal(wq.dataSync().reshape(w.shape), w)
+    got = tf.ops.conv2d(tf.ops.tensor(x), wq, 1, "same").dataSync().reshape(want.shape)
+    assert rel_err(got, want) <= 1e-5
+    qd = rng.integers(0, 256, (3, 3, 64, 1), dtype=np.uint8)
+    wd = oracle.dequant_u8(qd, scale, mn)
+    cid = oracle.compute_conv2d_info(x.shape, wd.shape, 1, 1, "same", None, True)
+    wantd = oracle.depthwise_conv2d(x, wd, cid)
+    gotd = tf.ops.depthwise_conv2d(tf.ops.tensor(x), bk.registerQuantized(list(qd.shape), qd, scale, mn), 1, "same")
+    assert ulp_diff(gotd.dataSync(), wantd) <= 2
+
+
+# ---- whole network ---------------------------------------------------------------------------
+@pytest.mark.parametrize("quantized", [False, True])
+def test_mobilenet_small_batch(tf, quantized):
+    from oracle import mobilenet as oracle_net
+    from tfjs_core_b200 import mobilenet
+    params = mobilenet.make_weights(4 if quantized else 3, quantized=quantized, gain=1.5)
+    x = mobilenet.make_input(3, 2)
+    want_logits, want_probs = oracle_net.forward(x, params)
+    net = mobilenet.MobileNetV1(params, tf.ENGINE.backend)
+    try:
+        for fwd in (net.forward_fused, net.forward_reference_api):
+            before = tf.ENGINE.backend.launchCount()
+            logits, probs = fwd(tf.ops.tensor(x))
+            launches = tf.ENGINE.backend.launchCount() - before
+            got = logits.dataSync().reshape(want_logits.shape)
+            assert rel_err(got, want_logits) <= 1e-4, fwd.__name__
+            assert (got.argmax(1) == want_logits.argmax(1)).all()
+            assert np.abs(probs.dataSync().reshape(want_probs.shape) - want_probs).max() <= 1e-5
+            assert launches == (30 if fwd == net.forward_fused else 77), launches
+    finally:
+        net.dispose()
+
+
+def test_memory_is_recycled(tf):
+    """tf.memory()-style leak check (engine_test.ts:307-368) plus the allocator's promise that a
+    steady-state loop does not call cudaMalloc."""
+    rng = _rng(71)
+    x = tf.ops.tensor(rng.uniform(-1, 1, (4, 28, 28, 32)).astype(np.float32))
+    w = tf.ops.tensor(rng.uniform(-1, 1, (1, 1, 32, 64)).astype(np.float32))
+
+    def step():
+        return tf.ENGINE.tidy(lambda: tf.ops.clip_by_value(tf.ops.conv2d(x, w, 1, "same"), 0, 6).dataSync())
+    step()
+    m0 = tf.ENGINE.memory()
+    for _ in range(5):
+        step()
+    m1 = tf.ENGINE.memory()
+    assert m1["numTensors"] == m0["numTensors"] and m1["numBytes"] == m0["numBytes"]
+    assert m1["numDeviceAllocs"] == m0["numDeviceAllocs"]
+    assert m1["numBytesInGPU"] == m0["numBytesInGPU"]

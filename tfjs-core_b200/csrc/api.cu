@@ -1,0 +1,254 @@
+// extern "C" entry points of the contraction, convolution and pooling kernels: argument
+// checking, operand preparation (weight repacking cache, transposes) and kernel selection.
+#include "common.cuh"
+
+namespace {
+
+// float32 view of a tensor for kernels that read plain floats; a quantised tensor gets a
+// cached dequantised copy (io_utils.ts:139 arithmetic).
+int float_view(tfjs_cuda_ctx* ctx, TensorEntry* t, const float** out) {
+  if (!t->quant.quantized) {
+    *out = (const float*)t->ptr;
+    return TFJS_CUDA_OK;
+  }
+  if (!t->deq || t->deq_version != t->version) {
+    if (!t->deq) {
+      void* p;
+      int rc = ctx_alloc(ctx, (size_t)t->size * 4, &p, &t->deq_capacity);
+      if (rc) return rc;
+      t->deq = (float*)p;
+    }
+    int rc = launch_dequant(ctx, (const uint8_t*)t->ptr, t->deq, t->size, t->quant.scale, t->quant.min);
+    if (rc) return rc;
+    t->deq_version = t->version;
+  }
+  *out = t->deq;
+  return TFJS_CUDA_OK;
+}
+
+// K-major tf32 hi/lo planes of a [K, N] operand (or of its [N, K] transpose), cached on the
+// tensor entry until the tensor is rewritten.  Weights are constants in inference, so the
+// repack runs once per weight tensor.
+int packed_weights(tfjs_cuda_ctx* ctx, TensorEntry* w, int64_t offset_elems, int64_t K, int64_t N,
+                   bool source_is_nk, bool cacheable, PackedWeights* out, bool* temporary) {
+  const int64_t kp = (K + 3) / 4 * 4;
+  PackedWeights& c = w->packed;
+  *temporary = !cacheable;
+  if (cacheable && c.hi && c.version == w->version && c.n == N && c.k == K &&
+      c.transposed_source == source_is_nk) {
+    *out = c;
+    return TFJS_CUDA_OK;
+  }
+  PackedWeights fresh;
+  fresh.n = N;
+  fresh.k = K;
+  fresh.kp = kp;
+  fresh.version = w->version;
+  fresh.transposed_source = source_is_nk;
+  void *hi, *lo;
+  int rc = ctx_alloc(ctx, (size_t)(N * kp) * 4, &hi, &fresh.capacity);
+  if (rc) return rc;
+  rc = ctx_alloc(ctx, (size_t)(N * kp) * 4, &lo, &fresh.capacity);
+  if (rc) {
+    ctx_free(ctx, hi, fresh.capacity);
+    return rc;
+  }
+  fresh.hi = (float*)hi;
+  fresh.lo = (float*)lo;
+  const bool u8 = w->quant.quantized;
+  const void* src = u8 ? (const void*)((const uint8_t*)w->ptr + offset_elems)
+                       : (const void*)((const float*)w->ptr + offset_elems);
+  rc = launch_pack_weights(ctx, src, u8, w->quant.scale, w->quant.min, K, N,
+                           source_is_nk ? 1 : N, source_is_nk ? K : 1, kp, fresh.hi, fresh.lo);
+  if (rc) {
+    ctx_free(ctx, hi, fresh.capacity);
+    ctx_free(ctx, lo, fresh.capacity);
+    return rc;
+  }
+  if (cacheable) {
+    if (c.hi) ctx_free(ctx, c.hi, c.capacity);
+    if (c.lo) ctx_free(ctx, c.lo, c.capacity);
+    c = fresh;
+  }
+  *out = fresh;
+  return TFJS_CUDA_OK;
+}
+
+void release_temporary(tfjs_cuda_ctx* ctx, const PackedWeights& p, bool temporary) {
+  if (!temporary) return;
+  ctx_free(ctx, p.hi, p.capacity);
+  ctx_free(ctx, p.lo, p.capacity);
+}
+
+// out[M, N] = epi(a[M, K] . w), with w a [K, N] (or [N, K] when source_is_nk) operand.
+int gemm_dispatch(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, TensorEntry* w,
+                  int64_t w_offset, bool source_is_nk, bool cacheable, float* out, int64_t N,
+                  const EpilogueArgs& epi) {
+  if (ctx->use_tensor_cores && tcgen05_gemm_supported(M, N, K)) {
+    PackedWeights pw;
+    bool temporary;
+    int rc = packed_weights(ctx, w, w_offset, K, N, source_is_nk, cacheable, &pw, &temporary);
+    if (rc) return rc;
+    rc = launch_gemm_tcgen05(ctx, a, M, K, pw.hi, pw.lo, pw.kp, out, N, epi, ctx->math_mode);
+    release_temporary(ctx, pw, temporary);
+    return rc;
+  }
+  const float* wf;
+  int rc = float_view(ctx, w, &wf);
+  if (rc) return rc;
+  wf += w_offset;
+  return launch_gemm_simt(ctx, a, wf, out, 1, (int)M, (int)N, (int)K, 0, K, 1, 0,
+                          source_is_nk ? 1 : N, source_is_nk ? K : 1, epi);
+}
+
+}  // namespace
+
+extern "C" int tfjs_cuda_batch_matmul(tfjs_cuda_ctx* ctx, tfjs_tensor_id a_id, tfjs_tensor_id b_id,
+                                      tfjs_tensor_id out_id, int32_t batch, int32_t a_d1,
+                                      int32_t a_d2, int32_t b_d1, int32_t b_d2, int transpose_a,
+                                      int transpose_b, const tfjs_epilogue* epi) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  TFJS_REQUIRE(ctx, batch >= 0 && a_d1 >= 0 && a_d2 >= 0 && b_d1 >= 0 && b_d2 >= 0, "negative extent");
+  const int64_t K = transpose_a ? a_d1 : a_d2;
+  const int64_t M = transpose_a ? a_d2 : a_d1;
+  const int64_t Kb = transpose_b ? b_d2 : b_d1;
+  const int64_t N = transpose_b ? b_d1 : b_d2;
+  // matmul.ts:81-87: inner shapes must match
+  TFJS_REQUIRE(ctx, K == Kb, "Error in matMul: inner shapes (%lld) and (%lld) must match",
+               (long long)K, (long long)Kb);
+  TensorEntry *a, *b, *o;
+  int rc = get_f32(ctx, a_id, (int64_t)batch * a_d1 * a_d2, "a", &a);
+  if (rc) return rc;
+  rc = get_f32(ctx, b_id, (int64_t)batch * b_d1 * b_d2, "b", &b);
+  if (rc) return rc;
+  rc = get_f32(ctx, out_id, (int64_t)batch * M * N, "matMul output", &o);
+  if (rc) return rc;
+  TFJS_REQUIRE(ctx, !a->quant.quantized && !o->quant.quantized, "only the b operand may be quantised");
+  EpilogueArgs e;
+  rc = resolve_epilogue(ctx, epi, N, &e);
+  if (rc) return rc;
+  o->version++;
+  if ((int64_t)batch * M * N == 0) return TFJS_CUDA_OK;  // matmul_test.ts:621-642
+  cudaSetDevice(ctx->device);
+  const bool tc = ctx->use_tensor_cores && tcgen05_gemm_supported(M, N, K);
+  if (!tc) {
+    const float* bf;
+    rc = float_view(ctx, b, &bf);
+    if (rc) return rc;
+    return launch_gemm_simt(ctx, (const float*)a->ptr, bf, (float*)o->ptr, batch, (int)M, (int)N, (int)K,
+                            (int64_t)a_d1 * a_d2, transpose_a ? 1 : a_d2, transpose_a ? a_d2 : 1,
+                            (int64_t)b_d1 * b_d2, transpose_b ? 1 : b_d2, transpose_b ? b_d2 : 1, e);
+  }
+  // Tensor-core path wants A as [M, K] with K contiguous.
+  const float* a_mk = (const float*)a->ptr;
+  void* a_scratch = nullptr;
+  size_t a_cap = 0;
+  if (transpose_a) {
+    rc = ctx_alloc(ctx, (size_t)batch * M * K * 4, &a_scratch, &a_cap);
+    if (rc) return rc;
+    rc = launch_transpose_batched(ctx, (const float*)a->ptr, (float*)a_scratch, batch, (int)K, (int)M);
+    if (rc) {
+      ctx_free(ctx, a_scratch, a_cap);
+      return rc;
+    }
+    a_mk = (const float*)a_scratch;
+  }
+  for (int bi = 0; bi < batch && !rc; bi++)
+    rc = gemm_dispatch(ctx, a_mk + (int64_t)bi * M * K, M, K, b, (int64_t)bi * K * N, transpose_b != 0,
+                       /*cacheable=*/batch == 1, (float*)o->ptr + (int64_t)bi * M * N, N, e);
+  if (a_scratch) ctx_free(ctx, a_scratch, a_cap);
+  return rc;
+}
+
+static int check_conv_info(tfjs_cuda_ctx* ctx, const tfjs_conv2d_info* ci) {
+  TFJS_REQUIRE(ctx, ci != nullptr, "convInfo is null");
+  TFJS_REQUIRE(ctx, ci->batchSize >= 0 && ci->inHeight >= 0 && ci->inWidth >= 0 && ci->inChannels >= 0 &&
+                        ci->outHeight >= 0 && ci->outWidth >= 0 && ci->outChannels >= 0,
+               "negative extent in convInfo");
+  TFJS_REQUIRE(ctx, ci->strideHeight >= 1 && ci->strideWidth >= 1 && ci->dilationHeight >= 1 &&
+                        ci->dilationWidth >= 1 && ci->filterHeight >= 1 && ci->filterWidth >= 1,
+               "strides, dilations and filter sizes must be positive");
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_tensor_id w_id,
+                                tfjs_tensor_id out_id, const tfjs_conv2d_info* ci,
+                                const tfjs_epilogue* epi) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  int rc = check_conv_info(ctx, ci);
+  if (rc) return rc;
+  const int64_t pixels = (int64_t)ci->batchSize * ci->outHeight * ci->outWidth;
+  TensorEntry *x, *w, *o;
+  rc = get_f32(ctx, x_id, (int64_t)ci->batchSize * ci->inHeight * ci->inWidth * ci->inChannels, "x", &x);
+  if (rc) return rc;
+  rc = get_f32(ctx, w_id, (int64_t)ci->filterHeight * ci->filterWidth * ci->inChannels * ci->outChannels,
+               "filter", &w);
+  if (rc) return rc;
+  rc = get_f32(ctx, out_id, pixels * ci->outChannels, "conv2d output", &o);
+  if (rc) return rc;
+  TFJS_REQUIRE(ctx, !x->quant.quantized && !o->quant.quantized, "only the filter may be quantised");
+  EpilogueArgs e;
+  rc = resolve_epilogue(ctx, epi, ci->outChannels, &e);
+  if (rc) return rc;
+  o->version++;
+  if (pixels * ci->outChannels == 0) return TFJS_CUDA_OK;
+  cudaSetDevice(ctx->device);
+  // A 1x1 stride-1 unpadded convolution over NHWC is the GEMM [B*H*W, Cin] x [Cin, Cout].
+  const bool pointwise = ci->filterHeight == 1 && ci->filterWidth == 1 && ci->strideHeight == 1 &&
+                         ci->strideWidth == 1 && ci->padTop == 0 && ci->padLeft == 0 &&
+                         ci->outHeight == ci->inHeight && ci->outWidth == ci->inWidth;
+  if (pointwise && ci->inChannels > 0)
+    return gemm_dispatch(ctx, (const float*)x->ptr, pixels, ci->inChannels, w, 0, false, true,
+                         (float*)o->ptr, ci->outChannels, e);
+  const float* wf;
+  rc = float_view(ctx, w, &wf);
+  if (rc) return rc;
+  return launch_conv2d_direct(ctx, (const float*)x->ptr, wf, (float*)o->ptr, *ci, e);
+}
+
+extern "C" int tfjs_cuda_depthwise_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_tensor_id w_id,
+                                          tfjs_tensor_id out_id, const tfjs_conv2d_info* ci,
+                                          const tfjs_epilogue* epi) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  int rc = check_conv_info(ctx, ci);
+  if (rc) return rc;
+  TFJS_REQUIRE(ctx, ci->inChannels == 0 || ci->outChannels % ci->inChannels == 0,
+               "depthwise outChannels must be a multiple of inChannels");
+  const int64_t out_n = (int64_t)ci->batchSize * ci->outHeight * ci->outWidth * ci->outChannels;
+  TensorEntry *x, *w, *o;
+  rc = get_f32(ctx, x_id, (int64_t)ci->batchSize * ci->inHeight * ci->inWidth * ci->inChannels, "x", &x);
+  if (rc) return rc;
+  rc = get_f32(ctx, w_id, (int64_t)ci->filterHeight * ci->filterWidth * ci->outChannels, "filter", &w);
+  if (rc) return rc;
+  rc = get_f32(ctx, out_id, out_n, "depthwiseConv2D output", &o);
+  if (rc) return rc;
+  TFJS_REQUIRE(ctx, !x->quant.quantized && !o->quant.quantized, "only the filter may be quantised");
+  EpilogueArgs e;
+  rc = resolve_epilogue(ctx, epi, ci->outChannels, &e);
+  if (rc) return rc;
+  o->version++;
+  if (out_n == 0) return TFJS_CUDA_OK;
+  cudaSetDevice(ctx->device);
+  const float* wf;
+  rc = float_view(ctx, w, &wf);
+  if (rc) return rc;
+  return launch_depthwise(ctx, (const float*)x->ptr, wf, (float*)o->ptr, *ci, e);
+}
+
+extern "C" int tfjs_cuda_pool2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_tensor_id out_id,
+                                const tfjs_conv2d_info* ci, int is_avg) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  int rc = check_conv_info(ctx, ci);
+  if (rc) return rc;
+  const int64_t out_n = (int64_t)ci->batchSize * ci->outHeight * ci->outWidth * ci->inChannels;
+  TensorEntry *x, *o;
+  rc = get_f32(ctx, x_id, (int64_t)ci->batchSize * ci->inHeight * ci->inWidth * ci->inChannels, "x", &x);
+  if (rc) return rc;
+  rc = get_f32(ctx, out_id, out_n, "pool output", &o);
+  if (rc) return rc;
+  TFJS_REQUIRE(ctx, !x->quant.quantized, "pooling takes float tensors");
+  o->version++;
+  if (out_n == 0) return TFJS_CUDA_OK;
+  cudaSetDevice(ctx->device);
+  return launch_pool2d(ctx, (const float*)x->ptr, (float*)o->ptr, *ci, is_avg);
+}

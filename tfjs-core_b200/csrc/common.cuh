@@ -1,0 +1,173 @@
+// Internal definitions shared by the translation units of libtfjs_cuda.so.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/tfjs_cuda.h"
+
+struct QuantInfo {
+  bool quantized = false;
+  double scale = 0.0, min = 0.0;
+};
+
+// Operand of a contraction repacked for the tensor-core kernel: K-major [N, Kp] float32,
+// tf32-rounded "hi" plane and (for 3xTF32) the "lo" residual plane.  Cached per weight
+// tensor and invalidated when the tensor is written.
+struct PackedWeights {
+  float* hi = nullptr;
+  float* lo = nullptr;
+  size_t capacity = 0;  // allocator size class of each plane
+  int64_t n = 0, k = 0, kp = 0;
+  uint64_t version = 0;
+  bool transposed_source = false;
+};
+
+struct TensorEntry {
+  void* ptr = nullptr;   // device storage (nullptr for zero-sized tensors)
+  size_t nbytes = 0;     // logical byte size (f32/i32: 4 per element, bool/quantised: 1)
+  size_t capacity = 0;   // size class of the buffer behind ptr
+  int dtype = TFJS_F32;
+  int rank = 0;
+  int64_t shape[8] = {0};
+  int64_t size = 0;      // element count
+  uint64_t version = 0;  // bumped on every write / kernel output
+  QuantInfo quant;
+  PackedWeights packed;
+  // float32 copy of a quantised tensor for the kernels that read plain floats
+  float* deq = nullptr;
+  size_t deq_capacity = 0;
+  uint64_t deq_version = 0;
+};
+
+struct tfjs_cuda_graph {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  // Buffers disposed while capturing stay owned by the graph: replays write to them.
+  std::vector<std::pair<void*, size_t>> held;
+  int64_t launches_per_replay = 0;
+};
+
+struct tfjs_cuda_event {
+  cudaEvent_t ev = nullptr;
+  int device = 0;
+};
+
+struct tfjs_cuda_ctx {
+  int device = 0;
+  int sm_count = 0;
+  cudaStream_t stream = nullptr;
+  std::string last_error;
+  std::unordered_map<tfjs_tensor_id, TensorEntry> tensors;
+  tfjs_tensor_id next_id = 1;
+  // caching allocator: size class -> free buffers
+  std::map<size_t, std::vector<void*>> free_lists;
+  int64_t bytes_in_use = 0, bytes_reserved = 0, num_device_allocs = 0, num_cached = 0;
+  // options
+  int math_mode = TFJS_MATH_TF32X3;
+  bool use_tensor_cores = true;
+  bool debug_sync = false;
+  // bookkeeping
+  int64_t launch_count = 0;
+  cudaEvent_t time_start = nullptr, time_stop = nullptr;
+  int64_t time_start_launches = 0;
+  // graph capture
+  tfjs_cuda_graph* capturing = nullptr;
+  int64_t capture_start_launches = 0;
+  // device-side status word written by kernels whose bounded waits gave up
+  int* d_status = nullptr;
+  int* h_status = nullptr;  // pinned mirror
+};
+
+int set_error(tfjs_cuda_ctx* ctx, int code, const char* fmt, ...);
+
+#define TFJS_CHECK_CUDA(ctx, expr)                                                        \
+  do {                                                                                    \
+    cudaError_t _e = (expr);                                                              \
+    if (_e != cudaSuccess)                                                                \
+      return set_error(ctx, _e == cudaErrorMemoryAllocation ? TFJS_CUDA_ERR_OOM           \
+                                                            : TFJS_CUDA_ERR_CUDA,         \
+                       "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__,  \
+                       __LINE__);                                                         \
+  } while (0)
+
+#define TFJS_REQUIRE(ctx, cond, ...)                                        \
+  do {                                                                      \
+    if (!(cond)) return set_error(ctx, TFJS_CUDA_ERR_INVALID_ARG, __VA_ARGS__); \
+  } while (0)
+
+// Called after every kernel launch: counts it and surfaces launch errors.
+int post_launch(tfjs_cuda_ctx* ctx, const char* what);
+
+// Allocator (context.cu).
+int ctx_alloc(tfjs_cuda_ctx* ctx, size_t nbytes, void** ptr, size_t* capacity);
+void ctx_free(tfjs_cuda_ctx* ctx, void* ptr, size_t capacity);
+
+TensorEntry* find_tensor(tfjs_cuda_ctx* ctx, tfjs_tensor_id id);
+// Looks the id up and checks dtype float32 with at least `min_elems` elements.
+int get_f32(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, int64_t min_elems, const char* what,
+            TensorEntry** out);
+
+static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Epilogue resolved to device pointers, passed by value to kernels.
+struct EpilogueArgs {
+  const float* bias = nullptr;
+  int bias_scalar = 0;  // 1: bias[0] for every channel
+  int activation = TFJS_ACT_LINEAR;
+  const float* prelu = nullptr;
+  int prelu_scalar = 0;
+  float clip_lo = 0.f, clip_hi = 0.f;
+};
+int resolve_epilogue(tfjs_cuda_ctx* ctx, const tfjs_epilogue* epi, int64_t channels,
+                     EpilogueArgs* out);
+
+// act(v + bias) with the NaN behaviour of MathBackendCPU: relu is Math.max(0, v) (keeps NaN),
+// clip is `v > hi ? hi : (v < lo ? lo : v)` (keeps NaN), prelu is `v < 0 ? a * v : v`.
+__device__ __forceinline__ float apply_epilogue(float v, int c, const EpilogueArgs& e) {
+  if (e.bias) v = v + (e.bias_scalar ? e.bias[0] : e.bias[c]);
+  switch (e.activation) {
+    case TFJS_ACT_RELU: v = (v < 0.f) ? 0.f : v; break;
+    case TFJS_ACT_PRELU: {
+      float a = e.prelu_scalar ? e.prelu[0] : e.prelu[c];
+      v = (v < 0.f) ? a * v : v;
+      break;
+    }
+    case TFJS_ACT_CLIP: v = (v > e.clip_hi) ? e.clip_hi : ((v < e.clip_lo) ? e.clip_lo : v); break;
+    default: break;
+  }
+  return v;
+}
+
+// ---- kernel launchers implemented in the other translation units -------------------------
+// gemm_simt.cu
+int launch_gemm_simt(tfjs_cuda_ctx* ctx, const float* a, const float* b, float* out, int batch,
+                     int M, int N, int K, int64_t a_batch, int64_t a_row, int64_t a_col,
+                     int64_t b_batch, int64_t b_row, int64_t b_col, const EpilogueArgs& epi);
+int launch_pack_weights(tfjs_cuda_ctx* ctx, const void* src, bool src_is_u8, double scale,
+                        double min, int64_t K, int64_t N, int64_t src_k_stride,
+                        int64_t src_n_stride, int64_t kp, float* hi, float* lo);
+int launch_transpose_batched(tfjs_cuda_ctx* ctx, const float* src, float* dst, int batch,
+                             int rows, int cols);
+int launch_dequant(tfjs_cuda_ctx* ctx, const uint8_t* q, float* out, int64_t n, double scale,
+                   double min);
+// gemm_tcgen05.cu
+bool tcgen05_gemm_supported(int64_t M, int64_t N, int64_t K);
+int launch_gemm_tcgen05(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K,
+                        const float* w_hi, const float* w_lo, int64_t kp, float* out, int64_t N,
+                        const EpilogueArgs& epi, int math_mode);
+// conv.cu
+int launch_conv2d_direct(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* y,
+                         const tfjs_conv2d_info& ci, const EpilogueArgs& epi);
+int launch_depthwise(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* y,
+                     const tfjs_conv2d_info& ci, const EpilogueArgs& epi);
+int launch_pool2d(tfjs_cuda_ctx* ctx, const float* x, float* y, const tfjs_conv2d_info& ci,
+                  int is_avg);

@@ -1,0 +1,570 @@
+// Context, caching allocator, tensor table, events, timing and graph capture.
+//
+// Plays the role of MathBackendCPU's storage half (tfjs-core/src/backends/cpu/
+// backend_cpu.ts:102-254) and of the wasm backend's id-keyed tensor table
+// (tfjs-backend-wasm/src/lib.cc:52-132), with device memory instead of typed arrays.
+#include <chrono>
+#include <thread>
+
+#include "common.cuh"
+
+int set_error(tfjs_cuda_ctx* ctx, int code, const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  if (ctx) ctx->last_error = buf;
+  return code;
+}
+
+static thread_local std::string g_create_error;
+
+int post_launch(tfjs_cuda_ctx* ctx, const char* what) {
+  ctx->launch_count++;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return set_error(ctx, TFJS_CUDA_ERR_CUDA, "launch of %s failed: %s", what,
+                     cudaGetErrorString(e));
+  if (ctx->debug_sync) {
+    e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess)
+      return set_error(ctx, TFJS_CUDA_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
+  }
+  return TFJS_CUDA_OK;
+}
+
+// ---- allocator ---------------------------------------------------------------------------
+// Buffers are recycled through per-size free lists so that the steady state of an inference
+// loop never calls cudaMalloc.  Reuse is stream-ordered: everything runs on ctx->stream.
+static size_t size_class(size_t n) {
+  if (n == 0) return 0;
+  if (n <= (1u << 20)) {
+    size_t c = 512;
+    while (c < n) c <<= 1;
+    return c;
+  }
+  const size_t mb = 1u << 20;
+  return (n + mb - 1) / mb * mb;
+}
+
+static void release_cached(tfjs_cuda_ctx* ctx) {
+  for (auto& kv : ctx->free_lists) {
+    for (void* p : kv.second) {
+      cudaFree(p);
+      ctx->bytes_reserved -= (int64_t)kv.first;
+    }
+    kv.second.clear();
+  }
+  ctx->num_cached = 0;
+}
+
+int ctx_alloc(tfjs_cuda_ctx* ctx, size_t nbytes, void** ptr, size_t* capacity) {
+  *ptr = nullptr;
+  *capacity = 0;
+  if (nbytes == 0) return TFJS_CUDA_OK;
+  const size_t cls = size_class(nbytes);
+  auto it = ctx->free_lists.find(cls);
+  if (it != ctx->free_lists.end() && !it->second.empty()) {
+    *ptr = it->second.back();
+    it->second.pop_back();
+    ctx->num_cached--;
+  } else {
+    cudaError_t e = cudaMalloc(ptr, cls);
+    if (e == cudaErrorMemoryAllocation) {
+      cudaGetLastError();
+      cudaStreamSynchronize(ctx->stream);
+      release_cached(ctx);
+      e = cudaMalloc(ptr, cls);
+    }
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      *ptr = nullptr;
+      return set_error(ctx, e == cudaErrorMemoryAllocation ? TFJS_CUDA_ERR_OOM : TFJS_CUDA_ERR_CUDA,
+                       "cudaMalloc(%zu) failed: %s", cls, cudaGetErrorString(e));
+    }
+    ctx->num_device_allocs++;
+    ctx->bytes_reserved += (int64_t)cls;
+  }
+  *capacity = cls;
+  ctx->bytes_in_use += (int64_t)cls;
+  return TFJS_CUDA_OK;
+}
+
+void ctx_free(tfjs_cuda_ctx* ctx, void* ptr, size_t capacity) {
+  if (!ptr) return;
+  ctx->bytes_in_use -= (int64_t)capacity;
+  if (ctx->capturing) {
+    // A captured graph keeps writing to this buffer on every replay.
+    ctx->capturing->held.emplace_back(ptr, capacity);
+    return;
+  }
+  ctx->free_lists[capacity].push_back(ptr);
+  ctx->num_cached++;
+}
+
+// ---- context -----------------------------------------------------------------------------
+extern "C" int tfjs_cuda_ctx_create(int device, tfjs_cuda_ctx** out) {
+  if (!out) return TFJS_CUDA_ERR_INVALID_ARG;
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    g_create_error = "no usable CUDA device";
+    return TFJS_CUDA_ERR_CUDA;
+  }
+  if (device < 0 || device >= count) {
+    g_create_error = "device ordinal out of range";
+    return TFJS_CUDA_ERR_INVALID_ARG;
+  }
+  if (cudaSetDevice(device) != cudaSuccess) {
+    cudaGetLastError();
+    g_create_error = "cudaSetDevice failed";
+    return TFJS_CUDA_ERR_CUDA;
+  }
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+    cudaGetLastError();
+    g_create_error = "cudaGetDeviceProperties failed";
+    return TFJS_CUDA_ERR_CUDA;
+  }
+  if (prop.major != 10) {
+    g_create_error = "this library is built for sm_100a (B200) only";
+    return TFJS_CUDA_ERR_UNSUPPORTED;
+  }
+  tfjs_cuda_ctx* ctx = new tfjs_cuda_ctx();
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  bool ok = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) == cudaSuccess &&
+            cudaEventCreate(&ctx->time_start) == cudaSuccess &&
+            cudaEventCreate(&ctx->time_stop) == cudaSuccess &&
+            cudaMalloc(&ctx->d_status, sizeof(int)) == cudaSuccess &&
+            cudaMallocHost(&ctx->h_status, sizeof(int)) == cudaSuccess &&
+            cudaMemset(ctx->d_status, 0, sizeof(int)) == cudaSuccess;
+  if (!ok) {
+    g_create_error = std::string("context setup failed: ") + cudaGetErrorString(cudaGetLastError());
+    tfjs_cuda_ctx_destroy(ctx);
+    return TFJS_CUDA_ERR_CUDA;
+  }
+  *ctx->h_status = 0;
+  *out = ctx;
+  return TFJS_CUDA_OK;
+}
+
+static void free_entry_buffers(tfjs_cuda_ctx* ctx, TensorEntry& t) {
+  ctx_free(ctx, t.ptr, t.capacity);
+  t.ptr = nullptr;
+  if (t.packed.hi) ctx_free(ctx, t.packed.hi, t.packed.capacity);
+  if (t.packed.lo) ctx_free(ctx, t.packed.lo, t.packed.capacity);
+  t.packed = PackedWeights();
+  if (t.deq) ctx_free(ctx, t.deq, t.deq_capacity);
+  t.deq = nullptr;
+}
+
+extern "C" int tfjs_cuda_ctx_destroy(tfjs_cuda_ctx* ctx) {
+  if (!ctx) return TFJS_CUDA_OK;
+  cudaSetDevice(ctx->device);
+  if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  ctx->capturing = nullptr;
+  for (auto& kv : ctx->tensors) free_entry_buffers(ctx, kv.second);
+  ctx->tensors.clear();
+  release_cached(ctx);
+  if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->h_status) cudaFreeHost(ctx->h_status);
+  if (ctx->time_start) cudaEventDestroy(ctx->time_start);
+  if (ctx->time_stop) cudaEventDestroy(ctx->time_stop);
+  if (ctx->stream) cudaStreamDestroy(ctx->stream);
+  cudaGetLastError();
+  delete ctx;
+  return TFJS_CUDA_OK;
+}
+
+extern "C" const char* tfjs_cuda_last_error(const tfjs_cuda_ctx* ctx) {
+  return ctx ? ctx->last_error.c_str() : g_create_error.c_str();
+}
+
+extern "C" int tfjs_cuda_ctx_set_option(tfjs_cuda_ctx* ctx, const char* key, double value) {
+  if (!ctx || !key) return TFJS_CUDA_ERR_INVALID_ARG;
+  if (!strcmp(key, "math_mode")) {
+    TFJS_REQUIRE(ctx, value == TFJS_MATH_TF32X3 || value == TFJS_MATH_TF32,
+                 "math_mode must be 0 (3xTF32) or 1 (TF32)");
+    ctx->math_mode = (int)value;
+  } else if (!strcmp(key, "use_tensor_cores")) {
+    ctx->use_tensor_cores = value != 0;
+  } else if (!strcmp(key, "debug_sync")) {
+    ctx->debug_sync = value != 0;
+  } else {
+    return set_error(ctx, TFJS_CUDA_ERR_INVALID_ARG, "unknown option '%s'", key);
+  }
+  return TFJS_CUDA_OK;
+}
+
+// Copies the device status word back and turns a non-zero value into an error.
+static int check_device_status(tfjs_cuda_ctx* ctx) {
+  if (*ctx->h_status != 0) {
+    int code = *ctx->h_status;
+    *ctx->h_status = 0;
+    cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
+    return set_error(ctx, TFJS_CUDA_ERR_TIMEOUT,
+                     "a kernel gave up on a bounded wait (device status %d)", code);
+  }
+  return TFJS_CUDA_OK;
+}
+
+static int sync_stream(tfjs_cuda_ctx* ctx, int timeout_ms) {
+  TFJS_REQUIRE(ctx, !ctx->capturing, "cannot synchronise while capturing a graph");
+  TFJS_CHECK_CUDA(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int),
+                                       cudaMemcpyDeviceToHost, ctx->stream));
+  if (timeout_ms < 0) {
+    TFJS_CHECK_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  } else {
+    auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+      cudaError_t e = cudaStreamQuery(ctx->stream);
+      if (e == cudaSuccess) break;
+      if (e != cudaErrorNotReady) {
+        cudaGetLastError();
+        return set_error(ctx, TFJS_CUDA_ERR_CUDA, "stream error: %s", cudaGetErrorString(e));
+      }
+      auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(
+                    std::chrono::steady_clock::now() - t0).count();
+      if (ms > timeout_ms)
+        return set_error(ctx, TFJS_CUDA_ERR_TIMEOUT, "sync timed out after %d ms", timeout_ms);
+      std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+  }
+  return check_device_status(ctx);
+}
+
+extern "C" int tfjs_cuda_ctx_sync(tfjs_cuda_ctx* ctx, int timeout_ms) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  cudaSetDevice(ctx->device);
+  return sync_stream(ctx, timeout_ms);
+}
+
+extern "C" int tfjs_cuda_ctx_memory(tfjs_cuda_ctx* ctx, tfjs_cuda_mem_stats* out) {
+  if (!ctx || !out) return TFJS_CUDA_ERR_INVALID_ARG;
+  out->num_tensors = (int64_t)ctx->tensors.size();
+  out->bytes_in_use = ctx->bytes_in_use;
+  out->bytes_reserved = ctx->bytes_reserved;
+  out->num_buffers_cached = ctx->num_cached;
+  out->num_device_allocs = ctx->num_device_allocs;
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_ctx_time_begin(tfjs_cuda_ctx* ctx) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  cudaSetDevice(ctx->device);
+  ctx->time_start_launches = ctx->launch_count;
+  TFJS_CHECK_CUDA(ctx, cudaEventRecord(ctx->time_start, ctx->stream));
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_ctx_time_end(tfjs_cuda_ctx* ctx, float* ms, int64_t* launches) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  cudaSetDevice(ctx->device);
+  TFJS_CHECK_CUDA(ctx, cudaEventRecord(ctx->time_stop, ctx->stream));
+  TFJS_CHECK_CUDA(ctx, cudaEventSynchronize(ctx->time_stop));
+  float t = 0.f;
+  TFJS_CHECK_CUDA(ctx, cudaEventElapsedTime(&t, ctx->time_start, ctx->time_stop));
+  if (ms) *ms = t;
+  if (launches) *launches = ctx->launch_count - ctx->time_start_launches;
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int64_t tfjs_cuda_ctx_launch_count(const tfjs_cuda_ctx* ctx) {
+  return ctx ? ctx->launch_count : 0;
+}
+
+extern "C" void* tfjs_cuda_ctx_stream(tfjs_cuda_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+// ---- tensors -----------------------------------------------------------------------------
+TensorEntry* find_tensor(tfjs_cuda_ctx* ctx, tfjs_tensor_id id) {
+  auto it = ctx->tensors.find(id);
+  return it == ctx->tensors.end() ? nullptr : &it->second;
+}
+
+static size_t dtype_size(int dtype) { return dtype == TFJS_BOOL ? 1 : 4; }
+
+static int register_impl(tfjs_cuda_ctx* ctx, tfjs_tensor_id* out_id, int rank, const int64_t* shape,
+                         int dtype, size_t elem_size) {
+  TFJS_REQUIRE(ctx, out_id != nullptr, "out_id is null");
+  TFJS_REQUIRE(ctx, rank >= 0 && rank <= 8, "rank %d out of range", rank);
+  TFJS_REQUIRE(ctx, dtype == TFJS_F32 || dtype == TFJS_I32 || dtype == TFJS_BOOL,
+               "unsupported dtype %d", dtype);
+  TensorEntry t;
+  t.dtype = dtype;
+  t.rank = rank;
+  t.size = 1;
+  for (int i = 0; i < rank; i++) {
+    TFJS_REQUIRE(ctx, shape[i] >= 0, "negative dimension");
+    t.shape[i] = shape[i];
+    t.size *= shape[i];
+  }
+  t.nbytes = (size_t)t.size * elem_size;
+  cudaSetDevice(ctx->device);
+  int rc = ctx_alloc(ctx, t.nbytes, &t.ptr, &t.capacity);
+  if (rc) return rc;
+  tfjs_tensor_id id = ctx->next_id++;
+  ctx->tensors.emplace(id, t);
+  *out_id = id;
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_tensor_register(tfjs_cuda_ctx* ctx, tfjs_tensor_id* out_id, int rank,
+                                         const int64_t* shape, int dtype) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  return register_impl(ctx, out_id, rank, shape, dtype, dtype_size(dtype));
+}
+
+extern "C" int tfjs_cuda_tensor_register_quantized(tfjs_cuda_ctx* ctx, tfjs_tensor_id* out_id,
+                                                   int rank, const int64_t* shape,
+                                                   const uint8_t* q, double scale, double min) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  TFJS_REQUIRE(ctx, q != nullptr, "quantised bytes are null");
+  int rc = register_impl(ctx, out_id, rank, shape, TFJS_F32, 1);
+  if (rc) return rc;
+  TensorEntry* t = find_tensor(ctx, *out_id);
+  t->quant.quantized = true;
+  t->quant.scale = scale;
+  t->quant.min = min;
+  if (t->nbytes)
+    TFJS_CHECK_CUDA(ctx, cudaMemcpyAsync(t->ptr, q, t->nbytes, cudaMemcpyHostToDevice, ctx->stream));
+  t->version++;
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_tensor_write(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, const void* host,
+                                      size_t nbytes) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  TensorEntry* t = find_tensor(ctx, id);
+  if (!t) return set_error(ctx, TFJS_CUDA_ERR_NOT_FOUND, "write: unknown tensor id %lld", (long long)id);
+  // backend_cpu.ts:125-127: writing null throws
+  TFJS_REQUIRE(ctx, host != nullptr || nbytes == 0, "MathBackendCUDA.write(): values cannot be null");
+  TFJS_REQUIRE(ctx, !t->quant.quantized, "cannot write float values into a quantised tensor");
+  TFJS_REQUIRE(ctx, nbytes == t->nbytes, "write: %zu bytes given, tensor holds %zu", nbytes, t->nbytes);
+  cudaSetDevice(ctx->device);
+  if (nbytes)
+    TFJS_CHECK_CUDA(ctx, cudaMemcpyAsync(t->ptr, host, nbytes, cudaMemcpyHostToDevice, ctx->stream));
+  t->version++;
+  return TFJS_CUDA_OK;
+}
+
+static int enqueue_read(tfjs_cuda_ctx* ctx, TensorEntry* t, void* host, size_t nbytes) {
+  if (t->quant.quantized) {
+    TFJS_REQUIRE(ctx, nbytes == (size_t)t->size * 4, "read: %zu bytes asked, tensor holds %zu",
+                 nbytes, (size_t)t->size * 4);
+    if (!nbytes) return TFJS_CUDA_OK;
+    void* tmp;
+    size_t cap;
+    int rc = ctx_alloc(ctx, nbytes, &tmp, &cap);
+    if (rc) return rc;
+    rc = launch_dequant(ctx, (const uint8_t*)t->ptr, (float*)tmp, t->size, t->quant.scale, t->quant.min);
+    if (!rc) {
+      cudaError_t e = cudaMemcpyAsync(host, tmp, nbytes, cudaMemcpyDeviceToHost, ctx->stream);
+      if (e != cudaSuccess) rc = set_error(ctx, TFJS_CUDA_ERR_CUDA, "read failed: %s", cudaGetErrorString(e));
+    }
+    ctx_free(ctx, tmp, cap);
+    return rc;
+  }
+  TFJS_REQUIRE(ctx, nbytes == t->nbytes, "read: %zu bytes asked, tensor holds %zu", nbytes, t->nbytes);
+  if (nbytes)
+    TFJS_CHECK_CUDA(ctx, cudaMemcpyAsync(host, t->ptr, nbytes, cudaMemcpyDeviceToHost, ctx->stream));
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_tensor_read(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, void* host, size_t nbytes) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  TensorEntry* t = find_tensor(ctx, id);
+  if (!t) return set_error(ctx, TFJS_CUDA_ERR_NOT_FOUND, "read: unknown tensor id %lld", (long long)id);
+  TFJS_REQUIRE(ctx, host != nullptr || nbytes == 0, "read: host buffer is null");
+  TFJS_REQUIRE(ctx, !ctx->capturing, "cannot read while capturing a graph");
+  cudaSetDevice(ctx->device);
+  int rc = enqueue_read(ctx, t, host, nbytes);
+  if (rc) return rc;
+  return sync_stream(ctx, -1);
+}
+
+extern "C" int tfjs_cuda_tensor_read_async(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, void* host,
+                                           size_t nbytes, tfjs_cuda_event** out_event) {
+  if (!ctx || !out_event) return TFJS_CUDA_ERR_INVALID_ARG;
+  TensorEntry* t = find_tensor(ctx, id);
+  if (!t) return set_error(ctx, TFJS_CUDA_ERR_NOT_FOUND, "read: unknown tensor id %lld", (long long)id);
+  TFJS_REQUIRE(ctx, host != nullptr || nbytes == 0, "read: host buffer is null");
+  TFJS_REQUIRE(ctx, !ctx->capturing, "cannot read while capturing a graph");
+  cudaSetDevice(ctx->device);
+  int rc = enqueue_read(ctx, t, host, nbytes);
+  if (rc) return rc;
+  tfjs_cuda_event* ev = new tfjs_cuda_event();
+  ev->device = ctx->device;
+  cudaError_t e = cudaEventCreateWithFlags(&ev->ev, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaEventRecord(ev->ev, ctx->stream);
+  if (e != cudaSuccess) {
+    if (ev->ev) cudaEventDestroy(ev->ev);
+    delete ev;
+    return set_error(ctx, TFJS_CUDA_ERR_CUDA, "event setup failed: %s", cudaGetErrorString(e));
+  }
+  *out_event = ev;
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_event_query(tfjs_cuda_event* ev) {
+  if (!ev) return TFJS_CUDA_ERR_INVALID_ARG;
+  cudaError_t e = cudaEventQuery(ev->ev);
+  if (e == cudaSuccess) return 1;
+  if (e == cudaErrorNotReady) return 0;
+  cudaGetLastError();
+  return TFJS_CUDA_ERR_CUDA;
+}
+
+extern "C" int tfjs_cuda_event_wait(tfjs_cuda_event* ev, int timeout_ms) {
+  if (!ev) return TFJS_CUDA_ERR_INVALID_ARG;
+  if (timeout_ms < 0) return cudaEventSynchronize(ev->ev) == cudaSuccess ? TFJS_CUDA_OK : TFJS_CUDA_ERR_CUDA;
+  auto t0 = std::chrono::steady_clock::now();
+  for (;;) {
+    int q = tfjs_cuda_event_query(ev);
+    if (q == 1) return TFJS_CUDA_OK;
+    if (q < 0) return q;
+    auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(
+                  std::chrono::steady_clock::now() - t0).count();
+    if (ms > timeout_ms) return TFJS_CUDA_ERR_TIMEOUT;
+    std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+}
+
+extern "C" int tfjs_cuda_event_destroy(tfjs_cuda_event* ev) {
+  if (!ev) return TFJS_CUDA_OK;
+  if (ev->ev) cudaEventDestroy(ev->ev);
+  delete ev;
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_tensor_dispose(tfjs_cuda_ctx* ctx, tfjs_tensor_id id) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  auto it = ctx->tensors.find(id);
+  if (it == ctx->tensors.end()) return TFJS_CUDA_OK;  // idempotent
+  free_entry_buffers(ctx, it->second);
+  ctx->tensors.erase(it);
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_tensor_device_ptr(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, void** ptr,
+                                           size_t* nbytes) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  TensorEntry* t = find_tensor(ctx, id);
+  if (!t) return set_error(ctx, TFJS_CUDA_ERR_NOT_FOUND, "unknown tensor id %lld", (long long)id);
+  if (ptr) *ptr = t->ptr;
+  if (nbytes) *nbytes = t->nbytes;
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_host_alloc(void** ptr, size_t nbytes) {
+  if (!ptr) return TFJS_CUDA_ERR_INVALID_ARG;
+  cudaError_t e = cudaMallocHost(ptr, nbytes ? nbytes : 1);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    *ptr = nullptr;
+    return TFJS_CUDA_ERR_OOM;
+  }
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_host_free(void* ptr) {
+  if (ptr) cudaFreeHost(ptr);
+  return TFJS_CUDA_OK;
+}
+
+int get_f32(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, int64_t min_elems, const char* what,
+            TensorEntry** out) {
+  TensorEntry* t = find_tensor(ctx, id);
+  if (!t) return set_error(ctx, TFJS_CUDA_ERR_NOT_FOUND, "%s: unknown tensor id %lld", what, (long long)id);
+  TFJS_REQUIRE(ctx, t->dtype == TFJS_F32, "%s must be stored as float32 (cast it first)", what);
+  TFJS_REQUIRE(ctx, t->size >= min_elems, "%s holds %lld elements, %lld needed", what,
+               (long long)t->size, (long long)min_elems);
+  *out = t;
+  return TFJS_CUDA_OK;
+}
+
+int resolve_epilogue(tfjs_cuda_ctx* ctx, const tfjs_epilogue* epi, int64_t channels,
+                     EpilogueArgs* out) {
+  *out = EpilogueArgs();
+  if (!epi) return TFJS_CUDA_OK;
+  if (epi->bias) {
+    TFJS_REQUIRE(ctx, epi->bias_len == 1 || epi->bias_len == channels,
+                 "fused bias must be a scalar or one value per output channel");
+    TensorEntry* b;
+    int rc = get_f32(ctx, epi->bias, epi->bias_len, "bias", &b);
+    if (rc) return rc;
+    TFJS_REQUIRE(ctx, !b->quant.quantized, "bias cannot be quantised");
+    out->bias = (const float*)b->ptr;
+    out->bias_scalar = epi->bias_len == 1 && channels != 1;
+  }
+  out->activation = epi->activation;
+  TFJS_REQUIRE(ctx, epi->activation >= TFJS_ACT_LINEAR && epi->activation <= TFJS_ACT_CLIP,
+               "unknown activation %d", epi->activation);
+  if (epi->activation == TFJS_ACT_PRELU) {
+    TFJS_REQUIRE(ctx, epi->prelu != 0, "prelu activation needs preluActivationWeights");
+    TFJS_REQUIRE(ctx, epi->prelu_len == 1 || epi->prelu_len == channels,
+                 "fused prelu weights must be a scalar or one value per output channel");
+    TensorEntry* p;
+    int rc = get_f32(ctx, epi->prelu, epi->prelu_len, "preluActivationWeights", &p);
+    if (rc) return rc;
+    out->prelu = (const float*)p->ptr;
+    out->prelu_scalar = epi->prelu_len == 1 && channels != 1;
+  }
+  out->clip_lo = epi->clip_lo;
+  out->clip_hi = epi->clip_hi;
+  return TFJS_CUDA_OK;
+}
+
+// ---- graph capture -----------------------------------------------------------------------
+extern "C" int tfjs_cuda_graph_begin(tfjs_cuda_ctx* ctx) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  TFJS_REQUIRE(ctx, !ctx->capturing, "a graph capture is already in progress");
+  cudaSetDevice(ctx->device);
+  TFJS_CHECK_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
+  ctx->capturing = new tfjs_cuda_graph();
+  ctx->capture_start_launches = ctx->launch_count;
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_graph_end(tfjs_cuda_ctx* ctx, tfjs_cuda_graph** out) {
+  if (!ctx || !out) return TFJS_CUDA_ERR_INVALID_ARG;
+  TFJS_REQUIRE(ctx, ctx->capturing, "no graph capture in progress");
+  tfjs_cuda_graph* g = ctx->capturing;
+  ctx->capturing = nullptr;
+  g->launches_per_replay = ctx->launch_count - ctx->capture_start_launches;
+  cudaError_t e = cudaStreamEndCapture(ctx->stream, &g->graph);
+  if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    tfjs_cuda_graph_destroy(ctx, g);
+    return set_error(ctx, TFJS_CUDA_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+  }
+  *out = g;
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_graph_launch(tfjs_cuda_ctx* ctx, tfjs_cuda_graph* g) {
+  if (!ctx || !g || !g->exec) return TFJS_CUDA_ERR_INVALID_ARG;
+  cudaSetDevice(ctx->device);
+  TFJS_CHECK_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
+  ctx->launch_count += g->launches_per_replay;
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_graph_destroy(tfjs_cuda_ctx* ctx, tfjs_cuda_graph* g) {
+  if (!g) return TFJS_CUDA_OK;
+  if (g->exec) cudaGraphExecDestroy(g->exec);
+  if (g->graph) cudaGraphDestroy(g->graph);
+  if (ctx) {
+    cudaStreamSynchronize(ctx->stream);
+    for (auto& p : g->held) {
+      ctx->bytes_in_use += (int64_t)p.second;  // ctx_free subtracts it again
+      ctx_free(ctx, p.first, p.second);
+    }
+  }
+  delete g;
+  return TFJS_CUDA_OK;
+}

@@ -1,0 +1,155 @@
+// CUDA-core GEMM for shapes the tensor-core kernel does not take, plus the operand
+// preparation kernels (weight repacking with tf32 hi/lo split, batched transpose).
+#include "common.cuh"
+
+namespace {
+
+// ---- fp32 GEMM with arbitrary operand strides ------------------------------------------------
+// out[b, i, j] = epilogue(sum_k a[b, i, k] * b[b, k, j]).  64x64 tile, 16-deep k slices in
+// shared memory, 4x4 outputs per thread, fmaf in ascending k.  Handles every transpose
+// combination of batchMatMul (backend_cpu.ts:491-540) through the strides.
+constexpr int TM = 64, TN = 64, TK = 16;
+
+__global__ void __launch_bounds__(256)
+gemm_simt_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
+                 int M, int N, int K, int64_t a_batch, int64_t a_row, int64_t a_col,
+                 int64_t b_batch, int64_t b_row, int64_t b_col, EpilogueArgs epi) {
+  __shared__ float as[TK][TM + 1];
+  __shared__ float bs[TK][TN + 1];
+  const int bz = blockIdx.z;
+  const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  const float* ab = a + bz * a_batch;
+  const float* bb = b + bz * b_batch;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += TK) {
+    for (int i = threadIdx.x; i < TM * TK; i += 256) {
+      // pick the faster-varying index along the contiguous dimension of each operand
+      int kk, mm;
+      if (a_col == 1) { kk = i % TK; mm = i / TK; } else { mm = i % TM; kk = i / TM; }
+      const int gm = m0 + mm, gk = k0 + kk;
+      as[kk][mm] = (gm < M && gk < K) ? ab[gm * a_row + gk * a_col] : 0.f;
+    }
+    for (int i = threadIdx.x; i < TN * TK; i += 256) {
+      int kk, nn;
+      if (b_col == 1) { nn = i % TN; kk = i / TN; } else { kk = i % TK; nn = i / TK; }
+      const int gn = n0 + nn, gk = k0 + kk;
+      bs[kk][nn] = (gn < N && gk < K) ? bb[gk * b_row + gn * b_col] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TK; kk++) {
+      float av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) av[i] = as[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; j++) bv[j] = bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  float* ob = out + (int64_t)bz * M * N;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int gm = m0 + ty * 4 + i;
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn < N) ob[(int64_t)gm * N + gn] = apply_epilogue(acc[i][j], gn, epi);
+    }
+  }
+}
+
+__device__ __forceinline__ float round_tf32(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return __uint_as_float(r);
+}
+
+// ---- weight repacking ------------------------------------------------------------------------
+// Source: a [K, N] matrix addressed through (k_stride, n_stride), float32 or uint8 affine
+// quantised (w = q*scale + min evaluated in float64, io_utils.ts:139).  Destination: K-major
+// planes [N, kp]: hi = tf32(w) rounded to nearest, lo = tf32(w - hi); columns k >= K are zero.
+// 32x32 shared-memory tile so that both the read and the write are coalesced.
+__global__ void pack_weights_kernel(const void* __restrict__ src, int src_is_u8, double scale,
+                                    double mn, int K, int N, int64_t k_stride, int64_t n_stride,
+                                    int kp, float* __restrict__ hi, float* __restrict__ lo) {
+  __shared__ float tile[32][33];
+  const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    int k, n;
+    if (n_stride == 1) { k = k0 + r; n = n0 + threadIdx.x; } else { n = n0 + r; k = k0 + threadIdx.x; }
+    float v = 0.f;
+    if (k < K && n < N) {
+      const int64_t off = k * k_stride + n * n_stride;
+      v = src_is_u8 ? (float)((double)((const uint8_t*)src)[off] * scale + mn)
+                    : ((const float*)src)[off];
+    }
+    tile[k - k0][n - n0] = v;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int n = n0 + r, k = k0 + threadIdx.x;
+    if (n < N && k < kp) {
+      const float v = tile[threadIdx.x][r];
+      const float h = round_tf32(v);
+      hi[(int64_t)n * kp + k] = h;
+      // A non-finite hi would turn the residual into NaN (inf - inf); keep it zero instead.
+      if (lo) lo[(int64_t)n * kp + k] = (fabsf(h) <= 3.4028234e38f) ? round_tf32(v - h) : 0.f;
+    }
+  }
+}
+
+// dst[b, c, r] = src[b, r, c]
+__global__ void transpose_batched_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                         int rows, int cols) {
+  __shared__ float tile[32][33];
+  const int64_t base = (int64_t)blockIdx.z * rows * cols;
+  const int r0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int gr = r0 + r, gc = c0 + threadIdx.x;
+    if (gr < rows && gc < cols) tile[r][threadIdx.x] = src[base + (int64_t)gr * cols + gc];
+  }
+  __syncthreads();
+  for (int c = threadIdx.y; c < 32; c += blockDim.y) {
+    const int gc = c0 + c, gr = r0 + threadIdx.x;
+    if (gr < rows && gc < cols) dst[base + (int64_t)gc * rows + gr] = tile[threadIdx.x][c];
+  }
+}
+
+}  // namespace
+
+int launch_gemm_simt(tfjs_cuda_ctx* ctx, const float* a, const float* b, float* out, int batch,
+                     int M, int N, int K, int64_t a_batch, int64_t a_row, int64_t a_col,
+                     int64_t b_batch, int64_t b_row, int64_t b_col, const EpilogueArgs& epi) {
+  if ((int64_t)batch * M * N == 0) return TFJS_CUDA_OK;
+  dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM, batch);
+  if (grid.y > 65535 || grid.z > 65535)
+    return set_error(ctx, TFJS_CUDA_ERR_UNSUPPORTED, "matrix too large for the CUDA-core GEMM");
+  gemm_simt_kernel<<<grid, 256, 0, ctx->stream>>>(a, b, out, M, N, K, a_batch, a_row, a_col, b_batch,
+                                                  b_row, b_col, epi);
+  return post_launch(ctx, "batchMatMul (CUDA cores)");
+}
+
+int launch_pack_weights(tfjs_cuda_ctx* ctx, const void* src, bool src_is_u8, double scale,
+                        double mn, int64_t K, int64_t N, int64_t src_k_stride, int64_t src_n_stride,
+                        int64_t kp, float* hi, float* lo) {
+  if (N * kp == 0) return TFJS_CUDA_OK;
+  dim3 grid((unsigned)ceil_div64(N, 32), (unsigned)ceil_div64(kp, 32));
+  pack_weights_kernel<<<grid, dim3(32, 8), 0, ctx->stream>>>(src, src_is_u8 ? 1 : 0, scale, mn, (int)K,
+                                                             (int)N, src_k_stride, src_n_stride,
+                                                             (int)kp, hi, lo);
+  return post_launch(ctx, "pack_weights");
+}
+
+int launch_transpose_batched(tfjs_cuda_ctx* ctx, const float* src, float* dst, int batch, int rows,
+                             int cols) {
+  if ((int64_t)batch * rows * cols == 0) return TFJS_CUDA_OK;
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32, batch);
+  transpose_batched_kernel<<<grid, dim3(32, 8), 0, ctx->stream>>>(src, dst, rows, cols);
+  return post_launch(ctx, "transpose");
+}

@@ -1,0 +1,515 @@
+// Tensor-core GEMM for sm_100a: out[M, N] = act(A[M, K] * W[K, N] + bias[N]), float32 in and
+// out, TF32 (one pass) or 3xTF32 (three passes on hi/lo splits) on tcgen05 with the
+// accumulator in tensor memory.
+//
+// This is the kernel behind KernelBackend.fusedBatchMatMul and the 1x1 fusedConv2d
+// (tfjs-core/src/backends/backend.ts:134-138, 414-418): a pointwise convolution over NHWC is
+// the GEMM [B*H*W, Cin] x [Cin, Cout].
+//
+// Structure (one persistent CTA per SM, warp specialised):
+//   warp 4      TMA producer: A tile [128 x 32] and W tile(s) [BLOCK_N x 32] per k-block into a
+//               ring of shared-memory stages (SWIZZLE_128B, K-major), mbarrier complete_tx.
+//   warps 6-9   (3xTF32 only) split the A stage in place: hi = tf32(a), lo = tf32(a - hi).
+//   warp 5      MMA issuer: one thread issues tcgen05.mma (M=128, N=BLOCK_N, K=8) per 32-byte
+//               k-step, commits stage release and accumulator-ready barriers.
+//   warps 0-3   epilogue: tcgen05.ld the accumulator (two TMEM buffers, so the next tile's
+//               MMAs overlap), add bias, apply the activation, stage through swizzled shared
+//               memory and write with TMA stores (which clip the M and N tails).
+// Every mbarrier wait is bounded; a wait that gives up sets the context's status word and the
+// CTA drains and frees its tensor memory.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 32;                        // 32 fp32 = 128 bytes = one swizzle row
+constexpr int A_STAGE_BYTES = BLOCK_M * BLOCK_K * 4;  // 16 KB
+constexpr int C_CHUNK_BYTES = 32 * 32 * 4;         // one warp's 32x32 output chunk
+constexpr int C_STAGING_BYTES = 4 * 2 * C_CHUNK_BYTES;
+constexpr int SMEM_LIMIT = 232448;                 // 227 KB
+constexpr int BARRIER_BYTES = 1024;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // ~2 s at 1.9 GHz
+
+__host__ __device__ constexpr int stage_bytes(int block_n, bool split) {
+  return (A_STAGE_BYTES + block_n * BLOCK_K * 4) * (split ? 2 : 1);
+}
+__host__ __device__ constexpr int num_stages(int block_n, bool split) {
+  int s = (SMEM_LIMIT - C_STAGING_BYTES - BARRIER_BYTES - 1024) / stage_bytes(block_n, split);
+  return s > 8 ? 8 : s;
+}
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait.  Returns false (and records `code` in the status word) when the barrier did
+// not complete within WAIT_LIMIT_CYCLES or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63) == 63) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], tf32 inputs, fp32 accumulate.
+__device__ __forceinline__ void tcgen05_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte rows, SWIZZLE_128B, 8-row groups
+// 1024 bytes apart.  Bit layout: start address >> 4 in [0,14), leading byte offset >> 4 in
+// [16,30) (unused for swizzled K-major), stride byte offset >> 4 in [32,46), descriptor
+// version 1 in [46,48), layout type 2 (SWIZZLE_128B) in [61,64).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::tf32: D format f32 (1) in [4,6), A and B format tf32 (2) in
+// [7,10) and [10,13), both operands K-major (bits 15, 16 = 0), N >> 3 in [17,23), M >> 4 in
+// [24,29).
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ float round_tf32(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return __uint_as_float(r);
+}
+
+struct GemmParams {
+  int M, N, K;
+  int num_m_tiles, num_n_tiles, num_k_blocks;
+  int* status;
+  EpilogueArgs epi;
+};
+
+template <int BLOCK_N, bool SPLIT>
+__global__ void __launch_bounds__(SPLIT ? 320 : 192, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                    const __grid_constant__ CUtensorMap map_w_hi,
+                    const __grid_constant__ CUtensorMap map_w_lo,
+                    const __grid_constant__ CUtensorMap map_c, GemmParams p) {
+  constexpr int STAGES = num_stages(BLOCK_N, SPLIT);
+  constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 4;
+  constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // two accumulators; a power of two >= 64
+  constexpr uint32_t TX_BYTES = A_STAGE_BYTES + B_STAGE_BYTES * (SPLIT ? 2 : 1);
+  static_assert(STAGES >= 2, "pipeline needs at least two stages");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* a_hi = smem;
+  uint8_t* a_lo = a_hi + STAGES * A_STAGE_BYTES;  // SPLIT only
+  uint8_t* b_hi = a_hi + STAGES * A_STAGE_BYTES * (SPLIT ? 2 : 1);
+  uint8_t* b_lo = b_hi + STAGES * B_STAGE_BYTES;  // SPLIT only
+  uint8_t* c_stage = b_hi + STAGES * B_STAGE_BYTES * (SPLIT ? 2 : 1);
+  uint64_t* bars = (uint64_t*)(c_stage + C_STAGING_BYTES);
+  uint64_t* full_bar = bars;                  // [STAGES] TMA -> consumers
+  uint64_t* empty_bar = bars + STAGES;        // [STAGES] MMA -> TMA
+  uint64_t* conv_bar = bars + 2 * STAGES;     // [STAGES] converters -> MMA (SPLIT)
+  uint64_t* tmem_full_bar = bars + 3 * STAGES;   // [2] MMA -> epilogue
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;  // [2] epilogue -> MMA
+  uint32_t* tmem_ptr_holder = (uint32_t*)(tmem_empty_bar + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_ptr_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+      mbar_init(smem_u32(&conv_bar[s]), 128);
+    }
+    for (int a = 0; a < 2; a++) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) {
+    // Tensor memory: the whole warp allocates, the same warp frees at the end.
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_ptr_holder)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_holder;
+
+  if (warp == 4) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / p.num_n_tiles) * BLOCK_M;
+        const int n0 = (tile % p.num_n_tiles) * BLOCK_N;
+        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 1);
+          if (!ok) break;
+          const uint32_t bar = smem_u32(&full_bar[stage]);
+          mbar_arrive_expect_tx(bar, TX_BYTES);
+          tma_load_2d(smem_u32(a_hi + stage * A_STAGE_BYTES), &map_a, bar, kb * BLOCK_K, m0);
+          tma_load_2d(smem_u32(b_hi + stage * B_STAGE_BYTES), &map_w_hi, bar, kb * BLOCK_K, n0);
+          if (SPLIT)
+            tma_load_2d(smem_u32(b_lo + stage * B_STAGE_BYTES), &map_w_lo, bar, kb * BLOCK_K, n0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BLOCK_M, BLOCK_N);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status, 2);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
+        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+          ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 3);
+          if (ok && SPLIT) ok = mbar_wait(smem_u32(&conv_bar[stage]), phase, abort_flag, p.status, 4);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t a_hi_s = smem_u32(a_hi + stage * A_STAGE_BYTES);
+          const uint32_t a_lo_s = smem_u32(a_lo + stage * A_STAGE_BYTES);
+          const uint32_t b_hi_s = smem_u32(b_hi + stage * B_STAGE_BYTES);
+          const uint32_t b_lo_s = smem_u32(b_lo + stage * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / 8; k++) {
+            const uint32_t koff = k * 32;  // 8 tf32 = 32 bytes inside the 128-byte swizzle row
+            const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+            if (SPLIT) {
+              // small terms first: lo*hi, hi*lo, then hi*hi
+              tcgen05_mma_tf32(tmem_d, make_smem_desc(a_lo_s + koff), make_smem_desc(b_hi_s + koff), idesc, accum);
+              tcgen05_mma_tf32(tmem_d, make_smem_desc(a_hi_s + koff), make_smem_desc(b_lo_s + koff), idesc, 1u);
+              tcgen05_mma_tf32(tmem_d, make_smem_desc(a_hi_s + koff), make_smem_desc(b_hi_s + koff), idesc, 1u);
+            } else {
+              tcgen05_mma_tf32(tmem_d, make_smem_desc(a_hi_s + koff), make_smem_desc(b_hi_s + koff), idesc, accum);
+            }
+          }
+          tcgen05_commit(smem_u32(&empty_bar[stage]));  // frees the stage once the MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) tcgen05_commit(smem_u32(&tmem_full_bar[acc]));  // accumulator complete
+      }
+    }
+  } else if (warp >= 6) {
+    // ---------------- 3xTF32 converters (SPLIT only) ----------------
+    if (SPLIT) {
+      const int t = threadIdx.x - 192;  // 0..127
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+          ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 5);
+          if (!ok) break;
+          float4* hi4 = reinterpret_cast<float4*>(a_hi + stage * A_STAGE_BYTES);
+          float4* lo4 = reinterpret_cast<float4*>(a_lo + stage * A_STAGE_BYTES);
+#pragma unroll
+          for (int i = 0; i < A_STAGE_BYTES / 16 / 128; i++) {
+            const int idx = t + i * 128;  // element-wise: the swizzled placement is preserved
+            float4 v = hi4[idx], h, l;
+            h.x = round_tf32(v.x); h.y = round_tf32(v.y); h.z = round_tf32(v.z); h.w = round_tf32(v.w);
+            // a non-finite hi keeps lo at zero (inf - inf would poison the product with NaN)
+            l.x = (fabsf(h.x) <= 3.4028234e38f) ? round_tf32(v.x - h.x) : 0.f;
+            l.y = (fabsf(h.y) <= 3.4028234e38f) ? round_tf32(v.y - h.y) : 0.f;
+            l.z = (fabsf(h.z) <= 3.4028234e38f) ? round_tf32(v.z - h.z) : 0.f;
+            l.w = (fabsf(h.w) <= 3.4028234e38f) ? round_tf32(v.w - h.w) : 0.f;
+            hi4[idx] = h;
+            lo4[idx] = l;
+          }
+          fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
+          mbar_arrive(smem_u32(&conv_bar[stage]));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue warps 0-3 ----------------
+    uint8_t* my_stage = c_stage + warp * 2 * C_CHUNK_BYTES;
+    int buf = 0;
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
+      const int m0 = (tile / p.num_n_tiles) * BLOCK_M;
+      const int n0 = (tile % p.num_n_tiles) * BLOCK_N;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 6);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      // TMEM address: lane in bits [16,32), column in [0,16); a warp may only touch lanes
+      // 32*(warp%4) .. +31, i.e. rows 32*warp .. +31 of the tile.
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + acc * BLOCK_N;
+#pragma unroll 1
+      for (int chunk = 0; chunk < BLOCK_N / 32; chunk++) {
+        const int c0 = n0 + chunk * 32;
+        if (c0 >= p.N) break;  // the whole chunk lies beyond the last column
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + chunk * 32, r);
+        tmem_ld_wait();
+        // the buffer used two chunks ago must have been read by its TMA store
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+        uint8_t* dst = my_stage + buf * C_CHUNK_BYTES + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          float4 o;
+          const int c = c0 + j * 4;
+          EpilogueArgs e = p.epi;
+          // columns beyond N hold zeros (W rows are zero-filled); keep bias reads in bounds
+          if (c + 3 < p.N) {
+            o.x = apply_epilogue(__uint_as_float(r[j * 4 + 0]), c + 0, e);
+            o.y = apply_epilogue(__uint_as_float(r[j * 4 + 1]), c + 1, e);
+            o.z = apply_epilogue(__uint_as_float(r[j * 4 + 2]), c + 2, e);
+            o.w = apply_epilogue(__uint_as_float(r[j * 4 + 3]), c + 3, e);
+          } else {
+            o.x = (c + 0 < p.N) ? apply_epilogue(__uint_as_float(r[j * 4 + 0]), c + 0, e) : 0.f;
+            o.y = (c + 1 < p.N) ? apply_epilogue(__uint_as_float(r[j * 4 + 1]), c + 1, e) : 0.f;
+            o.z = (c + 2 < p.N) ? apply_epilogue(__uint_as_float(r[j * 4 + 2]), c + 2, e) : 0.f;
+            o.w = 0.f;
+          }
+          // SWIZZLE_128B placement expected by the store's tensor map: 16-byte chunk j of row
+          // `lane` lives at chunk (j ^ (lane & 7)).
+          *reinterpret_cast<float4*>(dst + ((j ^ (lane & 7)) << 4)) = o;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&map_c, smem_u32(my_stage + buf * C_CHUNK_BYTES), c0, m0 + warp * 32);
+          tma_store_commit();
+        }
+        buf ^= 1;
+      }
+      // all of this warp's reads of the accumulator are done: hand it back to the MMA warp
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    __syncwarp();
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// 2-D row-major float32 matrix [rows, cols] (cols contiguous), box [box_rows, box_cols].
+bool encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+               uint32_t box_cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 4};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BLOCK_N, bool SPLIT>
+int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mh, const CUtensorMap& ml,
+                   const CUtensorMap& mc, const GemmParams& p) {
+  constexpr int smem_bytes = num_stages(BLOCK_N, SPLIT) * stage_bytes(BLOCK_N, SPLIT) + C_STAGING_BYTES +
+                             BARRIER_BYTES + 1024;
+  static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
+  auto kernel = gemm_tcgen05_kernel<BLOCK_N, SPLIT>;
+  static bool configured[64] = {false};  // the attribute is per device
+  if (!configured[ctx->device & 63]) {
+    TFJS_CHECK_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    configured[ctx->device & 63] = true;
+  }
+  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+  kernel<<<grid, SPLIT ? 320 : 192, smem_bytes, ctx->stream>>>(ma, mh, ml, mc, p);
+  return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32)" : "gemm_tcgen05 (TF32)");
+}
+
+}  // namespace
+
+bool tcgen05_gemm_supported(int64_t M, int64_t N, int64_t K) {
+  // TMA needs 16-byte row strides; tiles smaller than one MMA are left to the CUDA cores.
+  return M >= 1 && N >= 8 && K >= 4 && K % 4 == 0 && N % 4 == 0 && M < (1ll << 31) &&
+         N < (1ll << 31) && K < (1ll << 31) && get_encode_fn() != nullptr;
+}
+
+int launch_gemm_tcgen05(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, const float* w_hi,
+                        const float* w_lo, int64_t kp, float* out, int64_t N, const EpilogueArgs& epi,
+                        int math_mode) {
+  const bool split = math_mode == TFJS_MATH_TF32X3;
+  TFJS_REQUIRE(ctx, !split || w_lo != nullptr, "3xTF32 needs the residual weight plane");
+  int block_n;
+  if (N <= 32) block_n = 32;
+  else if (N <= 64) block_n = 64;
+  else if (N <= 128 || split) block_n = 128;
+  else block_n = (N % 256 == 0 || N > 512) ? 256 : 128;
+  // keep enough tiles in flight to fill the machine when M is small
+  const int64_t m_tiles = ceil_div64(M, BLOCK_M);
+  while (block_n > 32 && m_tiles * ceil_div64(N, block_n) < ctx->sm_count && block_n / 2 >= 32)
+    block_n /= 2;
+
+  CUtensorMap ma, mh, ml, mc;
+  bool ok = encode_2d(&ma, a, (uint64_t)M, (uint64_t)K, BLOCK_M, BLOCK_K) &&
+            encode_2d(&mh, w_hi, (uint64_t)N, (uint64_t)kp, (uint32_t)block_n, BLOCK_K) &&
+            encode_2d(&ml, split ? w_lo : w_hi, (uint64_t)N, (uint64_t)kp, (uint32_t)block_n, BLOCK_K) &&
+            encode_2d(&mc, out, (uint64_t)M, (uint64_t)N, 32, 32);
+  if (!ok) return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+
+  GemmParams p;
+  p.M = (int)M;
+  p.N = (int)N;
+  p.K = (int)K;
+  p.num_m_tiles = (int)m_tiles;
+  p.num_n_tiles = (int)ceil_div64(N, block_n);
+  p.num_k_blocks = (int)ceil_div64(K, BLOCK_K);
+  p.status = ctx->d_status;
+  p.epi = epi;
+  switch (block_n) {
+    case 32: return split ? launch_variant<32, true>(ctx, ma, mh, ml, mc, p) : launch_variant<32, false>(ctx, ma, mh, ml, mc, p);
+    case 64: return split ? launch_variant<64, true>(ctx, ma, mh, ml, mc, p) : launch_variant<64, false>(ctx, ma, mh, ml, mc, p);
+    case 128: return split ? launch_variant<128, true>(ctx, ma, mh, ml, mc, p) : launch_variant<128, false>(ctx, ma, mh, ml, mc, p);
+    default: return launch_variant<256, false>(ctx, ma, mh, ml, mc, p);
+  }
+}

@@ -1,0 +1,272 @@
+"""A small host-side stand-in for the parts of tfjs-core's Engine that call the backend.
+
+The real engine (tfjs-core/src/engine.ts) is TypeScript and runs unchanged on top of a
+KernelBackend; it cannot run here (no JavaScript toolchain), so this module replays its
+calling sequence against the same backend interface: backend registry with priorities and
+fallback on failed initialisation (engine.ts:220-359), tensor registry with per-dataId
+reference counts (engine.ts:502-572), tidy scopes (engine.ts:365-399, 675-718) and the
+runKernel dispatcher (engine.ts:435-498).  No autograd: the path is inference.
+"""
+import warnings
+
+import numpy as np
+
+NP_DTYPE = {"float32": np.float32, "int32": np.int32, "bool": np.uint8}
+
+
+class DataId:
+    """Opaque storage key; plays the role of the `dataId` object (tensor.ts:408-416)."""
+    __slots__ = ("__weakref__",)
+
+
+def size_from_shape(shape):
+    n = 1
+    for s in shape:
+        n *= int(s)
+    return n
+
+
+class Tensor:
+    """tensor.ts:419-484: a shape, a dtype and a dataId registered with the engine."""
+
+    def __init__(self, shape, dtype, values=None, data_id=None, backend=None):
+        self.shape = [int(s) for s in shape]
+        self.dtype = dtype
+        self.size = size_from_shape(self.shape)
+        self.dataId = data_id if data_id is not None else DataId()
+        self.isDisposed = False
+        ENGINE.registerTensor(self, backend)
+        if values is not None:
+            ENGINE.write(backend, self.dataId, values)
+
+    @staticmethod
+    def make(shape, data=None, dtype="float32", backend=None):
+        """Tensor.make (tensor.ts:474-484): data is {} for a backend-created output,
+        {'dataId': id} for an alias, {'values': array} for host data."""
+        data = data or {}
+        return Tensor(shape, dtype, data.get("values"), data.get("dataId"), backend)
+
+    @property
+    def rank(self):
+        return len(self.shape)
+
+    def dataSync(self):
+        self._throw_if_disposed()
+        return ENGINE.readSync(self.dataId)
+
+    def data(self):
+        """Asynchronous read: returns a handle whose .result() blocks (tensor.ts:616-630)."""
+        self._throw_if_disposed()
+        return ENGINE.read(self.dataId)
+
+    def dispose(self):
+        if self.isDisposed:
+            return
+        ENGINE.disposeTensor(self)
+        self.isDisposed = True
+
+    def _throw_if_disposed(self):
+        if self.isDisposed:
+            raise RuntimeError("Tensor is disposed.")
+
+    def reshape(self, shape):
+        from . import ops
+        return ops.reshape(self, shape)
+
+
+class Engine:
+    def __init__(self):
+        self.reset()
+
+    def reset(self):
+        for b in getattr(self, "registry", {}).values():
+            b.dispose()
+        self.registryFactory = {}   # name -> (factory, priority)
+        self.registry = {}          # name -> initialised backend
+        self.backendName = None
+        self.backendInstance = None
+        self.tensorInfo = {}        # DataId -> {backend, refCount, shape, dtype, bytes}
+        self.numTensors = 0
+        self.numBytes = 0
+        self.numDataBuffers = 0
+        self.scopeStack = []
+        self.kernelDepth = 0
+        self.kernelNames = []       # runKernel trace (profile-like): one entry per backend call
+
+    # ---- backend registry (engine.ts:220-359) ----
+    def registerBackend(self, name, factory, priority=1):
+        if name in self.registryFactory:
+            warnings.warn(f"{name} backend was already registered. Reusing existing backend factory.")
+            return False
+        self.registryFactory[name] = (factory, priority)
+        return True
+
+    def findBackend(self, name):
+        if name not in self.registry:
+            if name in self.registryFactory:
+                return self.registry[name] if self.initializeBackend(name) else None
+            return None
+        return self.registry[name]
+
+    def initializeBackend(self, name):
+        if name not in self.registryFactory:
+            raise ValueError(f"Cannot initialize backend {name}, no registration found.")
+        factory, _ = self.registryFactory[name]
+        try:
+            self.registry[name] = factory()
+            return True
+        except Exception as err:  # engine.ts:302-306: warn and let the caller fall back
+            warnings.warn(f"Initialization of backend {name} failed: {err}")
+            return False
+
+    def setBackend(self, name):
+        if name not in self.registryFactory:
+            raise ValueError(f"Backend name '{name}' not found in registry")
+        self.backendName = name
+        if name not in self.registry:
+            self.backendInstance = None
+            if not self.initializeBackend(name):
+                return False
+        self.backendInstance = self.registry[name]
+        return True
+
+    def initializeBackendsAndReturnBest(self):
+        """engine.ts:334-359: try factories by descending priority."""
+        if not self.registryFactory:
+            raise RuntimeError("No backend found in registry.")
+        for name in sorted(self.registryFactory, key=lambda n: -self.registryFactory[n][1]):
+            if self.initializeBackend(name):
+                return name, self.registry[name]
+        raise RuntimeError("Could not initialize any backends, all backend initializations failed.")
+
+    @property
+    def backend(self):
+        if self.backendInstance is None:
+            name, inst = self.initializeBackendsAndReturnBest()
+            self.backendName, self.backendInstance = name, inst
+        return self.backendInstance
+
+    def removeBackend(self, name):
+        self.registryFactory.pop(name, None)
+        b = self.registry.pop(name, None)
+        if b is not None:
+            b.dispose()
+            if self.backendInstance is b:
+                self.backendInstance = None
+                self.backendName = None
+
+    # ---- tensor registry (engine.ts:502-572) ----
+    def registerTensor(self, t, backend=None):
+        info = self.tensorInfo.get(t.dataId)
+        self.numTensors += 1
+        if info is None:
+            b = backend or self.backend
+            nbytes = t.size * (1 if t.dtype == "bool" else 4)
+            self.tensorInfo[t.dataId] = {"backend": b, "refCount": 0, "shape": t.shape,
+                                         "dtype": t.dtype, "bytes": nbytes}
+            self.numBytes += nbytes
+            self.numDataBuffers += 1
+            b.register(t.dataId, t.shape, t.dtype)
+            info = self.tensorInfo[t.dataId]
+        info["refCount"] += 1
+        if self.scopeStack:
+            self.scopeStack[-1]["track"].append(t)
+
+    def disposeTensor(self, t):
+        info = self.tensorInfo.get(t.dataId)
+        if info is None:
+            return
+        self.numTensors -= 1
+        if info["refCount"] <= 1:
+            self.numBytes -= info["bytes"]
+            self.numDataBuffers -= 1
+            info["backend"].disposeData(t.dataId)
+            del self.tensorInfo[t.dataId]
+        else:
+            info["refCount"] -= 1
+
+    def write(self, backend, data_id, values):
+        info = self.tensorInfo[data_id]
+        dest = backend or self.backend
+        if dest is not info["backend"]:
+            # engine.ts:843-851: the tensor migrates to the destination backend
+            info["backend"].disposeData(data_id)
+            info["backend"] = dest
+            dest.register(data_id, info["shape"], info["dtype"])
+        dest.write(data_id, values)
+
+    def readSync(self, data_id):
+        return self.tensorInfo[data_id]["backend"].readSync(data_id)
+
+    def read(self, data_id):
+        return self.tensorInfo[data_id]["backend"].read(data_id)
+
+    def moveData(self, dest_backend, data_id):
+        """engine.ts:361-363: host-staged copy between backends (DataStorage miss)."""
+        self.write(dest_backend, data_id, self.readSync(data_id))
+
+    # ---- scopes (engine.ts:365-399, 675-718) ----
+    def startScope(self, name=None):
+        self.scopeStack.append({"track": [], "name": name})
+
+    def endScope(self, result=None):
+        keep = set()
+        for t in _tensors_in(result):
+            keep.add(id(t))
+        scope = self.scopeStack.pop()
+        for t in scope["track"]:
+            if id(t) in keep or t.isDisposed:
+                continue
+            t.dispose()
+        if self.scopeStack:
+            for t in _tensors_in(result):
+                self.scopeStack[-1]["track"].append(t)
+
+    def tidy(self, fn):
+        self.startScope()
+        result = None
+        try:
+            result = fn()
+            return result
+        finally:
+            self.endScope(result)
+
+    # ---- kernel dispatch (engine.ts:435-498) ----
+    def runKernel(self, forward, name=None):
+        self.kernelDepth += 1
+        try:
+            if name:
+                self.kernelNames.append(name)
+            return forward(self.backend)
+        finally:
+            self.kernelDepth -= 1
+
+    def memory(self):
+        info = dict(self.backend.memory())
+        info.update(numTensors=self.numTensors, numDataBuffers=self.numDataBuffers,
+                    numBytes=self.numBytes)
+        return info
+
+    def time(self, fn):
+        return self.backend.time(fn)
+
+
+def _tensors_in(result):
+    if result is None:
+        return []
+    if isinstance(result, Tensor):
+        return [result]
+    if isinstance(result, (list, tuple)):
+        out = []
+        for r in result:
+            out.extend(_tensors_in(r))
+        return out
+    if isinstance(result, dict):
+        out = []
+        for r in result.values():
+            out.extend(_tensors_in(r))
+        return out
+    return []
+
+
+ENGINE = Engine()

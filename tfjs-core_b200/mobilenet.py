@@ -1,0 +1,184 @@
+"""MobileNetV1 (alpha 1.0, 224x224) inference written against the tfjs-core op surface.
+
+The reference repository holds no model code (models live in @tensorflow-models); this driver
+expresses the network with the ops an application would call (tf.fused.conv2d,
+tf.depthwiseConv2d, tf.add, tf.clipByValue, tf.avgPool, tf.softmax), which is 77 backend
+kernel calls per forward, and alternatively with the backend's fused extensions (relu6
+epilogues, fused depthwise, fused softmax), which is 30 launches.
+
+Weights are synthetic (seeded numpy PCG64): Glorot-uniform filters, N(0, 0.01) biases with
+batch-norm assumed folded; optionally every filter is stored as uint8 affine-quantised bytes
+(w = q*scale + min, the tfjs weights-manifest quantisation).
+"""
+import numpy as np
+
+from . import conv_util, ops
+from .engine import ENGINE
+
+PW_OUT = [64, 128, 128, 256, 256, 512, 512, 512, 512, 512, 512, 1024, 1024]
+DW_STRIDE = [1, 2, 1, 2, 1, 2, 1, 1, 1, 1, 1, 2, 1]
+NUM_CLASSES = 1000
+
+
+def layer_specs():
+    """[(name, kind, filter_shape, stride)] in execution order."""
+    specs = [("stem", "conv", (3, 3, 3, 32), 2)]
+    c = 32
+    for i, (co, s) in enumerate(zip(PW_OUT, DW_STRIDE), 1):
+        specs.append((f"dw{i}", "dw", (3, 3, c, 1), s))
+        specs.append((f"pw{i}", "conv", (1, 1, c, co), 1))
+        c = co
+    specs.append(("fc", "conv", (1, 1, c, NUM_CLASSES), 1))
+    return specs
+
+
+def _glorot(rng, shape, depthwise):
+    fh, fw, cin, cout = shape
+    if depthwise:
+        fan_in = fan_out = fh * fw
+    else:
+        fan_in, fan_out = fh * fw * cin, fh * fw * cout
+    lim = np.sqrt(6.0 / (fan_in + fan_out))
+    return rng.uniform(-lim, lim, size=shape)
+
+
+def make_weights(seed, quantized=False, gain=1.0):
+    """Host-side synthetic parameters.  Returns {name: {'w': float32 array | None, 'q': uint8
+    array | None, 'scale', 'min', 'b': float32 bias}} drawn in layer order."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    params = {}
+    for name, kind, shape, _ in layer_specs():
+        cout = shape[2] if kind == "dw" else shape[3]
+        if quantized:
+            q = rng.integers(0, 256, size=shape, dtype=np.uint8)
+            scale = float(rng.uniform(1e-3, 2e-2))
+            entry = {"w": None, "q": q, "scale": scale, "min": -128.0 * scale}
+        else:
+            entry = {"w": (gain * _glorot(rng, shape, kind == "dw")).astype(np.float32), "q": None}
+        entry["b"] = rng.normal(0.0, 0.01, size=cout).astype(np.float32)
+        params[name] = entry
+    return params
+
+
+def make_input(seed, batch, offset=0):
+    """Images ~U(-1, 1), NHWC float32.  `offset` skips that many images of the stream so that
+    shards of one global batch draw disjoint slices of the same sequence."""
+    rng = np.random.Generator(np.random.PCG64([seed, 12345]))
+    if offset:
+        rng.random(size=(offset, 224, 224, 3), dtype=np.float32)
+    return (rng.random(size=(batch, 224, 224, 3), dtype=np.float32) * 2.0 - 1.0).astype(np.float32)
+
+
+class MobileNetV1:
+    """Device-resident parameters plus the two forward paths."""
+
+    def __init__(self, params, backend=None):
+        self.backend = backend or ENGINE.backend
+        self.params = {}
+        for name, p in params.items():
+            if p["q"] is not None:
+                w = self.backend.registerQuantized(list(p["q"].shape), p["q"], p["scale"], p["min"])
+            else:
+                w = ops.tensor(p["w"])
+            self.params[name] = (w, ops.tensor(p["b"]))
+
+    def dispose(self):
+        for w, b in self.params.values():
+            w.dispose()
+            b.dispose()
+        self.params = {}
+
+    def forward_reference_api(self, x):
+        """The network as unmodified tf.* code expresses it at this version of the library:
+        no relu6 activation and no fused depthwise exist, so every layer is 2-3 backend calls
+        and softmax is the 8-kernel op-layer chain."""
+        def body():
+            w, b = self.params["stem"]
+            h = ops.fused_conv2d(x, w, 2, "same", bias=b, activation="linear")
+            h = ops.clip_by_value(h, 0, 6)
+            for i, s in enumerate(DW_STRIDE, 1):
+                w, b = self.params[f"dw{i}"]
+                h = ops.depthwise_conv2d(h, w, s, "same")
+                h = ops.add(h, b)
+                h = ops.clip_by_value(h, 0, 6)
+                w, b = self.params[f"pw{i}"]
+                h = ops.fused_conv2d(h, w, 1, "same", bias=b)
+                h = ops.clip_by_value(h, 0, 6)
+            h = ops.avg_pool(h, [7, 7], 1, "valid")
+            w, b = self.params["fc"]
+            h = ops.fused_conv2d(h, w, 1, "same", bias=b)
+            logits = ops.reshape(h, [h.shape[0], NUM_CLASSES])
+            return logits, ops.softmax(logits)
+        return ENGINE.tidy(body)
+
+    def forward_fused(self, x):
+        """The same network through the backend's fused extensions: 1 + 13*2 + 1 + 1 + 1 = 30
+        kernel launches."""
+        bk = self.backend
+
+        def body():
+            w, b = self.params["stem"]
+            ci = conv_util.compute_conv2d_info(x.shape, w.shape, 2, 1, "same")
+            h = bk.fusedConv2d(x, w, ci, b, "relu6")
+            for i, s in enumerate(DW_STRIDE, 1):
+                w, b = self.params[f"dw{i}"]
+                ci = conv_util.compute_conv2d_info(h.shape, w.shape, s, 1, "same", None, True)
+                h = bk.fusedDepthwiseConv2D(h, w, ci, b, "relu6")
+                w, b = self.params[f"pw{i}"]
+                ci = conv_util.compute_conv2d_info(h.shape, w.shape, 1, 1, "same")
+                h = bk.fusedConv2d(h, w, ci, b, "relu6")
+            ci = conv_util.compute_pool2d_info(h.shape, [7, 7], 1, 1, "valid")
+            h = bk.avgPool(h, ci)
+            w, b = self.params["fc"]
+            ci = conv_util.compute_conv2d_info(h.shape, w.shape, 1, 1, "same")
+            h = bk.fusedConv2d(h, w, ci, b, "linear")
+            logits = bk.reshape(h, [h.shape[0], NUM_CLASSES])
+            return logits, bk.softmax(logits)
+        return ENGINE.tidy(body)
+
+
+def algorithmic_bytes_per_image(quantized=False):
+    """Bytes one image moves if every tensor is touched once and epilogues are fused:
+    4*(|x| + |y|) per layer; weights are counted separately by weight_bytes()."""
+    total = 0
+    h = w = 224
+    c = 3
+    for name, kind, shape, s in layer_specs():
+        if name == "fc":
+            total += 4 * (7 * 7 * c + c)          # global average pool: in + out
+            total += 4 * (c + NUM_CLASSES)        # fc
+            total += 4 * (NUM_CLASSES * 2)        # softmax
+            break
+        ho, wo = -(-h // s), -(-w // s)
+        co = c if kind == "dw" else shape[3]
+        total += 4 * (h * w * c + ho * wo * co)
+        h, w, c = ho, wo, co
+    return total
+
+
+def weight_bytes(quantized=False):
+    total = 0
+    for name, kind, shape, _ in layer_specs():
+        n = int(np.prod(shape))
+        cout = shape[2] if kind == "dw" else shape[3]
+        total += n * (1 if quantized else 4) + 4 * cout
+    return total
+
+
+def flops_per_image():
+    total = 0
+    h = w = 224
+    c = 3
+    for name, kind, shape, s in layer_specs():
+        if name == "fc":
+            total += 7 * 7 * c + 2 * c * NUM_CLASSES
+            break
+        ho, wo = -(-h // s), -(-w // s)
+        if kind == "dw":
+            total += 2 * ho * wo * c * 9
+            co = c
+        else:
+            co = shape[3]
+            total += 2 * ho * wo * co * shape[0] * shape[1] * shape[2]
+        h, w, c = ho, wo, co
+    return total
