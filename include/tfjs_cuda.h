@@ -116,6 +116,13 @@ int tfjs_cuda_ctx_memory(tfjs_cuda_ctx* ctx, tfjs_cuda_mem_stats* out);
  * time between them, *num_launches the kernels this library launched in between. */
 int tfjs_cuda_ctx_time_begin(tfjs_cuda_ctx* ctx);
 int tfjs_cuda_ctx_time_end(tfjs_cuda_ctx* ctx, float* kernel_ms, int64_t* num_launches);
+/* Per-kernel device timing, the "extra profile info" of BackendTimingInfo (backend.ts:27-31)
+ * and the per-kernel rows of the DEBUG profiler (profiler.ts:30-74): between begin and end an
+ * event is recorded after every launch (up to max_launches); profile_get(i) returns the name
+ * and the device milliseconds of the i-th launch. */
+int tfjs_cuda_profile_begin(tfjs_cuda_ctx* ctx, int max_launches);
+int tfjs_cuda_profile_end(tfjs_cuda_ctx* ctx, int* num_launches);
+int tfjs_cuda_profile_get(tfjs_cuda_ctx* ctx, int index, const char** name, float* ms);
 /* Total kernels launched by this context since creation. */
 int64_t tfjs_cuda_ctx_launch_count(const tfjs_cuda_ctx* ctx);
 /* The cudaStream_t of the context (as void*), for callers that time with their own events. */
@@ -193,7 +200,12 @@ int tfjs_cuda_softmax_last(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id 
  * converts x's stored dtype to out's dtype (float->int truncates, ->bool is != 0). */
 int tfjs_cuda_cast(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id out);
 
-/* ---- extension: CUDA-graph capture of a sequence of calls on the context. */
+/* ---- extension: CUDA-graph capture of a sequence of calls on the context.
+ * Between begin and end, kernel calls are recorded instead of run.  Tensors disposed during
+ * the capture keep their buffers inside the graph (replays write to them) until
+ * graph_destroy; tensors created during the capture and still alive at graph_end (the
+ * outputs) are rewritten by every replay and must not be disposed before the graph is.
+ * tensor_read and ctx_sync are rejected while capturing. */
 int tfjs_cuda_graph_begin(tfjs_cuda_ctx* ctx);
 int tfjs_cuda_graph_end(tfjs_cuda_ctx* ctx, tfjs_cuda_graph** out);
 int tfjs_cuda_graph_launch(tfjs_cuda_ctx* ctx, tfjs_cuda_graph* graph);

@@ -60,6 +60,9 @@ SIGNATURES = {
     "tfjs_cuda_ctx_memory": (C.c_int, [_P, C.POINTER(MemStats)]),
     "tfjs_cuda_ctx_time_begin": (C.c_int, [_P]),
     "tfjs_cuda_ctx_time_end": (C.c_int, [_P, C.POINTER(C.c_float), _I64P]),
+    "tfjs_cuda_profile_begin": (C.c_int, [_P, C.c_int]),
+    "tfjs_cuda_profile_end": (C.c_int, [_P, C.POINTER(C.c_int)]),
+    "tfjs_cuda_profile_get": (C.c_int, [_P, C.c_int, C.POINTER(C.c_char_p), C.POINTER(C.c_float)]),
     "tfjs_cuda_ctx_launch_count": (C.c_int64, [_P]),
     "tfjs_cuda_ctx_stream": (_P, [_P]),
     "tfjs_cuda_tensor_register": (C.c_int, [_P, _I64P, C.c_int, _I64P, C.c_int]),

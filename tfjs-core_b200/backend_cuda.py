@@ -204,6 +204,21 @@ class BackendCuda:
     def sync(self, timeout_ms=-1):
         self._check(self._lib.tfjs_cuda_ctx_sync(self._ctx, int(timeout_ms)))
 
+    def profileBegin(self, max_launches=4096):
+        """Extension: start recording one device-time row per kernel launch."""
+        self._check(self._lib.tfjs_cuda_profile_begin(self._ctx, int(max_launches)))
+
+    def profileEnd(self):
+        """Returns [(kernel name, milliseconds)] for every launch since profileBegin()."""
+        n = C.c_int()
+        self._check(self._lib.tfjs_cuda_profile_end(self._ctx, C.byref(n)))
+        rows = []
+        for i in range(n.value):
+            name, ms = C.c_char_p(), C.c_float()
+            self._check(self._lib.tfjs_cuda_profile_get(self._ctx, i, C.byref(name), C.byref(ms)))
+            rows.append((name.value.decode(), ms.value))
+        return rows
+
     def launchCount(self):
         return self._lib.tfjs_cuda_ctx_launch_count(self._ctx)
 

@@ -52,7 +52,9 @@ struct tfjs_cuda_graph {
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
   // Buffers disposed while capturing stay owned by the graph: replays write to them.
-  std::vector<std::pair<void*, size_t>> held;
+  std::map<void*, size_t> held;
+  // held buffers that are free again inside the capture: later captured kernels may reuse them
+  std::map<size_t, std::vector<void*>> reusable;
   int64_t launches_per_replay = 0;
 };
 
@@ -79,6 +81,11 @@ struct tfjs_cuda_ctx {
   int64_t launch_count = 0;
   cudaEvent_t time_start = nullptr, time_stop = nullptr;
   int64_t time_start_launches = 0;
+  // per-kernel profile: while enabled, an event is recorded after every launch
+  bool profiling = false;
+  std::vector<cudaEvent_t> profile_events;   // [0] is the start marker
+  std::vector<const char*> profile_names;    // name of the launch that precedes event i+1
+  size_t profile_used = 0;
   // graph capture
   tfjs_cuda_graph* capturing = nullptr;
   int64_t capture_start_launches = 0;

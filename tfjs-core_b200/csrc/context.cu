@@ -31,6 +31,50 @@ int post_launch(tfjs_cuda_ctx* ctx, const char* what) {
     if (e != cudaSuccess)
       return set_error(ctx, TFJS_CUDA_ERR_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
   }
+  if (ctx->profiling && !ctx->capturing && ctx->profile_used + 1 < ctx->profile_events.size()) {
+    cudaEventRecord(ctx->profile_events[ctx->profile_used + 1], ctx->stream);
+    ctx->profile_names[ctx->profile_used] = what;
+    ctx->profile_used++;
+  }
+  return TFJS_CUDA_OK;
+}
+
+// ---- per-kernel profile --------------------------------------------------------------------
+// The stream is in-order, so the time between the events that bracket a launch is that
+// kernel's duration (plus any idle gap before it, which vanishes once the host runs ahead).
+extern "C" int tfjs_cuda_profile_begin(tfjs_cuda_ctx* ctx, int max_launches) {
+  if (!ctx || max_launches < 1) return TFJS_CUDA_ERR_INVALID_ARG;
+  TFJS_REQUIRE(ctx, !ctx->capturing, "cannot profile while capturing a graph");
+  cudaSetDevice(ctx->device);
+  while (ctx->profile_events.size() < (size_t)max_launches + 1) {
+    cudaEvent_t ev;
+    TFJS_CHECK_CUDA(ctx, cudaEventCreate(&ev));
+    ctx->profile_events.push_back(ev);
+  }
+  ctx->profile_names.assign(ctx->profile_events.size(), nullptr);
+  ctx->profile_used = 0;
+  TFJS_CHECK_CUDA(ctx, cudaEventRecord(ctx->profile_events[0], ctx->stream));
+  ctx->profiling = true;
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_profile_end(tfjs_cuda_ctx* ctx, int* num_launches) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  ctx->profiling = false;
+  cudaSetDevice(ctx->device);
+  if (ctx->profile_used)
+    TFJS_CHECK_CUDA(ctx, cudaEventSynchronize(ctx->profile_events[ctx->profile_used]));
+  if (num_launches) *num_launches = (int)ctx->profile_used;
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_profile_get(tfjs_cuda_ctx* ctx, int index, const char** name, float* ms) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  TFJS_REQUIRE(ctx, index >= 0 && (size_t)index < ctx->profile_used, "profile index out of range");
+  float t = 0.f;
+  TFJS_CHECK_CUDA(ctx, cudaEventElapsedTime(&t, ctx->profile_events[index], ctx->profile_events[index + 1]));
+  if (name) *name = ctx->profile_names[index];
+  if (ms) *ms = t;
   return TFJS_CUDA_OK;
 }
 
@@ -64,6 +108,19 @@ int ctx_alloc(tfjs_cuda_ctx* ctx, size_t nbytes, void** ptr, size_t* capacity) {
   *capacity = 0;
   if (nbytes == 0) return TFJS_CUDA_OK;
   const size_t cls = size_class(nbytes);
+  if (ctx->capturing) {
+    // Buffers released earlier in this capture can serve later captured kernels: the graph
+    // replays its nodes in the captured order, so the reuse stays stream-ordered.
+    auto rit = ctx->capturing->reusable.find(cls);
+    if (rit != ctx->capturing->reusable.end() && !rit->second.empty()) {
+      *ptr = rit->second.back();
+      rit->second.pop_back();
+      ctx->capturing->held.erase(*ptr);  // owned by a tensor again; re-held if freed later
+      *capacity = cls;
+      ctx->bytes_in_use += (int64_t)cls;
+      return TFJS_CUDA_OK;
+    }
+  }
   auto it = ctx->free_lists.find(cls);
   if (it != ctx->free_lists.end() && !it->second.empty()) {
     *ptr = it->second.back();
@@ -96,7 +153,8 @@ void ctx_free(tfjs_cuda_ctx* ctx, void* ptr, size_t capacity) {
   ctx->bytes_in_use -= (int64_t)capacity;
   if (ctx->capturing) {
     // A captured graph keeps writing to this buffer on every replay.
-    ctx->capturing->held.emplace_back(ptr, capacity);
+    ctx->capturing->held[ptr] = capacity;
+    ctx->capturing->reusable[capacity].push_back(ptr);
     return;
   }
   ctx->free_lists[capacity].push_back(ptr);
@@ -172,6 +230,7 @@ extern "C" int tfjs_cuda_ctx_destroy(tfjs_cuda_ctx* ctx) {
   release_cached(ctx);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
+  for (cudaEvent_t ev : ctx->profile_events) cudaEventDestroy(ev);
   if (ctx->time_start) cudaEventDestroy(ctx->time_start);
   if (ctx->time_stop) cudaEventDestroy(ctx->time_stop);
   if (ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -535,6 +594,7 @@ extern "C" int tfjs_cuda_graph_end(tfjs_cuda_ctx* ctx, tfjs_cuda_graph** out) {
   tfjs_cuda_graph* g = ctx->capturing;
   ctx->capturing = nullptr;
   g->launches_per_replay = ctx->launch_count - ctx->capture_start_launches;
+  g->reusable.clear();
   cudaError_t e = cudaStreamEndCapture(ctx->stream, &g->graph);
   if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
   if (e != cudaSuccess) {

@@ -116,6 +116,12 @@ class MobileNetV1:
         kernel launches."""
         bk = self.backend
 
+        def then(new, old):
+            # free each activation as soon as its consumer is enqueued, so that two buffers of
+            # every size circulate instead of one per layer
+            old.dispose()
+            return new
+
         def body():
             w, b = self.params["stem"]
             ci = conv_util.compute_conv2d_info(x.shape, w.shape, 2, 1, "same")
@@ -123,16 +129,16 @@ class MobileNetV1:
             for i, s in enumerate(DW_STRIDE, 1):
                 w, b = self.params[f"dw{i}"]
                 ci = conv_util.compute_conv2d_info(h.shape, w.shape, s, 1, "same", None, True)
-                h = bk.fusedDepthwiseConv2D(h, w, ci, b, "relu6")
+                h = then(bk.fusedDepthwiseConv2D(h, w, ci, b, "relu6"), h)
                 w, b = self.params[f"pw{i}"]
                 ci = conv_util.compute_conv2d_info(h.shape, w.shape, 1, 1, "same")
-                h = bk.fusedConv2d(h, w, ci, b, "relu6")
+                h = then(bk.fusedConv2d(h, w, ci, b, "relu6"), h)
             ci = conv_util.compute_pool2d_info(h.shape, [7, 7], 1, 1, "valid")
-            h = bk.avgPool(h, ci)
+            h = then(bk.avgPool(h, ci), h)
             w, b = self.params["fc"]
             ci = conv_util.compute_conv2d_info(h.shape, w.shape, 1, 1, "same")
-            h = bk.fusedConv2d(h, w, ci, b, "linear")
-            logits = bk.reshape(h, [h.shape[0], NUM_CLASSES])
+            h = then(bk.fusedConv2d(h, w, ci, b, "linear"), h)
+            logits = then(bk.reshape(h, [h.shape[0], NUM_CLASSES]), h)
             return logits, bk.softmax(logits)
         return ENGINE.tidy(body)
 
