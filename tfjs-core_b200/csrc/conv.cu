@@ -152,61 +152,63 @@ __global__ void depthwise_generic_kernel(const float* __restrict__ x, const floa
   }
 }
 
-// Fast path: 3x3, dilation 1, channel multiplier 1, C % 4 == 0 (every MobileNet depthwise
-// layer).  A thread owns 4 consecutive channels of TILE_W consecutive output columns of one
-// output row: the 3 x (TILE_W*S + 2) input window is loaded once as float4 (128-bit NHWC
-// loads, consecutive threads on consecutive channel quads => fully coalesced rows) and every
-// loaded value feeds up to 3 outputs from registers, so each input row is fetched once per
-// output row it contributes to (L2 absorbs the 3x / 1.5x vertical reuse).
-template <int S, int TILE_W>
-__global__ void __launch_bounds__(256)
-depthwise3x3_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                    float* __restrict__ y, tfjs_conv2d_info ci, EpilogueArgs epi) {
-  constexpr int IN_W = (TILE_W - 1) * S + 3;
-  const int C4 = ci.inChannels >> 2;
-  const int w_tiles = (ci.outWidth + TILE_W - 1) / TILE_W;
-  const int64_t total = (int64_t)ci.batchSize * ci.outHeight * w_tiles * C4;
-  const float4* x4 = reinterpret_cast<const float4*>(x);
-  const float4* w4 = reinterpret_cast<const float4*>(w);
-  float4* y4 = reinterpret_cast<float4*>(y);
-  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total;
-       t += (int64_t)gridDim.x * blockDim.x) {
-    const int c4 = (int)(t % C4);
-    int64_t r = t / C4;
-    const int wt = (int)(r % w_tiles);
-    r /= w_tiles;
-    const int yr = (int)(r % ci.outHeight);
-    const int b = (int)(r / ci.outHeight);
-    const int yc0 = wt * TILE_W;
-    // (sic) rows use padLeft, columns use padTop, as the reference does.
-    const int xr0 = yr * S - ci.padLeft;
-    const int xc0 = yc0 * S - ci.padTop;
-    float4 wv[9];
+// Shared-memory float4 load the compiler may not hoist: the filter taps are re-read every
+// step on purpose, keeping them out of the register file (36 registers) for occupancy.
+__device__ __forceinline__ float4 lds128_volatile(const float4* p) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"((uint32_t)__cvta_generic_to_shared(p)));
+  return v;
+}
+
+template <int ACT>
+__device__ __forceinline__ float activate(float v, float lo, float hi) {
+  if (ACT == TFJS_ACT_RELU) return max_nan(v, 0.f);              // Math.max(0, v): keeps NaN
+  if (ACT == TFJS_ACT_CLIP) return min_nan(max_nan(v, lo), hi);  // v > hi ? hi : (v < lo ? lo : v)
+  return v;
+}
+
+// Fast path: 3x3, dilation 1, channel multiplier 1, C % 4 == 0, stride 1 or 2 (every MobileNet
+// depthwise layer).  A thread owns 4 channels of TW adjacent output columns and walks down a
+// strip of output rows with the 3 x IN_W input window in registers.  The three window rows
+// live in three register banks whose roles (top / middle / bottom) rotate from step to step,
+// so nothing is copied: as soon as the taps of the top row are issued, the row that enters
+// the window next is loaded into its registers (128-bit NHWC loads, consecutive threads on
+// consecutive channel quads) and is first needed as the bottom row of the following step,
+// which hides the load latency behind two thirds of a step.  A block covers a slice of at
+// most 128 channel quads (blockIdx.y) and stages only that slice of the filter in shared
+// memory; blocks are persistent (one wave).  Taps outside the image are skipped, not
+// multiplied by zero, as the reference skips them (backend_cpu.ts:2002-2014); accumulation
+// order is wR, wC ascending with one float32 rounding per tap (fmaf).
+template <int S, int TW, int ACT>
+struct DepthwiseStrip {
+  static constexpr int IN_W = (TW - 1) * S + 3;
+  float4 R[3][IN_W];   // window rows; which is top/middle/bottom rotates
+  bool rk[3];          // row inside the image (border items only)
+  bool ck[IN_W];       // column inside the image (border items only)
+  float4 acc[TW];
+
+  template <bool INTERIOR>
+  __device__ __forceinline__ void load(int slot, const float4* rp, bool row_ok, int C4) {
+    if (!INTERIOR) rk[slot] = row_ok;
 #pragma unroll
-    for (int k = 0; k < 9; k++) wv[k] = __ldg(w4 + k * C4 + c4);
-    float4 acc[TILE_W];
+    for (int i = 0; i < IN_W; i++) {
+      if (INTERIOR) R[slot][i] = rp[i * C4];
+      else R[slot][i] = (row_ok && ck[i]) ? rp[i * C4] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+
+  template <bool INTERIOR>
+  __device__ __forceinline__ void taps(int slot, int wr, const float4* w_s, int cbn, int c_local) {
+    if (!INTERIOR && !rk[slot]) return;  // the whole filter row lies outside: skipped
 #pragma unroll
-    for (int j = 0; j < TILE_W; j++) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int wc = 0; wc < 3; ++wc) {
+      const float4 f = lds128_volatile(&w_s[(wr * 3 + wc) * cbn + c_local]);
 #pragma unroll
-    for (int wr = 0; wr < 3; ++wr) {
-      const int xr = xr0 + wr;
-      if (xr < 0 || xr >= ci.inHeight) continue;
-      const float4* row = x4 + ((int64_t)b * ci.inHeight + xr) * ci.inWidth * C4 + c4;
-      float4 in[IN_W];
-#pragma unroll
-      for (int i = 0; i < IN_W; i++) {
-        const int xc = xc0 + i;
-        // NaN marks an out-of-bounds tap: it is skipped below, never multiplied.
-        in[i] = (xc >= 0 && xc < ci.inWidth) ? row[(int64_t)xc * C4] : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll
-      for (int j = 0; j < TILE_W; j++) {
-#pragma unroll
-        for (int wc = 0; wc < 3; ++wc) {
-          const int xc = xc0 + j * S + wc;
-          if (xc < 0 || xc >= ci.inWidth) continue;  // skipped tap: no MAC, like the reference
-          const float4 v = in[j * S + wc];
-          const float4 f = wv[wr * 3 + wc];
+      for (int j = 0; j < TW; j++) {
+        if (INTERIOR || ck[j * S + wc]) {
+          const float4 v = R[slot][j * S + wc];
           acc[j].x = fmaf(v.x, f.x, acc[j].x);
           acc[j].y = fmaf(v.y, f.y, acc[j].y);
           acc[j].z = fmaf(v.z, f.z, acc[j].z);
@@ -214,17 +216,130 @@ depthwise3x3_kernel(const float* __restrict__ x, const float* __restrict__ w,
         }
       }
     }
-    float4* yrow = y4 + (((int64_t)b * ci.outHeight + yr) * ci.outWidth + yc0) * C4 + c4;
+  }
+
+  // One output row.  A = register bank holding the top row.  prow points at the top input
+  // row of this step's window (column xi0, this thread's channel quad).
+  template <int A, bool INTERIOR>
+  __device__ __forceinline__ void step(const float4* prow, int yi, bool more, int64_t row_stride,
+                                       const tfjs_conv2d_info& ci, int C4, const float4* w_s, int cbn,
+                                       int c_local, float4* yrow, int cols_left, bool has_bias,
+                                       const float4& bias4, float lo, float hi) {
+    constexpr int B = (A + 1) % 3, C = (A + 2) % 3;
 #pragma unroll
-    for (int j = 0; j < TILE_W; j++) {
-      if (yc0 + j >= ci.outWidth) break;
-      float4 o;
-      o.x = apply_epilogue(acc[j].x, c4 * 4 + 0, epi);
-      o.y = apply_epilogue(acc[j].y, c4 * 4 + 1, epi);
-      o.z = apply_epilogue(acc[j].z, c4 * 4 + 2, epi);
-      o.w = apply_epilogue(acc[j].w, c4 * 4 + 3, epi);
-      yrow[(int64_t)j * C4] = o;
+    for (int j = 0; j < TW; j++) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    taps<INTERIOR>(A, 0, w_s, cbn, c_local);
+    // bank A is free: fetch the row that enters the window next (input row yi + 3)
+    if (more) load<INTERIOR>(A, prow + 3 * row_stride, yi + 3 >= 0 && yi + 3 < ci.inHeight, C4);
+    taps<INTERIOR>(B, 1, w_s, cbn, c_local);
+    if (S == 2 && more) load<INTERIOR>(B, prow + 4 * row_stride, yi + 4 >= 0 && yi + 4 < ci.inHeight, C4);
+    taps<INTERIOR>(C, 2, w_s, cbn, c_local);
+#pragma unroll
+    for (int j = 0; j < TW; j++) {
+      if (j < cols_left) {
+        float4 o = acc[j];
+        if (has_bias) { o.x += bias4.x; o.y += bias4.y; o.z += bias4.z; o.w += bias4.w; }
+        o.x = activate<ACT>(o.x, lo, hi);
+        o.y = activate<ACT>(o.y, lo, hi);
+        o.z = activate<ACT>(o.z, lo, hi);
+        o.w = activate<ACT>(o.w, lo, hi);
+        yrow[j * C4] = o;
+      }
     }
+  }
+
+  template <bool INTERIOR>
+  __device__ __forceinline__ void run(const float4* xb, float4* yb, int yo0, int yo1, int xo0, int xi0,
+                                      const tfjs_conv2d_info& ci, int C4, const float4* w_s, int cbn,
+                                      int c_local, bool has_bias, const float4& bias4, float lo,
+                                      float hi) {
+    const int64_t row_stride = (int64_t)ci.inWidth * C4;
+    const int64_t out_stride = (int64_t)ci.outWidth * C4;
+    if (!INTERIOR) {
+#pragma unroll
+      for (int i = 0; i < IN_W; i++) ck[i] = (xi0 + i >= 0) && (xi0 + i < ci.inWidth);
+    }
+    // (sic) rows use padLeft, as backend_cpu.ts:2000 does
+    int yi = yo0 * S - ci.padLeft;
+    const float4* prow = xb + (int64_t)yi * row_stride + (int64_t)xi0 * C4;
+    float4* yrow = yb + (int64_t)yo0 * out_stride + (int64_t)xo0 * C4;
+    const int cols_left = ci.outWidth - xo0;
+#pragma unroll
+    for (int k = 0; k < 3; k++)
+      load<INTERIOR>(k, prow + k * row_stride, yi + k >= 0 && yi + k < ci.inHeight, C4);
+    int yo = yo0;
+    // bank of the top row: 0, 1, 2, 0, ... for stride 1 and 0, 2, 1, 0, ... for stride 2
+    while (true) {
+      step<0, INTERIOR>(prow, yi, yo + 1 < yo1, row_stride, ci, C4, w_s, cbn, c_local, yrow, cols_left,
+                        has_bias, bias4, lo, hi);
+      if (++yo >= yo1) break;
+      prow += S * row_stride; yi += S; yrow += out_stride;
+      step<(S == 1 ? 1 : 2), INTERIOR>(prow, yi, yo + 1 < yo1, row_stride, ci, C4, w_s, cbn, c_local, yrow,
+                                       cols_left, has_bias, bias4, lo, hi);
+      if (++yo >= yo1) break;
+      prow += S * row_stride; yi += S; yrow += out_stride;
+      step<(S == 1 ? 2 : 1), INTERIOR>(prow, yi, yo + 1 < yo1, row_stride, ci, C4, w_s, cbn, c_local, yrow,
+                                       cols_left, has_bias, bias4, lo, hi);
+      if (++yo >= yo1) break;
+      prow += S * row_stride; yi += S; yrow += out_stride;
+    }
+  }
+};
+
+template <int S, int TW, int ACT>
+__global__ void __launch_bounds__(128, 4)
+depthwise3x3_strip_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                          float* __restrict__ y, tfjs_conv2d_info ci, EpilogueArgs epi,
+                          int rows_per_strip, int cb /* channel quads per block */) {
+  constexpr int IN_W = (TW - 1) * S + 3;
+  extern __shared__ float4 w_s[];  // [9][quads of this slice]
+  const int C4 = ci.inChannels >> 2;
+  const int c4_base = blockIdx.y * cb;
+  const int cbn = min(cb, C4 - c4_base);
+  for (int i = threadIdx.x; i < 9 * cbn; i += blockDim.x)
+    w_s[i] = reinterpret_cast<const float4*>(w)[(i / cbn) * C4 + c4_base + (i % cbn)];
+  __syncthreads();
+  const int groups = blockDim.x / cb;  // pixel groups per block
+  const int c_local = threadIdx.x % cb;
+  const int group = threadIdx.x / cb;
+  if (group >= groups || c_local >= cbn) return;
+  const int c4 = c4_base + c_local;
+  const int strips = (ci.outHeight + rows_per_strip - 1) / rows_per_strip;
+  const int w_tiles = (ci.outWidth + TW - 1) / TW;
+  const int64_t items = (int64_t)ci.batchSize * strips * w_tiles;
+  const bool has_bias = epi.bias != nullptr;
+  float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (has_bias) {
+    if (epi.bias_scalar) {
+      const float bv = __ldg(epi.bias);
+      bias4 = make_float4(bv, bv, bv, bv);
+    } else {
+      bias4 = __ldg(reinterpret_cast<const float4*>(epi.bias) + c4);
+    }
+  }
+  DepthwiseStrip<S, TW, ACT> ds;
+  for (int64_t item = (int64_t)blockIdx.x * groups + group; item < items;
+       item += (int64_t)gridDim.x * groups) {
+    const int wt = (int)(item % w_tiles);
+    const int64_t rest = item / w_tiles;
+    const int strip = (int)(rest % strips);
+    const int b = (int)(rest / strips);
+    const int yo0 = strip * rows_per_strip;
+    const int yo1 = min(yo0 + rows_per_strip, ci.outHeight);
+    const int xo0 = wt * TW;
+    const int xi0 = xo0 * S - ci.padTop;  // (sic) columns use padTop, backend_cpu.ts:2010
+    const float4* xb = reinterpret_cast<const float4*>(x) + (int64_t)b * ci.inHeight * ci.inWidth * C4 + c4;
+    float4* yb = reinterpret_cast<float4*>(y) + (int64_t)b * ci.outHeight * ci.outWidth * C4 + c4;
+    const int yi_first = yo0 * S - ci.padLeft;
+    const int yi_last = (yo1 - 1) * S - ci.padLeft + 2;
+    const bool interior = xi0 >= 0 && xi0 + IN_W <= ci.inWidth && yi_first >= 0 &&
+                          yi_last < ci.inHeight && xo0 + TW <= ci.outWidth;
+    if (interior)
+      ds.template run<true>(xb, yb, yo0, yo1, xo0, xi0, ci, C4, w_s, cbn, c_local, has_bias, bias4,
+                            epi.clip_lo, epi.clip_hi);
+    else
+      ds.template run<false>(xb, yb, yo0, yo1, xo0, xi0, ci, C4, w_s, cbn, c_local, has_bias, bias4,
+                             epi.clip_lo, epi.clip_hi);
   }
 }
 
@@ -322,18 +437,41 @@ int launch_depthwise(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* 
   const bool fast = ci.filterHeight == 3 && ci.filterWidth == 3 && ci.dilationHeight == 1 &&
                     ci.dilationWidth == 1 && ci.outChannels == ci.inChannels &&
                     ci.inChannels % 4 == 0 && ci.strideHeight == ci.strideWidth &&
-                    (ci.strideHeight == 1 || ci.strideHeight == 2) &&
+                    (ci.strideHeight == 1 || ci.strideHeight == 2) && epi.activation != TFJS_ACT_PRELU &&
                     (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) == 0;
   if (fast) {
-    constexpr int TILE_W = 4;
-    const int64_t work = (int64_t)ci.batchSize * ci.outHeight * ((ci.outWidth + TILE_W - 1) / TILE_W) *
-                         (ci.inChannels / 4);
-    const int grid = grid_1d(work, 256, ctx->sm_count, 8);
-    if (ci.strideHeight == 1)
-      depthwise3x3_kernel<1, TILE_W><<<grid, 256, 0, ctx->stream>>>(x, w, y, ci, epi);
-    else
-      depthwise3x3_kernel<2, TILE_W><<<grid, 256, 0, ctx->stream>>>(x, w, y, ci, epi);
-    return post_launch(ctx, "depthwiseConv2D (3x3)");
+    const int C4 = ci.inChannels / 4;
+    const int cb = C4 < 128 ? C4 : 128;                // channel quads per block
+    const int slices = (C4 + cb - 1) / cb;
+    const int groups = 128 / cb;                       // pixel groups per block
+    const size_t smem = (size_t)9 * cb * sizeof(float4);
+    const int tw = ci.strideHeight == 1 ? 2 : 1;
+    const int64_t cols = (ci.outWidth + tw - 1) / tw;
+    const int resident = ctx->sm_count * 4;  // one wave of blocks (4 per SM by register use)
+    // strips of output rows: long enough to amortise the halo rows, short enough to give every
+    // resident thread work on the small late layers
+    int rows = 8;
+    while (rows > 2 && (int64_t)ci.batchSize * ((ci.outHeight + rows - 1) / rows) * cols * slices <
+                           (int64_t)resident * groups)
+      rows /= 2;
+    const int64_t items = (int64_t)ci.batchSize * ((ci.outHeight + rows - 1) / rows) * cols;
+    int64_t gx = (items + groups - 1) / groups;
+    if (gx > resident / slices) gx = resident / slices > 0 ? resident / slices : 1;
+    dim3 grid((unsigned)gx, (unsigned)slices);
+#define TFJS_LAUNCH_DW(ACT)                                                                            \
+  do {                                                                                                 \
+    if (ci.strideHeight == 1)                                                                          \
+      depthwise3x3_strip_kernel<1, 2, ACT><<<grid, 128, smem, ctx->stream>>>(x, w, y, ci, epi, rows, cb); \
+    else                                                                                               \
+      depthwise3x3_strip_kernel<2, 1, ACT><<<grid, 128, smem, ctx->stream>>>(x, w, y, ci, epi, rows, cb); \
+  } while (0)
+    switch (epi.activation) {
+      case TFJS_ACT_RELU: TFJS_LAUNCH_DW(TFJS_ACT_RELU); break;
+      case TFJS_ACT_CLIP: TFJS_LAUNCH_DW(TFJS_ACT_CLIP); break;
+      default: TFJS_LAUNCH_DW(TFJS_ACT_LINEAR); break;
+    }
+#undef TFJS_LAUNCH_DW
+    return post_launch(ctx, "depthwiseConv2D (3x3 strip)");
   }
   depthwise_generic_kernel<<<grid_1d(total, 256, ctx->sm_count, 8), 256, 0, ctx->stream>>>(x, w, y, ci, epi);
   return post_launch(ctx, "depthwiseConv2D (generic)");

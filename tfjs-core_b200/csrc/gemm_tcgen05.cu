@@ -7,12 +7,12 @@
 // the GEMM [B*H*W, Cin] x [Cin, Cout].
 //
 // Structure (one persistent CTA per SM, warp specialised):
-//   warp 4      TMA producer: A tile [128 x 32] and W tile(s) [BLOCK_N x 32] per k-block into a
+//   warp 8      TMA producer: A tile [128 x 32] and W tile(s) [BLOCK_N x 32] per k-block into a
 //               ring of shared-memory stages (SWIZZLE_128B, K-major), mbarrier complete_tx.
-//   warps 6-9   (3xTF32 only) split the A stage in place: hi = tf32(a), lo = tf32(a - hi).
-//   warp 5      MMA issuer: one thread issues tcgen05.mma (M=128, N=BLOCK_N, K=8) per 32-byte
+//   warps 10-13 (3xTF32 only) split the A stage in place: hi = tf32(a), lo = tf32(a - hi).
+//   warp 9      MMA issuer: one thread issues tcgen05.mma (M=128, N=BLOCK_N, K=8) per 32-byte
 //               k-step, commits stage release and accumulator-ready barriers.
-//   warps 0-3   epilogue: tcgen05.ld the accumulator (two TMEM buffers, so the next tile's
+//   warps 0-7   epilogue: tcgen05.ld the accumulator (two TMEM buffers, so the next tile's
 //               MMAs overlap), add bias, apply the activation, stage through swizzled shared
 //               memory and write with TMA stores (which clip the M and N tails).
 // Every mbarrier wait is bounded; a wait that gives up sets the context's status word and the
@@ -27,7 +27,9 @@ constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 32;                        // 32 fp32 = 128 bytes = one swizzle row
 constexpr int A_STAGE_BYTES = BLOCK_M * BLOCK_K * 4;  // 16 KB
 constexpr int C_CHUNK_BYTES = 32 * 32 * 4;         // one warp's 32x32 output chunk
-constexpr int C_STAGING_BYTES = 4 * 2 * C_CHUNK_BYTES;
+constexpr int EPI_WARPS = 8;                      // two warps per TMEM lane quarter
+constexpr int C_STAGING_BYTES = EPI_WARPS * C_CHUNK_BYTES;
+constexpr int BIAS_STAGING_BYTES = EPI_WARPS * 256;  // per warp: 32 bias values + 32 prelu slopes
 constexpr int SMEM_LIMIT = 232448;                 // 227 KB
 constexpr int BARRIER_BYTES = 1024;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // ~2 s at 1.9 GHz
@@ -36,7 +38,7 @@ __host__ __device__ constexpr int stage_bytes(int block_n, bool split) {
   return (A_STAGE_BYTES + block_n * BLOCK_K * 4) * (split ? 2 : 1);
 }
 __host__ __device__ constexpr int num_stages(int block_n, bool split) {
-  int s = (SMEM_LIMIT - C_STAGING_BYTES - BARRIER_BYTES - 1024) / stage_bytes(block_n, split);
+  int s = (SMEM_LIMIT - C_STAGING_BYTES - BIAS_STAGING_BYTES - BARRIER_BYTES - 1024) / stage_bytes(block_n, split);
   return s > 8 ? 8 : s;
 }
 
@@ -73,6 +75,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   const long long t0 = clock64();
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (it > 8) __nanosleep(20);  // leave the issue slots to the warps that have work
     if ((it & 63) == 63) {
       if (*abort_flag) return false;
       if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
@@ -175,6 +178,40 @@ __device__ __forceinline__ float round_tf32(float v) {
   return __uint_as_float(r);
 }
 
+// Bias and activation of one 32x32 output chunk in registers: thread `lane` owns row `lane`,
+// v[] holds its 32 accumulator columns.  Arithmetic order follows MathBackendCPU's unfused
+// passes: float32(acc) + bias, then the activation (backend_cpu.ts:542-555).  relu is
+// Math.max(0, x) and clip is `x > hi ? hi : (x < lo ? lo : x)`: both keep NaN, which the
+// NaN-propagating min/max reproduce.  bias_s/alpha_s are this warp's 32 staged values in shared
+// memory, read as broadcast float4.  Columns beyond N carry meaningless values; the TMA store
+// clips them.
+template <int ACT>
+__device__ __forceinline__ void finish_chunk(float (&v)[32], bool has_bias, const float* bias_s,
+                                             const float* alpha_s, const EpilogueArgs& e) {
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    if (has_bias) {
+      const float4 b = *reinterpret_cast<const float4*>(bias_s + j * 4);
+      v[j * 4 + 0] += b.x;
+      v[j * 4 + 1] += b.y;
+      v[j * 4 + 2] += b.z;
+      v[j * 4 + 3] += b.w;
+    }
+    if (ACT == TFJS_ACT_PRELU) {
+      const float4 a = *reinterpret_cast<const float4*>(alpha_s + j * 4);
+      v[j * 4 + 0] = (v[j * 4 + 0] < 0.f) ? a.x * v[j * 4 + 0] : v[j * 4 + 0];
+      v[j * 4 + 1] = (v[j * 4 + 1] < 0.f) ? a.y * v[j * 4 + 1] : v[j * 4 + 1];
+      v[j * 4 + 2] = (v[j * 4 + 2] < 0.f) ? a.z * v[j * 4 + 2] : v[j * 4 + 2];
+      v[j * 4 + 3] = (v[j * 4 + 3] < 0.f) ? a.w * v[j * 4 + 3] : v[j * 4 + 3];
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      if (ACT == TFJS_ACT_RELU) v[j * 4 + i] = max_nan(v[j * 4 + i], 0.f);
+      if (ACT == TFJS_ACT_CLIP) v[j * 4 + i] = min_nan(max_nan(v[j * 4 + i], e.clip_lo), e.clip_hi);
+    }
+  }
+}
+
 struct GemmParams {
   int M, N, K;
   int num_m_tiles, num_n_tiles, num_k_blocks;
@@ -183,7 +220,7 @@ struct GemmParams {
 };
 
 template <int BLOCK_N, bool SPLIT>
-__global__ void __launch_bounds__(SPLIT ? 320 : 192, 1)
+__global__ void __launch_bounds__(SPLIT ? 448 : 320, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_w_hi,
                     const __grid_constant__ CUtensorMap map_w_lo,
@@ -201,7 +238,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   uint8_t* b_hi = a_hi + STAGES * A_STAGE_BYTES * (SPLIT ? 2 : 1);
   uint8_t* b_lo = b_hi + STAGES * B_STAGE_BYTES;  // SPLIT only
   uint8_t* c_stage = b_hi + STAGES * B_STAGE_BYTES * (SPLIT ? 2 : 1);
-  uint64_t* bars = (uint64_t*)(c_stage + C_STAGING_BYTES);
+  uint8_t* bias_stage = c_stage + C_STAGING_BYTES;
+  uint64_t* bars = (uint64_t*)(bias_stage + BIAS_STAGING_BYTES);
   uint64_t* full_bar = bars;                  // [STAGES] TMA -> consumers
   uint64_t* empty_bar = bars + STAGES;        // [STAGES] MMA -> TMA
   uint64_t* conv_bar = bars + 2 * STAGES;     // [STAGES] converters -> MMA (SPLIT)
@@ -222,12 +260,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(smem_u32(&tmem_full_bar[a]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[a]), 4);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), BLOCK_N >= 64 ? EPI_WARPS : 4);
     }
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     // Tensor memory: the whole warp allocates, the same warp frees at the end.
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_ptr_holder)),
@@ -240,7 +278,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_ptr_holder;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       int stage = 0;
@@ -262,7 +300,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(BLOCK_M, BLOCK_N);
@@ -305,10 +343,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         if (ok) tcgen05_commit(smem_u32(&tmem_full_bar[acc]));  // accumulator complete
       }
     }
-  } else if (warp >= 6) {
+  } else if (warp >= 10) {
     // ---------------- 3xTF32 converters (SPLIT only) ----------------
     if (SPLIT) {
-      const int t = threadIdx.x - 192;  // 0..127
+      const int t = threadIdx.x - 320;  // 0..127
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -338,74 +376,101 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       }
     }
   } else {
-    // ---------------- epilogue warps 0-3 ----------------
-    uint8_t* my_stage = c_stage + warp * 2 * C_CHUNK_BYTES;
-    int buf = 0;
-    int local = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
-      const int m0 = (tile / p.num_n_tiles) * BLOCK_M;
-      const int n0 = (tile % p.num_n_tiles) * BLOCK_N;
-      const int acc = local & 1;
-      const uint32_t acc_phase = (local >> 1) & 1;
-      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 6);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tcgen05_fence_after();
-      // TMEM address: lane in bits [16,32), column in [0,16); a warp may only touch lanes
-      // 32*(warp%4) .. +31, i.e. rows 32*warp .. +31 of the tile.
-      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + acc * BLOCK_N;
-#pragma unroll 1
-      for (int chunk = 0; chunk < BLOCK_N / 32; chunk++) {
-        const int c0 = n0 + chunk * 32;
-        if (c0 >= p.N) break;  // the whole chunk lies beyond the last column
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + chunk * 32, r);
-        tmem_ld_wait();
-        // the buffer used two chunks ago must have been read by its TMA store
-        if (lane == 0) tma_store_wait_read<1>();
-        __syncwarp();
-        uint8_t* dst = my_stage + buf * C_CHUNK_BYTES + lane * 128;
+    // ---------------- epilogue warps 0-7 ----------------
+    // Warps w and w+4 share TMEM lane quarter w%4 (rows 32*(w%4) .. +31 of the tile) and split
+    // the tile's 32-column chunks between them: warp half h takes chunks h, h+2, h+4, ...
+    constexpr int CHUNKS = BLOCK_N / 32;
+    constexpr int MY_CHUNKS = CHUNKS >= 2 ? CHUNKS / 2 : 1;
+    const int quarter = warp & 3;
+    const int half = warp >> 2;
+    if (CHUNKS >= 2 || half == 0) {
+      uint8_t* stage_buf = c_stage + warp * C_CHUNK_BYTES;
+      float* bias_s = reinterpret_cast<float*>(bias_stage + warp * 256);
+      float* alpha_s = bias_s + 32;
+      const bool has_bias = p.epi.bias != nullptr;
+      const bool has_alpha = p.epi.activation == TFJS_ACT_PRELU;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
+        const int m0 = (tile / p.num_n_tiles) * BLOCK_M;
+        const int n0 = (tile % p.num_n_tiles) * BLOCK_N;
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        // One coalesced load per chunk fetches its 32 bias values (and prelu slopes), issued
+        // before waiting for the accumulator so that the latency hides behind the MMAs.
+        float bias_l[MY_CHUNKS], alpha_l[MY_CHUNKS];
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-          float4 o;
-          const int c = c0 + j * 4;
-          EpilogueArgs e = p.epi;
-          // columns beyond N hold zeros (W rows are zero-filled); keep bias reads in bounds
-          if (c + 3 < p.N) {
-            o.x = apply_epilogue(__uint_as_float(r[j * 4 + 0]), c + 0, e);
-            o.y = apply_epilogue(__uint_as_float(r[j * 4 + 1]), c + 1, e);
-            o.z = apply_epilogue(__uint_as_float(r[j * 4 + 2]), c + 2, e);
-            o.w = apply_epilogue(__uint_as_float(r[j * 4 + 3]), c + 3, e);
-          } else {
-            o.x = (c + 0 < p.N) ? apply_epilogue(__uint_as_float(r[j * 4 + 0]), c + 0, e) : 0.f;
-            o.y = (c + 1 < p.N) ? apply_epilogue(__uint_as_float(r[j * 4 + 1]), c + 1, e) : 0.f;
-            o.z = (c + 2 < p.N) ? apply_epilogue(__uint_as_float(r[j * 4 + 2]), c + 2, e) : 0.f;
-            o.w = 0.f;
+        for (int i = 0; i < MY_CHUNKS; i++) {
+          const int cl = n0 + (CHUNKS >= 2 ? 2 * i + half : 0) * 32 + lane;
+          bias_l[i] = 0.f;
+          alpha_l[i] = 0.f;
+          if (has_bias) bias_l[i] = p.epi.bias_scalar ? __ldg(p.epi.bias) : (cl < p.N ? __ldg(p.epi.bias + cl) : 0.f);
+          if (has_alpha) alpha_l[i] = p.epi.prelu_scalar ? __ldg(p.epi.prelu) : (cl < p.N ? __ldg(p.epi.prelu + cl) : 0.f);
+        }
+        ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 6);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tcgen05_fence_after();
+        // TMEM address: lane in bits [16,32), column in [0,16)
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BLOCK_N;
+        bool released = false;
+#pragma unroll
+        for (int i = 0; i < MY_CHUNKS; i++) {
+          const int chunk = CHUNKS >= 2 ? 2 * i + half : 0;
+          const int c0 = n0 + chunk * 32;
+          if (c0 >= p.N) break;  // the rest of this warp's chunks lie beyond the last column
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + chunk * 32, r);
+          __syncwarp();
+          bias_s[lane] = bias_l[i];
+          if (has_alpha) alpha_s[lane] = alpha_l[i];
+          tmem_ld_wait();
+          __syncwarp();
+          if (i == MY_CHUNKS - 1) {
+            // this warp's last read of the accumulator: hand it back to the MMA warp right away
+            tcgen05_fence_before();
+            if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+            released = true;
           }
+          float v[32];
+#pragma unroll
+          for (int k = 0; k < 32; k++) v[k] = __uint_as_float(r[k]);
+          switch (p.epi.activation) {
+            case TFJS_ACT_RELU: finish_chunk<TFJS_ACT_RELU>(v, has_bias, bias_s, alpha_s, p.epi); break;
+            case TFJS_ACT_PRELU: finish_chunk<TFJS_ACT_PRELU>(v, has_bias, bias_s, alpha_s, p.epi); break;
+            case TFJS_ACT_CLIP: finish_chunk<TFJS_ACT_CLIP>(v, has_bias, bias_s, alpha_s, p.epi); break;
+            default: finish_chunk<TFJS_ACT_LINEAR>(v, has_bias, bias_s, alpha_s, p.epi); break;
+          }
+          // the staging buffer must have been read by this warp's previous TMA store
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
           // SWIZZLE_128B placement expected by the store's tensor map: 16-byte chunk j of row
           // `lane` lives at chunk (j ^ (lane & 7)).
-          *reinterpret_cast<float4*>(dst + ((j ^ (lane & 7)) << 4)) = o;
+          uint8_t* dst = stage_buf + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; j++)
+            *reinterpret_cast<float4*>(dst + ((j ^ (lane & 7)) << 4)) =
+                make_float4(v[j * 4 + 0], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+          fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA engine
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&map_c, smem_u32(stage_buf), c0, m0 + quarter * 32);
+            tma_store_commit();
+          }
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_2d(&map_c, smem_u32(my_stage + buf * C_CHUNK_BYTES), c0, m0 + warp * 32);
-          tma_store_commit();
+        if (!released) {
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
         }
-        buf ^= 1;
       }
-      // all of this warp's reads of the accumulator are done: hand it back to the MMA warp
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
     }
     if (lane == 0) tma_store_wait_all();
   }
 
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     __syncwarp();
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
@@ -452,7 +517,7 @@ bool encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
 template <int BLOCK_N, bool SPLIT>
 int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mh, const CUtensorMap& ml,
                    const CUtensorMap& mc, const GemmParams& p) {
-  constexpr int smem_bytes = num_stages(BLOCK_N, SPLIT) * stage_bytes(BLOCK_N, SPLIT) + C_STAGING_BYTES +
+  constexpr int smem_bytes = num_stages(BLOCK_N, SPLIT) * stage_bytes(BLOCK_N, SPLIT) + C_STAGING_BYTES + BIAS_STAGING_BYTES +
                              BARRIER_BYTES + 1024;
   static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
   auto kernel = gemm_tcgen05_kernel<BLOCK_N, SPLIT>;
@@ -463,7 +528,7 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtensorMap&
   }
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-  kernel<<<grid, SPLIT ? 320 : 192, smem_bytes, ctx->stream>>>(ma, mh, ml, mc, p);
+  kernel<<<grid, SPLIT ? 448 : 320, smem_bytes, ctx->stream>>>(ma, mh, ml, mc, p);
   return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32)" : "gemm_tcgen05 (TF32)");
 }
 
