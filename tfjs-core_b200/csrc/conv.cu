@@ -171,32 +171,74 @@ __device__ __forceinline__ float activate(float v, float lo, float hi) {
 
 // Fast path: 3x3, dilation 1, channel multiplier 1, C % 4 == 0, stride 1 or 2 (every MobileNet
 // depthwise layer).  A thread owns 4 channels of TW adjacent output columns and walks down a
-// strip of output rows with the 3 x IN_W input window in registers.  The three window rows
-// live in three register banks whose roles (top / middle / bottom) rotate from step to step,
-// so nothing is copied: as soon as the taps of the top row are issued, the row that enters
-// the window next is loaded into its registers (128-bit NHWC loads, consecutive threads on
-// consecutive channel quads) and is first needed as the bottom row of the following step,
-// which hides the load latency behind two thirds of a step.  A block covers a slice of at
-// most 128 channel quads (blockIdx.y) and stages only that slice of the filter in shared
-// memory; blocks are persistent (one wave).  Taps outside the image are skipped, not
-// multiplied by zero, as the reference skips them (backend_cpu.ts:2002-2014); accumulation
-// order is wR, wC ascending with one float32 rounding per tap (fmaf).
-template <int S, int TW, int ACT>
+// strip of output rows with the 3 x IN_W input window in registers.
+//  - Input rows stream through a per-thread ring in shared memory filled with cp.async
+//    (16-byte LDGSTS straight from L2, consecutive threads on consecutive channel quads), DEPTH-1
+//    rows ahead of their use, so that the HBM latency is covered by several steps of arithmetic
+//    without holding registers for data in flight.  Each thread reads back only what it copied
+//    itself, so cp.async.wait_group is the only synchronisation.
+//  - The three window rows live in three register banks whose roles (top / middle / bottom)
+//    rotate from step to step, so nothing is shifted: the bank of the top row is refilled from
+//    the ring as soon as its taps are issued.
+//  - A block covers a slice of at most 128 channel quads (blockIdx.y) and stages only that
+//    slice of the filter in shared memory; blocks are persistent (one wave).
+// Taps outside the image are skipped, not multiplied by zero, as the reference skips them
+// (backend_cpu.ts:2002-2014); accumulation order is wR, wC ascending with one float32 rounding
+// per tap (fmaf), so results match the reference bit for bit up to double rounding.
+template <int S, int TW, int ACT, int DEPTH>
 struct DepthwiseStrip {
   static constexpr int IN_W = (TW - 1) * S + 3;
   float4 R[3][IN_W];   // window rows; which is top/middle/bottom rotates
   bool rk[3];          // row inside the image (border items only)
   bool ck[IN_W];       // column inside the image (border items only)
   float4 acc[TW];
+  // ring state
+  uint32_t ring;       // shared-memory address of this thread's slot 0, column 0
+  int slot_in, slot_out;   // next ring slot to fill / to drain
+  int rows_issued, rows_total, yi_issue;
+  const float4* p_issue;   // global address of the next row to request (column xi0)
 
+  static __device__ __forceinline__ uint32_t slot_addr(uint32_t ring, int slot, int i) {
+    return ring + (uint32_t)((slot * IN_W + i) * 128 * 16);
+  }
+
+  // Requests the next input row (if any is left) and closes one cp.async group either way, so
+  // that "DEPTH - 1 groups may be pending" always means "the row about to be drained is here".
   template <bool INTERIOR>
-  __device__ __forceinline__ void load(int slot, const float4* rp, bool row_ok, int C4) {
-    if (!INTERIOR) rk[slot] = row_ok;
+  __device__ __forceinline__ void issue(int64_t row_stride, int C4, int in_height) {
+    if (rows_issued < rows_total) {
+      const bool row_ok = INTERIOR || (yi_issue >= 0 && yi_issue < in_height);
+      if (row_ok) {
+#pragma unroll
+        for (int i = 0; i < IN_W; i++)
+          if (INTERIOR || ck[i])
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(slot_addr(ring, slot_in, i)),
+                         "l"(p_issue + i * C4)
+                         : "memory");
+      }
+      p_issue += row_stride;
+      yi_issue++;
+      rows_issued++;
+      slot_in = (slot_in + 1 == DEPTH) ? 0 : slot_in + 1;
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+
+  // Moves the oldest ring row into register bank `bank`.
+  template <bool INTERIOR>
+  __device__ __forceinline__ void drain(int bank, int yi, int64_t row_stride, int C4, int in_height) {
+    issue<INTERIOR>(row_stride, C4, in_height);
+    asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
+    if (!INTERIOR) rk[bank] = (yi >= 0) && (yi < in_height);
 #pragma unroll
     for (int i = 0; i < IN_W; i++) {
-      if (INTERIOR) R[slot][i] = rp[i * C4];
-      else R[slot][i] = (row_ok && ck[i]) ? rp[i * C4] : make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 v;
+      asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                   : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                   : "r"(slot_addr(ring, slot_out, i)));
+      R[bank][i] = v;  // unspecified where the tap is outside the image; never used there
     }
+    slot_out = (slot_out + 1 == DEPTH) ? 0 : slot_out + 1;
   }
 
   template <bool INTERIOR>
@@ -218,21 +260,20 @@ struct DepthwiseStrip {
     }
   }
 
-  // One output row.  A = register bank holding the top row.  prow points at the top input
-  // row of this step's window (column xi0, this thread's channel quad).
+  // One output row.  A = register bank holding the top row; yi = input row of the top row.
   template <int A, bool INTERIOR>
-  __device__ __forceinline__ void step(const float4* prow, int yi, bool more, int64_t row_stride,
-                                       const tfjs_conv2d_info& ci, int C4, const float4* w_s, int cbn,
-                                       int c_local, float4* yrow, int cols_left, bool has_bias,
-                                       const float4& bias4, float lo, float hi) {
+  __device__ __forceinline__ void step(int yi, bool more, int64_t row_stride, int in_height, int C4,
+                                       const float4* w_s, int cbn, int c_local, float4* yrow,
+                                       int cols_left, bool has_bias, const float4& bias4, float lo,
+                                       float hi) {
     constexpr int B = (A + 1) % 3, C = (A + 2) % 3;
 #pragma unroll
     for (int j = 0; j < TW; j++) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
     taps<INTERIOR>(A, 0, w_s, cbn, c_local);
-    // bank A is free: fetch the row that enters the window next (input row yi + 3)
-    if (more) load<INTERIOR>(A, prow + 3 * row_stride, yi + 3 >= 0 && yi + 3 < ci.inHeight, C4);
+    // bank A is free: it receives the row that enters the window next (input row yi + 3)
+    if (more) drain<INTERIOR>(A, yi + 3, row_stride, C4, in_height);
     taps<INTERIOR>(B, 1, w_s, cbn, c_local);
-    if (S == 2 && more) load<INTERIOR>(B, prow + 4 * row_stride, yi + 4 >= 0 && yi + 4 < ci.inHeight, C4);
+    if (S == 2 && more) drain<INTERIOR>(B, yi + 4, row_stride, C4, in_height);
     taps<INTERIOR>(C, 2, w_s, cbn, c_local);
 #pragma unroll
     for (int j = 0; j < TW; j++) {
@@ -255,44 +296,54 @@ struct DepthwiseStrip {
                                       float hi) {
     const int64_t row_stride = (int64_t)ci.inWidth * C4;
     const int64_t out_stride = (int64_t)ci.outWidth * C4;
+    const int in_height = ci.inHeight;
     if (!INTERIOR) {
 #pragma unroll
       for (int i = 0; i < IN_W; i++) ck[i] = (xi0 + i >= 0) && (xi0 + i < ci.inWidth);
     }
     // (sic) rows use padLeft, as backend_cpu.ts:2000 does
     int yi = yo0 * S - ci.padLeft;
-    const float4* prow = xb + (int64_t)yi * row_stride + (int64_t)xi0 * C4;
     float4* yrow = yb + (int64_t)yo0 * out_stride + (int64_t)xo0 * C4;
     const int cols_left = ci.outWidth - xo0;
+    rows_total = (yo1 - yo0 - 1) * S + 3;
+    rows_issued = 0;
+    yi_issue = yi;
+    p_issue = xb + (int64_t)yi * row_stride + (int64_t)xi0 * C4;
+    slot_in = slot_out = 0;
 #pragma unroll
-    for (int k = 0; k < 3; k++)
-      load<INTERIOR>(k, prow + k * row_stride, yi + k >= 0 && yi + k < ci.inHeight, C4);
+    for (int d = 0; d < DEPTH - 1; d++) issue<INTERIOR>(row_stride, C4, in_height);
+#pragma unroll
+    for (int k = 0; k < 3; k++) drain<INTERIOR>(k, yi + k, row_stride, C4, in_height);
     int yo = yo0;
     // bank of the top row: 0, 1, 2, 0, ... for stride 1 and 0, 2, 1, 0, ... for stride 2
     while (true) {
-      step<0, INTERIOR>(prow, yi, yo + 1 < yo1, row_stride, ci, C4, w_s, cbn, c_local, yrow, cols_left,
+      step<0, INTERIOR>(yi, yo + 1 < yo1, row_stride, in_height, C4, w_s, cbn, c_local, yrow, cols_left,
                         has_bias, bias4, lo, hi);
       if (++yo >= yo1) break;
-      prow += S * row_stride; yi += S; yrow += out_stride;
-      step<(S == 1 ? 1 : 2), INTERIOR>(prow, yi, yo + 1 < yo1, row_stride, ci, C4, w_s, cbn, c_local, yrow,
+      yi += S; yrow += out_stride;
+      step<(S == 1 ? 1 : 2), INTERIOR>(yi, yo + 1 < yo1, row_stride, in_height, C4, w_s, cbn, c_local, yrow,
                                        cols_left, has_bias, bias4, lo, hi);
       if (++yo >= yo1) break;
-      prow += S * row_stride; yi += S; yrow += out_stride;
-      step<(S == 1 ? 2 : 1), INTERIOR>(prow, yi, yo + 1 < yo1, row_stride, ci, C4, w_s, cbn, c_local, yrow,
+      yi += S; yrow += out_stride;
+      step<(S == 1 ? 2 : 1), INTERIOR>(yi, yo + 1 < yo1, row_stride, in_height, C4, w_s, cbn, c_local, yrow,
                                        cols_left, has_bias, bias4, lo, hi);
       if (++yo >= yo1) break;
-      prow += S * row_stride; yi += S; yrow += out_stride;
+      yi += S; yrow += out_stride;
     }
+    // every requested row was drained; close the bookkeeping groups before the ring is reused
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
   }
 };
 
-template <int S, int TW, int ACT>
-__global__ void __launch_bounds__(128, 4)
+template <int S, int TW, int ACT, int MINB, int DEPTH>
+__global__ void __launch_bounds__(128, MINB)
 depthwise3x3_strip_kernel(const float* __restrict__ x, const float* __restrict__ w,
                           float* __restrict__ y, tfjs_conv2d_info ci, EpilogueArgs epi,
                           int rows_per_strip, int cb /* channel quads per block */) {
   constexpr int IN_W = (TW - 1) * S + 3;
-  extern __shared__ float4 w_s[];  // [9][quads of this slice]
+  extern __shared__ float4 smem_dw[];
+  float4* ring_s = smem_dw;                         // [DEPTH][IN_W][128 threads]
+  float4* w_s = smem_dw + DEPTH * IN_W * 128;       // [9][quads of this slice]
   const int C4 = ci.inChannels >> 2;
   const int c4_base = blockIdx.y * cb;
   const int cbn = min(cb, C4 - c4_base);
@@ -317,7 +368,8 @@ depthwise3x3_strip_kernel(const float* __restrict__ x, const float* __restrict__
       bias4 = __ldg(reinterpret_cast<const float4*>(epi.bias) + c4);
     }
   }
-  DepthwiseStrip<S, TW, ACT> ds;
+  DepthwiseStrip<S, TW, ACT, DEPTH> ds;
+  ds.ring = (uint32_t)__cvta_generic_to_shared(ring_s + threadIdx.x);
   for (int64_t item = (int64_t)blockIdx.x * groups + group; item < items;
        item += (int64_t)gridDim.x * groups) {
     const int wt = (int)(item % w_tiles);
@@ -444,10 +496,13 @@ int launch_depthwise(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* 
     const int cb = C4 < 128 ? C4 : 128;                // channel quads per block
     const int slices = (C4 + cb - 1) / cb;
     const int groups = 128 / cb;                       // pixel groups per block
-    const size_t smem = (size_t)9 * cb * sizeof(float4);
+    constexpr int MINB = 4, DEPTH1 = 4, DEPTH2 = 6;    // blocks per SM; ring depth for stride 1 / 2
     const int tw = ci.strideHeight == 1 ? 2 : 1;
+    const int in_w = (tw - 1) * ci.strideHeight + 3;
+    const int depth = ci.strideHeight == 1 ? DEPTH1 : DEPTH2;
+    const size_t smem = ((size_t)depth * in_w * 128 + (size_t)9 * cb) * sizeof(float4);
     const int64_t cols = (ci.outWidth + tw - 1) / tw;
-    const int resident = ctx->sm_count * 4;  // one wave of blocks (4 per SM by register use)
+    const int resident = ctx->sm_count * MINB;  // one wave of blocks
     // strips of output rows: long enough to amortise the halo rows, short enough to give every
     // resident thread work on the small late layers
     int rows = 8;
@@ -458,12 +513,17 @@ int launch_depthwise(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* 
     int64_t gx = (items + groups - 1) / groups;
     if (gx > resident / slices) gx = resident / slices > 0 ? resident / slices : 1;
     dim3 grid((unsigned)gx, (unsigned)slices);
-#define TFJS_LAUNCH_DW(ACT)                                                                            \
-  do {                                                                                                 \
-    if (ci.strideHeight == 1)                                                                          \
-      depthwise3x3_strip_kernel<1, 2, ACT><<<grid, 128, smem, ctx->stream>>>(x, w, y, ci, epi, rows, cb); \
-    else                                                                                               \
-      depthwise3x3_strip_kernel<2, 1, ACT><<<grid, 128, smem, ctx->stream>>>(x, w, y, ci, epi, rows, cb); \
+#define TFJS_LAUNCH_DW(ACT)                                                                           \
+  do {                                                                                                \
+    if (ci.strideHeight == 1) {                                                                       \
+      auto k = depthwise3x3_strip_kernel<1, 2, ACT, MINB, DEPTH1>;                                     \
+      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                \
+      k<<<grid, 128, smem, ctx->stream>>>(x, w, y, ci, epi, rows, cb);                                \
+    } else {                                                                                          \
+      auto k = depthwise3x3_strip_kernel<2, 1, ACT, MINB, DEPTH2>;                                     \
+      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                \
+      k<<<grid, 128, smem, ctx->stream>>>(x, w, y, ci, epi, rows, cb);                                \
+    }                                                                                                 \
   } while (0)
     switch (epi.activation) {
       case TFJS_ACT_RELU: TFJS_LAUNCH_DW(TFJS_ACT_RELU); break;
