@@ -200,6 +200,27 @@ int tfjs_cuda_softmax_last(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id 
  * converts x's stored dtype to out's dtype (float->int truncates, ->bool is != 0). */
 int tfjs_cuda_cast(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id out);
 
+/* ---- matMul for callers that must not allocate device memory.
+ * No counterpart in the reference: tfjs-core has no notion of a caller that is forbidden to
+ * allocate.  out[m, n] = act(a[m, k] . b[k, n] + bias[n]) on the tensor cores, like
+ * tfjs_cuda_batch_matmul with batch 1 and no transposes, but every operand is a raw device
+ * pointer supplied by the caller (bias may be NULL) and the repacked copy of b that the kernel
+ * needs lives in a fixed 8 MiB array inside the library instead of allocator memory, so the
+ * call performs no cudaMalloc / cudaFree and touches neither the tensor table nor the buffer
+ * cache.  It is meant for hosts that pre-size all device memory (serving loops, plugins that are
+ * handed pointers by a framework whose pool they must not disturb).
+ * Limits: n * round_up(k, 4) <= 1 048 576 (e.g. 1024 x 1024); k and n multiples of 4, n >= 8;
+ * a and out 16-byte aligned; activation linear, relu or clip.  Larger or other shapes are
+ * rejected with an error message, never truncated.
+ * All calls on one device share the array (each call overwrites all of it that it reads, so
+ * nothing needs clearing): calls that overlap on the GPU race and must be serialised by the
+ * caller.  The first call on a device resolves the array's address; make it before any stream
+ * capture.  Arithmetic follows the context's "math_mode" option; work is enqueued on the
+ * context's stream. */
+int tfjs_cuda_matmul_static_scratch(tfjs_cuda_ctx* ctx, const float* a, const float* b,
+                                    const float* bias, float* out, int64_t m, int64_t k, int64_t n,
+                                    int activation, float clip_lo, float clip_hi);
+
 /* ---- extension: CUDA-graph capture of a sequence of calls on the context.
  * Between begin and end, kernel calls are recorded instead of run.  Tensors disposed during
  * the capture keep their buffers inside the graph (replays write to them) until

@@ -92,6 +92,8 @@ SIGNATURES = {
     "tfjs_cuda_reduce_last": (C.c_int, [_P, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_int64]),
     "tfjs_cuda_softmax_last": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int64, C.c_int64]),
     "tfjs_cuda_cast": (C.c_int, [_P, C.c_int64, C.c_int64]),
+    "tfjs_cuda_matmul_static_scratch": (C.c_int, [_P, _P, _P, _P, _P, C.c_int64, C.c_int64, C.c_int64,
+                                                  C.c_int, C.c_float, C.c_float]),
     "tfjs_cuda_graph_begin": (C.c_int, [_P]),
     "tfjs_cuda_graph_end": (C.c_int, [_P, C.POINTER(_P)]),
     "tfjs_cuda_graph_launch": (C.c_int, [_P, _P]),

@@ -12,7 +12,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libtfjs_cuda.so")
-SOURCES = ["context.cu", "elementwise.cu", "conv.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "api.cu"]
+SOURCES = ["context.cu", "elementwise.cu", "conv.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "api.cu",
+           "no_alloc.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC"]  # no --use_fast_math: results must match the reference
