@@ -41,16 +41,22 @@ def test_config1_fused_matmul(tf, mode):
 
 
 # ---- BASELINE config 2: fused conv2d 8x56x56x64 * 3x3x64x64, same, bias, relu, seed 1 ---------
-def test_config2_fused_conv2d(tf):
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
+def test_config2_fused_conv2d(tf, mode):
     rng = _rng(1)
     x = rng.uniform(0, 1, (8, 56, 56, 64)).astype(np.float32)
     w = rng.normal(0, np.sqrt(2.0 / (3 * 3 * 64)), (3, 3, 64, 64)).astype(np.float32)
     bias = rng.normal(0, 0.01, 64).astype(np.float32)
     ci = oracle.compute_conv2d_info(x.shape, w.shape, 1, 1, "same")
     want = oracle.fused_conv2d(x, w, ci, bias=bias, activation="relu")
-    got = tf.ops.fused_conv2d(tf.ops.tensor(x), tf.ops.tensor(w), 1, "same", bias=tf.ops.tensor(bias),
-                              activation="relu").dataSync().reshape(want.shape)
-    assert rel_err(got, want) <= 1e-5
+    bk = tf.ENGINE.backend
+    bk.setMathMode(mode)
+    try:
+        got = tf.ops.fused_conv2d(tf.ops.tensor(x), tf.ops.tensor(w), 1, "same", bias=tf.ops.tensor(bias),
+                                  activation="relu").dataSync().reshape(want.shape)
+    finally:
+        bk.setMathMode("3xtf32")
+    assert rel_err(got, want) <= TOL[mode]
 
 
 # ---- BASELINE config 3: depthwise 8x112x112x32 * 3x3x32x1 s2 same, then bias and relu6, seed 2 -
@@ -187,14 +193,59 @@ def test_depthwise_shapes(tf, shape, fshape, stride, pad, dil):
     ((1, 6, 6, 8), (3, 3, 8, 16), 1, 1, 1),
 ])
 def test_direct_conv_shapes(tf, shape, fshape, stride, pad, dil):
+    """The CUDA-core convolution kernels (tensor cores switched off) follow the reference's tap
+    order and agree to the last bits; the same shapes through the default dispatch (implicit
+    GEMM on the tensor cores where the shape allows) meet the 3xTF32 tolerance."""
     rng = _rng(sum(shape) + 1)
     x = rng.uniform(-1, 1, shape).astype(np.float32)
     w = rng.uniform(-1, 1, fshape).astype(np.float32)
     ci = oracle.compute_conv2d_info(shape, fshape, stride, dil, pad)
     want = oracle.conv2d(x, w, ci)
-    got = tf.ops.conv2d(tf.ops.tensor(x), tf.ops.tensor(w), stride, pad, "NHWC", dil)
+    bk = tf.ENGINE.backend
+    bk.setOption("use_tensor_cores", 0)
+    try:
+        got = tf.ops.conv2d(tf.ops.tensor(x), tf.ops.tensor(w), stride, pad, "NHWC", dil)
+    finally:
+        bk.setOption("use_tensor_cores", 1)
     assert got.shape == list(want.shape)
     assert ulp_diff(got.dataSync(), want) <= 2
+    got = tf.ops.conv2d(tf.ops.tensor(x), tf.ops.tensor(w), stride, pad, "NHWC", dil)
+    assert rel_err(got.dataSync().reshape(want.shape), want) <= 1e-5
+
+
+@pytest.mark.parametrize("shape,fshape,stride,pad,dil", [
+    ((2, 20, 20, 8), (3, 3, 8, 16), 1, "same", 1),       # K = 72: k-blocks straddle taps
+    ((1, 19, 23, 12), (3, 3, 12, 40), 2, "same", 1),     # odd sizes, stride 2, N tail
+    ((2, 16, 16, 64), (3, 3, 64, 64), 1, "same", 1),     # config-2 channel counts
+    ((1, 14, 14, 32), (5, 5, 32, 24), 1, "valid", 1),
+    ((1, 17, 17, 4), (3, 3, 4, 8), 1, "same", 2),        # dilation 2
+    ((3, 9, 9, 16), (1, 1, 16, 32), 2, "same", 1),       # strided 1x1 ("im2row" in the reference's specs)
+    ((2, 33, 31, 3), (3, 3, 3, 32), 2, "same", 1),       # 3-channel gather, odd width: unaligned rows
+    ((1, 32, 32, 3), (3, 3, 3, 16), 1, "same", 1),
+    ((1, 12, 12, 3), (2, 3, 3, 8), 1, "valid", 1),
+    ((70, 8, 8, 8), (3, 3, 8, 8), 1, "same", 1),         # many tiles, M tail
+])
+@pytest.mark.parametrize("mode", ["3xtf32", "tf32"])
+def test_implicit_gemm_conv(tf, shape, fshape, stride, pad, dil, mode):
+    rng = _rng(sum(shape) + sum(fshape))
+    x = rng.uniform(-1, 1, shape).astype(np.float32)
+    w = rng.uniform(-1, 1, fshape).astype(np.float32)
+    bias = rng.normal(0, 1, fshape[3]).astype(np.float32)
+    ci = oracle.compute_conv2d_info(shape, fshape, stride, dil, pad)
+    want = oracle.fused_conv2d(x, w, ci, bias=bias, activation="relu")
+    bk = tf.ENGINE.backend
+    bk.setMathMode(mode)
+    try:
+        before = bk.launchCount()
+        got = tf.ops.fused_conv2d(tf.ops.tensor(x), tf.ops.tensor(w), stride, pad, dilations=dil,
+                                  bias=tf.ops.tensor(bias), activation="relu")
+        t = bk.time(lambda: tf.ops.fused_conv2d(tf.ops.tensor(x), tf.ops.tensor(w), stride, pad, dilations=dil,
+                                                bias=tf.ops.tensor(bias), activation="relu"))
+    finally:
+        bk.setMathMode("3xtf32")
+    assert "launches" in t["getExtraProfileInfo"]() and bk.launchCount() > before
+    assert got.shape == list(want.shape)
+    assert rel_err(got.dataSync().reshape(want.shape), want) <= TOL[mode]
 
 
 def test_elementwise_and_reductions(tf):

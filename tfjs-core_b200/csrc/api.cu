@@ -30,12 +30,14 @@ int float_view(tfjs_cuda_ctx* ctx, TensorEntry* t, const float** out) {
 // tensor entry until the tensor is rewritten.  Weights are constants in inference, so the
 // repack runs once per weight tensor.
 int packed_weights(tfjs_cuda_ctx* ctx, TensorEntry* w, int64_t offset_elems, int64_t K, int64_t N,
-                   bool source_is_nk, bool cacheable, PackedWeights* out, bool* temporary) {
-  const int64_t kp = (K + 3) / 4 * 4;
+                   bool source_is_nk, bool cacheable, PackedWeights* out, bool* temporary,
+                   int row_len = 0, int row_pad = 0, int64_t k_packed = 0) {
+  // row_pad > 0: each run of row_len source rows becomes row_pad packed columns (k_packed total)
+  const int64_t kp = row_pad > 0 ? k_packed : (K + 3) / 4 * 4;
   PackedWeights& c = w->packed;
   *temporary = !cacheable;
   if (cacheable && c.hi && c.version == w->version && c.n == N && c.k == K &&
-      c.transposed_source == source_is_nk) {
+      c.transposed_source == source_is_nk && c.row_pad == row_pad) {
     *out = c;
     return TFJS_CUDA_OK;
   }
@@ -45,6 +47,7 @@ int packed_weights(tfjs_cuda_ctx* ctx, TensorEntry* w, int64_t offset_elems, int
   fresh.kp = kp;
   fresh.version = w->version;
   fresh.transposed_source = source_is_nk;
+  fresh.row_pad = row_pad;
   void *hi, *lo;
   int rc = ctx_alloc(ctx, (size_t)(N * kp) * 4, &hi, &fresh.capacity);
   if (rc) return rc;
@@ -58,8 +61,12 @@ int packed_weights(tfjs_cuda_ctx* ctx, TensorEntry* w, int64_t offset_elems, int
   const bool u8 = w->quant.quantized;
   const void* src = u8 ? (const void*)((const uint8_t*)w->ptr + offset_elems)
                        : (const void*)((const float*)w->ptr + offset_elems);
-  rc = launch_pack_weights(ctx, src, u8, w->quant.scale, w->quant.min, K, N,
-                           source_is_nk ? 1 : N, source_is_nk ? K : 1, kp, fresh.hi, fresh.lo);
+  if (row_pad > 0)
+    rc = launch_pack_weights_rows(ctx, src, u8, w->quant.scale, w->quant.min, K, N, row_len, row_pad, kp,
+                                  fresh.hi, fresh.lo);
+  else
+    rc = launch_pack_weights(ctx, src, u8, w->quant.scale, w->quant.min, K, N,
+                             source_is_nk ? 1 : N, source_is_nk ? K : 1, kp, fresh.hi, fresh.lo);
   if (rc) {
     ctx_free(ctx, hi, fresh.capacity);
     ctx_free(ctx, lo, fresh.capacity);
@@ -200,6 +207,21 @@ extern "C" int tfjs_cuda_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_te
   if (pointwise && ci->inChannels > 0)
     return gemm_dispatch(ctx, (const float*)x->ptr, pixels, ci->inChannels, w, 0, false, true,
                          (float*)o->ptr, ci->outChannels, e);
+  // Everything else with Cin % 4 == 0 (or the 3-channel, 3-wide stem) is an implicit GEMM: the
+  // A tile is gathered from the image by the kernel itself, K = fH * fW * Cin.
+  const int mode = ctx->use_tensor_cores ? tcgen05_conv_mode(*ci) : 0;
+  if (mode) {
+    const int64_t K = (int64_t)ci->filterHeight * ci->filterWidth * ci->inChannels;
+    const bool rgb = tcgen05_conv_k(*ci, mode) != K;
+    PackedWeights pw;
+    bool temporary;
+    rc = packed_weights(ctx, w, 0, K, ci->outChannels, false, true, &pw, &temporary,
+                        rgb ? ci->filterWidth * ci->inChannels : 0, rgb ? 10 : 0,
+                        rgb ? tcgen05_conv_k(*ci, mode) : 0);
+    if (rc) return rc;
+    return launch_conv_tcgen05(ctx, mode, (const float*)x->ptr, *ci, pw.hi, pw.lo, pw.kp, (float*)o->ptr, e,
+                               ctx->math_mode);
+  }
   const float* wf;
   rc = float_view(ctx, w, &wf);
   if (rc) return rc;

@@ -29,6 +29,7 @@ struct PackedWeights {
   int64_t n = 0, k = 0, kp = 0;
   uint64_t version = 0;
   bool transposed_source = false;
+  int row_pad = 0;  // > 0: filter rows padded to this many floats (Cin == 3 conv gather)
 };
 
 struct TensorEntry {
@@ -175,6 +176,9 @@ int launch_gemm_simt(tfjs_cuda_ctx* ctx, const float* a, const float* b, float* 
 int launch_pack_weights(tfjs_cuda_ctx* ctx, const void* src, bool src_is_u8, double scale,
                         double min, int64_t K, int64_t N, int64_t src_k_stride,
                         int64_t src_n_stride, int64_t kp, float* hi, float* lo);
+int launch_pack_weights_rows(tfjs_cuda_ctx* ctx, const void* src, bool src_is_u8, double scale,
+                             double min, int64_t K, int64_t N, int row_len, int row_pad, int64_t kp,
+                             float* hi, float* lo);
 int launch_transpose_batched(tfjs_cuda_ctx* ctx, const float* src, float* dst, int batch,
                              int rows, int cols);
 int launch_dequant(tfjs_cuda_ctx* ctx, const uint8_t* q, float* out, int64_t n, double scale,
@@ -183,6 +187,13 @@ int launch_dequant(tfjs_cuda_ctx* ctx, const uint8_t* q, float* out, int64_t n, 
 bool tcgen05_gemm_supported(int64_t M, int64_t N, int64_t K);
 int launch_gemm_tcgen05(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K,
                         const float* w_hi, const float* w_lo, int64_t kp, float* out, int64_t N,
+                        const EpilogueArgs& epi, int math_mode);
+// Implicit-GEMM convolution on the tensor cores: mode 0 = not eligible, otherwise the gather
+// flavour; tcgen05_conv_k is the contraction length the packed weights must have.
+int tcgen05_conv_mode(const tfjs_conv2d_info& ci);
+int64_t tcgen05_conv_k(const tfjs_conv2d_info& ci, int mode);
+int launch_conv_tcgen05(tfjs_cuda_ctx* ctx, int mode, const float* x, const tfjs_conv2d_info& ci,
+                        const float* w_hi, const float* w_lo, int64_t kp, float* out,
                         const EpilogueArgs& epi, int math_mode);
 // conv.cu
 int launch_conv2d_direct(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* y,

@@ -104,6 +104,30 @@ __global__ void pack_weights_kernel(const void* __restrict__ src, int src_is_u8,
   }
 }
 
+// Repack for the Cin == 3 implicit-GEMM gather: destination column k' = wr * row_pad + j holds
+// source row k = wr * row_len + j for j < row_len and zero otherwise (each filter row of
+// row_len = fW * Cin values is padded to row_pad).  The operand is tiny (27 x N), one thread per
+// destination element.
+__global__ void pack_weights_rows_kernel(const void* __restrict__ src, int src_is_u8, double scale,
+                                         double mn, int K, int N, int row_len, int row_pad, int kp,
+                                         float* __restrict__ hi, float* __restrict__ lo) {
+  const int64_t total = (int64_t)N * kp;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int n = (int)(i / kp), kd = (int)(i % kp);
+    const int wr = kd / row_pad, j = kd % row_pad;
+    const int k = wr * row_len + j;
+    float v = 0.f;
+    if (j < row_len && k < K) {
+      const int64_t off = (int64_t)k * N + n;
+      v = src_is_u8 ? (float)((double)((const uint8_t*)src)[off] * scale + mn) : ((const float*)src)[off];
+    }
+    const float h = round_tf32(v);
+    hi[i] = h;
+    if (lo) lo[i] = (fabsf(h) <= 3.4028234e38f) ? round_tf32(v - h) : 0.f;
+  }
+}
+
 // dst[b, c, r] = src[b, r, c]
 __global__ void transpose_batched_kernel(const float* __restrict__ src, float* __restrict__ dst,
                                          int rows, int cols) {
@@ -144,6 +168,16 @@ int launch_pack_weights(tfjs_cuda_ctx* ctx, const void* src, bool src_is_u8, dou
                                                              (int)N, src_k_stride, src_n_stride,
                                                              (int)kp, hi, lo);
   return post_launch(ctx, "pack_weights");
+}
+
+int launch_pack_weights_rows(tfjs_cuda_ctx* ctx, const void* src, bool src_is_u8, double scale, double mn,
+                             int64_t K, int64_t N, int row_len, int row_pad, int64_t kp, float* hi,
+                             float* lo) {
+  if (N * kp == 0) return TFJS_CUDA_OK;
+  const int blocks = (int)((N * kp + 255) / 256);
+  pack_weights_rows_kernel<<<blocks > 1024 ? 1024 : blocks, 256, 0, ctx->stream>>>(
+      src, src_is_u8 ? 1 : 0, scale, mn, (int)K, (int)N, row_len, row_pad, (int)kp, hi, lo);
+  return post_launch(ctx, "pack_weights (rows)");
 }
 
 int launch_transpose_batched(tfjs_cuda_ctx* ctx, const float* src, float* dst, int batch, int rows,

@@ -212,15 +212,48 @@ __device__ __forceinline__ void finish_chunk(float (&v)[32], bool has_bias, cons
   }
 }
 
+// Geometry of an implicit-GEMM convolution: row m of the A matrix is output pixel
+// (b, yo, xo) = unflatten(m), column kk is filter tap (wr, wc) and input channel ci.
+struct ConvGeom {
+  const float* x;
+  int inH, inW, Cin, outH, outW;
+  int sH, sW, dH, dW, padT, padL, fH, fW;
+};
+
 struct GemmParams {
   int M, N, K;
   int num_m_tiles, num_n_tiles, num_k_blocks;
   int* status;
   EpilogueArgs epi;
+  ConvGeom conv;  // AMODE != A_MATRIX only
 };
 
-template <int BLOCK_N, bool SPLIT>
-__global__ void __launch_bounds__(SPLIT ? 448 : 320, 1)
+// How the A operand reaches shared memory.
+constexpr int A_MATRIX = 0;     // dense [M, K] matrix, TMA
+constexpr int A_CONV_VEC = 1;   // NHWC image, Cin % 4 == 0: 16-byte cp.async gathers, K = (wr, wc, ci)
+constexpr int A_CONV_RGB = 2;   // NHWC image, Cin == 3, 3 columns wide filter: one 32-wide k-block,
+                                // K' = wr * 10 + wc * 3 + ci (each filter row padded to 10 floats so
+                                // that its 36 contiguous source bytes can move as 8-byte pieces)
+
+__device__ __forceinline__ void cp_async_16_zfill(uint32_t dst, const void* src, bool valid) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid ? 16 : 0)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_8_zfill(uint32_t dst, const void* src, bool valid) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(valid ? 8 : 0)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_4_zfill(uint32_t dst, const void* src, bool valid) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(valid ? 4 : 0)
+               : "memory");
+}
+// Byte offset `o` (multiple of 4) of row `r` in a SWIZZLE_128B K-major tile.
+__device__ __forceinline__ uint32_t swz(int r, int o) {
+  return (uint32_t)(r * 128 + ((((o >> 4) ^ (r & 7)) << 4) | (o & 15)));
+}
+
+template <int BLOCK_N, bool SPLIT, int AMODE>
+__global__ void __launch_bounds__((SPLIT || AMODE != A_MATRIX) ? 448 : 320, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_w_hi,
                     const __grid_constant__ CUtensorMap map_w_lo,
@@ -228,7 +261,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   constexpr int STAGES = num_stages(BLOCK_N, SPLIT);
   constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 4;
   constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // two accumulators; a power of two >= 64
-  constexpr uint32_t TX_BYTES = A_STAGE_BYTES + B_STAGE_BYTES * (SPLIT ? 2 : 1);
+  constexpr uint32_t TX_BYTES = (AMODE == A_MATRIX ? A_STAGE_BYTES : 0) + B_STAGE_BYTES * (SPLIT ? 2 : 1);
   static_assert(STAGES >= 2, "pipeline needs at least two stages");
 
   extern __shared__ uint8_t smem_raw[];
@@ -254,7 +287,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
-      mbar_init(smem_u32(&full_bar[s]), 1);
+      // the TMA producer's expect_tx arrival, plus one arrival per gather thread in conv modes
+      mbar_init(smem_u32(&full_bar[s]), AMODE == A_MATRIX ? 1 : 129);
       mbar_init(smem_u32(&empty_bar[s]), 1);
       mbar_init(smem_u32(&conv_bar[s]), 128);
     }
@@ -292,7 +326,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           if (!ok) break;
           const uint32_t bar = smem_u32(&full_bar[stage]);
           mbar_arrive_expect_tx(bar, TX_BYTES);
-          tma_load_2d(smem_u32(a_hi + stage * A_STAGE_BYTES), &map_a, bar, kb * BLOCK_K, m0);
+          if (AMODE == A_MATRIX)
+            tma_load_2d(smem_u32(a_hi + stage * A_STAGE_BYTES), &map_a, bar, kb * BLOCK_K, m0);
           tma_load_2d(smem_u32(b_hi + stage * B_STAGE_BYTES), &map_w_hi, bar, kb * BLOCK_K, n0);
           if (SPLIT)
             tma_load_2d(smem_u32(b_lo + stage * B_STAGE_BYTES), &map_w_lo, bar, kb * BLOCK_K, n0);
@@ -317,7 +352,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
         for (int kb = 0; kb < p.num_k_blocks; kb++) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 3);
-          if (ok && SPLIT) ok = mbar_wait(smem_u32(&conv_bar[stage]), phase, abort_flag, p.status, 4);
+          if (ok && SPLIT && AMODE == A_MATRIX)
+            ok = mbar_wait(smem_u32(&conv_bar[stage]), phase, abort_flag, p.status, 4);
           if (!ok) break;
           tcgen05_fence_after();
           const uint32_t a_hi_s = smem_u32(a_hi + stage * A_STAGE_BYTES);
@@ -344,8 +380,106 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       }
     }
   } else if (warp >= 10) {
-    // ---------------- 3xTF32 converters (SPLIT only) ----------------
-    if (SPLIT) {
+    if (AMODE != A_MATRIX) {
+      // ---------------- conv gather warps (one thread per tile row) ----------------
+      // Each thread copies its own row of every A stage with cp.async (zero-filled where the tap
+      // falls outside the image or beyond K), keeps LAG stages in flight, and hands a stage over
+      // to the MMA warp once its copies have landed: for 3xTF32 it first splits its row into
+      // tf32 hi/lo in place (the row is private to the thread), then fences the generic-proxy
+      // writes for the tensor core and arrives on the stage's full barrier.
+      const ConvGeom& g = p.conv;
+      const int t = threadIdx.x - 320;  // 0..127
+      constexpr int LAG = STAGES >= 4 ? 3 : STAGES - 1;
+      int stage = 0, hand_stage = 0;
+      uint32_t phase = 0;
+      int in_flight = 0;
+      bool ok = true;
+      auto hand_over = [&](int s) {
+        if (SPLIT) {
+          float4* hi4 = reinterpret_cast<float4*>(a_hi + s * A_STAGE_BYTES + t * 128);
+          float4* lo4 = reinterpret_cast<float4*>(a_lo + s * A_STAGE_BYTES + t * 128);
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            float4 v = hi4[i], h, l;
+            h.x = round_tf32(v.x); h.y = round_tf32(v.y); h.z = round_tf32(v.z); h.w = round_tf32(v.w);
+            l.x = (fabsf(h.x) <= 3.4028234e38f) ? round_tf32(v.x - h.x) : 0.f;
+            l.y = (fabsf(h.y) <= 3.4028234e38f) ? round_tf32(v.y - h.y) : 0.f;
+            l.z = (fabsf(h.z) <= 3.4028234e38f) ? round_tf32(v.z - h.z) : 0.f;
+            l.w = (fabsf(h.w) <= 3.4028234e38f) ? round_tf32(v.w - h.w) : 0.f;
+            hi4[i] = h;
+            lo4[i] = l;
+          }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(smem_u32(&full_bar[s]));
+      };
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m = (tile / p.num_n_tiles) * BLOCK_M + t;
+        const bool row_valid = m < p.M;
+        const int pix = row_valid ? m : 0;
+        const int xo = pix % g.outW;
+        const int yo = (pix / g.outW) % g.outH;
+        const int b = pix / (g.outW * g.outH);
+        const int yi0 = yo * g.sH - g.padT, xi0 = xo * g.sW - g.padL;
+        const float* xb = g.x + (int64_t)b * g.inH * g.inW * g.Cin;
+        int ci = 0, wc = 0, wr = 0;  // tap cursor of the vector gather (advances with kk)
+        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 7);
+          if (!ok) break;
+          const uint32_t row = smem_u32(a_hi + stage * A_STAGE_BYTES);
+          if (AMODE == A_CONV_VEC) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+              const int yi = yi0 + wr * g.dH, xi = xi0 + wc * g.dW;
+              const bool v = row_valid && wr < g.fH && yi >= 0 && yi < g.inH && xi >= 0 && xi < g.inW;
+              const float* src = v ? xb + ((int64_t)yi * g.inW + xi) * g.Cin + ci : g.x;
+              cp_async_16_zfill(row + swz(t, j * 16), src, v);
+              ci += 4;
+              if (ci >= g.Cin) { ci = 0; if (++wc == g.fW) { wc = 0; ++wr; } }
+            }
+          } else {
+            // Cin == 3, fW == 3, dW == 1: filter row wr is 9 contiguous floats of input row yi
+#pragma unroll
+            for (int r3 = 0; r3 < 3; r3++) {
+              const int yi = yi0 + r3 * g.dH;
+              const bool rv = row_valid && r3 < g.fH && yi >= 0 && yi < g.inH;
+              const float* src = rv ? xb + ((int64_t)yi * g.inW + xi0) * 3 : g.x;
+              const bool all_cols = xi0 >= 0 && xi0 + 3 <= g.inW;
+              const int o = r3 * 40;  // destination byte offset of this filter row
+              if (rv && all_cols && (((uintptr_t)src) & 7) == 0) {
+#pragma unroll
+                for (int q = 0; q < 4; q++) cp_async_8_zfill(row + swz(t, o + q * 8), src + q * 2, true);
+                cp_async_4_zfill(row + swz(t, o + 32), src + 8, true);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 9; e++) {
+                  const int xi = xi0 + e / 3;
+                  const bool v = rv && xi >= 0 && xi < g.inW;
+                  cp_async_4_zfill(row + swz(t, o + e * 4), v ? src + e : g.x, v);
+                }
+              }
+              cp_async_4_zfill(row + swz(t, o + 36), g.x, false);  // pad float of the filter row
+            }
+            cp_async_8_zfill(row + swz(t, 120), g.x, false);       // k' = 30, 31
+          }
+          asm volatile("cp.async.commit_group;" ::: "memory");
+          if (++in_flight > LAG) {
+            asm volatile("cp.async.wait_group %0;" ::"n"(LAG) : "memory");
+            hand_over(hand_stage);
+            if (++hand_stage == STAGES) hand_stage = 0;
+            --in_flight;
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      while (in_flight > 0 && ok) {
+        hand_over(hand_stage);
+        if (++hand_stage == STAGES) hand_stage = 0;
+        --in_flight;
+      }
+    } else if (SPLIT) {
+      // ---------------- 3xTF32 converters (SPLIT only) ----------------
       const int t = threadIdx.x - 320;  // 0..127
       int stage = 0;
       uint32_t phase = 0;
@@ -514,13 +648,13 @@ bool encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BLOCK_N, bool SPLIT>
+template <int BLOCK_N, bool SPLIT, int AMODE>
 int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mh, const CUtensorMap& ml,
                    const CUtensorMap& mc, const GemmParams& p) {
   constexpr int smem_bytes = num_stages(BLOCK_N, SPLIT) * stage_bytes(BLOCK_N, SPLIT) + C_STAGING_BYTES + BIAS_STAGING_BYTES +
                              BARRIER_BYTES + 1024;
   static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
-  auto kernel = gemm_tcgen05_kernel<BLOCK_N, SPLIT>;
+  auto kernel = gemm_tcgen05_kernel<BLOCK_N, SPLIT, AMODE>;
   static bool configured[64] = {false};  // the attribute is per device
   if (!configured[ctx->device & 63]) {
     TFJS_CHECK_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
@@ -528,21 +662,27 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtensorMap&
   }
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-  kernel<<<grid, SPLIT ? 448 : 320, smem_bytes, ctx->stream>>>(ma, mh, ml, mc, p);
-  return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32)" : "gemm_tcgen05 (TF32)");
+  kernel<<<grid, (SPLIT || AMODE != A_MATRIX) ? 448 : 320, smem_bytes, ctx->stream>>>(ma, mh, ml, mc, p);
+  if (AMODE == A_MATRIX) return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32)" : "gemm_tcgen05 (TF32)");
+  return post_launch(ctx, SPLIT ? "conv2d_tcgen05 (3xTF32)" : "conv2d_tcgen05 (TF32)");
 }
 
-}  // namespace
-
-bool tcgen05_gemm_supported(int64_t M, int64_t N, int64_t K) {
-  // TMA needs 16-byte row strides; tiles smaller than one MMA are left to the CUDA cores.
-  return M >= 1 && N >= 8 && K >= 4 && K % 4 == 0 && N % 4 == 0 && M < (1ll << 31) &&
-         N < (1ll << 31) && K < (1ll << 31) && get_encode_fn() != nullptr;
+template <int AMODE>
+int launch_mode(tfjs_cuda_ctx* ctx, int block_n, bool split, const CUtensorMap& ma, const CUtensorMap& mh,
+                const CUtensorMap& ml, const CUtensorMap& mc, const GemmParams& p) {
+  switch (block_n) {
+    case 32: return split ? launch_variant<32, true, AMODE>(ctx, ma, mh, ml, mc, p) : launch_variant<32, false, AMODE>(ctx, ma, mh, ml, mc, p);
+    case 64: return split ? launch_variant<64, true, AMODE>(ctx, ma, mh, ml, mc, p) : launch_variant<64, false, AMODE>(ctx, ma, mh, ml, mc, p);
+    case 128: return split ? launch_variant<128, true, AMODE>(ctx, ma, mh, ml, mc, p) : launch_variant<128, false, AMODE>(ctx, ma, mh, ml, mc, p);
+    default: return launch_variant<256, false, AMODE>(ctx, ma, mh, ml, mc, p);
+  }
 }
 
-int launch_gemm_tcgen05(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, const float* w_hi,
-                        const float* w_lo, int64_t kp, float* out, int64_t N, const EpilogueArgs& epi,
-                        int math_mode) {
+// Shared by the matrix and the convolution entry points.  `a` is the dense A matrix
+// (A_MATRIX) or null; K is the contraction length as laid out in the packed weights.
+int launch_common(tfjs_cuda_ctx* ctx, int amode, const float* a, const ConvGeom* conv, int64_t M, int64_t K,
+                  const float* w_hi, const float* w_lo, int64_t kp, float* out, int64_t N,
+                  const EpilogueArgs& epi, int math_mode) {
   const bool split = math_mode == TFJS_MATH_TF32X3;
   TFJS_REQUIRE(ctx, !split || w_lo != nullptr, "3xTF32 needs the residual weight plane");
   int block_n;
@@ -556,10 +696,11 @@ int launch_gemm_tcgen05(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K
     block_n /= 2;
 
   CUtensorMap ma, mh, ml, mc;
-  bool ok = encode_2d(&ma, a, (uint64_t)M, (uint64_t)K, BLOCK_M, BLOCK_K) &&
-            encode_2d(&mh, w_hi, (uint64_t)N, (uint64_t)kp, (uint32_t)block_n, BLOCK_K) &&
+  bool ok = encode_2d(&mh, w_hi, (uint64_t)N, (uint64_t)kp, (uint32_t)block_n, BLOCK_K) &&
             encode_2d(&ml, split ? w_lo : w_hi, (uint64_t)N, (uint64_t)kp, (uint32_t)block_n, BLOCK_K) &&
             encode_2d(&mc, out, (uint64_t)M, (uint64_t)N, 32, 32);
+  if (ok && amode == A_MATRIX) ok = encode_2d(&ma, a, (uint64_t)M, (uint64_t)K, BLOCK_M, BLOCK_K);
+  else ma = mh;  // unused by the conv modes
   if (!ok) return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
 
   GemmParams p;
@@ -571,10 +712,56 @@ int launch_gemm_tcgen05(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K
   p.num_k_blocks = (int)ceil_div64(K, BLOCK_K);
   p.status = ctx->d_status;
   p.epi = epi;
-  switch (block_n) {
-    case 32: return split ? launch_variant<32, true>(ctx, ma, mh, ml, mc, p) : launch_variant<32, false>(ctx, ma, mh, ml, mc, p);
-    case 64: return split ? launch_variant<64, true>(ctx, ma, mh, ml, mc, p) : launch_variant<64, false>(ctx, ma, mh, ml, mc, p);
-    case 128: return split ? launch_variant<128, true>(ctx, ma, mh, ml, mc, p) : launch_variant<128, false>(ctx, ma, mh, ml, mc, p);
-    default: return launch_variant<256, false>(ctx, ma, mh, ml, mc, p);
+  if (conv) p.conv = *conv;
+  else memset(&p.conv, 0, sizeof(p.conv));
+  switch (amode) {
+    case A_CONV_VEC: return launch_mode<A_CONV_VEC>(ctx, block_n, split, ma, mh, ml, mc, p);
+    case A_CONV_RGB: return launch_mode<A_CONV_RGB>(ctx, block_n, split, ma, mh, ml, mc, p);
+    default: return launch_mode<A_MATRIX>(ctx, block_n, split, ma, mh, ml, mc, p);
   }
+}
+
+}  // namespace
+
+bool tcgen05_gemm_supported(int64_t M, int64_t N, int64_t K) {
+  // TMA needs 16-byte row strides; tiles smaller than one MMA are left to the CUDA cores.
+  return M >= 1 && N >= 8 && K >= 4 && K % 4 == 0 && N % 4 == 0 && M < (1ll << 31) &&
+         N < (1ll << 31) && K < (1ll << 31) && get_encode_fn() != nullptr;
+}
+
+int launch_gemm_tcgen05(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, const float* w_hi,
+                        const float* w_lo, int64_t kp, float* out, int64_t N, const EpilogueArgs& epi,
+                        int math_mode) {
+  return launch_common(ctx, A_MATRIX, a, nullptr, M, K, w_hi, w_lo, kp, out, N, epi, math_mode);
+}
+
+// Which implicit-GEMM gather, if any, can take this convolution (0 = none).
+int tcgen05_conv_mode(const tfjs_conv2d_info& ci) {
+  const int64_t M = (int64_t)ci.batchSize * ci.outHeight * ci.outWidth;
+  const int64_t N = ci.outChannels;
+  if (M < 1 || M >= (1ll << 31) || N < 8 || N % 4 != 0 || get_encode_fn() == nullptr) return 0;
+  if ((int64_t)ci.batchSize * ci.inHeight * ci.inWidth * ci.inChannels >= (1ll << 31)) return 0;
+  if (ci.inChannels == 3 && ci.filterWidth == 3 && ci.filterHeight <= 3 && ci.dilationWidth == 1) return A_CONV_RGB;
+  if (ci.inChannels >= 4 && ci.inChannels % 4 == 0) return A_CONV_VEC;
+  return 0;
+}
+
+// Contraction length of the packed weights for a conv mode (see the K layouts above).
+int64_t tcgen05_conv_k(const tfjs_conv2d_info& ci, int mode) {
+  if (mode == A_CONV_RGB) return 32;
+  return (int64_t)ci.filterHeight * ci.filterWidth * ci.inChannels;
+}
+
+int launch_conv_tcgen05(tfjs_cuda_ctx* ctx, int mode, const float* x, const tfjs_conv2d_info& ci,
+                        const float* w_hi, const float* w_lo, int64_t kp, float* out,
+                        const EpilogueArgs& epi, int math_mode) {
+  ConvGeom g;
+  g.x = x;
+  g.inH = ci.inHeight; g.inW = ci.inWidth; g.Cin = ci.inChannels;
+  g.outH = ci.outHeight; g.outW = ci.outWidth;
+  g.sH = ci.strideHeight; g.sW = ci.strideWidth; g.dH = ci.dilationHeight; g.dW = ci.dilationWidth;
+  g.padT = ci.padTop; g.padL = ci.padLeft; g.fH = ci.filterHeight; g.fW = ci.filterWidth;
+  const int64_t M = (int64_t)ci.batchSize * ci.outHeight * ci.outWidth;
+  return launch_common(ctx, mode, nullptr, &g, M, tcgen05_conv_k(ci, mode), w_hi, w_lo, kp, out,
+                       ci.outChannels, epi, math_mode);
 }
