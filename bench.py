@@ -299,6 +299,12 @@ def run_cuda(args):
 
     # ---- per-kernel device times (eager, events between launches, same stream) ----
     prof_steps = min(args.steps, 5)
+    # one untimed eager pass first: the graph keeps its own buffers, so the eager path has to
+    # fill the allocator's free lists again (cudaMalloc must not land inside a measured launch)
+    lg, pr = net.forward_fused(x)
+    lg.dispose()
+    pr.dispose()
+    bk.sync()
     bk.profileBegin(launches_per_step * prof_steps + 8)
     for _ in range(prof_steps):
         lg, pr = net.forward_fused(x)
@@ -335,6 +341,10 @@ def run_cuda(args):
     net_gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
 
     # ---- end to end through the public API: pinned host -> device -> forward -> host ----
+    # Every step uploads its own input from pinned host memory and reads its probabilities back.
+    # Two input tensors (each with its own captured graph) alternate, and the upload of step
+    # i + 1 is issued with writeAsync before step i is launched, so it overlaps step i's kernels;
+    # the blocking read of step i's result closes the step.
     import ctypes as C
     lib = bk._lib
     nbytes = x_host.nbytes
@@ -342,31 +352,44 @@ def run_cuda(args):
     assert lib.tfjs_cuda_host_alloc(C.byref(pinned), nbytes) == 0
     C.memmove(pinned, x_host.ctypes.data, nbytes)
     out_bytes = per * 1000 * 4
+    xs = [x, ops.tensor(x_host)]
+    graphs, outs = [graph], [probs if graph is not None else None]
+    if graph is not None:
+        bk.graphBegin()
+        lg2, pr2 = net.forward_fused(xs[1])
+        graphs.append(bk.graphEnd())
+        outs.append(pr2)
 
-    def e2e_step():
-        bk.writeFromHostPointer(x.dataId, pinned, nbytes)
-        if graph is not None:
-            bk.graphLaunch(graph)
-            return probs.dataSync()
-        lg, pr = net.forward_fused(x)
-        res = pr.dataSync()
-        lg.dispose()
-        pr.dispose()
+    def e2e_run(n):
+        res = None
+        bk.writeAsync(xs[0].dataId, pinned, nbytes)
+        for i in range(n):
+            cur = i % 2
+            if i + 1 < n:
+                bk.writeAsync(xs[1 - cur].dataId, pinned, nbytes)
+            if graph is not None:
+                bk.graphLaunch(graphs[cur], inputs=[xs[cur]])
+                res = outs[cur].dataSync()
+            else:
+                lg, pr = net.forward_fused(xs[cur])
+                res = pr.dataSync()
+                lg.dispose()
+                pr.dispose()
         return res
 
-    for _ in range(max(1, min(args.warmup, 3))):
-        e2e_step()
+    e2e_run(max(2, min(args.warmup, 3)))
     bk.sync()
     d.barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        res = e2e_step()
+    res = e2e_run(args.steps)
     bk.sync()
     e2e_s = d.max(time.perf_counter() - t0)
     d.barrier()
-    assert np.isfinite(res).all()
+    assert np.isfinite(res).all() and np.allclose(res, first, rtol=0, atol=1e-6)
     e2e_value = cfg["global_batch"] * args.steps / e2e_s
     lib.tfjs_cuda_host_free(pinned)
+    if len(graphs) > 1:
+        bk.graphDestroy(graphs[1])
 
     # ---- CPU baseline beside it (rank 0, N = 1 only) ----
     cpu_baseline = None

@@ -134,6 +134,15 @@ int tfjs_cuda_tensor_register(tfjs_cuda_ctx* ctx, tfjs_tensor_id* out_id, int ra
                               const int64_t* shape, int dtype);
 int tfjs_cuda_tensor_write(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, const void* host, size_t nbytes);
 int tfjs_cuda_tensor_read(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, void* host, size_t nbytes);
+/* Extension of KernelBackend.write for pipelined input: the upload runs on a second stream, after
+ * the kernels already enqueued (which may still read the old contents) and concurrently with
+ * whatever is enqueued next.  Kernels and reads that take the tensor as an operand wait for it
+ * automatically; a captured graph cannot know its inputs, so call tensor_wait(ctx, id) before
+ * graph_launch for every tensor written this way.  `host` should be pinned memory
+ * (tfjs_cuda_host_alloc) and must stay valid until the upload has finished. */
+int tfjs_cuda_tensor_write_async(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, const void* host,
+                                 size_t nbytes);
+int tfjs_cuda_tensor_wait(tfjs_cuda_ctx* ctx, tfjs_tensor_id id);
 /* Non-blocking readback for KernelBackend.read(): the copy into `host` (pinned memory for a
  * truly asynchronous copy) completes when the event does. */
 int tfjs_cuda_tensor_read_async(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, void* host, size_t nbytes,

@@ -68,6 +68,8 @@ SIGNATURES = {
     "tfjs_cuda_tensor_register": (C.c_int, [_P, _I64P, C.c_int, _I64P, C.c_int]),
     "tfjs_cuda_tensor_write": (C.c_int, [_P, C.c_int64, _P, C.c_size_t]),
     "tfjs_cuda_tensor_read": (C.c_int, [_P, C.c_int64, _P, C.c_size_t]),
+    "tfjs_cuda_tensor_write_async": (C.c_int, [_P, C.c_int64, _P, C.c_size_t]),
+    "tfjs_cuda_tensor_wait": (C.c_int, [_P, C.c_int64]),
     "tfjs_cuda_tensor_read_async": (C.c_int, [_P, C.c_int64, _P, C.c_size_t, C.POINTER(_P)]),
     "tfjs_cuda_event_query": (C.c_int, [_P]),
     "tfjs_cuda_event_wait": (C.c_int, [_P, C.c_int]),

@@ -136,6 +136,12 @@ class BackendCuda:
         rec = self._rec(dataId)
         self._check(self._lib.tfjs_cuda_tensor_write(self._ctx, rec["id"], ptr, nbytes))
 
+    def writeAsync(self, dataId, ptr, nbytes):
+        """Extension: upload from pinned host memory on the copy stream, overlapping the kernels
+        enqueued next; consumers wait for it (pass the tensor to graphLaunch(inputs=...))."""
+        rec = self._rec(dataId)
+        self._check(self._lib.tfjs_cuda_tensor_write_async(self._ctx, rec["id"], ptr, nbytes))
+
     def readSync(self, dataId):
         rec = self._rec(dataId)
         n = size_from_shape(rec["shape"])
@@ -517,7 +523,11 @@ class BackendCuda:
         self._check(self._lib.tfjs_cuda_graph_end(self._ctx, C.byref(g)))
         return g
 
-    def graphLaunch(self, graph):
+    def graphLaunch(self, graph, inputs=()):
+        """Replays a captured graph.  `inputs`: tensors the graph reads that may have an
+        asynchronous upload (writeAsync) in flight; the replay is ordered after those uploads."""
+        for t in inputs:
+            self._check(self._lib.tfjs_cuda_tensor_wait(self._ctx, self._rec(t.dataId)["id"]))
         self._check(self._lib.tfjs_cuda_graph_launch(self._ctx, graph))
 
     def graphDestroy(self, graph):

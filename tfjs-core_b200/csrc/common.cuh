@@ -47,6 +47,9 @@ struct TensorEntry {
   float* deq = nullptr;
   size_t deq_capacity = 0;
   uint64_t deq_version = 0;
+  // asynchronous upload in flight on the copy stream (tensor_write_async)
+  cudaEvent_t copy_event = nullptr;
+  bool copy_pending = false;
 };
 
 struct tfjs_cuda_graph {
@@ -68,6 +71,8 @@ struct tfjs_cuda_ctx {
   int device = 0;
   int sm_count = 0;
   cudaStream_t stream = nullptr;
+  cudaStream_t copy_stream = nullptr;   // created on the first tensor_write_async
+  cudaEvent_t compute_mark = nullptr;   // orders an upload after the kernels already enqueued
   std::string last_error;
   std::unordered_map<tfjs_tensor_id, TensorEntry> tensors;
   tfjs_tensor_id next_id = 1;

@@ -218,6 +218,13 @@ static void free_entry_buffers(tfjs_cuda_ctx* ctx, TensorEntry& t) {
   t.packed = PackedWeights();
   if (t.deq) ctx_free(ctx, t.deq, t.deq_capacity);
   t.deq = nullptr;
+  if (t.copy_event) {
+    // the buffer goes back to the pool: later users are ordered on the compute stream only
+    if (t.copy_pending) cudaStreamWaitEvent(ctx->stream, t.copy_event, 0);
+    cudaEventDestroy(t.copy_event);
+    t.copy_event = nullptr;
+    t.copy_pending = false;
+  }
 }
 
 extern "C" int tfjs_cuda_ctx_destroy(tfjs_cuda_ctx* ctx) {
@@ -231,6 +238,11 @@ extern "C" int tfjs_cuda_ctx_destroy(tfjs_cuda_ctx* ctx) {
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   for (cudaEvent_t ev : ctx->profile_events) cudaEventDestroy(ev);
+  if (ctx->compute_mark) cudaEventDestroy(ctx->compute_mark);
+  if (ctx->copy_stream) {
+    cudaStreamSynchronize(ctx->copy_stream);
+    cudaStreamDestroy(ctx->copy_stream);
+  }
   if (ctx->time_start) cudaEventDestroy(ctx->time_start);
   if (ctx->time_stop) cudaEventDestroy(ctx->time_stop);
   if (ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -404,13 +416,64 @@ extern "C" int tfjs_cuda_tensor_write(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, con
   TFJS_REQUIRE(ctx, !t->quant.quantized, "cannot write float values into a quantised tensor");
   TFJS_REQUIRE(ctx, nbytes == t->nbytes, "write: %zu bytes given, tensor holds %zu", nbytes, t->nbytes);
   cudaSetDevice(ctx->device);
+  if (t->copy_pending) {  // an earlier asynchronous upload must not land after this one
+    TFJS_CHECK_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, t->copy_event, 0));
+    t->copy_pending = false;
+  }
   if (nbytes)
     TFJS_CHECK_CUDA(ctx, cudaMemcpyAsync(t->ptr, host, nbytes, cudaMemcpyHostToDevice, ctx->stream));
   t->version++;
   return TFJS_CUDA_OK;
 }
 
+// Makes work enqueued on the context's stream from now on wait for an asynchronous upload of
+// this tensor that may still be in flight on the copy stream.
+static int wait_for_upload(tfjs_cuda_ctx* ctx, TensorEntry* t) {
+  if (t->copy_pending) {
+    TFJS_CHECK_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, t->copy_event, 0));
+    t->copy_pending = false;
+  }
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_tensor_write_async(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, const void* host,
+                                            size_t nbytes) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  TensorEntry* t = find_tensor(ctx, id);
+  if (!t) return set_error(ctx, TFJS_CUDA_ERR_NOT_FOUND, "write: unknown tensor id %lld", (long long)id);
+  TFJS_REQUIRE(ctx, host != nullptr || nbytes == 0, "MathBackendCUDA.write(): values cannot be null");
+  TFJS_REQUIRE(ctx, !t->quant.quantized, "cannot write float values into a quantised tensor");
+  TFJS_REQUIRE(ctx, nbytes == t->nbytes, "write: %zu bytes given, tensor holds %zu", nbytes, t->nbytes);
+  TFJS_REQUIRE(ctx, !ctx->capturing, "asynchronous writes cannot be captured into a graph");
+  cudaSetDevice(ctx->device);
+  if (!ctx->copy_stream) {
+    TFJS_CHECK_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+    TFJS_CHECK_CUDA(ctx, cudaEventCreateWithFlags(&ctx->compute_mark, cudaEventDisableTiming));
+  }
+  if (!t->copy_event)
+    TFJS_CHECK_CUDA(ctx, cudaEventCreateWithFlags(&t->copy_event, cudaEventDisableTiming));
+  t->version++;
+  if (!nbytes) return TFJS_CUDA_OK;
+  // write-after-read: kernels already enqueued may still read the old contents
+  TFJS_CHECK_CUDA(ctx, cudaEventRecord(ctx->compute_mark, ctx->stream));
+  TFJS_CHECK_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->compute_mark, 0));
+  TFJS_CHECK_CUDA(ctx, cudaMemcpyAsync(t->ptr, host, nbytes, cudaMemcpyHostToDevice, ctx->copy_stream));
+  TFJS_CHECK_CUDA(ctx, cudaEventRecord(t->copy_event, ctx->copy_stream));
+  t->copy_pending = true;
+  return TFJS_CUDA_OK;
+}
+
+extern "C" int tfjs_cuda_tensor_wait(tfjs_cuda_ctx* ctx, tfjs_tensor_id id) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  TensorEntry* t = find_tensor(ctx, id);
+  if (!t) return set_error(ctx, TFJS_CUDA_ERR_NOT_FOUND, "wait: unknown tensor id %lld", (long long)id);
+  cudaSetDevice(ctx->device);
+  return wait_for_upload(ctx, t);
+}
+
 static int enqueue_read(tfjs_cuda_ctx* ctx, TensorEntry* t, void* host, size_t nbytes) {
+  int wrc = wait_for_upload(ctx, t);
+  if (wrc) return wrc;
   if (t->quant.quantized) {
     TFJS_REQUIRE(ctx, nbytes == (size_t)t->size * 4, "read: %zu bytes asked, tensor holds %zu",
                  nbytes, (size_t)t->size * 4);
@@ -542,7 +605,7 @@ int get_f32(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, int64_t min_elems, const char
   TFJS_REQUIRE(ctx, t->size >= min_elems, "%s holds %lld elements, %lld needed", what,
                (long long)t->size, (long long)min_elems);
   *out = t;
-  return TFJS_CUDA_OK;
+  return wait_for_upload(ctx, t);  // kernels that take this operand run after its upload
 }
 
 int resolve_epilogue(tfjs_cuda_ctx* ctx, const tfjs_epilogue* epi, int64_t channels,
