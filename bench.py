@@ -208,27 +208,6 @@ KERNEL_FAMILY = {"gemm_tcgen05 (TF32)": "gemm_tcgen05", "gemm_tcgen05 (3xTF32)":
                  "avgPool (global)": "global_avgpool", "softmax_last": "softmax"}
 
 
-def layer_algorithmic_bytes(batch, quantized):
-    """Algorithmic bytes of each of the 30 launches of the fused forward, in launch order:
-    4*(|x| + |y|) + filter bytes + 4*|bias| with every tensor counted once."""
-    from tfjs_core_b200 import mobilenet
-    out = []
-    h = w = 224
-    c = 3
-    wb = 1 if quantized else 4
-    for name, kind, shape, s in mobilenet.layer_specs():
-        if name == "fc":
-            out.append(4 * batch * (7 * 7 * c + c))
-            out.append(4 * batch * (c + 1000) + wb * c * 1000 + 4 * 1000)
-            out.append(4 * batch * 2000)
-            break
-        ho, wo = -(-h // s), -(-w // s)
-        co = c if kind == "dw" else shape[3]
-        out.append(4 * batch * (h * w * c + ho * wo * co) + wb * int(np.prod(shape)) + 4 * co)
-        h, w, c = ho, wo, co
-    return out
-
-
 def run_cuda(args):
     from tfjs_core_b200 import BackendCuda, ENGINE, mobilenet, ops
 
@@ -311,7 +290,7 @@ def run_cuda(args):
         lg.dispose()
         pr.dispose()
     rows = bk.profileEnd()
-    layer_bytes = layer_algorithmic_bytes(per, cfg["quantized"])
+    layer_bytes = mobilenet.layer_algorithmic_bytes(per, cfg["quantized"])
     fam = {}
     for i, (name, ms) in enumerate(rows):
         f = KERNEL_FAMILY.get(name, name)
@@ -333,7 +312,8 @@ def run_cuda(args):
                 "launches_per_step": fam[top]["launches"] // prof_steps,
                 "avg_launch_ms": fam[top]["ms"] / fam[top]["launches"],
                 "share_of_step": fam[top]["ms"] / total_ms,
-                "traffic": TRAFFIC_PER_LAUNCH.get(top)}
+                "traffic": (TRAFFIC_MB_PER_IMAGE_AND_LAUNCH[top] * 1e6 * per
+                            if top in TRAFFIC_MB_PER_IMAGE_AND_LAUNCH else None)}
     kernels = {k: {"ms_per_step": v["ms"] / prof_steps, "share": v["ms"] / total_ms,
                    "launches_per_step": v["launches"] // prof_steps,
                    "achieved_gbs": v["bytes"] / (v["ms"] * 1e-3) / 1e9} for k, v in fam.items()}
@@ -424,9 +404,12 @@ def run_cuda(args):
     d.close()
 
 
-# DRAM bytes per launch of each kernel family from the ncu captures summarised under
-# profiles/ (null until a capture exists).
-TRAFFIC_PER_LAUNCH = {}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel family, averaged over
+# the family's launches of one forward pass, from the batch-256 ncu capture summarised in
+# profiles/gemm_tcgen05_mobilenet.md; it grows in proportion to the batch.
+TRAFFIC_MB_PER_IMAGE_AND_LAUNCH = {"gemm_tcgen05": 4056.76 / 14 / 256,
+                                   "depthwise3x3_strip": 4610.62 / 13 / 256,
+                                   "conv2d_tcgen05": 505.0 / 256}
 
 
 def main():

@@ -143,6 +143,27 @@ class MobileNetV1:
         return ENGINE.tidy(body)
 
 
+def layer_algorithmic_bytes(batch, quantized):
+    """Algorithmic bytes of each of the 30 launches of the fused forward, in launch order:
+    4*(|x| + |y|) + filter bytes + 4*|bias| with every tensor counted once."""
+    out = []
+    h = w = 224
+    c = 3
+    wb = 1 if quantized else 4
+    for name, kind, shape, s in layer_specs():
+        if name == "fc":
+            out.append(4 * batch * (7 * 7 * c + c))
+            out.append(4 * batch * (c + 1000) + wb * c * 1000 + 4 * 1000)
+            out.append(4 * batch * 2000)
+            break
+        ho, wo = -(-h // s), -(-w // s)
+        co = c if kind == "dw" else shape[3]
+        out.append(4 * batch * (h * w * c + ho * wo * co) + wb * int(np.prod(shape)) + 4 * co)
+        h, w, c = ho, wo, co
+    return out
+
+
+
 def algorithmic_bytes_per_image(quantized=False):
     """Bytes one image moves if every tensor is touched once and epilogues are fused:
     4*(|x| + |y|) per layer; weights are counted separately by weight_bytes()."""

@@ -1,0 +1,55 @@
+#!/usr/bin/env python3
+"""Per-layer device times of one fused MobileNetV1 forward on the cuda backend.
+
+    python tfjs-core_b200/profile_layers.py [batch] [tf32|3xtf32] [q]
+
+Prints, for each of the 30 launches, the kernel name, the best device time over a few passes
+(events recorded between launches on the context's stream), the layer's algorithmic bytes and
+the bandwidth that corresponds to.  `q` stores the filters as uint8 (BASELINE config 5).  This is
+also the small-case command the ncu captures summarised under profiles/ were taken with.
+"""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import tfjs_core_b200 as tf  # noqa: E402
+from tfjs_core_b200 import mobilenet, ops  # noqa: E402
+
+
+def main():
+    batch = int(sys.argv[1]) if len(sys.argv) > 1 else 64
+    mode = sys.argv[2] if len(sys.argv) > 2 else "tf32"
+    quantized = len(sys.argv) > 3 and sys.argv[3] == "q"
+    reps = 4
+    bk = tf.BackendCuda(0, mode)
+    tf.ENGINE.registerBackend("profile-cuda", lambda: bk, 10)
+    tf.ENGINE.setBackend("profile-cuda")
+    params = mobilenet.make_weights(4 if quantized else 3, quantized=quantized, gain=1.5)
+    net = mobilenet.MobileNetV1(params, bk)
+    x = ops.tensor(mobilenet.make_input(3, batch))
+    for _ in range(2):
+        logits, probs = net.forward_fused(x)
+        probs.dataSync()
+        logits.dispose()
+        probs.dispose()
+    bk.profileBegin(40 * reps)
+    for _ in range(reps):
+        logits, probs = net.forward_fused(x)
+        logits.dispose()
+        probs.dispose()
+    rows = bk.profileEnd()
+    layer_bytes = mobilenet.layer_algorithmic_bytes(batch, quantized)
+    names = [s[0] for s in mobilenet.layer_specs()][:-1] + ["avgpool", "fc", "softmax"]
+    total = 0.0
+    for i in range(30):
+        ms = min(rows[i + 30 * r][1] for r in range(reps))
+        total += ms
+        print(f"{names[i]:8s} {rows[i][0]:28s} {ms * 1e3:9.1f} us {layer_bytes[i] / 1e6:9.1f} MB "
+              f"{layer_bytes[i] / ms / 1e6:7.0f} GB/s")
+    print(f"total {total:.3f} ms  {batch / total * 1e3:.0f} img/s  "
+          f"{sum(layer_bytes) / total / 1e6:.0f} GB/s algorithmic")
+
+
+if __name__ == "__main__":
+    main()
