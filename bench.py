@@ -46,6 +46,7 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample", type=int, default=12, help="images in the cpu_baseline sample")
+    ap.add_argument("--ref-threads", type=int, default=0, help="host threads of --impl reference (0 = all)")
     return ap.parse_args()
 
 
@@ -176,7 +177,7 @@ def run_reference(args):
     from tfjs_core_b200 import mobilenet
     oracle.build()
     cfg = workload_config(args, max(world, 1))
-    threads = os.cpu_count() or 1
+    threads = args.ref_threads or os.cpu_count() or 1
     params = mobilenet.make_weights(cfg["seed"], quantized=cfg["quantized"], gain=cfg["gain"])
     images = mobilenet.make_input(cfg["seed"], threads)
     for _ in range(args.warmup):
