@@ -204,6 +204,8 @@ def run_reference(args):
 
 # ---- this backend -------------------------------------------------------------------------------
 KERNEL_FAMILY = {"gemm_tcgen05 (TF32)": "gemm_tcgen05", "gemm_tcgen05 (3xTF32)": "gemm_tcgen05",
+                 "gemm_tcgen05 (TF32, uint8 weights)": "gemm_tcgen05",
+                 "gemm_tcgen05 (3xTF32, uint8 weights)": "gemm_tcgen05",
                  "conv2d_tcgen05 (TF32)": "conv2d_tcgen05", "conv2d_tcgen05 (3xTF32)": "conv2d_tcgen05",
                  "depthwiseConv2D (3x3 strip)": "depthwise3x3_strip", "conv2d (stem)": "conv2d_stem",
                  "avgPool (global)": "global_avgpool", "softmax_last": "softmax"}

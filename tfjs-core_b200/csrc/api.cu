@@ -92,6 +92,30 @@ int gemm_dispatch(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, Tens
                   int64_t w_offset, bool source_is_nk, bool cacheable, float* out, int64_t N,
                   const EpilogueArgs& epi) {
   if (ctx->use_tensor_cores && tcgen05_gemm_supported(M, N, K)) {
+    if (w->quant.quantized && cacheable && w_offset == 0) {
+      // Quantised weights stay uint8 in HBM: a K-major byte copy is cached once and the kernel
+      // dequantises each tile in shared memory.
+      const int64_t kq = (K + 15) / 16 * 16;
+      if (!w->packed_q || w->packed_q_version != w->version || w->packed_q_n != N ||
+          w->packed_q_k != K || w->packed_q_transposed != source_is_nk) {
+        if (w->packed_q) ctx_free(ctx, w->packed_q, w->packed_q_capacity);
+        w->packed_q = nullptr;
+        void* p;
+        int rc = ctx_alloc(ctx, (size_t)(N * kq), &p, &w->packed_q_capacity);
+        if (rc) return rc;
+        w->packed_q = (uint8_t*)p;
+        rc = launch_pack_u8(ctx, (const uint8_t*)w->ptr, K, N, source_is_nk ? 1 : N,
+                            source_is_nk ? K : 1, kq, w->packed_q);
+        if (rc) return rc;
+        w->packed_q_version = w->version;
+        w->packed_q_n = N;
+        w->packed_q_k = K;
+        w->packed_q_kq = kq;
+        w->packed_q_transposed = source_is_nk;
+      }
+      return launch_gemm_tcgen05_u8(ctx, a, M, K, w->packed_q, kq, w->quant.scale, w->quant.min, out,
+                                    N, epi, ctx->math_mode);
+    }
     PackedWeights pw;
     bool temporary;
     int rc = packed_weights(ctx, w, w_offset, K, N, source_is_nk, cacheable, &pw, &temporary);

@@ -47,6 +47,13 @@ struct TensorEntry {
   float* deq = nullptr;
   size_t deq_capacity = 0;
   uint64_t deq_version = 0;
+  // K-major uint8 copy [N, kq] of a quantised contraction operand: the tensor-core GEMM loads
+  // these bytes with TMA and dequantises them in shared memory inside its main loop
+  uint8_t* packed_q = nullptr;
+  size_t packed_q_capacity = 0;
+  int64_t packed_q_n = 0, packed_q_k = 0, packed_q_kq = 0;
+  uint64_t packed_q_version = 0;
+  bool packed_q_transposed = false;
   // asynchronous upload in flight on the copy stream (tensor_write_async)
   cudaEvent_t copy_event = nullptr;
   bool copy_pending = false;
@@ -186,6 +193,8 @@ int launch_pack_weights_rows(tfjs_cuda_ctx* ctx, const void* src, bool src_is_u8
                              float* hi, float* lo);
 int launch_transpose_batched(tfjs_cuda_ctx* ctx, const float* src, float* dst, int batch,
                              int rows, int cols);
+int launch_pack_u8(tfjs_cuda_ctx* ctx, const uint8_t* src, int64_t K, int64_t N, int64_t k_stride,
+                   int64_t n_stride, int64_t kq, uint8_t* dst);
 int launch_dequant(tfjs_cuda_ctx* ctx, const uint8_t* q, float* out, int64_t n, double scale,
                    double min);
 // gemm_tcgen05.cu
@@ -193,6 +202,11 @@ bool tcgen05_gemm_supported(int64_t M, int64_t N, int64_t K);
 int launch_gemm_tcgen05(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K,
                         const float* w_hi, const float* w_lo, int64_t kp, float* out, int64_t N,
                         const EpilogueArgs& epi, int math_mode);
+// Same contraction with the weights as K-major uint8 [N, kq] (kq a multiple of 16, zero
+// padded): w = q*scale + min is evaluated in shared memory inside the main loop.
+int launch_gemm_tcgen05_u8(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K,
+                           const uint8_t* w_q, int64_t kq, double scale, double min, float* out,
+                           int64_t N, const EpilogueArgs& epi, int math_mode);
 // Implicit-GEMM convolution on the tensor cores: mode 0 = not eligible, otherwise the gather
 // flavour; tcgen05_conv_k is the contraction length the packed weights must have.
 int tcgen05_conv_mode(const tfjs_conv2d_info& ci);

@@ -218,6 +218,8 @@ static void free_entry_buffers(tfjs_cuda_ctx* ctx, TensorEntry& t) {
   t.packed = PackedWeights();
   if (t.deq) ctx_free(ctx, t.deq, t.deq_capacity);
   t.deq = nullptr;
+  if (t.packed_q) ctx_free(ctx, t.packed_q, t.packed_q_capacity);
+  t.packed_q = nullptr;
   if (t.copy_event) {
     // the buffer goes back to the pool: later users are ordered on the compute stream only
     if (t.copy_pending) cudaStreamWaitEvent(ctx->stream, t.copy_event, 0);

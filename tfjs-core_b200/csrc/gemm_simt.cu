@@ -128,6 +128,23 @@ __global__ void pack_weights_rows_kernel(const void* __restrict__ src, int src_i
   }
 }
 
+// uint8 [K, N] (addressed through strides) -> K-major uint8 [N, kq], zero padded in k.
+__global__ void pack_u8_kernel(const uint8_t* __restrict__ src, int K, int N, int64_t k_stride,
+                               int64_t n_stride, int kq, uint8_t* __restrict__ dst) {
+  __shared__ uint8_t tile[32][33];
+  const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    int k, n;
+    if (n_stride == 1) { k = k0 + r; n = n0 + threadIdx.x; } else { n = n0 + r; k = k0 + threadIdx.x; }
+    tile[k - k0][n - n0] = (k < K && n < N) ? src[k * k_stride + n * n_stride] : (uint8_t)0;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int n = n0 + r, k = k0 + threadIdx.x;
+    if (n < N && k < kq) dst[(int64_t)n * kq + k] = tile[threadIdx.x][r];
+  }
+}
+
 // dst[b, c, r] = src[b, r, c]
 __global__ void transpose_batched_kernel(const float* __restrict__ src, float* __restrict__ dst,
                                          int rows, int cols) {
@@ -178,6 +195,14 @@ int launch_pack_weights_rows(tfjs_cuda_ctx* ctx, const void* src, bool src_is_u8
   pack_weights_rows_kernel<<<blocks > 1024 ? 1024 : blocks, 256, 0, ctx->stream>>>(
       src, src_is_u8 ? 1 : 0, scale, mn, (int)K, (int)N, row_len, row_pad, (int)kp, hi, lo);
   return post_launch(ctx, "pack_weights (rows)");
+}
+
+int launch_pack_u8(tfjs_cuda_ctx* ctx, const uint8_t* src, int64_t K, int64_t N, int64_t k_stride,
+                   int64_t n_stride, int64_t kq, uint8_t* dst) {
+  if (N * kq == 0) return TFJS_CUDA_OK;
+  dim3 grid((unsigned)ceil_div64(N, 32), (unsigned)ceil_div64(kq, 32));
+  pack_u8_kernel<<<grid, dim3(32, 8), 0, ctx->stream>>>(src, (int)K, (int)N, k_stride, n_stride, (int)kq, dst);
+  return post_launch(ctx, "pack_weights (uint8)");
 }
 
 int launch_transpose_batched(tfjs_cuda_ctx* ctx, const float* src, float* dst, int batch, int rows,

@@ -32,13 +32,23 @@ constexpr int C_STAGING_BYTES = EPI_WARPS * C_CHUNK_BYTES;
 constexpr int BIAS_STAGING_BYTES = EPI_WARPS * 256;  // per warp: 32 bias values + 32 prelu slopes
 constexpr int SMEM_LIMIT = 232448;                 // 227 KB
 constexpr int BARRIER_BYTES = 1024;
+constexpr int LUT_BYTES = 2048;  // uint8 weights: 256 dequantised tf32 hi values + 256 lo values
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // ~2 s at 1.9 GHz
 
-__host__ __device__ constexpr int stage_bytes(int block_n, bool split) {
-  return (A_STAGE_BYTES + block_n * BLOCK_K * 4) * (split ? 2 : 1);
+constexpr int WQ_SLOTS = 2;  // uint8 weights: ring of dequantised weight tiles
+__host__ __device__ constexpr int stage_bytes(int block_n, bool split, bool wq = false) {
+  // wq: a stage holds the A tile and the raw uint8 weight tile (block_n rows of 32 bytes); the
+  // dequantised tf32 tiles live in their own short ring, so that many small stages can be in
+  // flight while only WQ_SLOTS expanded tiles take up shared memory
+  return wq ? A_STAGE_BYTES * (split ? 2 : 1) + block_n * BLOCK_K
+            : (A_STAGE_BYTES + block_n * BLOCK_K * 4) * (split ? 2 : 1);
 }
-__host__ __device__ constexpr int num_stages(int block_n, bool split) {
-  int s = (SMEM_LIMIT - C_STAGING_BYTES - BIAS_STAGING_BYTES - BARRIER_BYTES - 1024) / stage_bytes(block_n, split);
+__host__ __device__ constexpr int wq_ring_bytes(int block_n, bool split, bool wq) {
+  return wq ? WQ_SLOTS * block_n * BLOCK_K * 4 * (split ? 2 : 1) + LUT_BYTES : 0;
+}
+__host__ __device__ constexpr int num_stages(int block_n, bool split, bool wq = false) {
+  int s = (SMEM_LIMIT - C_STAGING_BYTES - BIAS_STAGING_BYTES - BARRIER_BYTES - 1024 -
+           wq_ring_bytes(block_n, split, wq)) / stage_bytes(block_n, split, wq);
   return s > 8 ? 8 : s;
 }
 
@@ -226,6 +236,11 @@ struct GemmParams {
   int* status;
   EpilogueArgs epi;
   ConvGeom conv;  // AMODE != A_MATRIX only
+  double q_scale, q_min;  // WQ only: w = q * q_scale + q_min, evaluated in float64
+  // WQ, TF32: set when the host has checked, for all 256 byte values, that one float32 fma
+  // followed by the tf32 rounding gives the same bits as the float64 evaluation
+  float q_scale32, q_min32;
+  int q_arith;
 };
 
 // How the A operand reaches shared memory.
@@ -252,25 +267,42 @@ __device__ __forceinline__ uint32_t swz(int r, int o) {
   return (uint32_t)(r * 128 + ((((o >> 4) ^ (r & 7)) << 4) | (o & 15)));
 }
 
-template <int BLOCK_N, bool SPLIT, int AMODE>
-__global__ void __launch_bounds__((SPLIT || AMODE != A_MATRIX) ? 448 : 320, 1)
+// WQ: the weights arrive as raw uint8 affine-quantised bytes (K-major [N, Kq], map_w_hi is a
+// uint8 tensor map) and are dequantised in shared memory by the converter warps, k-block by
+// k-block, inside the main loop: w = float32(float64(q) * scale + min) (io_utils.ts:139), then
+// the tf32 hi (/lo) split straight into the swizzled operand tile the tensor core reads.
+template <int BLOCK_N, bool SPLIT, int AMODE, bool WQ>
+__global__ void __launch_bounds__((SPLIT || WQ || AMODE != A_MATRIX) ? 448 : 320, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_w_hi,
                     const __grid_constant__ CUtensorMap map_w_lo,
                     const __grid_constant__ CUtensorMap map_c, GemmParams p) {
-  constexpr int STAGES = num_stages(BLOCK_N, SPLIT);
+  static_assert(!WQ || AMODE == A_MATRIX, "in-loop dequantisation is implemented for the matrix mode");
+  constexpr int STAGES = num_stages(BLOCK_N, SPLIT, WQ);
   constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 4;
-  constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // two accumulators; a power of two >= 64
-  constexpr uint32_t TX_BYTES = (AMODE == A_MATRIX ? A_STAGE_BYTES : 0) + B_STAGE_BYTES * (SPLIT ? 2 : 1);
+  constexpr int Q_STAGE_BYTES = BLOCK_N * BLOCK_K;  // uint8 tile
+  // Two accumulator buffers (the epilogue drains one while the MMAs fill the other).  In 3xTF32
+  // each buffer is a pair: the hi*hi products accumulate in one tile and the small lo*hi + hi*lo
+  // correction terms in another, and the epilogue adds the two in float32.  The tensor core
+  // truncates when it aligns an addend to the running sum, so keeping the corrections out of the
+  // large sum removes two thirds of those truncations from it.
+  constexpr int ACC_COLS = SPLIT ? 2 * BLOCK_N : BLOCK_N;  // TMEM columns per buffer
+  constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;             // a power of two >= 64
+  static_assert(TMEM_COLS <= 512, "tensor memory has 512 columns");
+  constexpr uint32_t TX_BYTES = (AMODE == A_MATRIX ? A_STAGE_BYTES : 0) +
+                                (WQ ? Q_STAGE_BYTES : B_STAGE_BYTES * (SPLIT ? 2 : 1));
   static_assert(STAGES >= 2, "pipeline needs at least two stages");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* a_hi = smem;
   uint8_t* a_lo = a_hi + STAGES * A_STAGE_BYTES;  // SPLIT only
+  // tf32 weight tiles: one per stage, or (WQ) a ring of WQ_SLOTS tiles filled by the converters
+  constexpr int B_TILES = WQ ? WQ_SLOTS : STAGES;
   uint8_t* b_hi = a_hi + STAGES * A_STAGE_BYTES * (SPLIT ? 2 : 1);
-  uint8_t* b_lo = b_hi + STAGES * B_STAGE_BYTES;  // SPLIT only
-  uint8_t* c_stage = b_hi + STAGES * B_STAGE_BYTES * (SPLIT ? 2 : 1);
+  uint8_t* b_lo = b_hi + B_TILES * B_STAGE_BYTES;  // SPLIT only
+  uint8_t* b_q = b_hi + B_TILES * B_STAGE_BYTES * (SPLIT ? 2 : 1);  // WQ only: raw bytes per stage
+  uint8_t* c_stage = b_q + (WQ ? STAGES * Q_STAGE_BYTES : 0);
   uint8_t* bias_stage = c_stage + C_STAGING_BYTES;
   uint64_t* bars = (uint64_t*)(bias_stage + BIAS_STAGING_BYTES);
   uint64_t* full_bar = bars;                  // [STAGES] TMA -> consumers
@@ -278,8 +310,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   uint64_t* conv_bar = bars + 2 * STAGES;     // [STAGES] converters -> MMA (SPLIT)
   uint64_t* tmem_full_bar = bars + 3 * STAGES;   // [2] MMA -> epilogue
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;  // [2] epilogue -> MMA
-  uint32_t* tmem_ptr_holder = (uint32_t*)(tmem_empty_bar + 2);
+  uint64_t* slot_full_bar = tmem_empty_bar + 2;  // [WQ_SLOTS] converters -> MMA (WQ)
+  uint64_t* slot_empty_bar = slot_full_bar + WQ_SLOTS;  // [WQ_SLOTS] MMA -> converters (WQ)
+  uint32_t* tmem_ptr_holder = (uint32_t*)(slot_empty_bar + WQ_SLOTS);
   volatile int* abort_flag = (volatile int*)(tmem_ptr_holder + 1);
+  float* lut_hi = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + BARRIER_BYTES);  // WQ only
+  float* lut_lo = lut_hi + 256;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -291,6 +327,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(smem_u32(&full_bar[s]), AMODE == A_MATRIX ? 1 : 129);
       mbar_init(smem_u32(&empty_bar[s]), 1);
       mbar_init(smem_u32(&conv_bar[s]), 128);
+    }
+    for (int d = 0; d < WQ_SLOTS; d++) {
+      mbar_init(smem_u32(&slot_full_bar[d]), 128);
+      mbar_init(smem_u32(&slot_empty_bar[d]), 1);
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(smem_u32(&tmem_full_bar[a]), 1);
@@ -306,6 +346,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                  "r"(TMEM_COLS)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (WQ && threadIdx.x >= 320) {
+    // A byte has 256 values: dequantise each once per CTA, w = float32(float64(q)*scale + min)
+    // (io_utils.ts:139), and keep its tf32 hi / lo split; the main loop only looks bytes up.
+    for (int q = threadIdx.x - 320; q < 256; q += 128) {
+      const float w = (float)((double)q * p.q_scale + p.q_min);
+      const float h = round_tf32(w);
+      lut_hi[q] = h;
+      lut_lo[q] = (fabsf(h) <= 3.4028234e38f) ? round_tf32(w - h) : 0.f;
+    }
   }
   tcgen05_fence_before();
   __syncthreads();
@@ -328,9 +378,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           mbar_arrive_expect_tx(bar, TX_BYTES);
           if (AMODE == A_MATRIX)
             tma_load_2d(smem_u32(a_hi + stage * A_STAGE_BYTES), &map_a, bar, kb * BLOCK_K, m0);
-          tma_load_2d(smem_u32(b_hi + stage * B_STAGE_BYTES), &map_w_hi, bar, kb * BLOCK_K, n0);
-          if (SPLIT)
-            tma_load_2d(smem_u32(b_lo + stage * B_STAGE_BYTES), &map_w_lo, bar, kb * BLOCK_K, n0);
+          if (WQ) {
+            tma_load_2d(smem_u32(b_q + stage * Q_STAGE_BYTES), &map_w_hi, bar, kb * BLOCK_K, n0);
+          } else {
+            tma_load_2d(smem_u32(b_hi + stage * B_STAGE_BYTES), &map_w_hi, bar, kb * BLOCK_K, n0);
+            if (SPLIT)
+              tma_load_2d(smem_u32(b_lo + stage * B_STAGE_BYTES), &map_w_lo, bar, kb * BLOCK_K, n0);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -341,6 +395,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       constexpr uint32_t idesc = make_idesc(BLOCK_M, BLOCK_N);
       int stage = 0;
       uint32_t phase = 0;
+      int slot = 0;  // WQ: position in the ring of dequantised weight tiles
+      uint32_t slot_phase = 0;
       bool ok = true;
       int local = 0;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
@@ -349,31 +405,38 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status, 2);
         if (!ok) break;
         tcgen05_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
+        const uint32_t tmem_d = tmem_base + acc * ACC_COLS;
+        const uint32_t tmem_corr = tmem_d + BLOCK_N;  // 3xTF32 only
         for (int kb = 0; kb < p.num_k_blocks; kb++) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 3);
-          if (ok && SPLIT && AMODE == A_MATRIX)
+          if (ok && WQ)
+            ok = mbar_wait(smem_u32(&slot_full_bar[slot]), slot_phase, abort_flag, p.status, 4);
+          else if (ok && SPLIT && AMODE == A_MATRIX)
             ok = mbar_wait(smem_u32(&conv_bar[stage]), phase, abort_flag, p.status, 4);
           if (!ok) break;
           tcgen05_fence_after();
+          const int b_tile = WQ ? slot : stage;
           const uint32_t a_hi_s = smem_u32(a_hi + stage * A_STAGE_BYTES);
           const uint32_t a_lo_s = smem_u32(a_lo + stage * A_STAGE_BYTES);
-          const uint32_t b_hi_s = smem_u32(b_hi + stage * B_STAGE_BYTES);
-          const uint32_t b_lo_s = smem_u32(b_lo + stage * B_STAGE_BYTES);
+          const uint32_t b_hi_s = smem_u32(b_hi + b_tile * B_STAGE_BYTES);
+          const uint32_t b_lo_s = smem_u32(b_lo + b_tile * B_STAGE_BYTES);
 #pragma unroll
           for (int k = 0; k < BLOCK_K / 8; k++) {
             const uint32_t koff = k * 32;  // 8 tf32 = 32 bytes inside the 128-byte swizzle row
             const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
             if (SPLIT) {
-              // small terms first: lo*hi, hi*lo, then hi*hi
-              tcgen05_mma_tf32(tmem_d, make_smem_desc(a_lo_s + koff), make_smem_desc(b_hi_s + koff), idesc, accum);
-              tcgen05_mma_tf32(tmem_d, make_smem_desc(a_hi_s + koff), make_smem_desc(b_lo_s + koff), idesc, 1u);
-              tcgen05_mma_tf32(tmem_d, make_smem_desc(a_hi_s + koff), make_smem_desc(b_hi_s + koff), idesc, 1u);
+              tcgen05_mma_tf32(tmem_corr, make_smem_desc(a_lo_s + koff), make_smem_desc(b_hi_s + koff), idesc, accum);
+              tcgen05_mma_tf32(tmem_corr, make_smem_desc(a_hi_s + koff), make_smem_desc(b_lo_s + koff), idesc, 1u);
+              tcgen05_mma_tf32(tmem_d, make_smem_desc(a_hi_s + koff), make_smem_desc(b_hi_s + koff), idesc, accum);
             } else {
               tcgen05_mma_tf32(tmem_d, make_smem_desc(a_hi_s + koff), make_smem_desc(b_hi_s + koff), idesc, accum);
             }
           }
           tcgen05_commit(smem_u32(&empty_bar[stage]));  // frees the stage once the MMAs have read it
+          if (WQ) {
+            tcgen05_commit(smem_u32(&slot_empty_bar[slot]));
+            if (++slot == WQ_SLOTS) { slot = 0; slot_phase ^= 1; }
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (ok) tcgen05_commit(smem_u32(&tmem_full_bar[acc]));  // accumulator complete
@@ -478,33 +541,93 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         if (++hand_stage == STAGES) hand_stage = 0;
         --in_flight;
       }
-    } else if (SPLIT) {
-      // ---------------- 3xTF32 converters (SPLIT only) ----------------
+    } else if (SPLIT || WQ) {
+      // ---------------- converter warps (matrix mode) ----------------
+      // 3xTF32: split the A stage in place into tf32 hi / lo.  WQ: dequantise the uint8 weight
+      // tile of the stage into the swizzled tf32 hi (/lo) tile(s).
       const int t = threadIdx.x - 320;  // 0..127
       int stage = 0;
       uint32_t phase = 0;
+      int slot = 0;
+      uint32_t slot_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         for (int kb = 0; kb < p.num_k_blocks; kb++) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 5);
+          if (ok && WQ)
+            ok = mbar_wait(smem_u32(&slot_empty_bar[slot]), slot_phase ^ 1, abort_flag, p.status, 6);
           if (!ok) break;
-          float4* hi4 = reinterpret_cast<float4*>(a_hi + stage * A_STAGE_BYTES);
-          float4* lo4 = reinterpret_cast<float4*>(a_lo + stage * A_STAGE_BYTES);
+          if (SPLIT) {
+            float4* hi4 = reinterpret_cast<float4*>(a_hi + stage * A_STAGE_BYTES);
+            float4* lo4 = reinterpret_cast<float4*>(a_lo + stage * A_STAGE_BYTES);
 #pragma unroll
-          for (int i = 0; i < A_STAGE_BYTES / 16 / 128; i++) {
-            const int idx = t + i * 128;  // element-wise: the swizzled placement is preserved
-            float4 v = hi4[idx], h, l;
-            h.x = round_tf32(v.x); h.y = round_tf32(v.y); h.z = round_tf32(v.z); h.w = round_tf32(v.w);
-            // a non-finite hi keeps lo at zero (inf - inf would poison the product with NaN)
-            l.x = (fabsf(h.x) <= 3.4028234e38f) ? round_tf32(v.x - h.x) : 0.f;
-            l.y = (fabsf(h.y) <= 3.4028234e38f) ? round_tf32(v.y - h.y) : 0.f;
-            l.z = (fabsf(h.z) <= 3.4028234e38f) ? round_tf32(v.z - h.z) : 0.f;
-            l.w = (fabsf(h.w) <= 3.4028234e38f) ? round_tf32(v.w - h.w) : 0.f;
-            hi4[idx] = h;
-            lo4[idx] = l;
+            for (int i = 0; i < A_STAGE_BYTES / 16 / 128; i++) {
+              const int idx = t + i * 128;  // element-wise: the swizzled placement is preserved
+              float4 v = hi4[idx], h, l;
+              h.x = round_tf32(v.x); h.y = round_tf32(v.y); h.z = round_tf32(v.z); h.w = round_tf32(v.w);
+              // a non-finite hi keeps lo at zero (inf - inf would poison the product with NaN)
+              l.x = (fabsf(h.x) <= 3.4028234e38f) ? round_tf32(v.x - h.x) : 0.f;
+              l.y = (fabsf(h.y) <= 3.4028234e38f) ? round_tf32(v.y - h.y) : 0.f;
+              l.z = (fabsf(h.z) <= 3.4028234e38f) ? round_tf32(v.z - h.z) : 0.f;
+              l.w = (fabsf(h.w) <= 3.4028234e38f) ? round_tf32(v.w - h.w) : 0.f;
+              hi4[idx] = h;
+              lo4[idx] = l;
+            }
+          }
+          if (WQ) {
+            // the uint8 tile is [BLOCK_N rows][32 bytes]; a thread dequantises 16 bytes at a time
+            const uint8_t* q_tile = b_q + stage * Q_STAGE_BYTES;
+            uint8_t* w_hi = b_hi + slot * B_STAGE_BYTES;
+            uint8_t* w_lo = b_lo + slot * B_STAGE_BYTES;
+            if (!SPLIT && p.q_arith) {
+              // arithmetic form: byte -> float through the 2^23 mantissa trick, one fma, then
+              // round-to-nearest (ties away) to tf32 on the bit pattern
+              const float s32 = p.q_scale32, m32 = p.q_min32;
+              for (int c = t; c < BLOCK_N * 2; c += 128) {
+                const int n = c >> 1, half = c & 1;
+                const uint4 raw = *reinterpret_cast<const uint4*>(q_tile + n * 32 + half * 16);
+                const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                  uint32_t h[4];
+#pragma unroll
+                  for (int e = 0; e < 4; e++) {
+                    const float qf = __uint_as_float(__byte_perm(words[j], 0x4B000000u, 0x7540u + e)) - 8388608.f;
+                    // the tensor core reads the upper 19 bits only, so adding half a tf32 ulp
+                    // to the bit pattern is the round-to-nearest (ties away)
+                    h[e] = __float_as_uint(fmaf(qf, s32, m32)) + 0x1000u;
+                  }
+                  *reinterpret_cast<uint4*>(w_hi + swz(n, (half * 16 + j * 4) * 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                }
+              }
+            } else {
+              for (int c = t; c < BLOCK_N * 2; c += 128) {
+                const int n = c >> 1, half = c & 1;
+                const uint4 raw = *reinterpret_cast<const uint4*>(q_tile + n * 32 + half * 16);
+                const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                  float h[4], l[4];
+#pragma unroll
+                  for (int e = 0; e < 4; e++) {
+                    const uint32_t q = (words[j] >> (8 * e)) & 0xffu;
+                    h[e] = lut_hi[q];
+                    if (SPLIT) l[e] = lut_lo[q];
+                  }
+                  const uint32_t off = swz(n, (half * 16 + j * 4) * 4);
+                  *reinterpret_cast<float4*>(w_hi + off) = make_float4(h[0], h[1], h[2], h[3]);
+                  if (SPLIT) *reinterpret_cast<float4*>(w_lo + off) = make_float4(l[0], l[1], l[2], l[3]);
+                }
+              }
+            }
           }
           fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
-          mbar_arrive(smem_u32(&conv_bar[stage]));
+          if (WQ) {
+            mbar_arrive(smem_u32(&slot_full_bar[slot]));
+            if (++slot == WQ_SLOTS) { slot = 0; slot_phase ^= 1; }
+          } else {
+            mbar_arrive(smem_u32(&conv_bar[stage]));
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -546,7 +669,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         if (!ok) break;
         tcgen05_fence_after();
         // TMEM address: lane in bits [16,32), column in [0,16)
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BLOCK_N;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * ACC_COLS;
         bool released = false;
 #pragma unroll
         for (int i = 0; i < MY_CHUNKS; i++) {
@@ -559,6 +682,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           bias_s[lane] = bias_l[i];
           if (has_alpha) alpha_s[lane] = alpha_l[i];
           tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int k = 0; k < 32; k++) v[k] = __uint_as_float(r[k]);
+          if (SPLIT) {
+            // add the correction tile (lo*hi + hi*lo) to the hi*hi tile
+            tmem_ld_32x32b_x32(taddr + BLOCK_N + chunk * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int k = 0; k < 32; k++) v[k] += __uint_as_float(r[k]);
+          }
           __syncwarp();
           if (i == MY_CHUNKS - 1) {
             // this warp's last read of the accumulator: hand it back to the MMA warp right away
@@ -566,9 +699,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
             released = true;
           }
-          float v[32];
-#pragma unroll
-          for (int k = 0; k < 32; k++) v[k] = __uint_as_float(r[k]);
           switch (p.epi.activation) {
             case TFJS_ACT_RELU: finish_chunk<TFJS_ACT_RELU>(v, has_bias, bias_s, alpha_s, p.epi); break;
             case TFJS_ACT_PRELU: finish_chunk<TFJS_ACT_PRELU>(v, has_bias, bias_s, alpha_s, p.epi); break;
@@ -648,13 +778,13 @@ bool encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BLOCK_N, bool SPLIT, int AMODE>
+template <int BLOCK_N, bool SPLIT, int AMODE, bool WQ = false>
 int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mh, const CUtensorMap& ml,
                    const CUtensorMap& mc, const GemmParams& p) {
-  constexpr int smem_bytes = num_stages(BLOCK_N, SPLIT) * stage_bytes(BLOCK_N, SPLIT) + C_STAGING_BYTES + BIAS_STAGING_BYTES +
-                             BARRIER_BYTES + 1024;
+  constexpr int smem_bytes = wq_ring_bytes(BLOCK_N, SPLIT, WQ) + num_stages(BLOCK_N, SPLIT, WQ) * stage_bytes(BLOCK_N, SPLIT, WQ) + C_STAGING_BYTES +
+                             BIAS_STAGING_BYTES + BARRIER_BYTES + 1024;
   static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
-  auto kernel = gemm_tcgen05_kernel<BLOCK_N, SPLIT, AMODE>;
+  auto kernel = gemm_tcgen05_kernel<BLOCK_N, SPLIT, AMODE, WQ>;
   static bool configured[64] = {false};  // the attribute is per device
   if (!configured[ctx->device & 63]) {
     TFJS_CHECK_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
@@ -662,7 +792,8 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtensorMap&
   }
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-  kernel<<<grid, (SPLIT || AMODE != A_MATRIX) ? 448 : 320, smem_bytes, ctx->stream>>>(ma, mh, ml, mc, p);
+  kernel<<<grid, (SPLIT || WQ || AMODE != A_MATRIX) ? 448 : 320, smem_bytes, ctx->stream>>>(ma, mh, ml, mc, p);
+  if (WQ) return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32, uint8 weights)" : "gemm_tcgen05 (TF32, uint8 weights)");
   if (AMODE == A_MATRIX) return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32)" : "gemm_tcgen05 (TF32)");
   return post_launch(ctx, SPLIT ? "conv2d_tcgen05 (3xTF32)" : "conv2d_tcgen05 (TF32)");
 }
@@ -678,13 +809,54 @@ int launch_mode(tfjs_cuda_ctx* ctx, int block_n, bool split, const CUtensorMap& 
   }
 }
 
+int launch_quantized(tfjs_cuda_ctx* ctx, int block_n, bool split, const CUtensorMap& ma, const CUtensorMap& mq,
+                     const CUtensorMap& mc, const GemmParams& p) {
+  switch (block_n) {
+    case 32: return split ? launch_variant<32, true, A_MATRIX, true>(ctx, ma, mq, mq, mc, p) : launch_variant<32, false, A_MATRIX, true>(ctx, ma, mq, mq, mc, p);
+    case 64: return split ? launch_variant<64, true, A_MATRIX, true>(ctx, ma, mq, mq, mc, p) : launch_variant<64, false, A_MATRIX, true>(ctx, ma, mq, mq, mc, p);
+    case 128: return split ? launch_variant<128, true, A_MATRIX, true>(ctx, ma, mq, mq, mc, p) : launch_variant<128, false, A_MATRIX, true>(ctx, ma, mq, mq, mc, p);
+    default: return launch_variant<256, false, A_MATRIX, true>(ctx, ma, mq, mq, mc, p);
+  }
+}
+
+// True when, for every byte value q, tf32(fma(float(q), float(scale), float(min))) has the same
+// bits as tf32(float32(double(q) * scale + min)): the kernel may then dequantise with float32
+// arithmetic and still feed the tensor core exactly what the float64 formula would.
+bool dequant_exact_in_float32(double scale, double min) {
+  const float s32 = (float)scale, m32 = (float)min;
+  for (int q = 0; q < 256; q++) {
+    const float want = (float)((double)q * scale + min);
+    const float got = fmaf((float)q, s32, m32);
+    uint32_t wb, gb;
+    memcpy(&wb, &want, 4);
+    memcpy(&gb, &got, 4);
+    if ((wb & 0x7f800000u) == 0x7f800000u || (gb & 0x7f800000u) == 0x7f800000u) return false;
+    if (((wb + 0x1000u) & 0xffffe000u) != ((gb + 0x1000u) & 0xffffe000u)) return false;
+  }
+  return true;
+}
+
+// uint8 K-major [rows, cols] matrix, box [box_rows, 32 bytes], no swizzle.
+bool encode_2d_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols};
+  cuuint32_t box[2] = {BLOCK_K, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // Shared by the matrix and the convolution entry points.  `a` is the dense A matrix
 // (A_MATRIX) or null; K is the contraction length as laid out in the packed weights.
 int launch_common(tfjs_cuda_ctx* ctx, int amode, const float* a, const ConvGeom* conv, int64_t M, int64_t K,
                   const float* w_hi, const float* w_lo, int64_t kp, float* out, int64_t N,
-                  const EpilogueArgs& epi, int math_mode) {
+                  const EpilogueArgs& epi, int math_mode, const uint8_t* w_q = nullptr, double q_scale = 0.0,
+                  double q_min = 0.0) {
   const bool split = math_mode == TFJS_MATH_TF32X3;
-  TFJS_REQUIRE(ctx, !split || w_lo != nullptr, "3xTF32 needs the residual weight plane");
+  TFJS_REQUIRE(ctx, w_q != nullptr || !split || w_lo != nullptr, "3xTF32 needs the residual weight plane");
   int block_n;
   if (N <= 32) block_n = 32;
   else if (N <= 64) block_n = 64;
@@ -696,9 +868,14 @@ int launch_common(tfjs_cuda_ctx* ctx, int amode, const float* a, const ConvGeom*
     block_n /= 2;
 
   CUtensorMap ma, mh, ml, mc;
-  bool ok = encode_2d(&mh, w_hi, (uint64_t)N, (uint64_t)kp, (uint32_t)block_n, BLOCK_K) &&
-            encode_2d(&ml, split ? w_lo : w_hi, (uint64_t)N, (uint64_t)kp, (uint32_t)block_n, BLOCK_K) &&
-            encode_2d(&mc, out, (uint64_t)M, (uint64_t)N, 32, 32);
+  bool ok = encode_2d(&mc, out, (uint64_t)M, (uint64_t)N, 32, 32);
+  if (w_q) {
+    ok = ok && encode_2d_u8(&mh, w_q, (uint64_t)N, (uint64_t)kp, (uint32_t)block_n);
+    ml = mh;
+  } else {
+    ok = ok && encode_2d(&mh, w_hi, (uint64_t)N, (uint64_t)kp, (uint32_t)block_n, BLOCK_K) &&
+         encode_2d(&ml, split ? w_lo : w_hi, (uint64_t)N, (uint64_t)kp, (uint32_t)block_n, BLOCK_K);
+  }
   if (ok && amode == A_MATRIX) ok = encode_2d(&ma, a, (uint64_t)M, (uint64_t)K, BLOCK_M, BLOCK_K);
   else ma = mh;  // unused by the conv modes
   if (!ok) return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
@@ -714,6 +891,12 @@ int launch_common(tfjs_cuda_ctx* ctx, int amode, const float* a, const ConvGeom*
   p.epi = epi;
   if (conv) p.conv = *conv;
   else memset(&p.conv, 0, sizeof(p.conv));
+  p.q_scale = q_scale;
+  p.q_min = q_min;
+  p.q_scale32 = (float)q_scale;
+  p.q_min32 = (float)q_min;
+  p.q_arith = (w_q && !split && dequant_exact_in_float32(q_scale, q_min)) ? 1 : 0;
+  if (w_q) return launch_quantized(ctx, block_n, split, ma, mh, mc, p);
   switch (amode) {
     case A_CONV_VEC: return launch_mode<A_CONV_VEC>(ctx, block_n, split, ma, mh, ml, mc, p);
     case A_CONV_RGB: return launch_mode<A_CONV_RGB>(ctx, block_n, split, ma, mh, ml, mc, p);
@@ -733,6 +916,15 @@ int launch_gemm_tcgen05(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K
                         const float* w_lo, int64_t kp, float* out, int64_t N, const EpilogueArgs& epi,
                         int math_mode) {
   return launch_common(ctx, A_MATRIX, a, nullptr, M, K, w_hi, w_lo, kp, out, N, epi, math_mode);
+}
+
+// Matrix-mode GEMM whose weights are raw uint8 bytes, K-major [N, kq] (kq a multiple of 16),
+// dequantised inside the main loop.
+int launch_gemm_tcgen05_u8(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, const uint8_t* w_q,
+                           int64_t kq, double scale, double min, float* out, int64_t N,
+                           const EpilogueArgs& epi, int math_mode) {
+  return launch_common(ctx, A_MATRIX, a, nullptr, M, K, nullptr, nullptr, kq, out, N, epi, math_mode, w_q,
+                       scale, min);
 }
 
 // Which implicit-GEMM gather, if any, can take this convolution (0 = none).
