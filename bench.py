@@ -42,6 +42,9 @@ def parse_args():
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--workload", default="cfg5", choices=["cfg5", "cfg4"])
     ap.add_argument("--math", default="tf32", choices=["tf32", "3xtf32"])
+    ap.add_argument("--dequant", default="cached", choices=["cached", "in-loop"],
+                    help="uint8 weights of the GEMM layers: expanded once into cached tf32 planes, or "
+                         "kept uint8 and dequantised in shared memory inside the GEMM main loop")
     ap.add_argument("--global-batch", type=int, default=0, help="override the workload's batch")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -220,6 +223,7 @@ def run_cuda(args):
     bk = BackendCuda(d.local_rank, args.math)
     ENGINE.registerBackend("bench-cuda", lambda: bk, 10)
     assert ENGINE.setBackend("bench-cuda")
+    bk.setOption("dequant_in_gemm", 1 if args.dequant == "in-loop" else 0)
 
     params = mobilenet.make_weights(cfg["seed"], quantized=cfg["quantized"], gain=cfg["gain"])
     net = mobilenet.MobileNetV1(params, bk)
@@ -392,7 +396,7 @@ def run_cuda(args):
             "scaling": cfg["scaling"], "vs_baseline": None, "dtype": "tf32" if args.math == "tf32" else "3xtf32",
             "data": "synthetic",
             "config": {"workload": cfg["name"], "global_batch": cfg["global_batch"], "per_gpu_batch": per,
-                       "math_mode": args.math, "launch": "eager" if graph is None else "cuda-graph replay",
+                       "math_mode": args.math, "dequant": args.dequant, "launch": "eager" if graph is None else "cuda-graph replay",
                        "l2": "every step streams %.1f GB of activations per GPU (> 126 MB L2) between reuses"
                              % (step_bytes / 1e9)},
             "roofline": roofline, "net_hbm": {"algorithmic_gb_per_step": step_bytes / 1e9,

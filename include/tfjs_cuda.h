@@ -106,7 +106,10 @@ int tfjs_cuda_ctx_create(int device_ordinal, tfjs_cuda_ctx** out);
 int tfjs_cuda_ctx_destroy(tfjs_cuda_ctx* ctx);
 const char* tfjs_cuda_last_error(const tfjs_cuda_ctx* ctx);
 /* Flags mirrored from ENV.registerFlag (environment.ts:32-142).  Keys: "math_mode"
- * (tfjs_math_mode), "use_tensor_cores" (0 forces the CUDA-core kernels), "debug_sync". */
+ * (tfjs_math_mode), "use_tensor_cores" (0 forces the CUDA-core kernels), "debug_sync",
+ * "dequant_in_gemm" (quantised matMul / 1x1 conv2d weights: 0, the default, expands them once
+ * into cached tf32 planes; 1 keeps them uint8 in device memory and dequantises each tile in
+ * shared memory inside the GEMM main loop; the results are bit-identical). */
 int tfjs_cuda_ctx_set_option(tfjs_cuda_ctx* ctx, const char* key, double value);
 /* Blocks until all enqueued work is done; TFJS_CUDA_ERR_TIMEOUT after timeout_ms (<0: none). */
 int tfjs_cuda_ctx_sync(tfjs_cuda_ctx* ctx, int timeout_ms);

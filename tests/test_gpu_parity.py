@@ -341,6 +341,7 @@ def test_quantized_matmul_dequantised_in_the_main_loop(tf, math, m, k, n, transp
     rng = _rng(1000 + m + k + n)
     bk = tf.ENGINE.backend
     bk.setMathMode(math)
+    bk.setOption("dequant_in_gemm", 1)
     try:
         a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
         q = rng.integers(0, 256, (n, k) if transpose_b else (k, n), dtype=np.uint8)
@@ -354,7 +355,13 @@ def test_quantized_matmul_dequantised_in_the_main_loop(tf, math, m, k, n, transp
         assert np.array_equal(got_q, got_f)
         want = oracle.fused_matmul(a[None], w[None], False, transpose_b, bias=bias, activation="relu")[0]
         assert rel_err(got_q, want) <= (1e-3 if math == "tf32" else 1e-5)
+        # the same call with the option off takes the cached float planes: identical bits again
+        bk.setOption("dequant_in_gemm", 0)
+        got_c = tf.ops.fused_matmul(tf.ops.tensor(a), wq, False, transpose_b, bias=tf.ops.tensor(bias),
+                                    activation="relu").dataSync().reshape(m, n)
+        assert np.array_equal(got_c, got_q)
     finally:
+        bk.setOption("dequant_in_gemm", 0)
         bk.setMathMode("3xtf32")
 
 
@@ -385,7 +392,7 @@ def test_mobilenet_end_to_end_float_weights(tf):
         net.dispose()
 
 
-@pytest.mark.parametrize("quantized", [False, True])
+@pytest.mark.parametrize("quantized", [False, True, "in-loop"])
 def test_mobilenet_every_layer_against_the_oracle(tf, quantized):
     """Each of the 28 weighted layers is run on the device with the ORACLE's activations as
     input and compared with the oracle's output of that layer.  (With the uint8 weights of
@@ -395,10 +402,12 @@ def test_mobilenet_every_layer_against_the_oracle(tf, quantized):
     from oracle import mobilenet as oracle_net
     from tfjs_core_b200 import conv_util, mobilenet
     bk = tf.ENGINE.backend
-    params = mobilenet.make_weights(4 if quantized else 3, quantized=quantized, gain=1.5)
+    params = mobilenet.make_weights(4 if quantized else 3, quantized=bool(quantized), gain=1.5)
     x = mobilenet.make_input(3, 2)
     _, _, inter = oracle_net.forward(x, params, return_intermediates=True)
     net = mobilenet.MobileNetV1(params, bk)
+    # "in-loop": the pointwise layers keep their weights uint8 and dequantise inside the GEMM
+    bk.setOption("dequant_in_gemm", 1 if quantized == "in-loop" else 0)
     try:
         prev = x
         for name, kind, shape, stride in mobilenet.layer_specs():
@@ -429,6 +438,7 @@ def test_mobilenet_every_layer_against_the_oracle(tf, quantized):
             out.dispose()
             prev = want
     finally:
+        bk.setOption("dequant_in_gemm", 0)
         net.dispose()
 
 

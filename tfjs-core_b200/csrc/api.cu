@@ -92,7 +92,7 @@ int gemm_dispatch(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, Tens
                   int64_t w_offset, bool source_is_nk, bool cacheable, float* out, int64_t N,
                   const EpilogueArgs& epi) {
   if (ctx->use_tensor_cores && tcgen05_gemm_supported(M, N, K)) {
-    if (w->quant.quantized && cacheable && w_offset == 0) {
+    if (ctx->dequant_in_gemm && w->quant.quantized && cacheable && w_offset == 0) {
       // Quantised weights stay uint8 in HBM: a K-major byte copy is cached once and the kernel
       // dequantises each tile in shared memory.
       const int64_t kq = (K + 15) / 16 * 16;

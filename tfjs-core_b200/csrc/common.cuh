@@ -90,6 +90,9 @@ struct tfjs_cuda_ctx {
   int math_mode = TFJS_MATH_TF32X3;
   bool use_tensor_cores = true;
   bool debug_sync = false;
+  // Quantised matmul / 1x1-conv weights: false expands them once into cached tf32 planes, true
+  // keeps them uint8 and dequantises every tile in shared memory inside the GEMM main loop.
+  bool dequant_in_gemm = false;
   // bookkeeping
   int64_t launch_count = 0;
   cudaEvent_t time_start = nullptr, time_stop = nullptr;

@@ -262,6 +262,26 @@ __device__ __forceinline__ void cp_async_4_zfill(uint32_t dst, const void* src, 
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(valid ? 4 : 0)
                : "memory");
 }
+// Packed pairs of float32 (sm_100 f32x2 arithmetic): one instruction per two elements.
+__device__ __forceinline__ uint64_t pack_f32x2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, uint32_t& lo, uint32_t& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
 // Byte offset `o` (multiple of 4) of row `r` in a SWIZZLE_128B K-major tile.
 __device__ __forceinline__ uint32_t swz(int r, int o) {
   return (uint32_t)(r * 128 + ((((o >> 4) ^ (r & 7)) << 4) | (o & 15)));
@@ -271,14 +291,21 @@ __device__ __forceinline__ uint32_t swz(int r, int o) {
 // uint8 tensor map) and are dequantised in shared memory by the converter warps, k-block by
 // k-block, inside the main loop: w = float32(float64(q) * scale + min) (io_utils.ts:139), then
 // the tf32 hi (/lo) split straight into the swizzled operand tile the tensor core reads.
+// Threads per CTA: 10 warps, plus 4 converter / gather warps, or 8 converter warps when the
+// weights are dequantised in the loop.
+__host__ __device__ constexpr int cta_threads(bool split, int amode, bool wq) {
+  return wq ? 576 : ((split || amode != A_MATRIX) ? 448 : 320);
+}
+
 template <int BLOCK_N, bool SPLIT, int AMODE, bool WQ>
-__global__ void __launch_bounds__((SPLIT || WQ || AMODE != A_MATRIX) ? 448 : 320, 1)
+__global__ void __launch_bounds__(cta_threads(SPLIT, AMODE, WQ), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_w_hi,
                     const __grid_constant__ CUtensorMap map_w_lo,
                     const __grid_constant__ CUtensorMap map_c, GemmParams p) {
   static_assert(!WQ || AMODE == A_MATRIX, "in-loop dequantisation is implemented for the matrix mode");
   constexpr int STAGES = num_stages(BLOCK_N, SPLIT, WQ);
+  constexpr int NCONV = cta_threads(SPLIT, AMODE, WQ) - 320;  // converter (or gather) threads
   constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 4;
   constexpr int Q_STAGE_BYTES = BLOCK_N * BLOCK_K;  // uint8 tile
   // Two accumulator buffers (the epilogue drains one while the MMAs fill the other).  In 3xTF32
@@ -294,7 +321,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   static_assert(STAGES >= 2, "pipeline needs at least two stages");
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // 1024-byte alignment by an offset on the __shared__ array itself: the pointers derived from
+  // it stay in the shared address space (an integer round trip would make every access generic)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* a_hi = smem;
   uint8_t* a_lo = a_hi + STAGES * A_STAGE_BYTES;  // SPLIT only
   // tf32 weight tiles: one per stage, or (WQ) a ring of WQ_SLOTS tiles filled by the converters
@@ -329,7 +358,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(smem_u32(&conv_bar[s]), 128);
     }
     for (int d = 0; d < WQ_SLOTS; d++) {
-      mbar_init(smem_u32(&slot_full_bar[d]), 128);
+      mbar_init(smem_u32(&slot_full_bar[d]), NCONV);
       mbar_init(smem_u32(&slot_empty_bar[d]), 1);
     }
     for (int a = 0; a < 2; a++) {
@@ -350,7 +379,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   if (WQ && threadIdx.x >= 320) {
     // A byte has 256 values: dequantise each once per CTA, w = float32(float64(q)*scale + min)
     // (io_utils.ts:139), and keep its tf32 hi / lo split; the main loop only looks bytes up.
-    for (int q = threadIdx.x - 320; q < 256; q += 128) {
+    for (int q = threadIdx.x - 320; q < 256; q += NCONV) {
       const float w = (float)((double)q * p.q_scale + p.q_min);
       const float h = round_tf32(w);
       lut_hi[q] = h;
@@ -561,8 +590,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             float4* hi4 = reinterpret_cast<float4*>(a_hi + stage * A_STAGE_BYTES);
             float4* lo4 = reinterpret_cast<float4*>(a_lo + stage * A_STAGE_BYTES);
 #pragma unroll
-            for (int i = 0; i < A_STAGE_BYTES / 16 / 128; i++) {
-              const int idx = t + i * 128;  // element-wise: the swizzled placement is preserved
+            for (int i = 0; i < A_STAGE_BYTES / 16 / NCONV; i++) {
+              const int idx = t + i * NCONV;  // element-wise: the swizzled placement is preserved
               float4 v = hi4[idx], h, l;
               h.x = round_tf32(v.x); h.y = round_tf32(v.y); h.z = round_tf32(v.z); h.w = round_tf32(v.w);
               // a non-finite hi keeps lo at zero (inf - inf would poison the product with NaN)
@@ -582,8 +611,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             if (!SPLIT && p.q_arith) {
               // arithmetic form: byte -> float through the 2^23 mantissa trick, one fma, then
               // round-to-nearest (ties away) to tf32 on the bit pattern
-              const float s32 = p.q_scale32, m32 = p.q_min32;
-              for (int c = t; c < BLOCK_N * 2; c += 128) {
+              const uint32_t s32 = __float_as_uint(p.q_scale32), m32 = __float_as_uint(p.q_min32);
+              const uint64_t s2 = pack_f32x2(s32, s32), m2 = pack_f32x2(m32, m32);
+              const uint64_t neg_magic2 = pack_f32x2(0xCB000000u, 0xCB000000u);  // -2^23 twice
+              for (int c = t; c < BLOCK_N * 2; c += NCONV) {
                 const int n = c >> 1, half = c & 1;
                 const uint4 raw = *reinterpret_cast<const uint4*>(q_tile + n * 32 + half * 16);
                 const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -591,17 +622,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 for (int j = 0; j < 4; j++) {
                   uint32_t h[4];
 #pragma unroll
-                  for (int e = 0; e < 4; e++) {
-                    const float qf = __uint_as_float(__byte_perm(words[j], 0x4B000000u, 0x7540u + e)) - 8388608.f;
+                  for (int e = 0; e < 4; e += 2) {
+                    // 0x4B0000qq is the float 2^23 + q: subtracting 2^23 leaves q exactly
+                    const uint64_t r2 = pack_f32x2(__byte_perm(words[j], 0x4B000000u, 0x7540u + e),
+                                                   __byte_perm(words[j], 0x4B000000u, 0x7541u + e));
+                    unpack_f32x2(fma_f32x2(add_f32x2(r2, neg_magic2), s2, m2), h[e], h[e + 1]);
                     // the tensor core reads the upper 19 bits only, so adding half a tf32 ulp
                     // to the bit pattern is the round-to-nearest (ties away)
-                    h[e] = __float_as_uint(fmaf(qf, s32, m32)) + 0x1000u;
+                    h[e] += 0x1000u;
+                    h[e + 1] += 0x1000u;
                   }
                   *reinterpret_cast<uint4*>(w_hi + swz(n, (half * 16 + j * 4) * 4)) = make_uint4(h[0], h[1], h[2], h[3]);
                 }
               }
             } else {
-              for (int c = t; c < BLOCK_N * 2; c += 128) {
+              for (int c = t; c < BLOCK_N * 2; c += NCONV) {
                 const int n = c >> 1, half = c & 1;
                 const uint4 raw = *reinterpret_cast<const uint4*>(q_tile + n * 32 + half * 16);
                 const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -792,7 +827,7 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtensorMap&
   }
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-  kernel<<<grid, (SPLIT || WQ || AMODE != A_MATRIX) ? 448 : 320, smem_bytes, ctx->stream>>>(ma, mh, ml, mc, p);
+  kernel<<<grid, cta_threads(SPLIT, AMODE, WQ), smem_bytes, ctx->stream>>>(ma, mh, ml, mc, p);
   if (WQ) return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32, uint8 weights)" : "gemm_tcgen05 (TF32, uint8 weights)");
   if (AMODE == A_MATRIX) return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32)" : "gemm_tcgen05 (TF32)");
   return post_launch(ctx, SPLIT ? "conv2d_tcgen05 (3xTF32)" : "conv2d_tcgen05 (TF32)");

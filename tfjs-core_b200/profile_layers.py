@@ -1,11 +1,11 @@
 #!/usr/bin/env python3
 """Per-layer device times of one fused MobileNetV1 forward on the cuda backend.
 
-    python tfjs-core_b200/profile_layers.py [batch] [tf32|3xtf32] [q]
+    python tfjs-core_b200/profile_layers.py [batch] [tf32|3xtf32] [q|q-in-loop]
 
 Prints, for each of the 30 launches, the kernel name, the best device time over a few passes
 (events recorded between launches on the context's stream), the layer's algorithmic bytes and
-the bandwidth that corresponds to.  `q` stores the filters as uint8 (BASELINE config 5).  This is
+the bandwidth that corresponds to.  `q` stores the filters as uint8 (BASELINE config 5); `q-in-loop` also keeps the GEMM weights uint8 and dequantises them inside the GEMM main loop.  This is
 also the small-case command the ncu captures summarised under profiles/ were taken with.
 """
 import os
@@ -20,11 +20,13 @@ from tfjs_core_b200 import mobilenet, ops  # noqa: E402
 def main():
     batch = int(sys.argv[1]) if len(sys.argv) > 1 else 64
     mode = sys.argv[2] if len(sys.argv) > 2 else "tf32"
-    quantized = len(sys.argv) > 3 and sys.argv[3] == "q"
+    quantized = len(sys.argv) > 3 and sys.argv[3] in ("q", "q-in-loop")
+    in_loop = len(sys.argv) > 3 and sys.argv[3] == "q-in-loop"
     reps = 4
     bk = tf.BackendCuda(0, mode)
     tf.ENGINE.registerBackend("profile-cuda", lambda: bk, 10)
     tf.ENGINE.setBackend("profile-cuda")
+    bk.setOption("dequant_in_gemm", 1 if in_loop else 0)
     params = mobilenet.make_weights(4 if quantized else 3, quantized=quantized, gain=1.5)
     net = mobilenet.MobileNetV1(params, bk)
     x = ops.tensor(mobilenet.make_input(3, batch))
