@@ -6,7 +6,7 @@ tfjs backend does (tf.registerBackend(name, factory, priority), tfjs-core/src/gl
 device context lazily, so importing works on a machine without a GPU; using the backend
 there fails loudly (there is no CPU fallback inside it).
 """
-from . import _ffi, conv_util, ops  # noqa: F401
+from . import _ffi, conv_util, ops, weights_loader  # noqa: F401
 from .backend_cuda import BackendCuda, CudaError  # noqa: F401
 from .engine import ENGINE, Tensor  # noqa: F401
 

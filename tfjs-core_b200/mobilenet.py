@@ -60,6 +60,38 @@ def make_weights(seed, quantized=False, gain=1.0):
     return params
 
 
+def write_manifest(params, directory, shard_bytes=1 << 20):
+    """Saves `params` (the dict make_weights returns) as a tfjs weights manifest: one group,
+    entries `<layer>/filter` (uint8-quantised with the layer's scale / min when the layer has
+    `q`, else float32) and `<layer>/bias`, the concatenated bytes cut into shard files of
+    `shard_bytes`.  Returns the manifest (also written to weights_manifest.json)."""
+    import json
+    import os
+    entries, chunks = [], []
+    for name, _, _, _ in layer_specs():
+        p = params[name]
+        if p["q"] is not None:
+            entries.append({"name": f"{name}/filter", "dtype": "float32", "shape": list(p["q"].shape),
+                            "quantization": {"min": p["min"], "scale": p["scale"], "dtype": "uint8"}})
+            chunks.append(p["q"].tobytes())
+        else:
+            entries.append({"name": f"{name}/filter", "dtype": "float32", "shape": list(p["w"].shape)})
+            chunks.append(np.ascontiguousarray(p["w"], "<f4").tobytes())
+        entries.append({"name": f"{name}/bias", "dtype": "float32", "shape": list(p["b"].shape)})
+        chunks.append(np.ascontiguousarray(p["b"], "<f4").tobytes())
+    blob = b"".join(chunks)
+    paths = []
+    for i in range(0, len(blob), shard_bytes):
+        path = f"group1-shard{i // shard_bytes + 1}of{-(-len(blob) // shard_bytes)}"
+        with open(os.path.join(directory, path), "wb") as f:
+            f.write(blob[i:i + shard_bytes])
+        paths.append(path)
+    manifest = [{"paths": paths, "weights": entries}]
+    with open(os.path.join(directory, "weights_manifest.json"), "w") as f:
+        json.dump(manifest, f)
+    return manifest
+
+
 def make_input(seed, batch, offset=0):
     """Images ~U(-1, 1), NHWC float32.  `offset` skips that many images of the stream so that
     shards of one global batch draw disjoint slices of the same sequence."""
@@ -81,6 +113,16 @@ class MobileNetV1:
             else:
                 w = ops.tensor(p["w"])
             self.params[name] = (w, ops.tensor(p["b"]))
+
+    @classmethod
+    def from_named_tensors(cls, named, backend=None):
+        """The network over tensors that already live on the backend, as tf.io.loadWeights
+        returns them: `named["<layer>/filter"]` and `named["<layer>/bias"]` for every layer of
+        layer_specs()."""
+        net = cls({}, backend)
+        for name, _, _, _ in layer_specs():
+            net.params[name] = (named[f"{name}/filter"], named[f"{name}/bias"])
+        return net
 
     def dispose(self):
         for w, b in self.params.values():
