@@ -188,6 +188,18 @@ int tfjs_cuda_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id filter
 int tfjs_cuda_depthwise_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id filter,
                                tfjs_tensor_id out, const tfjs_conv2d_info* info,
                                const tfjs_epilogue* epi);
+/* Extension: the op pair of tf.separableConv2d (ops/conv.ts:574-654) with an epilogue after each
+ * half: out = pw_epi(conv2d_1x1(dw_epi(depthwiseConv2D(x, dw_filter)), pw_filter)).  `dw_info` is
+ * the depthwise Conv2DInfo; pw_filter is [1, 1, dw_info->outChannels, out_channels]; out is
+ * [batch, outHeight, outWidth, out_channels].  3x3 filters with stride 1 or 2, a channel count
+ * that is a multiple of 32 up to 256 and up to 256 output channels run, in TF32 mode, as one
+ * kernel that keeps the depthwise result in shared memory; other shapes run the two kernels back
+ * to back.  Results are bit-identical to the two separate calls.  Option "fuse_separable" = 0
+ * forces the two-kernel form. */
+int tfjs_cuda_separable_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id dw_filter,
+                               tfjs_tensor_id pw_filter, tfjs_tensor_id out,
+                               const tfjs_conv2d_info* dw_info, int32_t out_channels,
+                               const tfjs_epilogue* dw_epi, const tfjs_epilogue* pw_epi);
 /* KernelBackend.avgPool / maxPool (backend.ts:453-462; CPU :2273-2343, 2869-2873). */
 int tfjs_cuda_pool2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id out,
                      const tfjs_conv2d_info* info, int is_avg);

@@ -1,0 +1,167 @@
+"""fusedSeparableConv2d: depthwise 3x3 (+bias, activation) fused into the pointwise GEMM.
+
+The fused kernel performs the arithmetic of the two separate kernels operation for operation,
+so in TF32 mode its output must equal theirs bit for bit; against the CPU oracle it is held to
+the contraction tolerance.  Shapes cover whole and overhanging 8x16 patches, both strides, the
+smallest and largest channel counts the kernel takes, and shapes it does not take (those run
+the two kernels inside the same call).
+"""
+import numpy as np
+import pytest
+
+import oracle
+from gpu_util import rel_err, tf  # noqa: F401
+
+pytestmark = pytest.mark.gpu
+
+
+def _rng(seed):
+    return np.random.Generator(np.random.PCG64(seed))
+
+
+def _case(tf, b, h, w, c, n, stride, seed, dw_act="relu6", pw_act="relu6", bias=True):
+    from tfjs_core_b200 import conv_util
+    bk = tf.ENGINE.backend
+    rng = _rng(seed)
+    x = rng.uniform(-1, 1, (b, h, w, c)).astype(np.float32)
+    wd = rng.normal(0, 0.5, (3, 3, c, 1)).astype(np.float32)
+    wp = rng.uniform(-1, 1, (1, 1, c, n)).astype(np.float32) / np.float32(np.sqrt(c))
+    bd = rng.normal(0, 0.3, c).astype(np.float32) if bias else None
+    bp = rng.normal(0, 0.3, n).astype(np.float32) if bias else None
+    ci = conv_util.compute_conv2d_info(x.shape, wd.shape, stride, 1, "same", None, True)
+    t = lambda a: None if a is None else tf.ops.tensor(a)  # noqa: E731
+    xt, wdt, wpt, bdt, bpt = t(x), t(wd), t(wp), t(bd), t(bp)
+    fused = bk.fusedSeparableConv2d(xt, wdt, wpt, ci, bdt, dw_act, bpt, pw_act)
+    mid = bk.fusedDepthwiseConv2D(xt, wdt, ci, bdt, dw_act)
+    ci2 = conv_util.compute_conv2d_info(mid.shape, wp.shape, 1, 1, "valid")
+    two = bk.fusedConv2d(mid, wpt, ci2, bpt, pw_act)
+    got, ref = fused.dataSync().reshape(two.shape), two.dataSync().reshape(two.shape)
+    return x, wd, wp, bd, bp, ci, got, ref
+
+
+def _oracle(x, wd, wp, bd, bp, stride, dw_act, pw_act):
+    def act(y, a):
+        if a == "relu6":
+            return oracle.unary("clip", y, 0, 6)
+        if a == "relu":
+            return oracle.unary("relu", y)
+        return y
+    ci = oracle.compute_conv2d_info(x.shape, wd.shape, stride, 1, "same", None, True)
+    mid = oracle.depthwise_conv2d(x, wd, ci)
+    if bd is not None:
+        mid = oracle.binary("add", mid, bd)
+    mid = act(mid, dw_act)
+    ci2 = oracle.compute_conv2d_info(mid.shape, wp.shape, 1, 1, "valid")
+    y = oracle.conv2d(mid, wp, ci2)
+    if bp is not None:
+        y = oracle.binary("add", y, bp)
+    return act(y, pw_act)
+
+
+SHAPES = [
+    # b, h, w, c, n, stride
+    (2, 16, 16, 32, 64, 1),     # whole patches, one k-block
+    (2, 20, 23, 64, 96, 1),     # patches overhang right and bottom; N not a multiple of 32
+    (1, 14, 14, 128, 128, 2),   # stride 2, odd output size 7x7
+    (3, 17, 19, 256, 256, 2),   # stride 2, overhang, largest C and N
+    (2, 28, 28, 256, 256, 1),
+    (1, 7, 7, 32, 8, 1),        # one partial patch, smallest N
+    (5, 9, 40, 96, 200, 1),
+]
+
+
+@pytest.mark.parametrize("b,h,w,c,n,stride", SHAPES)
+def test_fused_equals_the_two_kernels_and_matches_the_oracle(tf, b, h, w, c, n, stride):
+    bk = tf.ENGINE.backend
+    bk.setMathMode("tf32")
+    try:
+        before = bk.launchCount()
+        x, wd, wp, bd, bp, ci, got, ref = _case(tf, b, h, w, c, n, stride, seed=b * 1000 + c + n)
+        assert np.array_equal(got, ref)
+        want = _oracle(x, wd, wp, bd, bp, stride, "relu6", "relu6")
+        assert rel_err(got, want) <= 1e-3
+        # pack weights (first use) + fused + depthwise + pointwise = at most 5 launches: the fused
+        # call was a single kernel
+        assert bk.launchCount() - before <= 5
+    finally:
+        bk.setMathMode("3xtf32")
+
+
+@pytest.mark.parametrize("dw_act,pw_act,bias", [("linear", "linear", False), ("relu", "linear", True),
+                                                 (("clip", -0.5, 0.75), "relu", True)])
+def test_fused_epilogue_variants(tf, dw_act, pw_act, bias):
+    bk = tf.ENGINE.backend
+    bk.setMathMode("tf32")
+    try:
+        _, _, _, _, _, _, got, ref = _case(tf, 2, 24, 20, 64, 128, 1, seed=77, dw_act=dw_act, pw_act=pw_act,
+                                           bias=bias)
+        assert np.array_equal(got, ref)
+    finally:
+        bk.setMathMode("3xtf32")
+
+
+@pytest.mark.parametrize("c,n,mode", [(512, 512, "tf32"), (64, 512, "tf32"), (40, 64, "tf32"), (64, 64, "3xtf32")])
+def test_shapes_outside_the_fused_kernel_run_the_two_kernels(tf, c, n, mode):
+    bk = tf.ENGINE.backend
+    bk.setMathMode(mode)
+    try:
+        x, wd, wp, bd, bp, ci, got, ref = _case(tf, 1, 14, 14, c, n, 1, seed=c + n)
+        assert np.array_equal(got, ref)
+    finally:
+        bk.setMathMode("3xtf32")
+
+
+def test_option_off_forces_two_kernels_with_identical_output(tf):
+    bk = tf.ENGINE.backend
+    bk.setMathMode("tf32")
+    try:
+        _, _, _, _, _, _, fused, _ = _case(tf, 2, 16, 16, 32, 64, 1, seed=5)
+        bk.setOption("fuse_separable", 0)
+        _, _, _, _, _, _, unfused, _ = _case(tf, 2, 16, 16, 32, 64, 1, seed=5)
+        assert np.array_equal(fused, unfused)
+    finally:
+        bk.setOption("fuse_separable", 1)
+        bk.setMathMode("3xtf32")
+
+
+def test_quantised_filters(tf):
+    """uint8 depthwise and pointwise filters (config 5) through the fused kernel."""
+    from tfjs_core_b200 import conv_util
+    bk = tf.ENGINE.backend
+    bk.setMathMode("tf32")
+    try:
+        rng = _rng(9)
+        x = rng.uniform(-1, 1, (2, 16, 32, 64)).astype(np.float32)
+        qd = rng.integers(0, 256, (3, 3, 64, 1), dtype=np.uint8)
+        qp = rng.integers(0, 256, (1, 1, 64, 128), dtype=np.uint8)
+        s, m = 0.004, -0.5
+        wd, wp = oracle.dequant_u8(qd, s, m), oracle.dequant_u8(qp, s, m)
+        ci = conv_util.compute_conv2d_info(x.shape, wd.shape, 1, 1, "same", None, True)
+        xt = tf.ops.tensor(x)
+        got = bk.fusedSeparableConv2d(xt, bk.registerQuantized(list(qd.shape), qd, s, m),
+                                      bk.registerQuantized(list(qp.shape), qp, s, m), ci, None, "relu6", None,
+                                      "relu6").dataSync()
+        ref = bk.fusedSeparableConv2d(xt, tf.ops.tensor(wd), tf.ops.tensor(wp), ci, None, "relu6", None,
+                                      "relu6").dataSync()
+        assert np.array_equal(got, ref)
+    finally:
+        bk.setMathMode("3xtf32")
+
+
+def test_mobilenet_with_fused_blocks_equals_the_layerwise_forward(tf):
+    from tfjs_core_b200 import mobilenet
+    bk = tf.ENGINE.backend
+    bk.setMathMode("tf32")
+    params = mobilenet.make_weights(4, quantized=True)
+    net = mobilenet.MobileNetV1(params, bk)
+    try:
+        x = tf.ops.tensor(mobilenet.make_input(11, 3))
+        a = [t.dataSync() for t in net.forward_fused(x)]
+        before = bk.launchCount()
+        b = [t.dataSync() for t in net.forward_separable(x)]
+        launches = bk.launchCount() - before
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+        assert launches == 1 + 5 + 2 * 8 + 3, launches
+    finally:
+        net.dispose()
+        bk.setMathMode("3xtf32")

@@ -87,6 +87,9 @@ SIGNATURES = {
                                    C.POINTER(Epilogue)]),
     "tfjs_cuda_depthwise_conv2d": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int64, C.POINTER(ConvInfo),
                                              C.POINTER(Epilogue)]),
+    "tfjs_cuda_separable_conv2d": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                             C.POINTER(ConvInfo), C.c_int32, C.POINTER(Epilogue),
+                                             C.POINTER(Epilogue)]),
     "tfjs_cuda_pool2d": (C.c_int, [_P, C.c_int64, C.c_int64, C.POINTER(ConvInfo), C.c_int]),
     "tfjs_cuda_binary": (C.c_int, [_P, C.c_int, C.c_int64, C.c_int, _I64P, C.c_int64, C.c_int, _I64P,
                                    C.c_int64]),

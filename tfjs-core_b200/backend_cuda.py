@@ -383,6 +383,39 @@ class BackendCuda:
             out = self._compose_epilogue(out, bias, activation, None)
         return out
 
+    def fusedSeparableConv2d(self, x, depthwiseFilter, pointwiseFilter, convInfo, dwBias=None,
+                             dwActivation=None, pwBias=None, pwActivation=None):
+        """Extension: tf.separableConv2d's op pair (ops/conv.ts:574-654) with bias + activation
+        after each half, `convInfo` being the depthwise Conv2DInfo and pointwiseFilter
+        [1, 1, convInfo.outChannels, outDepth].  Eligible shapes run as one kernel that never
+        writes the depthwise result to device memory; results equal the two separate calls."""
+        self._assert_numeric([x, depthwiseFilter, pointwiseFilter, dwBias, pwBias], "separableConv2d")
+        out_depth = pointwiseFilter.shape[3]
+        if pointwiseFilter.shape[:3] != [1, 1, convInfo.outChannels]:
+            raise ValueError(
+                f"Error in separableConv2d: the third dimension of pointwise filter must be "
+                f"{convInfo.outChannels}, but got {pointwiseFilter.shape[2]}.")
+        dw_epi, tmps1, compose1 = self._epilogue(dwBias, dwActivation, None, convInfo.outChannels)
+        pw_epi, tmps2, compose2 = self._epilogue(pwBias, pwActivation, None, out_depth)
+        if compose1 or compose2:
+            # a bias that is not a channel vector: the two-call form handles the broadcast
+            self._free_tmp(*tmps1, *tmps2)
+            mid = self.fusedDepthwiseConv2D(x, depthwiseFilter, convInfo, dwBias, dwActivation)
+            from . import conv_util
+            ci = conv_util.compute_conv2d_info(mid.shape, pointwiseFilter.shape, 1, 1, "valid")
+            out = self.fusedConv2d(mid, pointwiseFilter, ci, pwBias, pwActivation)
+            mid.dispose()
+            return out
+        xid, tx = self._id(x)
+        did, td = self._id(depthwiseFilter)
+        pid, tp = self._id(pointwiseFilter)
+        out = self._out([convInfo.batchSize, convInfo.outHeight, convInfo.outWidth, out_depth])
+        oid = self._rec(out.dataId)["id"]
+        self._check(self._lib.tfjs_cuda_separable_conv2d(
+            self._ctx, xid, did, pid, oid, C.byref(convInfo), int(out_depth), C.byref(dw_epi), C.byref(pw_epi)))
+        self._free_tmp(tx, td, tp, *tmps1, *tmps2)
+        return out
+
     # ---- pooling -------------------------------------------------------------------------
     def _pool(self, x, convInfo, is_avg):
         self._assert_numeric(x, "pool")

@@ -298,3 +298,59 @@ extern "C" int tfjs_cuda_pool2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_te
   cudaSetDevice(ctx->device);
   return launch_pool2d(ctx, (const float*)x->ptr, (float*)o->ptr, *ci, is_avg);
 }
+
+// y = pw_act(conv1x1(dw_act(depthwise(x, dw_filter) + dw_bias), pw_filter) + pw_bias).  Shapes the
+// fused tensor-core kernel takes run in one launch without the intermediate in device memory;
+// everything else runs the depthwise and the pointwise kernel back to back through a scratch
+// buffer.  Either way the arithmetic is that of the two separate calls.
+extern "C" int tfjs_cuda_separable_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_tensor_id dw_filter_id,
+                                          tfjs_tensor_id pw_filter_id, tfjs_tensor_id out_id,
+                                          const tfjs_conv2d_info* dw, int32_t out_channels,
+                                          const tfjs_epilogue* dw_epi, const tfjs_epilogue* pw_epi) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  int rc = check_conv_info(ctx, dw);
+  if (rc) return rc;
+  TFJS_REQUIRE(ctx, out_channels >= 0, "negative extent");
+  TFJS_REQUIRE(ctx, dw->inChannels == 0 || dw->outChannels % dw->inChannels == 0,
+               "depthwise outChannels must be a multiple of inChannels");
+  const int64_t pixels = (int64_t)dw->batchSize * dw->outHeight * dw->outWidth;
+  const int64_t C = dw->outChannels, N = out_channels;
+  TensorEntry *x, *wd, *wp, *o;
+  rc = get_f32(ctx, x_id, (int64_t)dw->batchSize * dw->inHeight * dw->inWidth * dw->inChannels, "x", &x);
+  if (rc) return rc;
+  rc = get_f32(ctx, dw_filter_id, (int64_t)dw->filterHeight * dw->filterWidth * C, "depthwise filter", &wd);
+  if (rc) return rc;
+  rc = get_f32(ctx, pw_filter_id, C * N, "pointwise filter", &wp);
+  if (rc) return rc;
+  rc = get_f32(ctx, out_id, pixels * N, "separableConv2d output", &o);
+  if (rc) return rc;
+  TFJS_REQUIRE(ctx, !x->quant.quantized && !o->quant.quantized, "only the filters may be quantised");
+  EpilogueArgs de, pe;
+  rc = resolve_epilogue(ctx, dw_epi, C, &de);
+  if (rc) return rc;
+  rc = resolve_epilogue(ctx, pw_epi, N, &pe);
+  if (rc) return rc;
+  o->version++;
+  if (pixels * N == 0) return TFJS_CUDA_OK;
+  cudaSetDevice(ctx->device);
+  const float* wdf;
+  rc = float_view(ctx, wd, &wdf);
+  if (rc) return rc;
+  if (ctx->use_tensor_cores && ctx->fuse_separable &&
+      sepconv_tcgen05_supported(*dw, N, de.activation, pe.activation, ctx->math_mode)) {
+    PackedWeights pw;
+    bool temporary;
+    rc = packed_weights(ctx, wp, 0, C, N, false, true, &pw, &temporary);
+    if (rc) return rc;
+    return launch_sepconv_tcgen05(ctx, (const float*)x->ptr, *dw, wdf, de, pw.hi, pw.kp, (float*)o->ptr, N, pe);
+  }
+  TFJS_REQUIRE(ctx, C > 0, "separableConv2d needs at least one channel");
+  void* mid;
+  size_t mid_cap;
+  rc = ctx_alloc(ctx, (size_t)(pixels * C) * 4, &mid, &mid_cap);
+  if (rc) return rc;
+  rc = launch_depthwise(ctx, (const float*)x->ptr, wdf, (float*)mid, *dw, de);
+  if (!rc) rc = gemm_dispatch(ctx, (const float*)mid, pixels, C, wp, 0, false, true, (float*)o->ptr, N, pe);
+  ctx_free(ctx, mid, mid_cap);
+  return rc;
+}

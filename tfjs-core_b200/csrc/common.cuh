@@ -93,6 +93,8 @@ struct tfjs_cuda_ctx {
   // Quantised matmul / 1x1-conv weights: false expands them once into cached tf32 planes, true
   // keeps them uint8 and dequantises every tile in shared memory inside the GEMM main loop.
   bool dequant_in_gemm = false;
+  // separable_conv2d: true lets eligible shapes run as one fused kernel
+  bool fuse_separable = true;
   // bookkeeping
   int64_t launch_count = 0;
   cudaEvent_t time_start = nullptr, time_stop = nullptr;
@@ -217,6 +219,14 @@ int64_t tcgen05_conv_k(const tfjs_conv2d_info& ci, int mode);
 int launch_conv_tcgen05(tfjs_cuda_ctx* ctx, int mode, const float* x, const tfjs_conv2d_info& ci,
                         const float* w_hi, const float* w_lo, int64_t kp, float* out,
                         const EpilogueArgs& epi, int math_mode);
+// sepconv_tcgen05.cu: depthwise 3x3 (+bias, activation) fused into the pointwise GEMM that
+// consumes it; `supported` says whether the fused kernel takes the shapes (else the caller runs
+// the two kernels back to back).
+bool sepconv_tcgen05_supported(const tfjs_conv2d_info& dw, int64_t N, int dw_activation, int pw_activation,
+                               int math_mode);
+int launch_sepconv_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& dw, const float* dw_filter,
+                           const EpilogueArgs& dw_epi, const float* w_hi, int64_t kp, float* y, int64_t N,
+                           const EpilogueArgs& pw_epi);
 // conv.cu
 int launch_conv2d_direct(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* y,
                          const tfjs_conv2d_info& ci, const EpilogueArgs& epi);

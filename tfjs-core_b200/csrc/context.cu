@@ -269,6 +269,8 @@ extern "C" int tfjs_cuda_ctx_set_option(tfjs_cuda_ctx* ctx, const char* key, dou
     ctx->debug_sync = value != 0;
   } else if (!strcmp(key, "dequant_in_gemm")) {
     ctx->dequant_in_gemm = value != 0;
+  } else if (!strcmp(key, "fuse_separable")) {
+    ctx->fuse_separable = value != 0;
   } else {
     return set_error(ctx, TFJS_CUDA_ERR_INVALID_ARG, "unknown option '%s'", key);
   }

@@ -1,0 +1,505 @@
+// Fused depthwise-separable block for sm_100a:
+//   y = act2( pointwise1x1( act1( depthwise3x3(x) + bias1 ) ) + bias2 )
+// i.e. KernelBackend.depthwiseConv2D (+ add, clip) followed by fusedConv2d with a 1x1 filter
+// (tfjs-core/src/backends/backend.ts:431-434, 414-418; the op pair of tf.separableConv2d,
+// ops/conv.ts:574-654, with MobileNet's bias and relu6 between the two).  The depthwise output
+// never reaches device memory: it is computed into shared memory as the A operand of the
+// pointwise GEMM, which runs on tcgen05 with its accumulator in tensor memory.
+//
+// One persistent CTA per SM works on patches of 8 x 16 output pixels (= the 128 rows of one MMA):
+//   warp 8      producer: per 32-channel k-block, TMA-loads the pointwise weight tile
+//               [BLOCK_N x 32] and the input window of the patch ((8-1)*S+3 rows x (16-1)*S+3
+//               columns x 32 channels; 16 channels at a time for stride 2) through a 4-D tensor
+//               map whose out-of-range reads return zero, which is SAME padding.
+//   warps 10-17 depthwise: each thread owns 4 channels of 4 (stride 1) or 2 (stride 2) adjacent
+//               output pixels, accumulates the 9 taps in the reference's order with one fmaf per
+//               tap, adds the bias, applies the activation and writes 16 bytes of the swizzled
+//               K-major A tile (two slots, so the next k-block is computed while the tensor core
+//               reads the current one).
+//   warp 9      one thread issues tcgen05.mma (M = 128, N = BLOCK_N, K = 8) into one of two TMEM
+//               accumulators and commits the barriers that free the slots.
+//   warps 0-7   epilogue: tcgen05.ld, bias, activation, swizzled staging, 4-D TMA store of
+//               [2 rows x 16 columns x 32 channels] boxes (the store clips patches that overhang
+//               the image).
+// The arithmetic is that of the two separate kernels, operation for operation, so the results are
+// bit-identical to running them back to back.  Every mbarrier wait is bounded.
+#include "tcgen05_ptx.cuh"
+
+namespace {
+
+constexpr int PH = 8, PW = 16;                    // output patch
+constexpr int BLOCK_K = 32;
+constexpr int A_TILE_BYTES = 128 * BLOCK_K * 4;   // 16 KB
+constexpr int A_SLOTS = 2;
+constexpr int EPI_WARPS = 8;
+constexpr int C_CHUNK_BYTES = 32 * 32 * 4;
+constexpr int C_STAGING_BYTES = EPI_WARPS * C_CHUNK_BYTES;
+constexpr int BIAS_STAGING_BYTES = EPI_WARPS * 128;
+constexpr int DW_THREADS = 256;
+constexpr int THREADS = 320 + DW_THREADS;
+constexpr int MAX_C = 256;                        // depthwise channels (= K of the GEMM)
+constexpr int DW_TABLE_BYTES = 10 * MAX_C * 4;    // 9 filter taps + bias per channel
+constexpr int BARRIER_BYTES = 512;
+constexpr int SMEM_LIMIT = 232448;
+
+template <int S>
+struct Raw {
+  static constexpr int CH = S == 1 ? 32 : 16;          // channels per raw stage
+  static constexpr int PARTS = BLOCK_K / CH;           // raw stages per k-block
+  static constexpr int ROWS = (PH - 1) * S + 3;
+  static constexpr int COLS = (PW - 1) * S + 3;
+  static constexpr int BYTES = ROWS * COLS * CH * 4;
+  static constexpr int STRIDE = (BYTES + 1023) / 1024 * 1024;
+  static constexpr int PIX = S == 1 ? 4 : 2;           // adjacent output pixels per thread
+};
+
+__host__ __device__ constexpr int w_stages(int block_n) { return block_n >= 256 ? 2 : (block_n >= 128 ? 3 : 4); }
+template <int S>
+__host__ __device__ constexpr int raw_stages(int block_n) {
+  int left = SMEM_LIMIT - 1024 - A_SLOTS * A_TILE_BYTES - w_stages(block_n) * block_n * BLOCK_K * 4 -
+             C_STAGING_BYTES - BIAS_STAGING_BYTES - DW_TABLE_BYTES - BARRIER_BYTES;
+  int n = left / Raw<S>::STRIDE;
+  return n > 4 ? 4 : n;
+}
+
+struct SepParams {
+  int B, inH, inW, C, outH, outW, N;
+  int pad_r, pad_c;                 // first input row / column of output (0, 0) is -pad
+  int tiles_y, tiles_x, num_tiles, num_k_blocks;
+  const float* dw_filter;           // [3, 3, C, 1]
+  const float* dw_bias;             // [C] or null
+  int dw_bias_scalar;
+  int dw_act;
+  float dw_lo, dw_hi;
+  EpilogueArgs epi;                 // of the pointwise convolution
+  int* status;
+};
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
+                                            int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2,
+                                             int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(map),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const float4& v) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
+template <int ACT>
+__device__ __forceinline__ float dw_activate(float v, float lo, float hi) {
+  if (ACT == TFJS_ACT_RELU) return max_nan(v, 0.f);
+  if (ACT == TFJS_ACT_CLIP) return min_nan(max_nan(v, lo), hi);
+  return v;
+}
+
+// Depthwise 3x3 of one raw stage: thread t computes PIX adjacent output pixels x 4 channels from
+// the window in shared memory and writes them into the A tile.  `table` holds the 9 filter taps
+// and the bias of every channel ([10][C] floats).
+template <int S, int ACT>
+__device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t table, int t, int part, int kb,
+                                        const SepParams& p, bool has_bias) {
+  using R = Raw<S>;
+  constexpr int QUADS = R::CH / 4;
+  constexpr int GROUPS_PER_ROW = PW / R::PIX;
+  constexpr int WIN = (R::PIX - 1) * S + 3;
+  const int q = t % QUADS;
+  const int g = t / QUADS;
+  const int r = g / GROUPS_PER_ROW;
+  const int c0 = (g % GROUPS_PER_ROW) * R::PIX;
+  const int ch = kb * BLOCK_K + part * R::CH + q * 4;
+  float4 acc[R::PIX];
+#pragma unroll
+  for (int j = 0; j < R::PIX; j++) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int dr = 0; dr < 3; dr++) {
+    const uint32_t row = raw + (uint32_t)(((r * S + dr) * R::COLS + c0 * S) * (R::CH * 4) + q * 16);
+    float4 in[WIN];
+#pragma unroll
+    for (int i = 0; i < WIN; i++) in[i] = lds128(row + i * (R::CH * 4));
+#pragma unroll
+    for (int wc = 0; wc < 3; wc++) {
+      const float4 f = lds128(table + (uint32_t)(((dr * 3 + wc) * p.C + ch) * 4));
+#pragma unroll
+      for (int j = 0; j < R::PIX; j++) {
+        const float4 v = in[j * S + wc];
+        acc[j].x = fmaf(v.x, f.x, acc[j].x);
+        acc[j].y = fmaf(v.y, f.y, acc[j].y);
+        acc[j].z = fmaf(v.z, f.z, acc[j].z);
+        acc[j].w = fmaf(v.w, f.w, acc[j].w);
+      }
+    }
+  }
+  const float4 b = lds128(table + (uint32_t)((9 * p.C + ch) * 4));
+  const int chunk = part * QUADS + q;  // 16-byte chunk of the 128-byte A row
+#pragma unroll
+  for (int j = 0; j < R::PIX; j++) {
+    float4 o = acc[j];
+    if (has_bias) { o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w; }
+    o.x = dw_activate<ACT>(o.x, p.dw_lo, p.dw_hi);
+    o.y = dw_activate<ACT>(o.y, p.dw_lo, p.dw_hi);
+    o.z = dw_activate<ACT>(o.z, p.dw_lo, p.dw_hi);
+    o.w = dw_activate<ACT>(o.w, p.dw_lo, p.dw_hi);
+    sts128(a_tile + swz(r * PW + c0 + j, chunk * 16), o);
+  }
+}
+
+template <int BLOCK_N, int S>
+__global__ void __launch_bounds__(THREADS, 1)
+sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                       const __grid_constant__ CUtensorMap map_y, SepParams p) {
+  using R = Raw<S>;
+  constexpr int W_STAGES = w_stages(BLOCK_N);
+  constexpr int RAW_STAGES = raw_stages<S>(BLOCK_N);
+  static_assert(RAW_STAGES >= 2, "the input ring needs two stages");
+  constexpr int W_STAGE_BYTES = BLOCK_N * BLOCK_K * 4;
+  constexpr uint32_t TMEM_COLS = 2 * BLOCK_N < 32 ? 32 : 2 * BLOCK_N;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* a_tiles = smem;                                   // [A_SLOTS][16 KB], SWIZZLE_128B
+  uint8_t* w_tiles = a_tiles + A_SLOTS * A_TILE_BYTES;       // [W_STAGES][BLOCK_N x 128 B]
+  uint8_t* c_stage = w_tiles + W_STAGES * W_STAGE_BYTES;     // [8 warps][4 KB]
+  uint8_t* raw = c_stage + C_STAGING_BYTES;                  // [RAW_STAGES][window]
+  uint8_t* table = raw + RAW_STAGES * R::STRIDE;             // [10][C] floats
+  uint8_t* bias_stage = table + DW_TABLE_BYTES;
+  uint64_t* bars = (uint64_t*)(bias_stage + BIAS_STAGING_BYTES);
+  uint64_t* raw_full = bars;                       // [RAW_STAGES] TMA -> depthwise warps
+  uint64_t* raw_empty = raw_full + RAW_STAGES;     // [RAW_STAGES] depthwise warps -> TMA
+  uint64_t* w_full = raw_empty + RAW_STAGES;       // [W_STAGES] TMA -> MMA
+  uint64_t* w_empty = w_full + W_STAGES;           // [W_STAGES] MMA -> TMA
+  uint64_t* a_full = w_empty + W_STAGES;           // [A_SLOTS] depthwise warps -> MMA
+  uint64_t* a_empty = a_full + A_SLOTS;            // [A_SLOTS] MMA -> depthwise warps
+  uint64_t* tmem_full_bar = a_empty + A_SLOTS;     // [2] MMA -> epilogue
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;    // [2] epilogue -> MMA
+  uint32_t* tmem_ptr_holder = (uint32_t*)(tmem_empty_bar + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_ptr_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < RAW_STAGES; s++) {
+      mbar_init(smem_u32(&raw_full[s]), 1);
+      mbar_init(smem_u32(&raw_empty[s]), DW_THREADS);
+    }
+    for (int s = 0; s < W_STAGES; s++) {
+      mbar_init(smem_u32(&w_full[s]), 1);
+      mbar_init(smem_u32(&w_empty[s]), 1);
+    }
+    for (int s = 0; s < A_SLOTS; s++) {
+      mbar_init(smem_u32(&a_full[s]), DW_THREADS);
+      mbar_init(smem_u32(&a_empty[s]), 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), EPI_WARPS);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 9) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_ptr_holder)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  // depthwise filter taps and bias of every channel: [tap][C], then the bias row
+  {
+    float* tab = reinterpret_cast<float*>(table);
+    for (int i = threadIdx.x; i < 9 * p.C; i += THREADS) tab[i] = __ldg(p.dw_filter + i);
+    for (int i = threadIdx.x; i < p.C; i += THREADS)
+      tab[9 * p.C + i] = p.dw_bias ? __ldg(p.dw_bias + (p.dw_bias_scalar ? 0 : i)) : 0.f;
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_holder;
+  const int tiles_per_image = p.tiles_y * p.tiles_x;
+
+  if (warp == 8) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int rs = 0, ws = 0;
+      uint32_t rphase = 0, wphase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        const int b = tile / tiles_per_image;
+        const int rem = tile - b * tiles_per_image;
+        const int ty = rem / p.tiles_x, tx = rem - ty * p.tiles_x;
+        const int x0 = tx * PW * S - p.pad_c, y0 = ty * PH * S - p.pad_r;
+        for (int kb = 0; kb < p.num_k_blocks && ok; kb++) {
+          ok = mbar_wait(smem_u32(&w_empty[ws]), wphase ^ 1, abort_flag, p.status, 11);
+          if (!ok) break;
+          mbar_arrive_expect_tx(smem_u32(&w_full[ws]), W_STAGE_BYTES);
+          tma_load_2d(smem_u32(w_tiles + ws * W_STAGE_BYTES), &map_w, smem_u32(&w_full[ws]), kb * BLOCK_K, 0);
+          if (++ws == W_STAGES) { ws = 0; wphase ^= 1; }
+          for (int part = 0; part < R::PARTS; part++) {
+            ok = mbar_wait(smem_u32(&raw_empty[rs]), rphase ^ 1, abort_flag, p.status, 12);
+            if (!ok) break;
+            mbar_arrive_expect_tx(smem_u32(&raw_full[rs]), R::BYTES);
+            tma_load_4d(smem_u32(raw + rs * R::STRIDE), &map_x, smem_u32(&raw_full[rs]),
+                        kb * BLOCK_K + part * R::CH, x0, y0, b);
+            if (++rs == RAW_STAGES) { rs = 0; rphase ^= 1; }
+          }
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(128, BLOCK_N);
+      int ws = 0, slot = 0, local = 0;
+      uint32_t wphase = 0, sphase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, local++) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status, 13);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
+        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+          ok = mbar_wait(smem_u32(&w_full[ws]), wphase, abort_flag, p.status, 14);
+          if (ok) ok = mbar_wait(smem_u32(&a_full[slot]), sphase, abort_flag, p.status, 15);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t a_s = smem_u32(a_tiles + slot * A_TILE_BYTES);
+          const uint32_t w_s = smem_u32(w_tiles + ws * W_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / 8; k++)
+            tcgen05_mma_tf32(tmem_d, make_smem_desc(a_s + k * 32), make_smem_desc(w_s + k * 32), idesc,
+                             (kb > 0 || k > 0) ? 1u : 0u);
+          tcgen05_commit(smem_u32(&w_empty[ws]));
+          tcgen05_commit(smem_u32(&a_empty[slot]));
+          if (++ws == W_STAGES) { ws = 0; wphase ^= 1; }
+          if (++slot == A_SLOTS) { slot = 0; sphase ^= 1; }
+        }
+        if (ok) tcgen05_commit(smem_u32(&tmem_full_bar[acc]));
+      }
+    }
+  } else if (warp >= 10) {
+    // ---------------- depthwise warps ----------------
+    const int t = threadIdx.x - 320;
+    const uint32_t table_s = smem_u32(table);
+    const bool has_bias = p.dw_bias != nullptr;
+    int rs = 0, slot = 0;
+    uint32_t rphase = 0, sphase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      for (int kb = 0; kb < p.num_k_blocks && ok; kb++) {
+        ok = mbar_wait(smem_u32(&a_empty[slot]), sphase ^ 1, abort_flag, p.status, 16);
+        if (!ok) break;
+        const uint32_t a_s = smem_u32(a_tiles + slot * A_TILE_BYTES);
+        for (int part = 0; part < R::PARTS; part++) {
+          ok = mbar_wait(smem_u32(&raw_full[rs]), rphase, abort_flag, p.status, 17);
+          if (!ok) break;
+          const uint32_t raw_s = smem_u32(raw + rs * R::STRIDE);
+          switch (p.dw_act) {
+            case TFJS_ACT_RELU: dw_part<S, TFJS_ACT_RELU>(raw_s, a_s, table_s, t, part, kb, p, has_bias); break;
+            case TFJS_ACT_CLIP: dw_part<S, TFJS_ACT_CLIP>(raw_s, a_s, table_s, t, part, kb, p, has_bias); break;
+            default: dw_part<S, TFJS_ACT_LINEAR>(raw_s, a_s, table_s, t, part, kb, p, has_bias); break;
+          }
+          mbar_arrive(smem_u32(&raw_empty[rs]));  // this thread has read all it needs of the window
+          if (++rs == RAW_STAGES) { rs = 0; rphase ^= 1; }
+        }
+        if (!ok) break;
+        fence_proxy_async_smem();  // generic-proxy writes of the A tile -> visible to the tensor core
+        mbar_arrive(smem_u32(&a_full[slot]));
+        if (++slot == A_SLOTS) { slot = 0; sphase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------- epilogue warps 0-7 ----------------
+    // Warps w and w+4 share TMEM lane quarter w%4 (patch rows 2*(w%4), 2*(w%4)+1) and split the
+    // 32-channel chunks of the tile between them.
+    constexpr int CHUNKS = BLOCK_N / 32;
+    constexpr int MY_CHUNKS = CHUNKS / 2;
+    static_assert(CHUNKS >= 2, "BLOCK_N >= 64");
+    const int quarter = warp & 3;
+    const int half = warp >> 2;
+    uint8_t* stage_buf = c_stage + warp * C_CHUNK_BYTES;
+    float* bias_s = reinterpret_cast<float*>(bias_stage + warp * 128);
+    const bool has_bias = p.epi.bias != nullptr;
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, local++) {
+      const int b = tile / tiles_per_image;
+      const int rem = tile - b * tiles_per_image;
+      const int ty = rem / p.tiles_x, tx = rem - ty * p.tiles_x;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      float bias_l[MY_CHUNKS];
+#pragma unroll
+      for (int i = 0; i < MY_CHUNKS; i++) {
+        const int cl = (2 * i + half) * 32 + lane;
+        bias_l[i] = 0.f;
+        if (has_bias) bias_l[i] = p.epi.bias_scalar ? __ldg(p.epi.bias) : (cl < p.N ? __ldg(p.epi.bias + cl) : 0.f);
+      }
+      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 18);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BLOCK_N;
+      bool released = false;
+#pragma unroll
+      for (int i = 0; i < MY_CHUNKS; i++) {
+        const int chunk = 2 * i + half;
+        const int c0 = chunk * 32;
+        if (c0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + chunk * 32, r);
+        __syncwarp();
+        bias_s[lane] = bias_l[i];
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int k = 0; k < 32; k++) v[k] = __uint_as_float(r[k]);
+        __syncwarp();
+        if (i == MY_CHUNKS - 1) {
+          tcgen05_fence_before();
+          if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+          released = true;
+        }
+        switch (p.epi.activation) {
+          case TFJS_ACT_RELU: finish_chunk<TFJS_ACT_RELU>(v, has_bias, bias_s, bias_s, p.epi); break;
+          case TFJS_ACT_CLIP: finish_chunk<TFJS_ACT_CLIP>(v, has_bias, bias_s, bias_s, p.epi); break;
+          default: finish_chunk<TFJS_ACT_LINEAR>(v, has_bias, bias_s, bias_s, p.epi); break;
+        }
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+        uint8_t* dst = stage_buf + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+          *reinterpret_cast<float4*>(dst + ((j ^ (lane & 7)) << 4)) =
+              make_float4(v[j * 4 + 0], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          // lanes 0-15 hold patch row 2*quarter, lanes 16-31 the next one: a [2 x 16 x 32] box
+          tma_store_4d(&map_y, smem_u32(stage_buf), c0, tx * PW, ty * PH + quarter * 2, b);
+          tma_store_commit();
+        }
+      }
+      if (!released) {
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
+      }
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    __syncwarp();
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+template <int BLOCK_N, int S>
+int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my,
+                   const SepParams& p) {
+  constexpr int smem_bytes = 1024 + A_SLOTS * A_TILE_BYTES + w_stages(BLOCK_N) * BLOCK_N * BLOCK_K * 4 +
+                             C_STAGING_BYTES + raw_stages<S>(BLOCK_N) * Raw<S>::STRIDE + DW_TABLE_BYTES +
+                             BIAS_STAGING_BYTES + BARRIER_BYTES;
+  static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
+  auto kernel = sepconv_tcgen05_kernel<BLOCK_N, S>;
+  static bool configured[8] = {false};
+  if (!configured[ctx->device & 7]) {
+    TFJS_CHECK_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    configured[ctx->device & 7] = true;
+  }
+  const int grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
+  kernel<<<grid, THREADS, smem_bytes, ctx->stream>>>(mx, mw, my, p);
+  return post_launch(ctx, S == 1 ? "separableConv2d (fused dw3x3 s1 + pw, TF32)"
+                                 : "separableConv2d (fused dw3x3 s2 + pw, TF32)");
+}
+
+template <int S>
+int launch_stride(tfjs_cuda_ctx* ctx, int block_n, const CUtensorMap& mx, const CUtensorMap& mw,
+                  const CUtensorMap& my, const SepParams& p) {
+  switch (block_n) {
+    case 64: return launch_variant<64, S>(ctx, mx, mw, my, p);
+    case 128: return launch_variant<128, S>(ctx, mx, mw, my, p);
+    default: return launch_variant<256, S>(ctx, mx, mw, my, p);
+  }
+}
+
+}  // namespace
+
+// Depthwise 3x3 (stride 1 or 2, dilation 1, channel multiplier 1, C a multiple of 32 up to 256)
+// feeding a pointwise convolution with 8..256 output channels, in TF32.
+bool sepconv_tcgen05_supported(const tfjs_conv2d_info& dw, int64_t N, int dw_activation, int pw_activation,
+                               int math_mode) {
+  const int64_t out_px = (int64_t)dw.batchSize * dw.outHeight * dw.outWidth;
+  return math_mode == TFJS_MATH_TF32 && dw.filterHeight == 3 && dw.filterWidth == 3 && dw.dilationHeight == 1 &&
+         dw.dilationWidth == 1 && dw.strideHeight == dw.strideWidth && (dw.strideHeight == 1 || dw.strideHeight == 2) &&
+         dw.outChannels == dw.inChannels && dw.inChannels % 32 == 0 && dw.inChannels >= 32 &&
+         dw.inChannels <= MAX_C && N >= 8 && N <= 256 && N % 4 == 0 && out_px >= 1 && dw.batchSize < 65536 &&
+         (int64_t)dw.batchSize * dw.inHeight * dw.inWidth * dw.inChannels < (1ll << 40) &&
+         dw_activation != TFJS_ACT_PRELU && pw_activation != TFJS_ACT_PRELU &&
+         tcgen05_gemm_supported(128, N, dw.inChannels);
+}
+
+int launch_sepconv_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& dw, const float* dw_filter,
+                           const EpilogueArgs& dw_epi, const float* w_hi, int64_t kp, float* y, int64_t N,
+                           const EpilogueArgs& pw_epi) {
+  const int S = dw.strideHeight;
+  const int C = dw.inChannels;
+  const int block_n = N <= 64 ? 64 : (N <= 128 ? 128 : 256);
+  CUtensorMap mx, mw, my;
+  const uint64_t xd[4] = {(uint64_t)C, (uint64_t)dw.inWidth, (uint64_t)dw.inHeight, (uint64_t)dw.batchSize};
+  const uint64_t xs[3] = {(uint64_t)C * 4, (uint64_t)dw.inWidth * C * 4, (uint64_t)dw.inHeight * dw.inWidth * C * 4};
+  const uint32_t xb1[4] = {(uint32_t)Raw<1>::CH, (uint32_t)Raw<1>::COLS, (uint32_t)Raw<1>::ROWS, 1};
+  const uint32_t xb2[4] = {(uint32_t)Raw<2>::CH, (uint32_t)Raw<2>::COLS, (uint32_t)Raw<2>::ROWS, 1};
+  const uint64_t wd[2] = {(uint64_t)kp, (uint64_t)N};
+  const uint64_t ws[1] = {(uint64_t)kp * 4};
+  const uint32_t wb[2] = {BLOCK_K, (uint32_t)block_n};
+  const uint64_t yd[4] = {(uint64_t)N, (uint64_t)dw.outWidth, (uint64_t)dw.outHeight, (uint64_t)dw.batchSize};
+  const uint64_t ys[3] = {(uint64_t)N * 4, (uint64_t)dw.outWidth * N * 4, (uint64_t)dw.outHeight * dw.outWidth * N * 4};
+  const uint32_t yb[4] = {32, PW, 2, 1};
+  const bool ok =
+      tma_encode_tiled(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, x, xd, xs, S == 1 ? xb1 : xb2, CU_TENSOR_MAP_SWIZZLE_NONE) &&
+      tma_encode_tiled(&mw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, w_hi, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B) &&
+      tma_encode_tiled(&my, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, y, yd, ys, yb, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!ok) return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+  SepParams p;
+  p.B = dw.batchSize;
+  p.inH = dw.inHeight;
+  p.inW = dw.inWidth;
+  p.C = C;
+  p.outH = dw.outHeight;
+  p.outW = dw.outWidth;
+  p.N = (int)N;
+  p.pad_r = dw.padLeft;  // (sic) the reference's depthwise uses padLeft for rows and padTop for
+  p.pad_c = dw.padTop;   // columns (backend_cpu.ts:2000, 2010)
+  p.tiles_y = (dw.outHeight + PH - 1) / PH;
+  p.tiles_x = (dw.outWidth + PW - 1) / PW;
+  p.num_tiles = dw.batchSize * p.tiles_y * p.tiles_x;
+  p.num_k_blocks = C / BLOCK_K;
+  p.dw_filter = dw_filter;
+  p.dw_bias = dw_epi.bias;
+  p.dw_bias_scalar = dw_epi.bias_scalar;
+  p.dw_act = dw_epi.activation;
+  p.dw_lo = dw_epi.clip_lo;
+  p.dw_hi = dw_epi.clip_hi;
+  p.epi = pw_epi;
+  p.status = ctx->d_status;
+  return S == 1 ? launch_stride<1>(ctx, block_n, mx, mw, my, p) : launch_stride<2>(ctx, block_n, mx, mw, my, p);
+}

@@ -185,6 +185,39 @@ class MobileNetV1:
         return ENGINE.tidy(body)
 
 
+def _forward_separable(self, x):
+    """forward_fused with each depthwise + pointwise pair issued as one fusedSeparableConv2d
+    call: the blocks the fused kernel takes (3x3 depthwise over at most 256 channels into at
+    most 256 output channels: blocks 1-5) keep the depthwise result on chip, the others run
+    their two kernels inside the call."""
+    bk = self.backend
+
+    def then(new, old):
+        old.dispose()
+        return new
+
+    def body():
+        w, b = self.params["stem"]
+        ci = conv_util.compute_conv2d_info(x.shape, w.shape, 2, 1, "same")
+        h = bk.fusedConv2d(x, w, ci, b, "relu6")
+        for i, s in enumerate(DW_STRIDE, 1):
+            wd, bd = self.params[f"dw{i}"]
+            wp, bp = self.params[f"pw{i}"]
+            ci = conv_util.compute_conv2d_info(h.shape, wd.shape, s, 1, "same", None, True)
+            h = then(bk.fusedSeparableConv2d(h, wd, wp, ci, bd, "relu6", bp, "relu6"), h)
+        ci = conv_util.compute_pool2d_info(h.shape, [7, 7], 1, 1, "valid")
+        h = then(bk.avgPool(h, ci), h)
+        w, b = self.params["fc"]
+        ci = conv_util.compute_conv2d_info(h.shape, w.shape, 1, 1, "same")
+        h = then(bk.fusedConv2d(h, w, ci, b, "linear"), h)
+        logits = then(bk.reshape(h, [h.shape[0], NUM_CLASSES]), h)
+        return logits, bk.softmax(logits)
+    return ENGINE.tidy(body)
+
+
+MobileNetV1.forward_separable = _forward_separable
+
+
 def layer_algorithmic_bytes(batch, quantized):
     """Algorithmic bytes of each of the 30 launches of the fused forward, in launch order:
     4*(|x| + |y|) + filter bytes + 4*|bias| with every tensor counted once."""
