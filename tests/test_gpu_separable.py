@@ -74,6 +74,7 @@ SHAPES = [
 def test_fused_equals_the_two_kernels_and_matches_the_oracle(tf, b, h, w, c, n, stride):
     bk = tf.ENGINE.backend
     bk.setMathMode("tf32")
+    bk.setOption("fuse_separable", 2)  # also the shapes the default leaves to the two kernels
     try:
         before = bk.launchCount()
         x, wd, wp, bd, bp, ci, got, ref = _case(tf, b, h, w, c, n, stride, seed=b * 1000 + c + n)
@@ -84,6 +85,7 @@ def test_fused_equals_the_two_kernels_and_matches_the_oracle(tf, b, h, w, c, n, 
         # call was a single kernel
         assert bk.launchCount() - before <= 5
     finally:
+        bk.setOption("fuse_separable", 1)
         bk.setMathMode("3xtf32")
 
 
@@ -161,7 +163,7 @@ def test_mobilenet_with_fused_blocks_equals_the_layerwise_forward(tf):
         b = [t.dataSync() for t in net.forward_separable(x)]
         launches = bk.launchCount() - before
         assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
-        assert launches == 1 + 5 + 2 * 8 + 3, launches
+        assert launches == 1 + 4 + 2 * 9 + 3, launches  # blocks 1-4 fused by default
     finally:
         net.dispose()
         bk.setMathMode("3xtf32")

@@ -336,7 +336,9 @@ extern "C" int tfjs_cuda_separable_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_i
   const float* wdf;
   rc = float_view(ctx, wd, &wdf);
   if (rc) return rc;
-  if (ctx->use_tensor_cores && ctx->fuse_separable &&
+  // fuse_separable: 1 fuses where it measures faster than the two kernels (up to 128 channels:
+  // beyond that the fused kernel is bound by shared-memory bandwidth), 2 wherever it can
+  if (ctx->use_tensor_cores && ctx->fuse_separable && (ctx->fuse_separable >= 2 || C <= 128) &&
       sepconv_tcgen05_supported(*dw, N, de.activation, pe.activation, ctx->math_mode)) {
     PackedWeights pw;
     bool temporary;

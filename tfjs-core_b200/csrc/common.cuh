@@ -93,8 +93,9 @@ struct tfjs_cuda_ctx {
   // Quantised matmul / 1x1-conv weights: false expands them once into cached tf32 planes, true
   // keeps them uint8 and dequantises every tile in shared memory inside the GEMM main loop.
   bool dequant_in_gemm = false;
-  // separable_conv2d: true lets eligible shapes run as one fused kernel
-  bool fuse_separable = true;
+  // separable_conv2d: 0 = always two kernels, 1 = one fused kernel where that is faster,
+  // 2 = fused wherever the kernel takes the shape
+  int fuse_separable = 1;
   // bookkeeping
   int64_t launch_count = 0;
   cudaEvent_t time_start = nullptr, time_stop = nullptr;

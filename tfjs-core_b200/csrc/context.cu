@@ -270,7 +270,8 @@ extern "C" int tfjs_cuda_ctx_set_option(tfjs_cuda_ctx* ctx, const char* key, dou
   } else if (!strcmp(key, "dequant_in_gemm")) {
     ctx->dequant_in_gemm = value != 0;
   } else if (!strcmp(key, "fuse_separable")) {
-    ctx->fuse_separable = value != 0;
+    TFJS_REQUIRE(ctx, value == 0 || value == 1 || value == 2, "fuse_separable must be 0, 1 or 2");
+    ctx->fuse_separable = (int)value;
   } else {
     return set_error(ctx, TFJS_CUDA_ERR_INVALID_ARG, "unknown option '%s'", key);
   }

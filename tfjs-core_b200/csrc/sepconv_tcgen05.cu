@@ -9,8 +9,8 @@
 // One persistent CTA per SM works on patches of 8 x 16 output pixels (= the 128 rows of one MMA):
 //   warp 8      producer: per 32-channel k-block, TMA-loads the pointwise weight tile
 //               [BLOCK_N x 32] and the input window of the patch ((8-1)*S+3 rows x (16-1)*S+3
-//               columns x 32 channels; 16 channels at a time for stride 2) through a 4-D tensor
-//               map whose out-of-range reads return zero, which is SAME padding.
+//               columns x 32 channels; in two halves of 4 patch rows for stride 2) through a 4-D
+//               tensor map whose out-of-range reads return zero, which is SAME padding.
 //   warps 10-17 depthwise: each thread owns 4 channels of 4 (stride 1) or 2 (stride 2) adjacent
 //               output pixels, accumulates the 9 taps in the reference's order with one fmaf per
 //               tap, adds the bias, applies the activation and writes 16 bytes of the swizzled
@@ -42,15 +42,18 @@ constexpr int DW_TABLE_BYTES = 10 * MAX_C * 4;    // 9 filter taps + bias per ch
 constexpr int BARRIER_BYTES = 512;
 constexpr int SMEM_LIMIT = 232448;
 
+// One raw stage = the input window of PART_ROWS patch rows x 16 columns x 32 channels (every
+// pixel a full 128-byte line, so that the window reads are free of bank conflicts).  Stride 2
+// doubles the window, so its patch is loaded as two halves of 4 rows.
 template <int S>
 struct Raw {
-  static constexpr int CH = S == 1 ? 32 : 16;          // channels per raw stage
-  static constexpr int PARTS = BLOCK_K / CH;           // raw stages per k-block
-  static constexpr int ROWS = (PH - 1) * S + 3;
+  static constexpr int PARTS = S;                      // raw stages per k-block
+  static constexpr int PART_ROWS = PH / PARTS;         // patch rows per raw stage
+  static constexpr int ROWS = (PART_ROWS - 1) * S + 3;
   static constexpr int COLS = (PW - 1) * S + 3;
-  static constexpr int BYTES = ROWS * COLS * CH * 4;
+  static constexpr int BYTES = ROWS * COLS * BLOCK_K * 4;
   static constexpr int STRIDE = (BYTES + 1023) / 1024 * 1024;
-  static constexpr int PIX = S == 1 ? 4 : 2;           // adjacent output pixels per thread
+  static constexpr int PIX = PW * PART_ROWS * 8 / DW_THREADS;  // adjacent output pixels per thread: 4 / 2
 };
 
 __host__ __device__ constexpr int w_stages(int block_n) { return block_n >= 256 ? 2 : (block_n >= 128 ? 3 : 4); }
@@ -111,23 +114,22 @@ template <int S, int ACT>
 __device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t table, int t, int part, int kb,
                                         const SepParams& p, bool has_bias) {
   using R = Raw<S>;
-  constexpr int QUADS = R::CH / 4;
   constexpr int GROUPS_PER_ROW = PW / R::PIX;
   constexpr int WIN = (R::PIX - 1) * S + 3;
-  const int q = t % QUADS;
-  const int g = t / QUADS;
-  const int r = g / GROUPS_PER_ROW;
+  const int q = t & 7;                         // channel quad of the k-block
+  const int g = t >> 3;                        // 0..31
+  const int r = g / GROUPS_PER_ROW;            // row inside this part
   const int c0 = (g % GROUPS_PER_ROW) * R::PIX;
-  const int ch = kb * BLOCK_K + part * R::CH + q * 4;
+  const int ch = kb * BLOCK_K + q * 4;
   float4 acc[R::PIX];
 #pragma unroll
   for (int j = 0; j < R::PIX; j++) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
   for (int dr = 0; dr < 3; dr++) {
-    const uint32_t row = raw + (uint32_t)(((r * S + dr) * R::COLS + c0 * S) * (R::CH * 4) + q * 16);
+    const uint32_t row = raw + (uint32_t)(((r * S + dr) * R::COLS + c0 * S) * (BLOCK_K * 4) + q * 16);
     float4 in[WIN];
 #pragma unroll
-    for (int i = 0; i < WIN; i++) in[i] = lds128(row + i * (R::CH * 4));
+    for (int i = 0; i < WIN; i++) in[i] = lds128(row + i * (BLOCK_K * 4));
 #pragma unroll
     for (int wc = 0; wc < 3; wc++) {
       const float4 f = lds128(table + (uint32_t)(((dr * 3 + wc) * p.C + ch) * 4));
@@ -142,7 +144,7 @@ __device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t 
     }
   }
   const float4 b = lds128(table + (uint32_t)((9 * p.C + ch) * 4));
-  const int chunk = part * QUADS + q;  // 16-byte chunk of the 128-byte A row
+  const int m0 = (part * R::PART_ROWS + r) * PW + c0;  // first of this thread's rows of the A tile
 #pragma unroll
   for (int j = 0; j < R::PIX; j++) {
     float4 o = acc[j];
@@ -151,7 +153,7 @@ __device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t 
     o.y = dw_activate<ACT>(o.y, p.dw_lo, p.dw_hi);
     o.z = dw_activate<ACT>(o.z, p.dw_lo, p.dw_hi);
     o.w = dw_activate<ACT>(o.w, p.dw_lo, p.dw_hi);
-    sts128(a_tile + swz(r * PW + c0 + j, chunk * 16), o);
+    sts128(a_tile + swz(m0 + j, q * 16), o);
   }
 }
 
@@ -250,8 +252,8 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
             ok = mbar_wait(smem_u32(&raw_empty[rs]), rphase ^ 1, abort_flag, p.status, 12);
             if (!ok) break;
             mbar_arrive_expect_tx(smem_u32(&raw_full[rs]), R::BYTES);
-            tma_load_4d(smem_u32(raw + rs * R::STRIDE), &map_x, smem_u32(&raw_full[rs]),
-                        kb * BLOCK_K + part * R::CH, x0, y0, b);
+            tma_load_4d(smem_u32(raw + rs * R::STRIDE), &map_x, smem_u32(&raw_full[rs]), kb * BLOCK_K, x0,
+                        y0 + part * R::PART_ROWS * S, b);
             if (++rs == RAW_STAGES) { rs = 0; rphase ^= 1; }
           }
         }
@@ -466,8 +468,8 @@ int launch_sepconv_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d
   CUtensorMap mx, mw, my;
   const uint64_t xd[4] = {(uint64_t)C, (uint64_t)dw.inWidth, (uint64_t)dw.inHeight, (uint64_t)dw.batchSize};
   const uint64_t xs[3] = {(uint64_t)C * 4, (uint64_t)dw.inWidth * C * 4, (uint64_t)dw.inHeight * dw.inWidth * C * 4};
-  const uint32_t xb1[4] = {(uint32_t)Raw<1>::CH, (uint32_t)Raw<1>::COLS, (uint32_t)Raw<1>::ROWS, 1};
-  const uint32_t xb2[4] = {(uint32_t)Raw<2>::CH, (uint32_t)Raw<2>::COLS, (uint32_t)Raw<2>::ROWS, 1};
+  const uint32_t xb1[4] = {BLOCK_K, (uint32_t)Raw<1>::COLS, (uint32_t)Raw<1>::ROWS, 1};
+  const uint32_t xb2[4] = {BLOCK_K, (uint32_t)Raw<2>::COLS, (uint32_t)Raw<2>::ROWS, 1};
   const uint64_t wd[2] = {(uint64_t)kp, (uint64_t)N};
   const uint64_t ws[1] = {(uint64_t)kp * 4};
   const uint32_t wb[2] = {BLOCK_K, (uint32_t)block_n};
