@@ -11,8 +11,8 @@ scaling, no collective on the data path; torch.distributed is used only for the 
 the max-over-ranks of the timings).  `--workload cfg4` runs config 4 instead (float32 weights,
 batch 64 per GPU).
 
-A step is one forward pass over the rank's shard: 30 kernel launches replayed from a CUDA
-graph.  `value` is images/s with the images resident in device memory; `e2e` repeats the
+A step is one forward pass over the rank's shard: 26 kernel launches (30 with --forward
+layerwise) replayed from a CUDA graph.  `value` is images/s with the images resident in device memory; `e2e` repeats the
 measurement through the public API with the shard in pinned host memory, copying it to the
 device and reading the probabilities back inside every timed step.
 """
@@ -45,6 +45,10 @@ def parse_args():
     ap.add_argument("--dequant", default="cached", choices=["cached", "in-loop"],
                     help="uint8 weights of the GEMM layers: expanded once into cached tf32 planes, or "
                          "kept uint8 and dequantised in shared memory inside the GEMM main loop")
+    ap.add_argument("--forward", default="separable", choices=["separable", "layerwise"],
+                    help="separable: each depthwise + pointwise pair is one fusedSeparableConv2d call (the "
+                         "first four pairs then run as single kernels that keep the depthwise result on "
+                         "chip); layerwise: one kernel per layer (30 launches)")
     ap.add_argument("--global-batch", type=int, default=0, help="override the workload's batch")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -206,7 +210,9 @@ def run_reference(args):
 
 
 # ---- this backend -------------------------------------------------------------------------------
-KERNEL_FAMILY = {"gemm_tcgen05 (TF32)": "gemm_tcgen05", "gemm_tcgen05 (3xTF32)": "gemm_tcgen05",
+KERNEL_FAMILY = {"separableConv2d (fused dw3x3 s1 + pw, TF32)": "separable_fused",
+                 "separableConv2d (fused dw3x3 s2 + pw, TF32)": "separable_fused",
+                 "gemm_tcgen05 (TF32)": "gemm_tcgen05", "gemm_tcgen05 (3xTF32)": "gemm_tcgen05",
                  "gemm_tcgen05 (TF32, uint8 weights)": "gemm_tcgen05",
                  "gemm_tcgen05 (3xTF32, uint8 weights)": "gemm_tcgen05",
                  "conv2d_tcgen05 (TF32)": "conv2d_tcgen05", "conv2d_tcgen05 (3xTF32)": "conv2d_tcgen05",
@@ -227,6 +233,7 @@ def run_cuda(args):
 
     params = mobilenet.make_weights(cfg["seed"], quantized=cfg["quantized"], gain=cfg["gain"])
     net = mobilenet.MobileNetV1(params, bk)
+    forward = net.forward_separable if args.forward == "separable" else net.forward_fused
     x_host = mobilenet.make_input(cfg["seed"], per, offset=0 if d.world == 1 else 0)
     # every rank draws its own slice of the global batch: different seeds per rank keep the
     # generation cheap (skipping d.rank * per images of one stream would cost minutes)
@@ -236,7 +243,7 @@ def run_cuda(args):
     x = ops.tensor(x_host)
 
     # eager pass: fills the weight-repack cache and the allocator's free lists
-    logits, probs = net.forward_fused(x)
+    logits, probs = forward(x)
     first = probs.dataSync()
     assert np.isfinite(first).all()
     logits.dispose()
@@ -245,15 +252,14 @@ def run_cuda(args):
     graph = None
     if not args.no_graph:
         bk.graphBegin()
-        logits, probs = net.forward_fused(x)
+        logits, probs = forward(x)
         graph = bk.graphEnd()
-    launches_per_step = 30
 
     def step():
         if graph is not None:
             bk.graphLaunch(graph)
             return None
-        lg, pr = net.forward_fused(x)
+        lg, pr = forward(x)
         lg.dispose()
         return pr
 
@@ -287,17 +293,20 @@ def run_cuda(args):
     prof_steps = min(args.steps, 5)
     # one untimed eager pass first: the graph keeps its own buffers, so the eager path has to
     # fill the allocator's free lists again (cudaMalloc must not land inside a measured launch)
-    lg, pr = net.forward_fused(x)
+    before = bk.launchCount()
+    lg, pr = forward(x)
+    launches_per_step = bk.launchCount() - before
     lg.dispose()
     pr.dispose()
     bk.sync()
     bk.profileBegin(launches_per_step * prof_steps + 8)
     for _ in range(prof_steps):
-        lg, pr = net.forward_fused(x)
+        lg, pr = forward(x)
         lg.dispose()
         pr.dispose()
     rows = bk.profileEnd()
-    layer_bytes = mobilenet.layer_algorithmic_bytes(per, cfg["quantized"])
+    layer_bytes = mobilenet.launch_algorithmic_bytes(per, cfg["quantized"],
+                                                     [name for name, _ in rows[:launches_per_step]])
     fam = {}
     for i, (name, ms) in enumerate(rows):
         f = KERNEL_FAMILY.get(name, name)
@@ -343,7 +352,7 @@ def run_cuda(args):
     graphs, outs = [graph], [probs if graph is not None else None]
     if graph is not None:
         bk.graphBegin()
-        lg2, pr2 = net.forward_fused(xs[1])
+        lg2, pr2 = forward(xs[1])
         graphs.append(bk.graphEnd())
         outs.append(pr2)
 
@@ -358,7 +367,7 @@ def run_cuda(args):
                 bk.graphLaunch(graphs[cur], inputs=[xs[cur]])
                 res = outs[cur].dataSync()
             else:
-                lg, pr = net.forward_fused(xs[cur])
+                lg, pr = forward(xs[cur])
                 res = pr.dataSync()
                 lg.dispose()
                 pr.dispose()
@@ -396,7 +405,8 @@ def run_cuda(args):
             "scaling": cfg["scaling"], "vs_baseline": None, "dtype": "tf32" if args.math == "tf32" else "3xtf32",
             "data": "synthetic",
             "config": {"workload": cfg["name"], "global_batch": cfg["global_batch"], "per_gpu_batch": per,
-                       "math_mode": args.math, "dequant": args.dequant, "launch": "eager" if graph is None else "cuda-graph replay",
+                       "math_mode": args.math, "dequant": args.dequant, "forward": args.forward,
+                       "launches_per_step": int(launches_per_step), "launch": "eager" if graph is None else "cuda-graph replay",
                        "l2": "every step streams %.1f GB of activations per GPU (> 126 MB L2) between reuses"
                              % (step_bytes / 1e9)},
             "roofline": roofline, "net_hbm": {"algorithmic_gb_per_step": step_bytes / 1e9,

@@ -239,6 +239,35 @@ def layer_algorithmic_bytes(batch, quantized):
 
 
 
+def launch_algorithmic_bytes(batch, quantized, kernel_names):
+    """Algorithmic bytes of each launch of one forward pass given the names of the kernels it
+    launched, in order: a launch whose name starts with 'separableConv2d (fused' covers a
+    depthwise + pointwise pair and counts the pair's input, output, filters and biases (the
+    intermediate tensor does not exist); every other launch counts its own layer."""
+    per_layer = layer_algorithmic_bytes(batch, quantized)
+    specs = layer_specs()
+    out, i = [], 0
+    h = w = 224
+    c = 3
+    sizes = []  # (in elements, out elements) per image for the 27 conv layers
+    for name, kind, shape, s in specs[:-1]:
+        ho, wo = -(-h // s), -(-w // s)
+        co = c if kind == "dw" else shape[3]
+        sizes.append((h * w * c, ho * wo * co))
+        h, w, c = ho, wo, co
+    for name in kernel_names:
+        if name.startswith("separableConv2d (fused"):
+            assert specs[i][1] == "dw" and specs[i + 1][1] == "conv", "fused launch out of place"
+            mid = sizes[i][1]
+            out.append(per_layer[i] + per_layer[i + 1] - 2 * 4 * batch * mid)
+            i += 2
+        else:
+            out.append(per_layer[i])
+            i += 1
+    assert i == len(per_layer), "kernel list does not cover the network"
+    return out
+
+
 def algorithmic_bytes_per_image(quantized=False):
     """Bytes one image moves if every tensor is touched once and epilogues are fused:
     4*(|x| + |y|) per layer; weights are counted separately by weight_bytes()."""

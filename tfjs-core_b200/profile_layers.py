@@ -1,9 +1,10 @@
 #!/usr/bin/env python3
 """Per-layer device times of one fused MobileNetV1 forward on the cuda backend.
 
-    python tfjs-core_b200/profile_layers.py [batch] [tf32|3xtf32] [q|q-in-loop]
+    python tfjs-core_b200/profile_layers.py [batch] [tf32|3xtf32] [f|q|q-in-loop] [separable|layerwise]
 
-Prints, for each of the 30 launches, the kernel name, the best device time over a few passes
+Prints, for each launch of one forward pass (26 with the fused depthwise + pointwise blocks,
+30 with `layerwise`), the kernel name, the best device time over a few passes
 (events recorded between launches on the context's stream), the layer's algorithmic bytes and
 the bandwidth that corresponds to.  `q` stores the filters as uint8 (BASELINE config 5); `q-in-loop` also keeps the GEMM weights uint8 and dequantises them inside the GEMM main loop.  This is
 also the small-case command the ncu captures summarised under profiles/ were taken with.
@@ -22,6 +23,7 @@ def main():
     mode = sys.argv[2] if len(sys.argv) > 2 else "tf32"
     quantized = len(sys.argv) > 3 and sys.argv[3] in ("q", "q-in-loop")
     in_loop = len(sys.argv) > 3 and sys.argv[3] == "q-in-loop"
+    layerwise = len(sys.argv) > 4 and sys.argv[4] == "layerwise"
     reps = 4
     bk = tf.BackendCuda(0, mode)
     tf.ENGINE.registerBackend("profile-cuda", lambda: bk, 10)
@@ -29,25 +31,32 @@ def main():
     bk.setOption("dequant_in_gemm", 1 if in_loop else 0)
     params = mobilenet.make_weights(4 if quantized else 3, quantized=quantized, gain=1.5)
     net = mobilenet.MobileNetV1(params, bk)
+    forward = net.forward_fused if layerwise else net.forward_separable
     x = ops.tensor(mobilenet.make_input(3, batch))
     for _ in range(2):
-        logits, probs = net.forward_fused(x)
+        before = bk.launchCount()
+        logits, probs = forward(x)
+        n = bk.launchCount() - before
         probs.dataSync()
         logits.dispose()
         probs.dispose()
-    bk.profileBegin(40 * reps)
+    bk.profileBegin((n + 2) * reps)
     for _ in range(reps):
-        logits, probs = net.forward_fused(x)
+        logits, probs = forward(x)
         logits.dispose()
         probs.dispose()
     rows = bk.profileEnd()
-    layer_bytes = mobilenet.layer_algorithmic_bytes(batch, quantized)
+    kernel_names = [name for name, _ in rows[:n]]
+    layer_bytes = mobilenet.launch_algorithmic_bytes(batch, quantized, kernel_names)
     names = [s[0] for s in mobilenet.layer_specs()][:-1] + ["avgpool", "fc", "softmax"]
-    total = 0.0
-    for i in range(30):
-        ms = min(rows[i + 30 * r][1] for r in range(reps))
+    total, layer = 0.0, 0
+    for i in range(n):
+        ms = min(rows[i + n * r][1] for r in range(reps))
         total += ms
-        print(f"{names[i]:8s} {rows[i][0]:28s} {ms * 1e3:9.1f} us {layer_bytes[i] / 1e6:9.1f} MB "
+        fused = kernel_names[i].startswith("separableConv2d (fused")
+        label = names[layer] + "+" + names[layer + 1] if fused else names[layer]
+        layer += 2 if fused else 1
+        print(f"{label:9s} {kernel_names[i]:44s} {ms * 1e3:9.1f} us {layer_bytes[i] / 1e6:9.1f} MB "
               f"{layer_bytes[i] / ms / 1e6:7.0f} GB/s")
     print(f"total {total:.3f} ms  {batch / total * 1e3:.0f} img/s  "
           f"{sum(layer_bytes) / total / 1e6:.0f} GB/s algorithmic")
