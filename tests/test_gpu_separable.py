@@ -167,3 +167,38 @@ def test_mobilenet_with_fused_blocks_equals_the_layerwise_forward(tf):
     finally:
         net.dispose()
         bk.setMathMode("3xtf32")
+
+
+# ---- the 3-channel 3x3 stem through the same kernel skeleton (window TMA + on-chip im2col) ----
+@pytest.mark.parametrize("b,h,w,n,stride,pad", [
+    (2, 224, 224, 32, 2, "same"),   # the network's stem: pad right / bottom only
+    (1, 20, 24, 40, 1, "same"),     # pad left 1: the window starts 1 float past a 16-byte boundary
+    (3, 17, 16, 8, 2, "valid"),
+    (2, 9, 12, 256, 2, "same"),     # odd height: pad top 1, left 0... widest N
+    (1, 33, 40, 64, 1, "valid"),
+])
+def test_rgb_stem_conv(tf, b, h, w, n, stride, pad):
+    bk = tf.ENGINE.backend
+    bk.setMathMode("tf32")
+    try:
+        rng = _rng(h * w + n)
+        # small integers are exact in tf32: the result must equal the oracle's bit for bit
+        x = rng.integers(-4, 5, (b, h, w, 3)).astype(np.float32)
+        wt = rng.integers(-3, 4, (3, 3, 3, n)).astype(np.float32)
+        bias = rng.integers(-5, 6, n).astype(np.float32)
+        ci = oracle.compute_conv2d_info(x.shape, wt.shape, stride, 1, pad)
+        want = oracle.fused_conv2d(x, wt, ci, bias=bias, activation="relu")
+        before = bk.launchCount()
+        got = tf.ops.fused_conv2d(tf.ops.tensor(x), tf.ops.tensor(wt), stride, pad, bias=tf.ops.tensor(bias),
+                                  activation="relu")
+        assert bk.launchCount() - before == 2  # weight repack + one kernel
+        assert np.array_equal(got.dataSync().reshape(want.shape), want)
+        # and real-valued data within the TF32 bound
+        x = rng.uniform(-1, 1, (b, h, w, 3)).astype(np.float32)
+        wt = rng.normal(0, 0.3, (3, 3, 3, n)).astype(np.float32)
+        want = oracle.fused_conv2d(x, wt, ci, bias=bias, activation="relu")
+        got = tf.ops.fused_conv2d(tf.ops.tensor(x), tf.ops.tensor(wt), stride, pad, bias=tf.ops.tensor(bias),
+                                  activation="relu")
+        assert rel_err(got.dataSync().reshape(want.shape), want) <= 1e-3
+    finally:
+        bk.setMathMode("3xtf32")

@@ -233,6 +233,15 @@ extern "C" int tfjs_cuda_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_te
                          (float*)o->ptr, ci->outChannels, e);
   // Everything else with Cin % 4 == 0 (or the 3-channel, 3-wide stem) is an implicit GEMM: the
   // A tile is gathered from the image by the kernel itself, K = fH * fW * Cin.
+  // The 3-channel 3x3 stem: the image window of a patch arrives by TMA and is rearranged into
+  // im2col rows in shared memory (TF32; other modes take the gather path below).
+  if (ctx->use_tensor_cores && conv_rgb_tcgen05_supported(*ci, e.activation, ctx->math_mode)) {
+    PackedWeights pw;
+    bool temporary;
+    rc = packed_weights(ctx, w, 0, 27, ci->outChannels, false, true, &pw, &temporary, 9, 10, 32);
+    if (rc) return rc;
+    return launch_conv_rgb_tcgen05(ctx, (const float*)x->ptr, *ci, pw.hi, pw.kp, (float*)o->ptr, e);
+  }
   const int mode = ctx->use_tensor_cores ? tcgen05_conv_mode(*ci) : 0;
   if (mode) {
     const int64_t K = (int64_t)ci->filterHeight * ci->filterWidth * ci->inChannels;

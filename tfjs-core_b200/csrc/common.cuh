@@ -228,6 +228,9 @@ bool sepconv_tcgen05_supported(const tfjs_conv2d_info& dw, int64_t N, int dw_act
 int launch_sepconv_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& dw, const float* dw_filter,
                            const EpilogueArgs& dw_epi, const float* w_hi, int64_t kp, float* y, int64_t N,
                            const EpilogueArgs& pw_epi);
+bool conv_rgb_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode);
+int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& ci, const float* w_hi,
+                            int64_t kp, float* y, const EpilogueArgs& epi);
 // conv.cu
 int launch_conv2d_direct(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* y,
                          const tfjs_conv2d_info& ci, const EpilogueArgs& epi);

@@ -45,24 +45,32 @@ constexpr int SMEM_LIMIT = 232448;
 // One raw stage = the input window of PART_ROWS patch rows x 16 columns x 32 channels (every
 // pixel a full 128-byte line, so that the window reads are free of bank conflicts).  Stride 2
 // doubles the window, so its patch is loaded as two halves of 4 rows.
-template <int S>
+constexpr int MODE_DW = 0;   // depthwise 3x3 over 32-channel k-blocks feeding the GEMM
+constexpr int MODE_RGB = 1;  // dense 3x3 convolution of a 3-channel image: the window rows are turned
+                             // into im2col rows (K' = 10 * filter row + 3 * filter column + channel)
+
+template <int S, int MODE>
 struct Raw {
-  static constexpr int PARTS = S;                      // raw stages per k-block
-  static constexpr int PART_ROWS = PH / PARTS;         // patch rows per raw stage
+  static constexpr int PARTS = MODE == MODE_DW ? S : 1;  // raw stages per k-block
+  static constexpr int PART_ROWS = PH / PARTS;           // patch rows per raw stage
   static constexpr int ROWS = (PART_ROWS - 1) * S + 3;
   static constexpr int COLS = (PW - 1) * S + 3;
-  static constexpr int BYTES = ROWS * COLS * BLOCK_K * 4;
+  // floats per window row: 32 channels per pixel, or (RGB) 3 per pixel plus up to 3 floats of
+  // slack in front so that the copy can start on a 16-byte boundary, rounded up to 16 bytes
+  static constexpr int ROW_FLOATS = MODE == MODE_DW ? COLS * BLOCK_K : (COLS * 3 + 3 + 3) / 4 * 4;
+  static constexpr int BYTES = ROWS * ROW_FLOATS * 4;
   static constexpr int STRIDE = (BYTES + 1023) / 1024 * 1024;
   static constexpr int PIX = PW * PART_ROWS * 8 / DW_THREADS;  // adjacent output pixels per thread: 4 / 2
 };
 
 __host__ __device__ constexpr int w_stages(int block_n) { return block_n >= 256 ? 2 : (block_n >= 128 ? 3 : 4); }
-template <int S>
+__host__ __device__ constexpr int epi_arrivals(int block_n) { return block_n >= 64 ? EPI_WARPS : 4; }
+template <int S, int MODE>
 __host__ __device__ constexpr int raw_stages(int block_n) {
   int left = SMEM_LIMIT - 1024 - A_SLOTS * A_TILE_BYTES - w_stages(block_n) * block_n * BLOCK_K * 4 -
              C_STAGING_BYTES - BIAS_STAGING_BYTES - DW_TABLE_BYTES - BARRIER_BYTES;
-  int n = left / Raw<S>::STRIDE;
-  return n > 4 ? 4 : n;
+  int n = left / Raw<S, MODE>::STRIDE;
+  return n > (MODE == MODE_DW ? 4 : 8) ? (MODE == MODE_DW ? 4 : 8) : n;
 }
 
 struct SepParams {
@@ -75,6 +83,7 @@ struct SepParams {
   int dw_act;
   float dw_lo, dw_hi;
   EpilogueArgs epi;                 // of the pointwise convolution
+  int rgb_off;                      // MODE_RGB: floats between the 16-byte aligned copy start and the window
   int* status;
 };
 
@@ -84,6 +93,18 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
+                                            int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ float lds32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
 }
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2,
                                              int c3) {
@@ -113,7 +134,7 @@ __device__ __forceinline__ float dw_activate(float v, float lo, float hi) {
 template <int S, int ACT>
 __device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t table, int t, int part, int kb,
                                         const SepParams& p, bool has_bias) {
-  using R = Raw<S>;
+  using R = Raw<S, MODE_DW>;
   constexpr int GROUPS_PER_ROW = PW / R::PIX;
   constexpr int WIN = (R::PIX - 1) * S + 3;
   const int q = t & 7;                         // channel quad of the k-block
@@ -157,16 +178,41 @@ __device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t 
   }
 }
 
-template <int BLOCK_N, int S>
+// MODE_RGB: thread t < 128 turns the 3 x 9 window floats of output pixel t (3 filter rows of 3 pixels
+// x 3 channels, contiguous in the NHWC image) into row t of the A tile, in the K' order the repacked
+// filter uses: floats 10*wr + 3*wc + ci, with zeros at 9, 19 and 29..31.
+template <int S>
+__device__ __forceinline__ void rgb_part(uint32_t raw, uint32_t a_tile, int t, const SepParams& p) {
+  using R = Raw<S, MODE_RGB>;
+  if (t >= 128) return;
+  const int r = t / PW, c = t % PW;
+  float v[3][9];
+#pragma unroll
+  for (int dr = 0; dr < 3; dr++) {
+    const uint32_t row = raw + (uint32_t)(((r * S + dr) * R::ROW_FLOATS + p.rgb_off + c * S * 3) * 4);
+#pragma unroll
+    for (int j = 0; j < 9; j++) v[dr][j] = lds32(row + j * 4);
+  }
+  sts128(a_tile + swz(t, 0), make_float4(v[0][0], v[0][1], v[0][2], v[0][3]));
+  sts128(a_tile + swz(t, 16), make_float4(v[0][4], v[0][5], v[0][6], v[0][7]));
+  sts128(a_tile + swz(t, 32), make_float4(v[0][8], 0.f, v[1][0], v[1][1]));
+  sts128(a_tile + swz(t, 48), make_float4(v[1][2], v[1][3], v[1][4], v[1][5]));
+  sts128(a_tile + swz(t, 64), make_float4(v[1][6], v[1][7], v[1][8], 0.f));
+  sts128(a_tile + swz(t, 80), make_float4(v[2][0], v[2][1], v[2][2], v[2][3]));
+  sts128(a_tile + swz(t, 96), make_float4(v[2][4], v[2][5], v[2][6], v[2][7]));
+  sts128(a_tile + swz(t, 112), make_float4(v[2][8], 0.f, 0.f, 0.f));
+}
+
+template <int BLOCK_N, int S, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                        const __grid_constant__ CUtensorMap map_y, SepParams p) {
-  using R = Raw<S>;
+  using R = Raw<S, MODE>;
   constexpr int W_STAGES = w_stages(BLOCK_N);
-  constexpr int RAW_STAGES = raw_stages<S>(BLOCK_N);
+  constexpr int RAW_STAGES = raw_stages<S, MODE>(BLOCK_N);
   static_assert(RAW_STAGES >= 2, "the input ring needs two stages");
   constexpr int W_STAGE_BYTES = BLOCK_N * BLOCK_K * 4;
-  constexpr uint32_t TMEM_COLS = 2 * BLOCK_N < 32 ? 32 : 2 * BLOCK_N;
+  constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // 64 .. 512
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -206,7 +252,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     }
     for (int a = 0; a < 2; a++) {
       mbar_init(smem_u32(&tmem_full_bar[a]), 1);
-      mbar_init(smem_u32(&tmem_empty_bar[a]), EPI_WARPS);
+      mbar_init(smem_u32(&tmem_empty_bar[a]), epi_arrivals(BLOCK_N));
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -219,7 +265,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   // depthwise filter taps and bias of every channel: [tap][C], then the bias row
-  {
+  if (MODE == MODE_DW) {
     float* tab = reinterpret_cast<float*>(table);
     for (int i = threadIdx.x; i < 9 * p.C; i += THREADS) tab[i] = __ldg(p.dw_filter + i);
     for (int i = threadIdx.x; i < p.C; i += THREADS)
@@ -252,8 +298,12 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
             ok = mbar_wait(smem_u32(&raw_empty[rs]), rphase ^ 1, abort_flag, p.status, 12);
             if (!ok) break;
             mbar_arrive_expect_tx(smem_u32(&raw_full[rs]), R::BYTES);
-            tma_load_4d(smem_u32(raw + rs * R::STRIDE), &map_x, smem_u32(&raw_full[rs]), kb * BLOCK_K, x0,
-                        y0 + part * R::PART_ROWS * S, b);
+            if (MODE == MODE_DW)
+              tma_load_4d(smem_u32(raw + rs * R::STRIDE), &map_x, smem_u32(&raw_full[rs]), kb * BLOCK_K, x0,
+                          y0 + part * R::PART_ROWS * S, b);
+            else  // image rows as runs of W*3 floats; the copy starts rgb_off floats before the window
+              tma_load_3d(smem_u32(raw + rs * R::STRIDE), &map_x, smem_u32(&raw_full[rs]), x0 * 3 - p.rgb_off,
+                          y0, b);
             if (++rs == RAW_STAGES) { rs = 0; rphase ^= 1; }
           }
         }
@@ -309,10 +359,14 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
           ok = mbar_wait(smem_u32(&raw_full[rs]), rphase, abort_flag, p.status, 17);
           if (!ok) break;
           const uint32_t raw_s = smem_u32(raw + rs * R::STRIDE);
-          switch (p.dw_act) {
-            case TFJS_ACT_RELU: dw_part<S, TFJS_ACT_RELU>(raw_s, a_s, table_s, t, part, kb, p, has_bias); break;
-            case TFJS_ACT_CLIP: dw_part<S, TFJS_ACT_CLIP>(raw_s, a_s, table_s, t, part, kb, p, has_bias); break;
-            default: dw_part<S, TFJS_ACT_LINEAR>(raw_s, a_s, table_s, t, part, kb, p, has_bias); break;
+          if (MODE == MODE_RGB) {
+            rgb_part<S>(raw_s, a_s, t, p);
+          } else {
+            switch (p.dw_act) {
+              case TFJS_ACT_RELU: dw_part<S, TFJS_ACT_RELU>(raw_s, a_s, table_s, t, part, kb, p, has_bias); break;
+              case TFJS_ACT_CLIP: dw_part<S, TFJS_ACT_CLIP>(raw_s, a_s, table_s, t, part, kb, p, has_bias); break;
+              default: dw_part<S, TFJS_ACT_LINEAR>(raw_s, a_s, table_s, t, part, kb, p, has_bias); break;
+            }
           }
           mbar_arrive(smem_u32(&raw_empty[rs]));  // this thread has read all it needs of the window
           if (++rs == RAW_STAGES) { rs = 0; rphase ^= 1; }
@@ -328,10 +382,10 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     // Warps w and w+4 share TMEM lane quarter w%4 (patch rows 2*(w%4), 2*(w%4)+1) and split the
     // 32-channel chunks of the tile between them.
     constexpr int CHUNKS = BLOCK_N / 32;
-    constexpr int MY_CHUNKS = CHUNKS / 2;
-    static_assert(CHUNKS >= 2, "BLOCK_N >= 64");
+    constexpr int MY_CHUNKS = CHUNKS >= 2 ? CHUNKS / 2 : 1;
     const int quarter = warp & 3;
     const int half = warp >> 2;
+    if (CHUNKS >= 2 || half == 0) {
     uint8_t* stage_buf = c_stage + warp * C_CHUNK_BYTES;
     float* bias_s = reinterpret_cast<float*>(bias_stage + warp * 128);
     const bool has_bias = p.epi.bias != nullptr;
@@ -346,7 +400,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       float bias_l[MY_CHUNKS];
 #pragma unroll
       for (int i = 0; i < MY_CHUNKS; i++) {
-        const int cl = (2 * i + half) * 32 + lane;
+        const int cl = (CHUNKS >= 2 ? 2 * i + half : 0) * 32 + lane;
         bias_l[i] = 0.f;
         if (has_bias) bias_l[i] = p.epi.bias_scalar ? __ldg(p.epi.bias) : (cl < p.N ? __ldg(p.epi.bias + cl) : 0.f);
       }
@@ -358,7 +412,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       bool released = false;
 #pragma unroll
       for (int i = 0; i < MY_CHUNKS; i++) {
-        const int chunk = 2 * i + half;
+        const int chunk = CHUNKS >= 2 ? 2 * i + half : 0;
         const int c0 = chunk * 32;
         if (c0 >= p.N) break;
         uint32_t r[32];
@@ -401,6 +455,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
         if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[acc]));
       }
     }
+    }
     if (lane == 0) tma_store_wait_all();
   }
 
@@ -414,14 +469,14 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   }
 }
 
-template <int BLOCK_N, int S>
+template <int BLOCK_N, int S, int MODE>
 int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my,
                    const SepParams& p) {
   constexpr int smem_bytes = 1024 + A_SLOTS * A_TILE_BYTES + w_stages(BLOCK_N) * BLOCK_N * BLOCK_K * 4 +
-                             C_STAGING_BYTES + raw_stages<S>(BLOCK_N) * Raw<S>::STRIDE + DW_TABLE_BYTES +
-                             BIAS_STAGING_BYTES + BARRIER_BYTES;
+                             C_STAGING_BYTES + raw_stages<S, MODE>(BLOCK_N) * Raw<S, MODE>::STRIDE +
+                             DW_TABLE_BYTES + BIAS_STAGING_BYTES + BARRIER_BYTES;
   static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
-  auto kernel = sepconv_tcgen05_kernel<BLOCK_N, S>;
+  auto kernel = sepconv_tcgen05_kernel<BLOCK_N, S, MODE>;
   static bool configured[8] = {false};
   if (!configured[ctx->device & 7]) {
     TFJS_CHECK_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
@@ -429,17 +484,20 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap&
   }
   const int grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
   kernel<<<grid, THREADS, smem_bytes, ctx->stream>>>(mx, mw, my, p);
+  if (MODE == MODE_RGB) return post_launch(ctx, "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32)");
   return post_launch(ctx, S == 1 ? "separableConv2d (fused dw3x3 s1 + pw, TF32)"
                                  : "separableConv2d (fused dw3x3 s2 + pw, TF32)");
 }
 
-template <int S>
+template <int S, int MODE>
 int launch_stride(tfjs_cuda_ctx* ctx, int block_n, const CUtensorMap& mx, const CUtensorMap& mw,
                   const CUtensorMap& my, const SepParams& p) {
   switch (block_n) {
-    case 64: return launch_variant<64, S>(ctx, mx, mw, my, p);
-    case 128: return launch_variant<128, S>(ctx, mx, mw, my, p);
-    default: return launch_variant<256, S>(ctx, mx, mw, my, p);
+    case 32:
+      if (MODE == MODE_RGB) return launch_variant<32, S, MODE_RGB>(ctx, mx, mw, my, p);  // else falls through
+    case 64: return launch_variant<64, S, MODE>(ctx, mx, mw, my, p);
+    case 128: return launch_variant<128, S, MODE>(ctx, mx, mw, my, p);
+    default: return launch_variant<256, S, MODE>(ctx, mx, mw, my, p);
   }
 }
 
@@ -468,8 +526,8 @@ int launch_sepconv_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d
   CUtensorMap mx, mw, my;
   const uint64_t xd[4] = {(uint64_t)C, (uint64_t)dw.inWidth, (uint64_t)dw.inHeight, (uint64_t)dw.batchSize};
   const uint64_t xs[3] = {(uint64_t)C * 4, (uint64_t)dw.inWidth * C * 4, (uint64_t)dw.inHeight * dw.inWidth * C * 4};
-  const uint32_t xb1[4] = {BLOCK_K, (uint32_t)Raw<1>::COLS, (uint32_t)Raw<1>::ROWS, 1};
-  const uint32_t xb2[4] = {BLOCK_K, (uint32_t)Raw<2>::COLS, (uint32_t)Raw<2>::ROWS, 1};
+  const uint32_t xb1[4] = {BLOCK_K, (uint32_t)Raw<1, MODE_DW>::COLS, (uint32_t)Raw<1, MODE_DW>::ROWS, 1};
+  const uint32_t xb2[4] = {BLOCK_K, (uint32_t)Raw<2, MODE_DW>::COLS, (uint32_t)Raw<2, MODE_DW>::ROWS, 1};
   const uint64_t wd[2] = {(uint64_t)kp, (uint64_t)N};
   const uint64_t ws[1] = {(uint64_t)kp * 4};
   const uint32_t wb[2] = {BLOCK_K, (uint32_t)block_n};
@@ -503,5 +561,64 @@ int launch_sepconv_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d
   p.dw_hi = dw_epi.clip_hi;
   p.epi = pw_epi;
   p.status = ctx->d_status;
-  return S == 1 ? launch_stride<1>(ctx, block_n, mx, mw, my, p) : launch_stride<2>(ctx, block_n, mx, mw, my, p);
+  p.rgb_off = 0;
+  return S == 1 ? launch_stride<1, MODE_DW>(ctx, block_n, mx, mw, my, p)
+                : launch_stride<2, MODE_DW>(ctx, block_n, mx, mw, my, p);
+}
+
+// Dense 3x3 convolution of a 3-channel NHWC image (the network's stem), stride 1 or 2, in TF32:
+// same kernel skeleton, the window arrives by TMA and is rearranged into im2col rows on chip.
+// `w_hi` is the filter repacked with each filter row padded to 10 floats ([N, 32]).
+bool conv_rgb_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode) {
+  return math_mode == TFJS_MATH_TF32 && ci.inChannels == 3 && ci.filterHeight == 3 && ci.filterWidth == 3 &&
+         ci.dilationHeight == 1 && ci.dilationWidth == 1 && ci.strideHeight == ci.strideWidth &&
+         (ci.strideHeight == 1 || ci.strideHeight == 2) && ci.inWidth % 4 == 0 && ci.outChannels >= 8 &&
+         ci.outChannels <= 256 && ci.outChannels % 4 == 0 && ci.batchSize >= 1 && ci.batchSize < 65536 &&
+         ci.outHeight >= 1 && ci.outWidth >= 1 && activation != TFJS_ACT_PRELU &&
+         tcgen05_gemm_supported(128, ci.outChannels, 32);
+}
+
+int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& ci, const float* w_hi,
+                            int64_t kp, float* y, const EpilogueArgs& epi) {
+  const int S = ci.strideHeight;
+  const int64_t N = ci.outChannels;
+  const int block_n = N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256));
+  CUtensorMap mx, mw, my;
+  const uint64_t xd[3] = {(uint64_t)ci.inWidth * 3, (uint64_t)ci.inHeight, (uint64_t)ci.batchSize};
+  const uint64_t xs[2] = {(uint64_t)ci.inWidth * 12, (uint64_t)ci.inHeight * ci.inWidth * 12};
+  const uint32_t xb1[3] = {(uint32_t)Raw<1, MODE_RGB>::ROW_FLOATS, (uint32_t)Raw<1, MODE_RGB>::ROWS, 1};
+  const uint32_t xb2[3] = {(uint32_t)Raw<2, MODE_RGB>::ROW_FLOATS, (uint32_t)Raw<2, MODE_RGB>::ROWS, 1};
+  const uint64_t wd[2] = {(uint64_t)kp, (uint64_t)N};
+  const uint64_t ws[1] = {(uint64_t)kp * 4};
+  const uint32_t wb[2] = {BLOCK_K, (uint32_t)block_n};
+  const uint64_t yd[4] = {(uint64_t)N, (uint64_t)ci.outWidth, (uint64_t)ci.outHeight, (uint64_t)ci.batchSize};
+  const uint64_t ys[3] = {(uint64_t)N * 4, (uint64_t)ci.outWidth * N * 4, (uint64_t)ci.outHeight * ci.outWidth * N * 4};
+  const uint32_t yb[4] = {32, PW, 2, 1};
+  const bool ok =
+      tma_encode_tiled(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, x, xd, xs, S == 1 ? xb1 : xb2, CU_TENSOR_MAP_SWIZZLE_NONE) &&
+      tma_encode_tiled(&mw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, w_hi, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B) &&
+      tma_encode_tiled(&my, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, y, yd, ys, yb, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!ok) return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+  SepParams p;
+  memset(&p, 0, sizeof(p));
+  p.B = ci.batchSize;
+  p.inH = ci.inHeight;
+  p.inW = ci.inWidth;
+  p.C = 3;
+  p.outH = ci.outHeight;
+  p.outW = ci.outWidth;
+  p.N = (int)N;
+  p.pad_r = ci.padTop;
+  p.pad_c = ci.padLeft;
+  p.tiles_y = (ci.outHeight + PH - 1) / PH;
+  p.tiles_x = (ci.outWidth + PW - 1) / PW;
+  p.num_tiles = ci.batchSize * p.tiles_y * p.tiles_x;
+  p.num_k_blocks = 1;
+  p.epi = epi;
+  // the window of a patch starts at float (tx*16*S - padLeft)*3 of its image row; 16*S*3 is a
+  // multiple of 4, so the distance to the 16-byte boundary below it is the same for every patch
+  p.rgb_off = ((-3 * ci.padLeft) % 4 + 4) % 4;
+  p.status = ctx->d_status;
+  return S == 1 ? launch_stride<1, MODE_RGB>(ctx, block_n, mx, mw, my, p)
+                : launch_stride<2, MODE_RGB>(ctx, block_n, mx, mw, my, p);
 }
