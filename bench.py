@@ -51,6 +51,7 @@ def parse_args():
                          "chip); layerwise: one kernel per layer (30 launches)")
     ap.add_argument("--global-batch", type=int, default=0, help="override the workload's batch")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a graph")
+    ap.add_argument("--pdl", action="store_true", help="programmatic dependent launch instead of plain stream order")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample", type=int, default=12, help="images in the cpu_baseline sample")
     ap.add_argument("--ref-threads", type=int, default=0, help="host threads of --impl reference (0 = all)")
@@ -230,6 +231,7 @@ def run_cuda(args):
     ENGINE.registerBackend("bench-cuda", lambda: bk, 10)
     assert ENGINE.setBackend("bench-cuda")
     bk.setOption("dequant_in_gemm", 1 if args.dequant == "in-loop" else 0)
+    bk.setOption("pdl", 1 if args.pdl else 0)
 
     params = mobilenet.make_weights(cfg["seed"], quantized=cfg["quantized"], gain=cfg["gain"])
     net = mobilenet.MobileNetV1(params, bk)

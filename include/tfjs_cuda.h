@@ -109,7 +109,9 @@ const char* tfjs_cuda_last_error(const tfjs_cuda_ctx* ctx);
  * (tfjs_math_mode), "use_tensor_cores" (0 forces the CUDA-core kernels), "debug_sync",
  * "dequant_in_gemm" (quantised matMul / 1x1 conv2d weights: 0, the default, expands them once
  * into cached tf32 planes; 1 keeps them uint8 in device memory and dequantises each tile in
- * shared memory inside the GEMM main loop; the results are bit-identical). */
+ * shared memory inside the GEMM main loop; the results are bit-identical), "fuse_separable"
+ * (see tfjs_cuda_separable_conv2d), "pdl" (1 launches the main kernels with programmatic stream
+ * serialization, so that a kernel's prologue overlaps its predecessor's tail; default 0). */
 int tfjs_cuda_ctx_set_option(tfjs_cuda_ctx* ctx, const char* key, double value);
 /* Blocks until all enqueued work is done; TFJS_CUDA_ERR_TIMEOUT after timeout_ms (<0: none). */
 int tfjs_cuda_ctx_sync(tfjs_cuda_ctx* ctx, int timeout_ms);

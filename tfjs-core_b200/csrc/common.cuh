@@ -96,6 +96,10 @@ struct tfjs_cuda_ctx {
   // separable_conv2d: 0 = always two kernels, 1 = one fused kernel where that is faster,
   // 2 = fused wherever the kernel takes the shape
   int fuse_separable = 1;
+  // launch the kernels that support it with programmatic stream serialization (off by default:
+  // with one persistent block per SM the next kernel's blocks cannot become resident before this
+  // kernel's blocks retire, and the measured step time is 0.5-3 % worse with it on)
+  bool use_pdl = false;
   // bookkeeping
   int64_t launch_count = 0;
   cudaEvent_t time_start = nullptr, time_stop = nullptr;
@@ -133,6 +137,25 @@ int set_error(tfjs_cuda_ctx* ctx, int code, const char* fmt, ...);
 // Called after every kernel launch: counts it and surfaces launch errors.
 int post_launch(tfjs_cuda_ctx* ctx, const char* what);
 
+// kernel<<<grid, block, smem, ctx->stream>>>(args...) with the programmatic-serialization launch
+// attribute when the context allows it (the kernel must call pdl_wait() before touching global
+// memory).  Errors surface through post_launch.
+template <typename... Params, typename... Args>
+inline void launch_ex(tfjs_cuda_ctx* ctx, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                      Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->use_pdl ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 // Allocator (context.cu).
 int ctx_alloc(tfjs_cuda_ctx* ctx, size_t nbytes, void** ptr, size_t* capacity);
 void ctx_free(tfjs_cuda_ctx* ctx, void* ptr, size_t capacity);
@@ -167,6 +190,18 @@ __device__ __forceinline__ float min_nan(float a, float b) {
   float d;
   asm("min.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
   return d;
+}
+
+// Programmatic dependent launch.  A kernel launched through launch_ex may start while the
+// kernel before it on the stream is still running; pdl_wait() blocks until that kernel (and
+// therefore everything before it) has completed and its writes are visible, and must precede
+// every access to global memory.  pdl_launch_dependents() then lets the next kernel's blocks be
+// scheduled as this kernel's blocks retire, so that its launch latency and prologue overlap
+// this kernel's tail.  It is called after pdl_wait(), which keeps the chain transitive: when a
+// kernel starts, all kernels before its predecessor have finished.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 // act(v + bias) with the NaN behaviour of MathBackendCPU: relu is Math.max(0, v) (keeps NaN),

@@ -269,6 +269,8 @@ extern "C" int tfjs_cuda_ctx_set_option(tfjs_cuda_ctx* ctx, const char* key, dou
     ctx->debug_sync = value != 0;
   } else if (!strcmp(key, "dequant_in_gemm")) {
     ctx->dequant_in_gemm = value != 0;
+  } else if (!strcmp(key, "pdl")) {
+    ctx->use_pdl = value != 0;
   } else if (!strcmp(key, "fuse_separable")) {
     TFJS_REQUIRE(ctx, value == 0 || value == 1 || value == 2, "fuse_separable must be 0, 1 or 2");
     ctx->fuse_separable = (int)value;

@@ -341,6 +341,8 @@ depthwise3x3_strip_kernel(const float* __restrict__ x, const float* __restrict__
                           float* __restrict__ y, tfjs_conv2d_info ci, EpilogueArgs epi,
                           int rows_per_strip, int cb /* channel quads per block */) {
   constexpr int IN_W = (TW - 1) * S + 3;
+  pdl_wait();
+  pdl_launch_dependents();
   extern __shared__ float4 smem_dw[];
   float4* ring_s = smem_dw;                         // [DEPTH][IN_W][128 threads]
   float4* w_s = smem_dw + DEPTH * IN_W * 128;       // [9][quads of this slice]
@@ -449,6 +451,44 @@ __global__ void global_avgpool_kernel(const float* __restrict__ x, float* __rest
   }
 }
 
+// Same pool for C % 4 == 0 and 16-byte aligned tensors: a thread owns 4 channels and keeps 7
+// 16-byte loads in flight; each channel is still summed tap by tap in float64.
+__global__ void global_avgpool_vec4_kernel(const float4* __restrict__ x, float4* __restrict__ y, int batch,
+                                           int hw, int C4) {
+  const int64_t total = (int64_t)batch * C4;
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total;
+       t += (int64_t)gridDim.x * blockDim.x) {
+    const int d = (int)(t % C4);
+    const int b = (int)(t / C4);
+    const float4* p = x + (int64_t)b * hw * C4 + d;
+    double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+    int i = 0;
+    for (; i + 7 <= hw; i += 7) {
+      float4 v[7];
+#pragma unroll
+      for (int j = 0; j < 7; j++) v[j] = __ldg(p + (int64_t)(i + j) * C4);
+#pragma unroll
+      for (int j = 0; j < 7; j++) {
+        s0 += (double)v[j].x;
+        s1 += (double)v[j].y;
+        s2 += (double)v[j].z;
+        s3 += (double)v[j].w;
+      }
+    }
+    for (; i < hw; i++) {
+      const float4 v = __ldg(p + (int64_t)i * C4);
+      s0 += (double)v.x;
+      s1 += (double)v.y;
+      s2 += (double)v.z;
+      s3 += (double)v.w;
+    }
+    const double n = (double)hw;
+    y[t] = make_float4((float)(s0 / n), (float)(s1 / n), (float)(s2 / n), (float)(s3 / n));
+  }
+}
+
 inline int grid_1d(int64_t work, int threads, int sm_count, int per_sm) {
   int64_t blocks = ceil_div64(work, threads);
   int64_t cap = (int64_t)sm_count * per_sm;
@@ -518,11 +558,11 @@ int launch_depthwise(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* 
     if (ci.strideHeight == 1) {                                                                       \
       auto k = depthwise3x3_strip_kernel<1, 2, ACT, MINB, DEPTH1>;                                     \
       cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                \
-      k<<<grid, 128, smem, ctx->stream>>>(x, w, y, ci, epi, rows, cb);                                \
+      launch_ex(ctx, k, grid, dim3(128), smem, x, w, y, ci, epi, rows, cb);                          \
     } else {                                                                                          \
       auto k = depthwise3x3_strip_kernel<2, 1, ACT, MINB, DEPTH2>;                                     \
       cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                \
-      k<<<grid, 128, smem, ctx->stream>>>(x, w, y, ci, epi, rows, cb);                                \
+      launch_ex(ctx, k, grid, dim3(128), smem, x, w, y, ci, epi, rows, cb);                          \
     }                                                                                                 \
   } while (0)
     switch (epi.activation) {
@@ -544,6 +584,11 @@ int launch_pool2d(tfjs_cuda_ctx* ctx, const float* x, float* y, const tfjs_conv2
   const bool global = is_avg && ci.outHeight == 1 && ci.outWidth == 1 && ci.padTop == 0 &&
                       ci.padLeft == 0 && ci.dilationHeight == 1 && ci.dilationWidth == 1 &&
                       ci.filterHeight == ci.inHeight && ci.filterWidth == ci.inWidth;
+  if (global && ci.inChannels % 4 == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0) {
+    launch_ex(ctx, global_avgpool_vec4_kernel, dim3(grid_1d(total / 4, 64, ctx->sm_count, 32)), dim3(64), 0,
+              (const float4*)x, (float4*)y, ci.batchSize, ci.inHeight * ci.inWidth, ci.inChannels / 4);
+    return post_launch(ctx, "avgPool (global)");
+  }
   if (global) {
     global_avgpool_kernel<<<grid_1d(total, 128, ctx->sm_count, 16), 128, 0, ctx->stream>>>(
         x, y, ci.batchSize, ci.inHeight * ci.inWidth, ci.inChannels);

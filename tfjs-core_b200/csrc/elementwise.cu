@@ -242,6 +242,69 @@ __global__ void softmax_last_kernel(const float* __restrict__ x, float* __restri
   }
 }
 
+// The same softmax with one 256-thread block per row and the row held in registers (up to
+// PER * 256 elements): the float64 exp / log chains of a row run on 8 warps instead of one.
+template <int PER>
+__global__ void __launch_bounds__(256) softmax_last_block_kernel(const float* __restrict__ x,
+                                                                  float* __restrict__ out, int64_t outer,
+                                                                  int inner) {
+  __shared__ float s_m[8];
+  __shared__ int s_any[8];
+  __shared__ double s_c[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int64_t row = blockIdx.x; row < outer; row += gridDim.x) {
+    const float* r = x + row * inner;
+    float v[PER];
+    float m = -INFINITY;
+    bool any = false;
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+      const int j = threadIdx.x + i * 256;
+      v[i] = j < inner ? r[j] : 0.f;
+      if (j < inner && v[i] == v[i] && (!any || v[i] > m)) { m = v[i]; any = true; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, (int)any, o);
+      if (oa && (!any || om > m)) { m = om; any = true; }
+    }
+    __syncthreads();  // the previous row's readers of the shared arrays are done
+    if (lane == 0) { s_m[warp] = m; s_any[warp] = any; }
+    __syncthreads();
+    m = -INFINITY;
+    any = false;
+#pragma unroll
+    for (int w = 0; w < 8; w++)
+      if (s_any[w] && (!any || s_m[w] > m)) { m = s_m[w]; any = true; }
+    const float first = r[0];
+    if (first != first || !any) m = first;  // NaN seed sticks (backend_cpu.ts:914)
+    double c = 0.0;
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+      if (threadIdx.x + i * 256 < inner) {
+        const float a = v[i] - m;
+        c += (double)(float)exp((double)a);
+      }
+    }
+    c = warp_sum(c);
+    if (lane == 0) s_c[warp] = c;
+    __syncthreads();
+    c = 0.0;
+#pragma unroll
+    for (int w = 0; w < 8; w++) c += s_c[w];
+    const float cf = (float)c;
+    const float d = (float)log((double)cf);
+    const float lse = m + d;
+#pragma unroll
+    for (int i = 0; i < PER; i++) {
+      const int j = threadIdx.x + i * 256;
+      if (j < inner) out[row * inner + j] = (float)exp((double)(v[i] - lse));
+    }
+  }
+}
+
 }  // namespace
 
 int launch_dequant(tfjs_cuda_ctx* ctx, const uint8_t* q, float* out, int64_t n, double scale,
@@ -436,7 +499,15 @@ extern "C" int tfjs_cuda_softmax_last(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id,
   o->version++;
   if (outer * inner == 0) return TFJS_CUDA_OK;
   cudaSetDevice(ctx->device);
-  softmax_last_kernel<<<grid_for(outer * 32, ctx->sm_count), kThreads, 0, ctx->stream>>>(
-      (const float*)x->ptr, (float*)o->ptr, outer, inner);
+  const int row_blocks = (int)(outer < (int64_t)ctx->sm_count * 8 ? outer : (int64_t)ctx->sm_count * 8);
+  if (inner >= 256 && inner <= 1024)
+    launch_ex(ctx, softmax_last_block_kernel<4>, dim3(row_blocks), dim3(256), 0, (const float*)x->ptr,
+              (float*)o->ptr, outer, (int)inner);
+  else if (inner > 1024 && inner <= 2048)
+    launch_ex(ctx, softmax_last_block_kernel<8>, dim3(row_blocks), dim3(256), 0, (const float*)x->ptr,
+              (float*)o->ptr, outer, (int)inner);
+  else
+    softmax_last_kernel<<<grid_for(outer * 32, ctx->sm_count), kThreads, 0, ctx->stream>>>(
+        (const float*)x->ptr, (float*)o->ptr, outer, inner);
   return post_launch(ctx, "softmax_last");
 }

@@ -180,6 +180,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_ptr_holder;
+  // everything above touched only shared and tensor memory; global memory from here on
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 8) {
     // ---------------- TMA producer ----------------
@@ -617,7 +620,7 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtensorMap&
   }
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-  kernel<<<grid, cta_threads(SPLIT, AMODE, WQ), smem_bytes, ctx->stream>>>(ma, mh, ml, mc, p);
+  launch_ex(ctx, kernel, dim3(grid), dim3(cta_threads(SPLIT, AMODE, WQ)), smem_bytes, ma, mh, ml, mc, p);
   if (WQ) return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32, uint8 weights)" : "gemm_tcgen05 (TF32, uint8 weights)");
   if (AMODE == A_MATRIX) return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32)" : "gemm_tcgen05 (TF32)");
   return post_launch(ctx, SPLIT ? "conv2d_tcgen05 (3xTF32)" : "conv2d_tcgen05 (TF32)");

@@ -264,6 +264,9 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  // only shared and tensor memory was touched so far; global memory from here on
+  pdl_wait();
+  pdl_launch_dependents();
   // depthwise filter taps and bias of every channel: [tap][C], then the bias row
   if (MODE == MODE_DW) {
     float* tab = reinterpret_cast<float*>(table);
@@ -483,7 +486,7 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap&
     configured[ctx->device & 7] = true;
   }
   const int grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
-  kernel<<<grid, THREADS, smem_bytes, ctx->stream>>>(mx, mw, my, p);
+  launch_ex(ctx, kernel, dim3(grid), dim3(THREADS), smem_bytes, mx, mw, my, p);
   if (MODE == MODE_RGB) return post_launch(ctx, "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32)");
   return post_launch(ctx, S == 1 ? "separableConv2d (fused dw3x3 s1 + pw, TF32)"
                                  : "separableConv2d (fused dw3x3 s2 + pw, TF32)");
