@@ -73,15 +73,56 @@ def workload_config(args, world):
 
 # ---- clocks ------------------------------------------------------------------------------------
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons of one GPU while a region runs."""
+    """Samples SM clock, power and throttle reasons of one GPU while a region runs: NVML reads
+    every 2 ms from a thread (read-only queries), or `nvidia-smi -lms` when pynvml is missing."""
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, device):
         self.device, self.rows, self.proc = device, [], None
+        self.samples, self.stop_flag, self.thread, self.nvml = [], False, None, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            index = device
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if visible:
+                entry = visible.split(",")[device].strip()
+                index = int(entry) if entry.isdigit() else None
+            self.handle = (pynvml.nvmlDeviceGetHandleByIndex(index) if index is not None
+                           else pynvml.nvmlDeviceGetHandleByUUID(entry))
+            self.nvml = pynvml
+        except Exception:
+            self.nvml = None
+
+    def _read_nvml(self):
+        n = self.nvml
+        reasons = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+        names = []
+        for name, bit in (("hw_slowdown", n.nvmlClocksEventReasonHwSlowdown),
+                          ("hw_thermal_slowdown", n.nvmlClocksEventReasonHwThermalSlowdown),
+                          ("sw_thermal_slowdown", n.nvmlClocksEventReasonSwThermalSlowdown),
+                          ("sw_power_cap", n.nvmlClocksEventReasonSwPowerCap)):
+            if reasons & bit:
+                names.append(name)
+        return (float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)),
+                float(n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)),
+                n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0, names)
+
+    def _loop(self):
+        while not self.stop_flag:
+            try:
+                self.samples.append(self._read_nvml())
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def start(self):
+        if self.nvml is not None:
+            self.thread = threading.Thread(target=self._loop, daemon=True)
+            self.thread.start()
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.device), f"--query-gpu={self.QUERY}",
@@ -96,13 +137,25 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
+        sm, mx, reasons, power = [], [], set(), []
+        if self.thread is not None:
+            try:  # one more read before the load goes away, so that short regions have a sample
+                self.samples.append(self._read_nvml())
+            except Exception:
+                pass
+            self.stop_flag = True
+            self.thread.join(timeout=1)
+            for s_, m_, p_, names in self.samples:
+                sm.append(s_)
+                mx.append(m_)
+                power.append(p_)
+                reasons.update(names)
         if self.proc:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
-        sm, mx, reasons, power = [], [], set(), []
         for r in self.rows:
             try:
                 sm.append(float(r[0]))
