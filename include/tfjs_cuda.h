@@ -64,7 +64,7 @@ typedef enum { TFJS_MATH_TF32X3 = 0, TFJS_MATH_TF32 = 1 } tfjs_math_mode;
 typedef enum { TFJS_BIN_ADD = 0, TFJS_BIN_SUB = 1, TFJS_BIN_MUL = 2, TFJS_BIN_DIV = 3,
                TFJS_BIN_PRELU = 4, TFJS_BIN_NOT_EQUAL = 5 } tfjs_binary_op;
 typedef enum { TFJS_UN_RELU = 0, TFJS_UN_CLIP = 1, TFJS_UN_EXP = 2, TFJS_UN_LOG = 3,
-               TFJS_UN_INT = 4 } tfjs_unary_op;
+               TFJS_UN_INT = 4, TFJS_UN_STEP = 5 /* p0 = alpha */ } tfjs_unary_op;
 typedef enum { TFJS_RED_SUM = 0, TFJS_RED_MAX = 1, TFJS_RED_ARGMAX = 2 } tfjs_reduce_op;
 
 /* Conv2DInfo, tfjs-core/src/ops/conv_util.ts:43-64, channelsLast (NHWC) only; padInfo is
@@ -203,6 +203,29 @@ int tfjs_cuda_separable_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor
                                tfjs_tensor_id pw_filter, tfjs_tensor_id out,
                                const tfjs_conv2d_info* dw_info, int32_t out_channels,
                                const tfjs_epilogue* dw_epi, const tfjs_epilogue* pw_epi);
+/* ---- gradient kernels, so that the engine's tape differentiates through this backend.  One
+ *      thread per output element walks the reference's loop nest with a float64 accumulator:
+ *      results are bit-identical to MathBackendCPU.  Dilation must be 1 (the op layer asserts
+ *      the same, ops/conv.ts:188-192).
+ * KernelBackend.conv2dDerInput / conv2dDerFilter (backend.ts:424-429; CPU :1686-1762, 1849-1898):
+ * dx [B,inH,inW,Cin] from dy [B,outH,outW,Cout] and filter; dW [fH,fW,Cin,Cout] from x and dy. */
+int tfjs_cuda_conv2d_der_input(tfjs_cuda_ctx* ctx, tfjs_tensor_id dy, tfjs_tensor_id filter,
+                               tfjs_tensor_id dx, const tfjs_conv2d_info* info);
+int tfjs_cuda_conv2d_der_filter(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id dy,
+                                tfjs_tensor_id dw, const tfjs_conv2d_info* info);
+/* KernelBackend.depthwiseConv2DDerInput / DerFilter (backend.ts:436-442; CPU :2037-2150). */
+int tfjs_cuda_depthwise_conv2d_der_input(tfjs_cuda_ctx* ctx, tfjs_tensor_id dy, tfjs_tensor_id filter,
+                                         tfjs_tensor_id dx, const tfjs_conv2d_info* info);
+int tfjs_cuda_depthwise_conv2d_der_filter(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id dy,
+                                          tfjs_tensor_id dw, const tfjs_conv2d_info* info);
+/* KernelBackend.maxPoolBackprop / avgPoolBackprop (backend.ts:456-466; CPU :2347-2509): dx of the
+ * pooled input x given dy of the pooled output. */
+int tfjs_cuda_pool2d_backprop(tfjs_cuda_ctx* ctx, tfjs_tensor_id dy, tfjs_tensor_id x, tfjs_tensor_id dx,
+                              const tfjs_conv2d_info* info, int is_avg);
+/* KernelBackend.transpose (backend.ts:216; the op layer uses it to move reduced axes inner-most,
+ * ops/reduction_ops.ts:115-121): out[i0..] = x permuted; `shape` is x's shape. */
+int tfjs_cuda_transpose(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id out, int rank,
+                        const int64_t* shape, const int32_t* perm);
 /* KernelBackend.avgPool / maxPool (backend.ts:453-462; CPU :2273-2343, 2869-2873). */
 int tfjs_cuda_pool2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id out,
                      const tfjs_conv2d_info* info, int is_avg);
@@ -212,7 +235,8 @@ int tfjs_cuda_pool2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id out,
 int tfjs_cuda_binary(tfjs_cuda_ctx* ctx, int op, tfjs_tensor_id a, int a_rank,
                      const int64_t* a_shape, tfjs_tensor_id b, int b_rank, const int64_t* b_shape,
                      tfjs_tensor_id out);
-/* KernelBackend.relu / clip / exp / log / int (backend.ts:300-346; CPU :1094-1275). */
+/* KernelBackend.relu / clip / exp / log / int / step (backend.ts:300-346, 401; CPU :1094-1275,
+ * 1520-1534). */
 int tfjs_cuda_unary(tfjs_cuda_ctx* ctx, int op, tfjs_tensor_id x, tfjs_tensor_id out, float p0,
                     float p1);
 /* KernelBackend.sum / max / argMax over the inner-most axes (backend.ts:183, 198, 255;

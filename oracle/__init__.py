@@ -34,6 +34,10 @@ class ConvInfo(C.Structure):
     def outShape(self):
         return (self.batchSize, self.outHeight, self.outWidth, self.outChannels)
 
+    @property
+    def inShape(self):
+        return [self.batchSize, self.inHeight, self.inWidth, self.inChannels]
+
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_}
 
@@ -41,7 +45,8 @@ class ConvInfo(C.Structure):
 def build(force=False):
     """Compile liboracle.so with the flags the Makefile states."""
     if force or not os.path.exists(_LIB_PATH) or (
-            os.path.getmtime(_LIB_PATH) < os.path.getmtime(os.path.join(_HERE, "oracle.c"))):
+            os.path.getmtime(_LIB_PATH) < max(os.path.getmtime(os.path.join(_HERE, f))
+                                              for f in ("oracle.c", "oracle_backward.c", "oracle.h"))):
         subprocess.check_call(["make", "-s", "-C", _HERE, "liboracle.so"])
     return _LIB_PATH
 
@@ -229,3 +234,54 @@ def fused_conv2d(x, w, ci, bias=None, activation=None, prelu=None):
     bias, prelu, bp, bn, pp, pn = _epilogue_args(bias, prelu)
     lib().tfo_fused_conv2d(_p(x), _p(w), _p(y), C.byref(ci), bp, bn, ACT[activation], pp, pn)
     return y
+
+
+# ---- gradient kernels (oracle_backward.c) ---------------------------------------------------------
+def conv2d_der_input(dy, w, ci):
+    """backend_cpu.ts:1686-1762"""
+    dy, w = _f32(dy), _f32(w)
+    dx = np.empty(ci.inShape, np.float32)
+    lib().tfo_conv2d_der_input(_p(dy), _p(w), _p(dx), C.byref(ci))
+    return dx
+
+
+def conv2d_der_filter(x, dy, ci):
+    """backend_cpu.ts:1849-1898"""
+    x, dy = _f32(x), _f32(dy)
+    dw = np.empty((ci.filterHeight, ci.filterWidth, ci.inChannels, ci.outChannels), np.float32)
+    lib().tfo_conv2d_der_filter(_p(x), _p(dy), _p(dw), C.byref(ci))
+    return dw
+
+
+def depthwise_der_input(dy, w, ci):
+    """backend_cpu.ts:2037-2102"""
+    dy, w = _f32(dy), _f32(w)
+    dx = np.empty(ci.inShape, np.float32)
+    lib().tfo_depthwise_der_input(_p(dy), _p(w), _p(dx), C.byref(ci))
+    return dx
+
+
+def depthwise_der_filter(x, dy, ci):
+    """backend_cpu.ts:2104-2150"""
+    x, dy = _f32(x), _f32(dy)
+    dw = np.empty((ci.filterHeight, ci.filterWidth, ci.inChannels, ci.outChannels // ci.inChannels), np.float32)
+    lib().tfo_depthwise_der_filter(_p(x), _p(dy), _p(dw), C.byref(ci))
+    return dw
+
+
+def pool_backprop(dy, x, ci, kind):
+    """backend_cpu.ts:2400-2509 maxPoolBackprop / avgPoolBackprop"""
+    dy, x = _f32(dy), _f32(x)
+    dx = np.empty(ci.inShape, np.float32)
+    pos = np.empty(ci.outShape, np.int32)
+    lib().tfo_pool_backprop(_p(dy), _p(x), _p(dx), pos.ctypes.data_as(C.c_void_p), C.byref(ci),
+                            int(kind == "avg"))
+    return dx
+
+
+def step(x, alpha=0.0):
+    """backend_cpu.ts:1520-1534"""
+    x = _f32(x)
+    out = np.empty(x.shape, np.float32)
+    lib().tfo_step(_p(x), _p(out), C.c_int64(x.size), C.c_double(alpha))
+    return out

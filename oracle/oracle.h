@@ -82,6 +82,20 @@ void tfo_fused_conv2d(const float* x, const float* w, float* y, const tfo_conv_i
                       const float* bias, int64_t bias_n, int act, const float* prelu,
                       int64_t prelu_n);
 
+/* ---- gradient kernels (oracle_backward.c) ---- */
+/* backend_cpu.ts:1686-1762 conv2dDerInput and :1849-1898 conv2dDerFilter */
+void tfo_conv2d_der_input(const float* dy, const float* w, float* dx, const tfo_conv_info* ci);
+void tfo_conv2d_der_filter(const float* x, const float* dy, float* dw, const tfo_conv_info* ci);
+/* backend_cpu.ts:2037-2102 depthwiseConv2DDerInput and :2104-2150 depthwiseConv2DDerFilter */
+void tfo_depthwise_der_input(const float* dy, const float* w, float* dx, const tfo_conv_info* ci);
+void tfo_depthwise_der_filter(const float* x, const float* dy, float* dw, const tfo_conv_info* ci);
+/* backend_cpu.ts:2400-2456 maxPoolBackprop (with maxPoolPositions :2347-2398; `pos` is scratch of
+ * the pooled output's size) and :2458-2509 avgPoolBackprop */
+void tfo_pool_backprop(const float* dy, const float* x, float* dx, int32_t* pos, const tfo_conv_info* ci,
+                       int is_avg);
+/* backend_cpu.ts:1520-1534 step */
+void tfo_step(const float* x, float* out, int64_t n, double alpha);
+
 #ifdef __cplusplus
 }
 #endif

@@ -16,7 +16,7 @@ F32, I32, BOOL = 0, 1, 2
 ACT = {None: 0, "linear": 0, "relu": 1, "prelu": 2, "clip": 3}
 MATH = {"3xtf32": 0, "tf32": 1}
 BINARY = {"add": 0, "sub": 1, "mul": 2, "div": 3, "prelu": 4, "notEqual": 5}
-UNARY = {"relu": 0, "clip": 1, "exp": 2, "log": 3, "int": 4}
+UNARY = {"relu": 0, "clip": 1, "exp": 2, "log": 3, "int": 4, "step": 5}
 REDUCE = {"sum": 0, "max": 1, "argMax": 2}
 
 
@@ -90,6 +90,14 @@ SIGNATURES = {
     "tfjs_cuda_separable_conv2d": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                              C.POINTER(ConvInfo), C.c_int32, C.POINTER(Epilogue),
                                              C.POINTER(Epilogue)]),
+    "tfjs_cuda_conv2d_der_input": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int64, C.POINTER(ConvInfo)]),
+    "tfjs_cuda_conv2d_der_filter": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int64, C.POINTER(ConvInfo)]),
+    "tfjs_cuda_depthwise_conv2d_der_input": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int64,
+                                                       C.POINTER(ConvInfo)]),
+    "tfjs_cuda_depthwise_conv2d_der_filter": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int64,
+                                                        C.POINTER(ConvInfo)]),
+    "tfjs_cuda_pool2d_backprop": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int64, C.POINTER(ConvInfo), C.c_int]),
+    "tfjs_cuda_transpose": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int, _I64P, C.POINTER(C.c_int32)]),
     "tfjs_cuda_pool2d": (C.c_int, [_P, C.c_int64, C.c_int64, C.POINTER(ConvInfo), C.c_int]),
     "tfjs_cuda_binary": (C.c_int, [_P, C.c_int, C.c_int64, C.c_int, _I64P, C.c_int64, C.c_int, _I64P,
                                    C.c_int64]),

@@ -487,6 +487,65 @@ class BackendCuda:
     def int(self, x):
         return self._unary("int", x, out_dtype="int32")
 
+    def step(self, x, alpha=0.0):
+        """backend.ts:401; CPU backend_cpu.ts:1520-1534 (the gradient of relu)."""
+        return self._unary("step", x, alpha)
+
+    # ---- gradient kernels (backend.ts:424-442, 456-466, 216) ------------------------------
+    def _conv_gradient(self, fn, first, second, out_shape, convInfo, name):
+        self._assert_numeric([first, second], name)
+        aid, ta = self._id(first)
+        bid, tb = self._id(second)
+        out = self._out(out_shape)
+        self._check(fn(self._ctx, aid, bid, self._rec(out.dataId)["id"], C.byref(convInfo)))
+        self._free_tmp(ta, tb)
+        return out
+
+    def conv2dDerInput(self, dy, filter, convInfo):
+        return self._conv_gradient(self._lib.tfjs_cuda_conv2d_der_input, dy, filter, convInfo.inShape,
+                                   convInfo, "conv2dDerInput")
+
+    def conv2dDerFilter(self, x, dy, convInfo):
+        shape = [convInfo.filterHeight, convInfo.filterWidth, convInfo.inChannels, convInfo.outChannels]
+        return self._conv_gradient(self._lib.tfjs_cuda_conv2d_der_filter, x, dy, shape, convInfo,
+                                   "conv2dDerFilter")
+
+    def depthwiseConv2DDerInput(self, dy, filter, convInfo):
+        return self._conv_gradient(self._lib.tfjs_cuda_depthwise_conv2d_der_input, dy, filter,
+                                   convInfo.inShape, convInfo, "depthwiseConv2DDerInput")
+
+    def depthwiseConv2DDerFilter(self, x, dy, convInfo):
+        shape = [convInfo.filterHeight, convInfo.filterWidth, convInfo.inChannels,
+                 convInfo.outChannels // max(convInfo.inChannels, 1)]
+        return self._conv_gradient(self._lib.tfjs_cuda_depthwise_conv2d_der_filter, x, dy, shape, convInfo,
+                                   "depthwiseConv2DDerFilter")
+
+    def _pool_backprop(self, dy, x, convInfo, is_avg):
+        self._assert_numeric([dy, x], "poolBackprop")
+        did, td = self._id(dy)
+        xid, tx = self._id(x)
+        out = self._out(x.shape)
+        self._check(self._lib.tfjs_cuda_pool2d_backprop(self._ctx, did, xid, self._rec(out.dataId)["id"],
+                                                        C.byref(convInfo), int(is_avg)))
+        self._free_tmp(td, tx)
+        return out
+
+    def maxPoolBackprop(self, dy, x, y, convInfo):
+        return self._pool_backprop(dy, x, convInfo, False)
+
+    def avgPoolBackprop(self, dy, x, convInfo):
+        return self._pool_backprop(dy, x, convInfo, True)
+
+    def transpose(self, x, perm):
+        self._assert_numeric(x, "transpose")
+        xid, tx = self._id(x)
+        out = self._out([x.shape[p] for p in perm])
+        perm_arr = (C.c_int32 * max(len(perm), 1))(*[int(p) for p in perm])
+        self._check(self._lib.tfjs_cuda_transpose(self._ctx, xid, self._rec(out.dataId)["id"], len(perm),
+                                                  _ffi.shape_array(x.shape), perm_arr))
+        self._free_tmp(tx)
+        return out
+
     # ---- reductions over the inner-most axes (backend.ts:183, 198, 255) ------------------
     def _reduce(self, op, x, axes, out_dtype):
         self._assert_numeric(x, op)

@@ -102,6 +102,7 @@ __device__ __forceinline__ float unary_apply(int op, float v, float p0, float p1
     case TFJS_UN_CLIP: return v > p1 ? p1 : (v < p0 ? p0 : v);
     case TFJS_UN_EXP: return (float)exp((double)v);
     case TFJS_UN_LOG: return (float)log((double)v);
+    case TFJS_UN_STEP: return (v != v) ? v : (v > 0.f ? 1.f : p0);  // backend_cpu.ts:1520-1534
     default: return v;
   }
 }
@@ -409,7 +410,7 @@ extern "C" int tfjs_cuda_binary(tfjs_cuda_ctx* ctx, int op, tfjs_tensor_id a_id,
 extern "C" int tfjs_cuda_unary(tfjs_cuda_ctx* ctx, int op, tfjs_tensor_id x_id,
                                tfjs_tensor_id out_id, float p0, float p1) {
   if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
-  TFJS_REQUIRE(ctx, op >= TFJS_UN_RELU && op <= TFJS_UN_INT, "unknown unary op %d", op);
+  TFJS_REQUIRE(ctx, op >= TFJS_UN_RELU && op <= TFJS_UN_STEP, "unknown unary op %d", op);
   TensorEntry* x;
   int rc = get_f32(ctx, x_id, 0, "x", &x);
   if (rc) return rc;
@@ -436,6 +437,7 @@ extern "C" int tfjs_cuda_unary(tfjs_cuda_ctx* ctx, int op, tfjs_tensor_id x_id,
     case TFJS_UN_RELU: unary_kernel<TFJS_UN_RELU><<<grid, kThreads, 0, ctx->stream>>>(xp, outp, n, p0, p1); break;
     case TFJS_UN_CLIP: unary_kernel<TFJS_UN_CLIP><<<grid, kThreads, 0, ctx->stream>>>(xp, outp, n, p0, p1); break;
     case TFJS_UN_EXP: unary_kernel<TFJS_UN_EXP><<<grid, kThreads, 0, ctx->stream>>>(xp, outp, n, p0, p1); break;
+    case TFJS_UN_STEP: unary_kernel<TFJS_UN_STEP><<<grid, kThreads, 0, ctx->stream>>>(xp, outp, n, p0, p1); break;
     default: unary_kernel<TFJS_UN_LOG><<<grid, kThreads, 0, ctx->stream>>>(xp, outp, n, p0, p1); break;
   }
   return post_launch(ctx, "unary");
