@@ -222,6 +222,10 @@ int tfjs_cuda_depthwise_conv2d_der_filter(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, 
  * pooled input x given dy of the pooled output. */
 int tfjs_cuda_pool2d_backprop(tfjs_cuda_ctx* ctx, tfjs_tensor_id dy, tfjs_tensor_id x, tfjs_tensor_id dx,
                               const tfjs_conv2d_info* info, int is_avg);
+/* Gradient of clipByValue (ops/unary_ops.ts:456-462) as one kernel: out = dy where
+ * lo <= x <= hi, else 0 (the reference composes greaterEqual, lessEqual, logicalAnd, where). */
+int tfjs_cuda_clip_backprop(tfjs_cuda_ctx* ctx, tfjs_tensor_id dy, tfjs_tensor_id x, tfjs_tensor_id out,
+                            float lo, float hi);
 /* KernelBackend.transpose (backend.ts:216; the op layer uses it to move reduced axes inner-most,
  * ops/reduction_ops.ts:115-121): out[i0..] = x permuted; `shape` is x's shape. */
 int tfjs_cuda_transpose(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id out, int rank,

@@ -97,6 +97,7 @@ SIGNATURES = {
     "tfjs_cuda_depthwise_conv2d_der_filter": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int64,
                                                         C.POINTER(ConvInfo)]),
     "tfjs_cuda_pool2d_backprop": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int64, C.POINTER(ConvInfo), C.c_int]),
+    "tfjs_cuda_clip_backprop": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int64, C.c_float, C.c_float]),
     "tfjs_cuda_transpose": (C.c_int, [_P, C.c_int64, C.c_int64, C.c_int, _I64P, C.POINTER(C.c_int32)]),
     "tfjs_cuda_pool2d": (C.c_int, [_P, C.c_int64, C.c_int64, C.POINTER(ConvInfo), C.c_int]),
     "tfjs_cuda_binary": (C.c_int, [_P, C.c_int, C.c_int64, C.c_int, _I64P, C.c_int64, C.c_int, _I64P,

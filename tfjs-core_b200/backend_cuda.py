@@ -536,6 +536,17 @@ class BackendCuda:
     def avgPoolBackprop(self, dy, x, convInfo):
         return self._pool_backprop(dy, x, convInfo, True)
 
+    def clipBackprop(self, dy, x, lo, hi):
+        """Extension: dy where lo <= x <= hi, else 0 (the gradient of clip as one kernel)."""
+        self._assert_numeric([dy, x], "clipBackprop")
+        did, td = self._id(dy)
+        xid, tx = self._id(x)
+        out = self._out(x.shape)
+        self._check(self._lib.tfjs_cuda_clip_backprop(self._ctx, did, xid, self._rec(out.dataId)["id"],
+                                                      float(lo), float(hi)))
+        self._free_tmp(td, tx)
+        return out
+
     def transpose(self, x, perm):
         self._assert_numeric(x, "transpose")
         xid, tx = self._id(x)

@@ -174,6 +174,14 @@ __global__ void pool_backprop_kernel(const float* __restrict__ dy, const int32_t
   }
 }
 
+// Gradient of clipByValue (ops/unary_ops.ts:456-462): dy where min <= x <= max, else 0.  One
+// kernel for the reference's greaterEqual / lessEqual / logicalAnd / where chain.
+__global__ void clip_backprop_kernel(const float* __restrict__ dy, const float* __restrict__ x,
+                                     float* __restrict__ out, int64_t n, float lo, float hi) {
+  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < n; t += (int64_t)gridDim.x * blockDim.x)
+    out[t] = (x[t] >= lo && x[t] <= hi) ? dy[t] : 0.f;
+}
+
 struct TransposeDesc {
   int rank;
   int64_t out_shape[8];
@@ -315,6 +323,25 @@ extern "C" int tfjs_cuda_pool2d_backprop(tfjs_cuda_ctx* ctx, tfjs_tensor_id dy_i
   }
   ctx_free(ctx, pos, cap);
   return rc;
+}
+
+extern "C" int tfjs_cuda_clip_backprop(tfjs_cuda_ctx* ctx, tfjs_tensor_id dy_id, tfjs_tensor_id x_id,
+                                       tfjs_tensor_id out_id, float lo, float hi) {
+  if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
+  TensorEntry *dy, *x, *o;
+  int rc = get_f32(ctx, x_id, 0, "x", &x);
+  if (rc) return rc;
+  rc = get_f32(ctx, dy_id, x->size, "dy", &dy);
+  if (rc) return rc;
+  rc = get_f32(ctx, out_id, x->size, "clip gradient", &o);
+  if (rc) return rc;
+  TFJS_REQUIRE(ctx, !x->quant.quantized && !dy->quant.quantized, "gradient kernels take float32 tensors");
+  o->version++;
+  if (x->size == 0) return TFJS_CUDA_OK;
+  cudaSetDevice(ctx->device);
+  clip_backprop_kernel<<<grid_for_elems(x->size, 256, ctx->sm_count), 256, 0, ctx->stream>>>(
+      (const float*)dy->ptr, (const float*)x->ptr, (float*)o->ptr, x->size, lo, hi);
+  return post_launch(ctx, "clipBackprop");
 }
 
 extern "C" int tfjs_cuda_transpose(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_tensor_id out_id, int rank,

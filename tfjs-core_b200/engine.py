@@ -35,9 +35,19 @@ class Tensor:
         self.size = size_from_shape(self.shape)
         self.dataId = data_id if data_id is not None else DataId()
         self.isDisposed = False
+        self.kept = False
+        Tensor._next_id += 1
+        self.id = Tensor._next_id   # tensor.ts:421: unique per Tensor object, the tape's key
         ENGINE.registerTensor(self, backend)
         if values is not None:
             ENGINE.write(backend, self.dataId, values)
+
+    _next_id = 0
+
+    def clone(self):
+        """A second Tensor over the same storage (engine.ts clone: shares the dataId)."""
+        self._throw_if_disposed()
+        return Tensor(self.shape, self.dtype, None, self.dataId)
 
     @staticmethod
     def make(shape, data=None, dtype="float32", backend=None):
@@ -92,6 +102,9 @@ class Engine:
         self.scopeStack = []
         self.kernelDepth = 0
         self.kernelNames = []       # runKernel trace (profile-like): one entry per backend call
+        self.activeTape = None      # list of tape nodes while a gradient scope records
+        self.gradientDepth = 0
+        self.nextTapeNodeId = 0
 
     # ---- backend registry (engine.ts:220-359) ----
     def registerBackend(self, name, factory, priority=1):
@@ -215,7 +228,7 @@ class Engine:
             keep.add(id(t))
         scope = self.scopeStack.pop()
         for t in scope["track"]:
-            if id(t) in keep or t.isDisposed:
+            if id(t) in keep or t.isDisposed or t.kept:
                 continue
             t.dispose()
         if self.scopeStack:
@@ -232,14 +245,98 @@ class Engine:
             self.endScope(result)
 
     # ---- kernel dispatch (engine.ts:435-498) ----
-    def runKernel(self, forward, name=None):
+    def runKernel(self, forward, name=None, inputs=None, backward=None):
+        """engine.ts:435-498.  `forward(backend)` or `forward(backend, save)` computes the result;
+        `inputs` is {name: Tensor}; `backward(dy, saved)` returns {name: () -> Tensor}, the gradient
+        with respect to each input.  While a tape records (engine.gradients), a node with the
+        inputs, the output and the gradient function is appended to it; `save(tensors)` keeps
+        clones of the tensors the gradient needs, so the caller may dispose its own handles."""
         self.kernelDepth += 1
+        saved = []
+
+        def save(tensors):
+            if self.activeTape is not None and self.kernelDepth == 1:
+                for t in tensors:
+                    saved.append(self.keep(t.clone()))
         try:
             if name:
                 self.kernelNames.append(name)
-            return forward(self.backend)
+            try:
+                takes_save = forward.__code__.co_argcount >= 2
+            except AttributeError:
+                takes_save = False
+            result = forward(self.backend, save) if takes_save else forward(self.backend)
         finally:
             self.kernelDepth -= 1
+        if self.activeTape is not None and self.kernelDepth == 0 and inputs and backward is not None:
+            self.nextTapeNodeId += 1
+            self.activeTape.append({"id": self.nextTapeNodeId, "name": name, "inputs": dict(inputs),
+                                    "outputs": [result], "saved": saved,
+                                    "gradient": (lambda dy, _s=saved: backward(dy, _s))})
+        return result
+
+    def keep(self, t):
+        """tf.keep (engine.ts:720-731): the tensor survives the enclosing tidy scopes."""
+        t.kept = True
+        return t
+
+    # ---- gradients (engine.ts:739-812, tape.ts) ----
+    def gradients(self, f, xs, dy=None):
+        """Returns (value, grads): value = f(), grads[i] = d sum(value * dy) / d xs[i].  f must
+        return one float32 Tensor computed from xs through ops that define gradients."""
+        from . import ops
+        assert xs, "gradients() received an empty list of xs."
+        if dy is not None and dy.dtype != "float32":
+            raise ValueError(f"dy must have 'float32' dtype, but has '{dy.dtype}'")
+        outer_tape = self.activeTape
+        self.activeTape = []
+        self.gradientDepth += 1
+        try:
+            y = f()
+            if not isinstance(y, Tensor):
+                raise ValueError("The result y returned by f() must be a tensor.")
+            tape = self.activeTape
+        finally:
+            self.gradientDepth -= 1
+            self.activeTape = outer_tape
+        filtered = get_filtered_nodes_x_to_y(tape, xs, y)
+        if not filtered and xs:
+            self._dispose_tape(tape)
+            raise ValueError("Cannot compute gradient of y=f(x) with respect to x. Make sure that the f "
+                             "you passed encloses all operations that lead from x to y.")
+        acc = {}
+        if dy is None:
+            dy = ops.tensor(np.ones(y.shape, np.float32), y.shape)
+            own_dy = True
+        else:
+            own_dy = False
+        acc[y.id] = dy
+        try:
+            backpropagate_gradients(acc, filtered)
+            grads = []
+            for x in xs:
+                g = acc.pop(x.id, None)
+                if g is None:
+                    g = ops.tensor(np.zeros(x.shape, np.float32), x.shape)
+                grads.append(g)
+        finally:
+            keep_ids = {id(g) for g in locals().get("grads", [])}
+            for g in acc.values():
+                if id(g) not in keep_ids and not (g is dy and not own_dy) and not g.isDisposed:
+                    g.dispose()
+            if own_dy and id(dy) not in keep_ids and not dy.isDisposed:
+                dy.dispose()
+            self._dispose_tape(tape)
+        return y, grads
+
+    @staticmethod
+    def _dispose_tape(tape):
+        for node in tape:
+            for t in node["saved"]:
+                if not t.isDisposed:
+                    t.kept = False
+                    t.dispose()
+            node["saved"] = []
 
     def memory(self):
         info = dict(self.backend.memory())
@@ -249,6 +346,66 @@ class Engine:
 
     def time(self, fn):
         return self.backend.time(fn)
+
+
+def get_filtered_nodes_x_to_y(tape, xs, y):
+    """tape.ts:38-125: the nodes on a path from any x to y, each with only the inputs that lie
+    on such a path."""
+    from_x = {x.id for x in xs}
+    nodes_from_x = set()
+    for i, node in enumerate(tape):
+        if any(t.id in from_x for t in node["inputs"].values()):
+            for out in node["outputs"]:
+                from_x.add(out.id)
+            nodes_from_x.add(i)
+    to_y = {y.id}
+    nodes_to_y = set()
+    for i in range(len(tape) - 1, -1, -1):
+        node = tape[i]
+        if any(out.id in to_y for out in node["outputs"]):
+            for t in node["inputs"].values():
+                to_y.add(t.id)
+            nodes_to_y.add(i)
+    filtered = []
+    for i, node in enumerate(tape):
+        if i in nodes_from_x and i in nodes_to_y:
+            pruned = {k: t for k, t in node["inputs"].items() if t.id in from_x}
+            filtered.append(dict(node, inputs=pruned))
+    return filtered
+
+
+def backpropagate_gradients(acc, filtered_tape):
+    """tape.ts:134-190: walks the tape backwards; `acc` maps tensor id -> accumulated gradient."""
+    from . import ops
+    for node in reversed(filtered_tape):
+        out = node["outputs"][0]
+        dy = acc.get(out.id)
+        if dy is None:
+            continue   # this output does not influence y
+        input_gradients = node["gradient"](dy)
+        for name, x in node["inputs"].items():
+            if name not in input_gradients:
+                raise ValueError(f"Cannot backprop through input {name}. Available gradients found: "
+                                 f"{list(input_gradients)}.")
+            dx = input_gradients[name]()
+            if dx.dtype != "float32":
+                raise ValueError(f"Error in gradient for op {node['name']}. The gradient of input "
+                                 f"{name} must have 'float32' dtype, but has '{dx.dtype}'")
+            if dx.shape != x.shape:
+                raise ValueError(f"Error in gradient for op {node['name']}. The gradient of input "
+                                 f"'{name}' has shape '{dx.shape}', which does not match the shape of "
+                                 f"the input '{x.shape}'")
+            cur = acc.get(x.id)
+            if cur is None:
+                acc[x.id] = dx
+            else:
+                acc[x.id] = ops.add(cur, dx)
+                cur.dispose()
+                dx.dispose()
+        # the gradient of an intermediate is not needed once it has been propagated
+        if dy is not None and out.id in acc and node is not filtered_tape[-1]:
+            done = acc.pop(out.id)
+            done.dispose()
 
 
 def _tensors_in(result):
