@@ -543,12 +543,26 @@ int launch_depthwise(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* 
     const size_t smem = ((size_t)depth * in_w * 128 + (size_t)9 * cb) * sizeof(float4);
     const int64_t cols = (ci.outWidth + tw - 1) / tw;
     const int resident = ctx->sm_count * MINB;  // one wave of blocks
-    // strips of output rows: long enough to amortise the halo rows, short enough to give every
-    // resident thread work on the small late layers
+    // Strips of output rows.  A strip costs its rows plus a start-up of about three row steps
+    // (ring fill, halo rows); the blocks of the one resident wave take ceil(items / capacity)
+    // strips each.  Pick the strip height that minimises rounds x (rows + start-up): long strips
+    // amortise the halo, short ones balance the wave on the small late layers.
     int rows = 8;
-    while (rows > 2 && (int64_t)ci.batchSize * ((ci.outHeight + rows - 1) / rows) * cols * slices <
-                           (int64_t)resident * groups)
-      rows /= 2;
+    {
+      const int64_t capacity = (int64_t)resident * groups / slices > 0 ? (int64_t)resident * groups / slices : 1;
+      int64_t best = -1;
+      for (int r = 2; r <= ci.outHeight && r <= 32; ++r) {
+        const int64_t strips_r = (ci.outHeight + r - 1) / r;
+        const int64_t items_r = (int64_t)ci.batchSize * strips_r * cols;
+        const int64_t rounds = (items_r + capacity - 1) / capacity;
+        const int64_t cost = rounds * (r + 3);
+        if (best < 0 || cost < best || (cost == best && r > rows)) {
+          best = cost;
+          rows = r;
+        }
+      }
+      if (ci.outHeight < 2) rows = 1;
+    }
     const int64_t items = (int64_t)ci.batchSize * ((ci.outHeight + rows - 1) / rows) * cols;
     int64_t gx = (items + groups - 1) / groups;
     if (gx > resident / slices) gx = resident / slices > 0 ? resident / slices : 1;
