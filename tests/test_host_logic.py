@@ -61,7 +61,21 @@ def test_mobilenet_accounting_matches_layer_table():
     # 1.1375 GFLOP per image
     assert mobilenet.algorithmic_bytes_per_image() * 64 + mobilenet.weight_bytes() == 2638567840
     assert mobilenet.weight_bytes() == 16884128
-    assert mobilenet.flops_per_image() * 64 == 72801976320 + 0 or mobilenet.flops_per_image() == 1137530880
+    assert mobilenet.flops_per_image() == 1137530880
+    # per-launch accounting: the layer-wise forward has 30 launches; with the first four
+    # depthwise + pointwise pairs fused there are 26, and the four intermediates (1.6 + 0.8 + 1.6 +
+    # 0.4 MB per image, written once and read once) drop out of the byte count
+    layerwise = mobilenet.layer_algorithmic_bytes(64, True)
+    names = (["conv2d_tcgen05 (3-channel 3x3, window TMA, TF32)"] +
+             ["separableConv2d (fused dw3x3 s1 + pw, TF32)"] * 4 +
+             ["depthwiseConv2D (3x3 strip)", "gemm_tcgen05 (TF32)"] * 9 +
+             ["avgPool (global)", "gemm_tcgen05 (TF32)", "softmax_last"])
+    fused = mobilenet.launch_algorithmic_bytes(64, True, names)
+    assert len(layerwise) == 30 and len(fused) == 26
+    mid = 4 * 64 * (112 * 112 * 32 + 56 * 56 * 64 + 56 * 56 * 128 + 28 * 28 * 128)
+    assert sum(layerwise) - sum(fused) == 2 * mid
+    with pytest.raises(AssertionError):
+        mobilenet.launch_algorithmic_bytes(64, True, names[:-1])
     specs = mobilenet.layer_specs()
     assert len(specs) == 28 and specs[0][2] == (3, 3, 3, 32) and specs[-1][2] == (1, 1, 1024, 1000)
 

@@ -304,28 +304,24 @@ class Engine:
             self._dispose_tape(tape)
             raise ValueError("Cannot compute gradient of y=f(x) with respect to x. Make sure that the f "
                              "you passed encloses all operations that lead from x to y.")
-        acc = {}
-        if dy is None:
-            dy = ops.tensor(np.ones(y.shape, np.float32), y.shape)
-            own_dy = True
-        else:
-            own_dy = False
-        acc[y.id] = dy
+        # Back-propagation runs in its own scope: every temporary it creates (clones, masks,
+        # partial sums, the gradients of intermediates) is disposed when the scope ends, only the
+        # gradients of xs survive (engine.ts:764-779 wraps this in tidy).
+        self.startScope("backprop")
+        grads = None
         try:
+            acc = {y.id: dy if dy is not None else ops.tensor(np.ones(y.shape, np.float32), y.shape)}
             backpropagate_gradients(acc, filtered)
             grads = []
             for x in xs:
-                g = acc.pop(x.id, None)
+                g = acc.get(x.id)
                 if g is None:
                     g = ops.tensor(np.zeros(x.shape, np.float32), x.shape)
+                elif g is dy:
+                    g = dy.clone()   # x is y itself: hand back a tensor the caller may dispose
                 grads.append(g)
         finally:
-            keep_ids = {id(g) for g in locals().get("grads", [])}
-            for g in acc.values():
-                if id(g) not in keep_ids and not (g is dy and not own_dy) and not g.isDisposed:
-                    g.dispose()
-            if own_dy and id(dy) not in keep_ids and not dy.isDisposed:
-                dy.dispose()
+            self.endScope(grads)
             self._dispose_tape(tape)
         return y, grads
 
@@ -402,10 +398,6 @@ def backpropagate_gradients(acc, filtered_tape):
                 acc[x.id] = ops.add(cur, dx)
                 cur.dispose()
                 dx.dispose()
-        # the gradient of an intermediate is not needed once it has been propagated
-        if dy is not None and out.id in acc and node is not filtered_tape[-1]:
-            done = acc.pop(out.id)
-            done.dispose()
 
 
 def _tensors_in(result):
