@@ -202,3 +202,38 @@ def test_rgb_stem_conv(tf, b, h, w, n, stride, pad):
         assert rel_err(got.dataSync().reshape(want.shape), want) <= 1e-3
     finally:
         bk.setMathMode("3xtf32")
+
+
+# ---- dense convolution fed entirely by TMA: one shifted-patch load per filter tap ----------------
+@pytest.mark.parametrize("b,h,w,cin,n,fh,fw,dil,pad", [
+    (8, 56, 56, 64, 64, 3, 3, 1, "same"),     # BASELINE config 2's shape
+    (2, 20, 23, 32, 40, 3, 3, 1, "same"),     # overhanging patches, N not a multiple of 32
+    (1, 9, 9, 64, 8, 5, 5, 2, "same"),        # dilation 2: taps reach 4 pixels out
+    (3, 16, 16, 96, 256, 1, 3, 1, "valid"),   # asymmetric filter, widest N
+    (2, 7, 30, 32, 32, 2, 2, 1, 1),           # numeric pad
+])
+def test_conv2d_shifted_patch_tma(tf, b, h, w, cin, n, fh, fw, dil, pad):
+    bk = tf.ENGINE.backend
+    bk.setMathMode("tf32")
+    try:
+        rng = _rng(h * 31 + cin + n)
+        x = rng.integers(-3, 4, (b, h, w, cin)).astype(np.float32)
+        wt = rng.integers(-2, 3, (fh, fw, cin, n)).astype(np.float32)
+        bias = rng.integers(-5, 6, n).astype(np.float32)
+        ci = oracle.compute_conv2d_info(x.shape, wt.shape, 1, dil, pad)
+        want = oracle.fused_conv2d(x, wt, ci, bias=bias, activation="relu")
+        bk.profileBegin(8)
+        got = tf.ops.fused_conv2d(tf.ops.tensor(x), tf.ops.tensor(wt), 1, pad, dilations=dil,
+                                  bias=tf.ops.tensor(bias), activation="relu")
+        names = [name for name, _ in bk.profileEnd()]
+        assert names[-1] == "conv2d_tcgen05 (shifted-patch TMA, TF32)", names
+        # small integers are exact in tf32: bit-identical to the oracle whatever the summation order
+        assert np.array_equal(got.dataSync().reshape(want.shape), want)
+        x = rng.uniform(-1, 1, x.shape).astype(np.float32)
+        wt = rng.normal(0, 0.2, wt.shape).astype(np.float32)
+        want = oracle.fused_conv2d(x, wt, ci, bias=bias, activation="relu")
+        got = tf.ops.fused_conv2d(tf.ops.tensor(x), tf.ops.tensor(wt), 1, pad, dilations=dil,
+                                  bias=tf.ops.tensor(bias), activation="relu")
+        assert rel_err(got.dataSync().reshape(want.shape), want) <= 1e-3
+    finally:
+        bk.setMathMode("3xtf32")

@@ -242,6 +242,16 @@ extern "C" int tfjs_cuda_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_te
     if (rc) return rc;
     return launch_conv_rgb_tcgen05(ctx, (const float*)x->ptr, *ci, pw.hi, pw.kp, (float*)o->ptr, e);
   }
+  // Cin a multiple of 32 at stride 1: each filter tap's A tile is one TMA load of the shifted
+  // output patch, no gather threads (TF32; 3xTF32 and strided shapes take the gather path below).
+  if (ctx->use_tensor_cores && conv_tma_tcgen05_supported(*ci, e.activation, ctx->math_mode)) {
+    PackedWeights pw;
+    bool temporary;
+    rc = packed_weights(ctx, w, 0, (int64_t)ci->filterHeight * ci->filterWidth * ci->inChannels,
+                        ci->outChannels, false, true, &pw, &temporary);
+    if (rc) return rc;
+    return launch_conv_tma_tcgen05(ctx, (const float*)x->ptr, *ci, pw.hi, pw.kp, (float*)o->ptr, e);
+  }
   const int mode = ctx->use_tensor_cores ? tcgen05_conv_mode(*ci) : 0;
   if (mode) {
     const int64_t K = (int64_t)ci->filterHeight * ci->filterWidth * ci->inChannels;

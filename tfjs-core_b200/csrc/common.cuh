@@ -266,6 +266,9 @@ int launch_sepconv_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d
 bool conv_rgb_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode);
 int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& ci, const float* w_hi,
                             int64_t kp, float* y, const EpilogueArgs& epi);
+bool conv_tma_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode);
+int launch_conv_tma_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& ci, const float* w_hi,
+                            int64_t kp, float* y, const EpilogueArgs& epi);
 // conv.cu
 int launch_conv2d_direct(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* y,
                          const tfjs_conv2d_info& ci, const EpilogueArgs& epi);

@@ -48,6 +48,10 @@ constexpr int SMEM_LIMIT = 232448;
 constexpr int MODE_DW = 0;   // depthwise 3x3 over 32-channel k-blocks feeding the GEMM
 constexpr int MODE_RGB = 1;  // dense 3x3 convolution of a 3-channel image: the window rows are turned
                              // into im2col rows (K' = 10 * filter row + 3 * filter column + channel)
+constexpr int MODE_CONV = 2; // dense convolution, Cin a multiple of 32, stride 1: the A tile of k-block
+                             // (filter row, filter column, 32-channel group) is the patch shifted by that
+                             // tap, loaded by TMA straight into the swizzled layout the tensor core reads;
+                             // no thread touches the operands (zero fill of the load is the padding)
 
 template <int S, int MODE>
 struct Raw {
@@ -58,7 +62,7 @@ struct Raw {
   // floats per window row: 32 channels per pixel, or (RGB) 3 per pixel plus up to 3 floats of
   // slack in front so that the copy can start on a 16-byte boundary, rounded up to 16 bytes
   static constexpr int ROW_FLOATS = MODE == MODE_DW ? COLS * BLOCK_K : (COLS * 3 + 3 + 3) / 4 * 4;
-  static constexpr int BYTES = ROWS * ROW_FLOATS * 4;
+  static constexpr int BYTES = MODE == MODE_CONV ? A_TILE_BYTES : ROWS * ROW_FLOATS * 4;
   static constexpr int STRIDE = (BYTES + 1023) / 1024 * 1024;
   static constexpr int PIX = PW * PART_ROWS * 8 / DW_THREADS;  // adjacent output pixels per thread: 4 / 2
 };
@@ -84,6 +88,7 @@ struct SepParams {
   float dw_lo, dw_hi;
   EpilogueArgs epi;                 // of the pointwise convolution
   int rgb_off;                      // MODE_RGB: floats between the 16-byte aligned copy start and the window
+  int fh, fw, dil_h, dil_w, cin_groups;  // MODE_CONV: filter size, dilation, Cin / 32
   int* status;
 };
 
@@ -213,6 +218,9 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   static_assert(RAW_STAGES >= 2, "the input ring needs two stages");
   constexpr int W_STAGE_BYTES = BLOCK_N * BLOCK_K * 4;
   constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // 64 .. 512
+  // who frees a raw stage: the depthwise / im2col threads that read it, or (MODE_CONV, where the
+  // stage is the A operand itself) the commit of the MMAs that read it
+  constexpr int RAW_READERS = MODE == MODE_CONV ? 1 : DW_THREADS;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -240,7 +248,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   if (threadIdx.x == 0) {
     for (int s = 0; s < RAW_STAGES; s++) {
       mbar_init(smem_u32(&raw_full[s]), 1);
-      mbar_init(smem_u32(&raw_empty[s]), DW_THREADS);
+      mbar_init(smem_u32(&raw_empty[s]), RAW_READERS);
     }
     for (int s = 0; s < W_STAGES; s++) {
       mbar_init(smem_u32(&w_full[s]), 1);
@@ -301,7 +309,12 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
             ok = mbar_wait(smem_u32(&raw_empty[rs]), rphase ^ 1, abort_flag, p.status, 12);
             if (!ok) break;
             mbar_arrive_expect_tx(smem_u32(&raw_full[rs]), R::BYTES);
-            if (MODE == MODE_DW)
+            if (MODE == MODE_CONV) {
+              const int tap = kb / p.cin_groups, cg = kb - tap * p.cin_groups;
+              const int wr = tap / p.fw, wc = tap - wr * p.fw;
+              tma_load_4d(smem_u32(raw + rs * R::STRIDE), &map_x, smem_u32(&raw_full[rs]), cg * BLOCK_K,
+                          x0 + wc * p.dil_w, y0 + wr * p.dil_h, b);
+            } else if (MODE == MODE_DW)
               tma_load_4d(smem_u32(raw + rs * R::STRIDE), &map_x, smem_u32(&raw_full[rs]), kb * BLOCK_K, x0,
                           y0 + part * R::PART_ROWS * S, b);
             else  // image rows as runs of W*3 floats; the copy starts rgb_off floats before the window
@@ -316,8 +329,8 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(128, BLOCK_N);
-      int ws = 0, slot = 0, local = 0;
-      uint32_t wphase = 0, sphase = 0;
+      int ws = 0, slot = 0, local = 0, rs = 0;
+      uint32_t wphase = 0, sphase = 0, rphase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, local++) {
         const int acc = local & 1;
@@ -328,23 +341,32 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
         const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
         for (int kb = 0; kb < p.num_k_blocks; kb++) {
           ok = mbar_wait(smem_u32(&w_full[ws]), wphase, abort_flag, p.status, 14);
-          if (ok) ok = mbar_wait(smem_u32(&a_full[slot]), sphase, abort_flag, p.status, 15);
+          if (ok && MODE == MODE_CONV) ok = mbar_wait(smem_u32(&raw_full[rs]), rphase, abort_flag, p.status, 15);
+          if (ok && MODE != MODE_CONV) ok = mbar_wait(smem_u32(&a_full[slot]), sphase, abort_flag, p.status, 15);
           if (!ok) break;
           tcgen05_fence_after();
-          const uint32_t a_s = smem_u32(a_tiles + slot * A_TILE_BYTES);
+          const uint32_t a_s = MODE == MODE_CONV ? smem_u32(raw + rs * R::STRIDE)
+                                                 : smem_u32(a_tiles + slot * A_TILE_BYTES);
           const uint32_t w_s = smem_u32(w_tiles + ws * W_STAGE_BYTES);
 #pragma unroll
           for (int k = 0; k < BLOCK_K / 8; k++)
             tcgen05_mma_tf32(tmem_d, make_smem_desc(a_s + k * 32), make_smem_desc(w_s + k * 32), idesc,
                              (kb > 0 || k > 0) ? 1u : 0u);
           tcgen05_commit(smem_u32(&w_empty[ws]));
-          tcgen05_commit(smem_u32(&a_empty[slot]));
+          if (MODE == MODE_CONV) {
+            tcgen05_commit(smem_u32(&raw_empty[rs]));
+            if (++rs == RAW_STAGES) { rs = 0; rphase ^= 1; }
+          } else {
+            tcgen05_commit(smem_u32(&a_empty[slot]));
+            if (++slot == A_SLOTS) { slot = 0; sphase ^= 1; }
+          }
           if (++ws == W_STAGES) { ws = 0; wphase ^= 1; }
-          if (++slot == A_SLOTS) { slot = 0; sphase ^= 1; }
         }
         if (ok) tcgen05_commit(smem_u32(&tmem_full_bar[acc]));
       }
     }
+  } else if (warp >= 10 && MODE == MODE_CONV) {
+    // nothing to do: the operands go from TMA to the tensor core
   } else if (warp >= 10) {
     // ---------------- depthwise warps ----------------
     const int t = threadIdx.x - 320;
@@ -488,6 +510,7 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap&
   const int grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
   launch_ex(ctx, kernel, dim3(grid), dim3(THREADS), smem_bytes, mx, mw, my, p);
   if (MODE == MODE_RGB) return post_launch(ctx, "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32)");
+  if (MODE == MODE_CONV) return post_launch(ctx, "conv2d_tcgen05 (shifted-patch TMA, TF32)");
   return post_launch(ctx, S == 1 ? "separableConv2d (fused dw3x3 s1 + pw, TF32)"
                                  : "separableConv2d (fused dw3x3 s2 + pw, TF32)");
 }
@@ -497,7 +520,8 @@ int launch_stride(tfjs_cuda_ctx* ctx, int block_n, const CUtensorMap& mx, const 
                   const CUtensorMap& my, const SepParams& p) {
   switch (block_n) {
     case 32:
-      if (MODE == MODE_RGB) return launch_variant<32, S, MODE_RGB>(ctx, mx, mw, my, p);  // else falls through
+      if (MODE != MODE_DW) return launch_variant<32, S, MODE == MODE_DW ? MODE_RGB : MODE>(ctx, mx, mw, my, p);
+      // depthwise mode has no 32-wide variant: falls through
     case 64: return launch_variant<64, S, MODE>(ctx, mx, mw, my, p);
     case 128: return launch_variant<128, S, MODE>(ctx, mx, mw, my, p);
     default: return launch_variant<256, S, MODE>(ctx, mx, mw, my, p);
@@ -624,4 +648,59 @@ int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2
   p.status = ctx->d_status;
   return S == 1 ? launch_stride<1, MODE_RGB>(ctx, block_n, mx, mw, my, p)
                 : launch_stride<2, MODE_RGB>(ctx, block_n, mx, mw, my, p);
+}
+
+// Dense convolution with Cin a multiple of 32 and stride 1 (any filter size and dilation), TF32:
+// every k-block's A tile is the output patch shifted by one filter tap, fetched by one TMA load.
+bool conv_tma_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode) {
+  return math_mode == TFJS_MATH_TF32 && ci.inChannels >= 32 && ci.inChannels % 32 == 0 && ci.strideHeight == 1 &&
+         ci.strideWidth == 1 && ci.outChannels >= 8 && ci.outChannels <= 256 && ci.outChannels % 4 == 0 &&
+         ci.batchSize >= 1 && ci.batchSize < 65536 && ci.outHeight >= 1 && ci.outWidth >= 1 &&
+         (int64_t)ci.filterHeight * ci.filterWidth * ci.inChannels < (1ll << 24) && activation != TFJS_ACT_PRELU &&
+         tcgen05_gemm_supported(128, ci.outChannels, ci.inChannels);
+}
+
+int launch_conv_tma_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& ci, const float* w_hi,
+                            int64_t kp, float* y, const EpilogueArgs& epi) {
+  const int64_t N = ci.outChannels;
+  const int C = ci.inChannels;
+  const int block_n = N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256));
+  CUtensorMap mx, mw, my;
+  const uint64_t xd[4] = {(uint64_t)C, (uint64_t)ci.inWidth, (uint64_t)ci.inHeight, (uint64_t)ci.batchSize};
+  const uint64_t xs[3] = {(uint64_t)C * 4, (uint64_t)ci.inWidth * C * 4, (uint64_t)ci.inHeight * ci.inWidth * C * 4};
+  const uint32_t xb[4] = {BLOCK_K, PW, PH, 1};
+  const uint64_t wd[2] = {(uint64_t)kp, (uint64_t)N};
+  const uint64_t ws[1] = {(uint64_t)kp * 4};
+  const uint32_t wb[2] = {BLOCK_K, (uint32_t)block_n};
+  const uint64_t yd[4] = {(uint64_t)N, (uint64_t)ci.outWidth, (uint64_t)ci.outHeight, (uint64_t)ci.batchSize};
+  const uint64_t ys[3] = {(uint64_t)N * 4, (uint64_t)ci.outWidth * N * 4, (uint64_t)ci.outHeight * ci.outWidth * N * 4};
+  const uint32_t yb[4] = {32, PW, 2, 1};
+  const bool ok =
+      tma_encode_tiled(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, x, xd, xs, xb, CU_TENSOR_MAP_SWIZZLE_128B) &&
+      tma_encode_tiled(&mw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, w_hi, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B) &&
+      tma_encode_tiled(&my, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, y, yd, ys, yb, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!ok) return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+  SepParams p;
+  memset(&p, 0, sizeof(p));
+  p.B = ci.batchSize;
+  p.inH = ci.inHeight;
+  p.inW = ci.inWidth;
+  p.C = C;
+  p.outH = ci.outHeight;
+  p.outW = ci.outWidth;
+  p.N = (int)N;
+  p.pad_r = ci.padTop;
+  p.pad_c = ci.padLeft;
+  p.tiles_y = (ci.outHeight + PH - 1) / PH;
+  p.tiles_x = (ci.outWidth + PW - 1) / PW;
+  p.num_tiles = ci.batchSize * p.tiles_y * p.tiles_x;
+  p.fh = ci.filterHeight;
+  p.fw = ci.filterWidth;
+  p.dil_h = ci.dilationHeight;
+  p.dil_w = ci.dilationWidth;
+  p.cin_groups = C / BLOCK_K;
+  p.num_k_blocks = ci.filterHeight * ci.filterWidth * p.cin_groups;
+  p.epi = epi;
+  p.status = ctx->d_status;
+  return launch_stride<1, MODE_CONV>(ctx, block_n, mx, mw, my, p);
 }
