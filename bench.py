@@ -479,7 +479,7 @@ def run_cuda(args):
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel family, averaged over
 # the family's launches of one forward pass, from the batch-256 (fused blocks: batch-128) ncu
 # captures summarised under profiles/; it grows in proportion to the batch.
-TRAFFIC_MB_PER_IMAGE_AND_LAUNCH = {"separable_fused": 1778.7 / 4 / 128,  # profiles/sepconv_tcgen05_mobilenet.md
+TRAFFIC_MB_PER_IMAGE_AND_LAUNCH = {"separable_fused": 1778.7 / 4 / 128,
                                    "gemm_tcgen05": 4056.76 / 14 / 256,
                                    "depthwise3x3_strip": 4610.62 / 13 / 256,
                                    "conv2d_tcgen05": 505.0 / 256}

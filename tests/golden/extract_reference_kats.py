@@ -5,7 +5,7 @@ Reads the literal arrays inside tfjs-core's jasmine spec files (as text; nothing
 executed) and writes them to ``reference_kats.json`` next to this script.  Run in a
 container where the reference checkout is mounted::
 
-    python tests/golden/extract_reference_kats.py /root/reference
+    python tests/golden/extract_reference_kats.py <path to the tfjs checkout>
 
 Each case records the spec file and the line of its ``it(...)`` so a reader can find it.
 Operands are located inside the spec body by element count: ``sized(n, k)`` is the k-th
@@ -305,7 +305,7 @@ def find_clip_occurrence(root, rel, name):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("-") else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("-") else os.environ.get("TFJS_REFERENCE", "reference")
     out = []
     for kind, rel, name, build, occ in CASES:
         if kind == "clip":

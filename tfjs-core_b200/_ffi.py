@@ -1,6 +1,6 @@
 """ctypes binding of the C ABI declared in include/tfjs_cuda.h.
 
-The same entry points are what the Node N-API shim binds; Python is the
+The same entry points are what a Node N-API shim binds; Python is the
 host language here because no JavaScript toolchain exists on the build or GPU machines.
 There is no fallback: if the shared library is missing this module raises.
 """
