@@ -217,7 +217,10 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   constexpr int RAW_STAGES = raw_stages<S, MODE>(BLOCK_N);
   static_assert(RAW_STAGES >= 2, "the input ring needs two stages");
   constexpr int W_STAGE_BYTES = BLOCK_N * BLOCK_K * 4;
-  constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // 64 .. 512
+  // Accumulator buffers in tensor memory: two, or four when a tile is only 32 columns wide; then
+  // each half of the epilogue warps drains every other tile, so two epilogues run at a time.
+  constexpr int NUM_ACC = BLOCK_N == 32 ? 4 : 2;
+  constexpr uint32_t TMEM_COLS = NUM_ACC * BLOCK_N;  // 128 .. 512
   // who frees a raw stage: the depthwise / im2col threads that read it, or (MODE_CONV, where the
   // stage is the A operand itself) the commit of the MMAs that read it
   constexpr int RAW_READERS = MODE == MODE_CONV ? 1 : DW_THREADS;
@@ -237,9 +240,9 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   uint64_t* w_empty = w_full + W_STAGES;           // [W_STAGES] MMA -> TMA
   uint64_t* a_full = w_empty + W_STAGES;           // [A_SLOTS] depthwise warps -> MMA
   uint64_t* a_empty = a_full + A_SLOTS;            // [A_SLOTS] MMA -> depthwise warps
-  uint64_t* tmem_full_bar = a_empty + A_SLOTS;     // [2] MMA -> epilogue
-  uint64_t* tmem_empty_bar = tmem_full_bar + 2;    // [2] epilogue -> MMA
-  uint32_t* tmem_ptr_holder = (uint32_t*)(tmem_empty_bar + 2);
+  uint64_t* tmem_full_bar = a_empty + A_SLOTS;           // [NUM_ACC] MMA -> epilogue
+  uint64_t* tmem_empty_bar = tmem_full_bar + NUM_ACC;    // [NUM_ACC] epilogue -> MMA
+  uint32_t* tmem_ptr_holder = (uint32_t*)(tmem_empty_bar + NUM_ACC);
   volatile int* abort_flag = (volatile int*)(tmem_ptr_holder + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -258,7 +261,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       mbar_init(smem_u32(&a_full[s]), DW_THREADS);
       mbar_init(smem_u32(&a_empty[s]), 1);
     }
-    for (int a = 0; a < 2; a++) {
+    for (int a = 0; a < NUM_ACC; a++) {
       mbar_init(smem_u32(&tmem_full_bar[a]), 1);
       mbar_init(smem_u32(&tmem_empty_bar[a]), epi_arrivals(BLOCK_N));
     }
@@ -333,8 +336,8 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       uint32_t wphase = 0, sphase = 0, rphase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, local++) {
-        const int acc = local & 1;
-        const uint32_t acc_phase = (local >> 1) & 1;
+        const int acc = local % NUM_ACC;
+        const uint32_t acc_phase = (local / NUM_ACC) & 1;
         ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status, 13);
         if (!ok) break;
         tcgen05_fence_after();
@@ -410,7 +413,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     constexpr int MY_CHUNKS = CHUNKS >= 2 ? CHUNKS / 2 : 1;
     const int quarter = warp & 3;
     const int half = warp >> 2;
-    if (CHUNKS >= 2 || half == 0) {
+    {
     uint8_t* stage_buf = c_stage + warp * C_CHUNK_BYTES;
     float* bias_s = reinterpret_cast<float*>(bias_stage + warp * 128);
     const bool has_bias = p.epi.bias != nullptr;
@@ -420,8 +423,9 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       const int b = tile / tiles_per_image;
       const int rem = tile - b * tiles_per_image;
       const int ty = rem / p.tiles_x, tx = rem - ty * p.tiles_x;
-      const int acc = local & 1;
-      const uint32_t acc_phase = (local >> 1) & 1;
+      if (CHUNKS == 1 && (local & 1) != half) continue;  // 32-wide tiles alternate between the halves
+      const int acc = local % NUM_ACC;
+      const uint32_t acc_phase = (local / NUM_ACC) & 1;
       float bias_l[MY_CHUNKS];
 #pragma unroll
       for (int i = 0; i < MY_CHUNKS; i++) {
