@@ -30,7 +30,8 @@ namespace {
 constexpr int PH = 8, PW = 16;                    // output patch
 constexpr int BLOCK_K = 32;
 constexpr int A_TILE_BYTES = 128 * BLOCK_K * 4;   // 16 KB
-constexpr int A_SLOTS = 2;
+constexpr int MAX_A_SLOTS = 3;
+__host__ __device__ constexpr int a_slots(int block_n, int s, int mode) { return (mode == 0 && s == 1 && block_n <= 128) ? 3 : 2; }
 constexpr int EPI_WARPS = 8;
 constexpr int C_CHUNK_BYTES = 32 * 32 * 4;
 constexpr int C_STAGING_BYTES = EPI_WARPS * C_CHUNK_BYTES;
@@ -71,7 +72,7 @@ __host__ __device__ constexpr int w_stages(int block_n) { return block_n >= 256 
 __host__ __device__ constexpr int epi_arrivals(int block_n) { return block_n >= 64 ? EPI_WARPS : 4; }
 template <int S, int MODE>
 __host__ __device__ constexpr int raw_stages(int block_n) {
-  int left = SMEM_LIMIT - 1024 - A_SLOTS * A_TILE_BYTES - w_stages(block_n) * block_n * BLOCK_K * 4 -
+  int left = SMEM_LIMIT - 1024 - a_slots(block_n, S, MODE) * A_TILE_BYTES - w_stages(block_n) * block_n * BLOCK_K * 4 -
              C_STAGING_BYTES - BIAS_STAGING_BYTES - DW_TABLE_BYTES - BARRIER_BYTES;
   int n = left / Raw<S, MODE>::STRIDE;
   return n > (MODE == MODE_DW ? 4 : 8) ? (MODE == MODE_DW ? 4 : 8) : n;
@@ -122,6 +123,10 @@ __device__ __forceinline__ float4 lds128(uint32_t addr) {
   asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
   return v;
 }
+// the same 16 bytes as two packed float pairs (x, y) and (z, w)
+__device__ __forceinline__ void lds128_pairs(uint32_t addr, uint64_t& lo, uint64_t& hi) {
+  asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(lo), "=l"(hi) : "r"(addr));
+}
 __device__ __forceinline__ void sts128(uint32_t addr, const float4& v) {
   asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
                : "memory");
@@ -147,38 +152,45 @@ __device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t 
   const int r = g / GROUPS_PER_ROW;            // row inside this part
   const int c0 = (g % GROUPS_PER_ROW) * R::PIX;
   const int ch = kb * BLOCK_K + q * 4;
-  float4 acc[R::PIX];
+  // the four channels travel as two packed float pairs: one fma.rn.f32x2 does two of the taps'
+  // multiply-adds, each lane rounding exactly like fmaf
+  uint64_t acc[R::PIX][2];
 #pragma unroll
-  for (int j = 0; j < R::PIX; j++) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j = 0; j < R::PIX; j++) acc[j][0] = acc[j][1] = 0ull;
 #pragma unroll
   for (int dr = 0; dr < 3; dr++) {
     const uint32_t row = raw + (uint32_t)(((r * S + dr) * R::COLS + c0 * S) * (BLOCK_K * 4) + q * 16);
-    float4 in[WIN];
+    uint64_t in[WIN][2];
 #pragma unroll
-    for (int i = 0; i < WIN; i++) in[i] = lds128(row + i * (BLOCK_K * 4));
+    for (int i = 0; i < WIN; i++) lds128_pairs(row + i * (BLOCK_K * 4), in[i][0], in[i][1]);
 #pragma unroll
     for (int wc = 0; wc < 3; wc++) {
-      const float4 f = lds128(table + (uint32_t)(((dr * 3 + wc) * p.C + ch) * 4));
+      uint64_t f0, f1;
+      lds128_pairs(table + (uint32_t)(((dr * 3 + wc) * p.C + ch) * 4), f0, f1);
 #pragma unroll
       for (int j = 0; j < R::PIX; j++) {
-        const float4 v = in[j * S + wc];
-        acc[j].x = fmaf(v.x, f.x, acc[j].x);
-        acc[j].y = fmaf(v.y, f.y, acc[j].y);
-        acc[j].z = fmaf(v.z, f.z, acc[j].z);
-        acc[j].w = fmaf(v.w, f.w, acc[j].w);
+        acc[j][0] = fma_f32x2(in[j * S + wc][0], f0, acc[j][0]);
+        acc[j][1] = fma_f32x2(in[j * S + wc][1], f1, acc[j][1]);
       }
     }
   }
-  const float4 b = lds128(table + (uint32_t)((9 * p.C + ch) * 4));
+  uint64_t b0, b1;
+  lds128_pairs(table + (uint32_t)((9 * p.C + ch) * 4), b0, b1);
   const int m0 = (part * R::PART_ROWS + r) * PW + c0;  // first of this thread's rows of the A tile
 #pragma unroll
   for (int j = 0; j < R::PIX; j++) {
-    float4 o = acc[j];
-    if (has_bias) { o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w; }
-    o.x = dw_activate<ACT>(o.x, p.dw_lo, p.dw_hi);
-    o.y = dw_activate<ACT>(o.y, p.dw_lo, p.dw_hi);
-    o.z = dw_activate<ACT>(o.z, p.dw_lo, p.dw_hi);
-    o.w = dw_activate<ACT>(o.w, p.dw_lo, p.dw_hi);
+    if (has_bias) {
+      acc[j][0] = add_f32x2(acc[j][0], b0);
+      acc[j][1] = add_f32x2(acc[j][1], b1);
+    }
+    uint32_t ox, oy, oz, ow;
+    unpack_f32x2(acc[j][0], ox, oy);
+    unpack_f32x2(acc[j][1], oz, ow);
+    float4 o;
+    o.x = dw_activate<ACT>(__uint_as_float(ox), p.dw_lo, p.dw_hi);
+    o.y = dw_activate<ACT>(__uint_as_float(oy), p.dw_lo, p.dw_hi);
+    o.z = dw_activate<ACT>(__uint_as_float(oz), p.dw_lo, p.dw_hi);
+    o.w = dw_activate<ACT>(__uint_as_float(ow), p.dw_lo, p.dw_hi);
     sts128(a_tile + swz(m0 + j, q * 16), o);
   }
 }
@@ -214,6 +226,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
                        const __grid_constant__ CUtensorMap map_y, SepParams p) {
   using R = Raw<S, MODE>;
   constexpr int W_STAGES = w_stages(BLOCK_N);
+  constexpr int A_SLOTS = a_slots(BLOCK_N, S, MODE);
   constexpr int RAW_STAGES = raw_stages<S, MODE>(BLOCK_N);
   static_assert(RAW_STAGES >= 2, "the input ring needs two stages");
   constexpr int W_STAGE_BYTES = BLOCK_N * BLOCK_K * 4;
@@ -501,7 +514,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 template <int BLOCK_N, int S, int MODE>
 int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my,
                    const SepParams& p) {
-  constexpr int smem_bytes = 1024 + A_SLOTS * A_TILE_BYTES + w_stages(BLOCK_N) * BLOCK_N * BLOCK_K * 4 +
+  constexpr int smem_bytes = 1024 + a_slots(BLOCK_N, S, MODE) * A_TILE_BYTES + w_stages(BLOCK_N) * BLOCK_N * BLOCK_K * 4 +
                              C_STAGING_BYTES + raw_stages<S, MODE>(BLOCK_N) * Raw<S, MODE>::STRIDE +
                              DW_TABLE_BYTES + BIAS_STAGING_BYTES + BARRIER_BYTES;
   static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
