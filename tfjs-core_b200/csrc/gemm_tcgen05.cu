@@ -190,10 +190,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // The ring holds few A tiles when the weight tile is large (3 stages at BLOCK_N = 256), too
+      // few bytes in flight to cover DRAM latency.  A second cursor runs PREFETCH k-blocks ahead of
+      // the loads and pulls the A tiles into L2, so that the loads themselves are L2 hits.
+      // (Only where the k loop is long, K >= 512: on the short-K layers, which run at the DRAM
+      // roofline anyway, the extra requests measured slower.)
+      const int PREFETCH = (AMODE == A_MATRIX && STAGES < 6 && p.num_k_blocks >= 16) ? 8 : 0;
+      int ptile = blockIdx.x, pkb = 0;
+      for (int i = 0; i < PREFETCH && ptile < num_tiles; i++) {
+        tma_prefetch_2d(&map_a, pkb * BLOCK_K, (ptile / p.num_n_tiles) * BLOCK_M);
+        if (++pkb == p.num_k_blocks) { pkb = 0; ptile += gridDim.x; }
+      }
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile / p.num_n_tiles) * BLOCK_M;
         const int n0 = (tile % p.num_n_tiles) * BLOCK_N;
         for (int kb = 0; kb < p.num_k_blocks; kb++) {
+          if (PREFETCH > 0 && ptile < num_tiles) {
+            tma_prefetch_2d(&map_a, pkb * BLOCK_K, (ptile / p.num_n_tiles) * BLOCK_M);
+            if (++pkb == p.num_k_blocks) { pkb = 0; ptile += gridDim.x; }
+          }
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 1);
           if (!ok) break;
           const uint32_t bar = smem_u32(&full_bar[stage]);
