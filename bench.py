@@ -270,6 +270,8 @@ KERNEL_FAMILY = {"separableConv2d (fused dw3x3 s1 + pw, TF32)": "separable_fused
                  "gemm_tcgen05 (TF32, uint8 weights)": "gemm_tcgen05",
                  "gemm_tcgen05 (3xTF32, uint8 weights)": "gemm_tcgen05",
                  "conv2d_tcgen05 (TF32)": "conv2d_tcgen05", "conv2d_tcgen05 (3xTF32)": "conv2d_tcgen05",
+                 "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32)": "conv2d_tcgen05",
+                 "conv2d_tcgen05 (shifted-patch TMA, TF32)": "conv2d_tcgen05",
                  "depthwiseConv2D (3x3 strip)": "depthwise3x3_strip", "conv2d (stem)": "conv2d_stem",
                  "avgPool (global)": "global_avgpool", "softmax_last": "softmax"}
 
@@ -479,10 +481,10 @@ def run_cuda(args):
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel family, averaged over
 # the family's launches of one forward pass, from the batch-256 (fused blocks: batch-128) ncu
 # captures summarised under profiles/; it grows in proportion to the batch.
-TRAFFIC_MB_PER_IMAGE_AND_LAUNCH = {"separable_fused": 1778.7 / 4 / 128,
-                                   "gemm_tcgen05": 4056.76 / 14 / 256,
-                                   "depthwise3x3_strip": 4610.62 / 13 / 256,
-                                   "conv2d_tcgen05": 505.0 / 256}
+TRAFFIC_MB_PER_IMAGE_AND_LAUNCH = {"separable_fused": 1779.9 / 4 / 128,
+                                   "gemm_tcgen05": 4062.4 / 14 / 256,
+                                   "depthwise3x3_strip": 4638.7 / 13 / 256,
+                                   "conv2d_tcgen05": 502.7 / 256}
 
 
 def main():
