@@ -591,6 +591,39 @@ int launch_depthwise(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* 
   return post_launch(ctx, "depthwiseConv2D (generic)");
 }
 
+// Global average pool through shared memory: a block stages the hw x 256-channel slab of one image
+// with 16-byte asynchronous copies (every copy of the block in flight at once, which is what a
+// small batch needs to cover the memory latency), then thread c sums channel c tap by tap in
+// float64 in the reference's order, so the result is bit-identical to the kernels above.
+constexpr int AVG_SLAB_CH = 256;
+__global__ void __launch_bounds__(AVG_SLAB_CH) global_avgpool_slab_kernel(const float* __restrict__ x,
+                                                                          float* __restrict__ y, int hw, int C) {
+  extern __shared__ __align__(16) float slab[];
+  const int chunks = (C + AVG_SLAB_CH - 1) / AVG_SLAB_CH;
+  const int b = blockIdx.x / chunks;
+  const int c0 = (blockIdx.x % chunks) * AVG_SLAB_CH;
+  const int width = min(AVG_SLAB_CH, C - c0);  // multiple of 4
+  const int quads = width / 4;
+  const float* src = x + (int64_t)b * hw * C + c0;
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(slab);
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int i = threadIdx.x; i < hw * quads; i += AVG_SLAB_CH) {
+    const int tap = i / quads, q = i % quads;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)(tap * AVG_SLAB_CH + q * 4) * 4),
+                 "l"(src + (int64_t)tap * C + q * 4)
+                 : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
+  if ((int)threadIdx.x < width) {
+    double s = 0.0;
+    for (int i = 0; i < hw; i++) s += (double)slab[i * AVG_SLAB_CH + threadIdx.x];
+    y[(int64_t)b * C + c0 + threadIdx.x] = (float)(s / (double)hw);
+  }
+}
+
 int launch_pool2d(tfjs_cuda_ctx* ctx, const float* x, float* y, const tfjs_conv2d_info& ci,
                   int is_avg) {
   const int64_t total = (int64_t)ci.batchSize * ci.outHeight * ci.outWidth * ci.inChannels;
@@ -598,6 +631,16 @@ int launch_pool2d(tfjs_cuda_ctx* ctx, const float* x, float* y, const tfjs_conv2
   const bool global = is_avg && ci.outHeight == 1 && ci.outWidth == 1 && ci.padTop == 0 &&
                       ci.padLeft == 0 && ci.dilationHeight == 1 && ci.dilationWidth == 1 &&
                       ci.filterHeight == ci.inHeight && ci.filterWidth == ci.inWidth;
+  const int hw = ci.inHeight * ci.inWidth;
+  if (global && ci.inChannels % 4 == 0 && ((uintptr_t)x & 15) == 0 && hw <= 56) {
+    const int chunks = (ci.inChannels + AVG_SLAB_CH - 1) / AVG_SLAB_CH;
+    const size_t smem = (size_t)hw * AVG_SLAB_CH * sizeof(float);
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(global_avgpool_slab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_ex(ctx, global_avgpool_slab_kernel, dim3((unsigned)(ci.batchSize * chunks)), dim3(AVG_SLAB_CH), smem, x, y,
+              hw, ci.inChannels);
+    return post_launch(ctx, "avgPool (global)");
+  }
   if (global && ci.inChannels % 4 == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0) {
     launch_ex(ctx, global_avgpool_vec4_kernel, dim3(grid_1d(total / 4, 64, ctx->sm_count, 32)), dim3(64), 0,
               (const float4*)x, (float4*)y, ci.batchSize, ci.inHeight * ci.inWidth, ci.inChannels / 4);

@@ -142,13 +142,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
-      // the TMA producer's expect_tx arrival, plus one arrival per gather thread in conv modes
-      mbar_init(smem_u32(&full_bar[s]), AMODE == A_MATRIX ? 1 : 129);
+      // the TMA producer's expect_tx arrival, plus one arrival per gather warp in conv modes (lane 0
+      // arrives for its warp after __syncwarp: per-thread arrivals on one barrier serialise in the
+      // shared-memory pipe)
+      mbar_init(smem_u32(&full_bar[s]), AMODE == A_MATRIX ? 1 : 1 + 128 / 32);
       mbar_init(smem_u32(&empty_bar[s]), 1);
-      mbar_init(smem_u32(&conv_bar[s]), 128);
+      mbar_init(smem_u32(&conv_bar[s]), 128 / 32);
     }
     for (int d = 0; d < WQ_SLOTS; d++) {
-      mbar_init(smem_u32(&slot_full_bar[d]), NCONV);
+      mbar_init(smem_u32(&slot_full_bar[d]), NCONV / 32);
       mbar_init(smem_u32(&slot_empty_bar[d]), 1);
     }
     for (int a = 0; a < 2; a++) {
@@ -311,7 +313,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           }
         }
         fence_proxy_async_smem();
-        mbar_arrive(smem_u32(&full_bar[s]));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&full_bar[s]));
       };
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m = (tile / p.num_n_tiles) * BLOCK_M + t;
@@ -324,7 +327,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         const float* xb = g.x + (int64_t)b * g.inH * g.inW * g.Cin;
         int ci = 0, wc = 0, wr = 0;  // tap cursor of the vector gather (advances with kk)
         for (int kb = 0; kb < p.num_k_blocks; kb++) {
-          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 7);
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 7));
           if (!ok) break;
           const uint32_t row = smem_u32(a_hi + stage * A_STAGE_BYTES);
           if (AMODE == A_CONV_VEC) {
@@ -393,6 +396,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 5);
           if (ok && WQ)
             ok = mbar_wait(smem_u32(&slot_empty_bar[slot]), slot_phase ^ 1, abort_flag, p.status, 6);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           if (SPLIT) {
             float4* hi4 = reinterpret_cast<float4*>(a_hi + stage * A_STAGE_BYTES);
@@ -465,11 +469,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             }
           }
           fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
+          __syncwarp();
           if (WQ) {
-            mbar_arrive(smem_u32(&slot_full_bar[slot]));
+            if (lane == 0) mbar_arrive(smem_u32(&slot_full_bar[slot]));
             if (++slot == WQ_SLOTS) { slot = 0; slot_phase ^= 1; }
           } else {
-            mbar_arrive(smem_u32(&conv_bar[stage]));
+            if (lane == 0) mbar_arrive(smem_u32(&conv_bar[stage]));
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -705,10 +710,30 @@ int launch_common(tfjs_cuda_ctx* ctx, int amode, const float* a, const ConvGeom*
   else if (N <= 64) block_n = 64;
   else if (N <= 128 || split) block_n = 128;
   else block_n = (N % 256 == 0 || N > 512) ? 256 : 128;
-  // keep enough tiles in flight to fill the machine when M is small
+  // When the widest tile leaves the machine under-filled, a narrower one may finish sooner.  Cost of
+  // a candidate = waves x (k-blocks x cycles per k-block + epilogue); a k-block is bound by the
+  // shared-memory traffic of its operands (written by TMA, read by the tensor core: measured
+  // about 2.9 cycles per 128-byte operand row), the epilogue by the tile's width.  A narrower
+  // tile must win by 10 % to be taken, because it re-reads A more often.
   const int64_t m_tiles = ceil_div64(M, BLOCK_M);
-  while (block_n > 32 && m_tiles * ceil_div64(N, block_n) < ctx->sm_count && block_n / 2 >= 32)
-    block_n /= 2;
+  if (m_tiles * ceil_div64(N, block_n) < 2 * (int64_t)ctx->sm_count) {
+    const int64_t k_blocks = ceil_div64(K, BLOCK_K);
+    auto cost = [&](int bn) {
+      const int64_t waves = ceil_div64(m_tiles * ceil_div64(N, bn), ctx->sm_count);
+      const double kb_cycles = 2.9 * (BLOCK_M + (split ? 2 : 1) * bn);
+      return (double)waves * ((double)k_blocks * kb_cycles + 6.0 * bn + 600.0);
+    };
+    int best = block_n;
+    double best_cost = cost(block_n);
+    for (int bn = block_n / 2; bn >= 32; bn /= 2) {
+      const double c = cost(bn);
+      if (c < 0.9 * best_cost) {
+        best = bn;
+        best_cost = c;
+      }
+    }
+    block_n = best;
+  }
 
   CUtensorMap ma, mh, ml, mc;
   bool ok = encode_2d(&mc, out, (uint64_t)M, (uint64_t)N, 32, 32);

@@ -236,7 +236,9 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   constexpr uint32_t TMEM_COLS = NUM_ACC * BLOCK_N;  // 128 .. 512
   // who frees a raw stage: the depthwise / im2col threads that read it, or (MODE_CONV, where the
   // stage is the A operand itself) the commit of the MMAs that read it
-  constexpr int RAW_READERS = MODE == MODE_CONV ? 1 : DW_THREADS;
+  // (one arrival per warp, by lane 0 after __syncwarp: 256 single-thread arrivals on one barrier
+  // serialise in the shared-memory pipe, which is the busiest unit of this kernel)
+  constexpr int RAW_READERS = MODE == MODE_CONV ? 1 : DW_THREADS / 32;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -271,7 +273,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       mbar_init(smem_u32(&w_empty[s]), 1);
     }
     for (int s = 0; s < A_SLOTS; s++) {
-      mbar_init(smem_u32(&a_full[s]), DW_THREADS);
+      mbar_init(smem_u32(&a_full[s]), DW_THREADS / 32);
       mbar_init(smem_u32(&a_empty[s]), 1);
     }
     for (int a = 0; a < NUM_ACC; a++) {
@@ -393,11 +395,11 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
       for (int kb = 0; kb < p.num_k_blocks && ok; kb++) {
-        ok = mbar_wait(smem_u32(&a_empty[slot]), sphase ^ 1, abort_flag, p.status, 16);
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&a_empty[slot]), sphase ^ 1, abort_flag, p.status, 16));
         if (!ok) break;
         const uint32_t a_s = smem_u32(a_tiles + slot * A_TILE_BYTES);
         for (int part = 0; part < R::PARTS; part++) {
-          ok = mbar_wait(smem_u32(&raw_full[rs]), rphase, abort_flag, p.status, 17);
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&raw_full[rs]), rphase, abort_flag, p.status, 17));
           if (!ok) break;
           const uint32_t raw_s = smem_u32(raw + rs * R::STRIDE);
           if (MODE == MODE_RGB) {
@@ -409,12 +411,14 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
               default: dw_part<S, TFJS_ACT_LINEAR>(raw_s, a_s, table_s, t, part, kb, p, has_bias); break;
             }
           }
-          mbar_arrive(smem_u32(&raw_empty[rs]));  // this thread has read all it needs of the window
+          __syncwarp();  // every lane has read all it needs of the window
+          if (lane == 0) mbar_arrive(smem_u32(&raw_empty[rs]));
           if (++rs == RAW_STAGES) { rs = 0; rphase ^= 1; }
         }
         if (!ok) break;
         fence_proxy_async_smem();  // generic-proxy writes of the A tile -> visible to the tensor core
-        mbar_arrive(smem_u32(&a_full[slot]));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&a_full[slot]));
         if (++slot == A_SLOTS) { slot = 0; sphase ^= 1; }
       }
     }
