@@ -195,9 +195,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       // The ring holds few A tiles when the weight tile is large (3 stages at BLOCK_N = 256), too
       // few bytes in flight to cover DRAM latency.  A second cursor runs PREFETCH k-blocks ahead of
       // the loads and pulls the A tiles into L2, so that the loads themselves are L2 hits.
-      // (Only where the k loop is long, K >= 512: on the short-K layers, which run at the DRAM
-      // roofline anyway, the extra requests measured slower.)
-      const int PREFETCH = (AMODE == A_MATRIX && STAGES < 6 && p.num_k_blocks >= 16) ? 8 : 0;
+      // (Only where an A tile is worked on for long: K >= 512, or K >= 256 with two or more column
+      // tiles.  On the other short-K layers, which run at the DRAM roofline anyway, the extra
+      // requests measured slower.)
+      const int PREFETCH = (AMODE == A_MATRIX && STAGES < 6 &&
+                            (p.num_k_blocks >= 16 || (p.num_k_blocks >= 8 && p.num_n_tiles >= 2)))
+                               ? 8
+                               : 0;
       int ptile = blockIdx.x, pkb = 0;
       for (int i = 0; i < PREFETCH && ptile < num_tiles; i++) {
         tma_prefetch_2d(&map_a, pkb * BLOCK_K, (ptile / p.num_n_tiles) * BLOCK_M);
@@ -580,6 +584,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     if (lane == 0) tma_store_wait_all();
   }
 
+  // A wait that gave up leaves copies and MMAs of this CTA in flight: give them time to land
+  // before the shared and tensor memory they target is released.
+  if (*abort_flag) {
+    for (int i = 0; i < 100; i++) __nanosleep(1000);
+  }
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 9) {

@@ -30,13 +30,17 @@ namespace {
 constexpr int PH = 8, PW = 16;                    // output patch
 constexpr int BLOCK_K = 32;
 constexpr int A_TILE_BYTES = 128 * BLOCK_K * 4;   // 16 KB
-constexpr int MAX_A_SLOTS = 3;
-__host__ __device__ constexpr int a_slots(int block_n, int s, int mode) { return (mode == 0 && s == 1 && block_n <= 128) ? 3 : 2; }
+constexpr int A_SLOTS = 2;
 constexpr int EPI_WARPS = 8;
 constexpr int C_CHUNK_BYTES = 32 * 32 * 4;
 constexpr int C_STAGING_BYTES = EPI_WARPS * C_CHUNK_BYTES;
 constexpr int BIAS_STAGING_BYTES = EPI_WARPS * 128;
 constexpr int DW_THREADS = 256;
+// The depthwise / im2col threads work as one group of 256 on every k-block (stride-2 depthwise) or as
+// two groups of 128 on alternate k-blocks.  With two groups every A slot, raw stage and barrier
+// belongs to one group only: a parity wait is only safe for a thread that watches every phase of
+// its barrier, and a group does not see the phases of the k-blocks it skips.
+__host__ __device__ constexpr int dw_groups(int s, int mode) { return (mode == 2 || (mode == 0 && s == 2)) ? 1 : 2; }
 constexpr int THREADS = 320 + DW_THREADS;
 constexpr int MAX_C = 256;                        // depthwise channels (= K of the GEMM)
 constexpr int DW_TABLE_BYTES = 10 * MAX_C * 4;    // 9 filter taps + bias per channel
@@ -65,17 +69,20 @@ struct Raw {
   static constexpr int ROW_FLOATS = MODE == MODE_DW ? COLS * BLOCK_K : (COLS * 3 + 3 + 3) / 4 * 4;
   static constexpr int BYTES = MODE == MODE_CONV ? A_TILE_BYTES : ROWS * ROW_FLOATS * 4;
   static constexpr int STRIDE = (BYTES + 1023) / 1024 * 1024;
-  static constexpr int PIX = PW * PART_ROWS * 8 / DW_THREADS;  // adjacent output pixels per thread: 4 / 2
+  static constexpr int GROUP_THREADS = DW_THREADS / dw_groups(S, MODE);
+  static constexpr int TR = S == 1 ? 2 : 1;                            // a thread's block of outputs: rows
+  static constexpr int TC = PW * PART_ROWS * 8 / (TR * GROUP_THREADS);  // and columns (4 / 2)
 };
 
 __host__ __device__ constexpr int w_stages(int block_n) { return block_n >= 256 ? 2 : (block_n >= 128 ? 3 : 4); }
 __host__ __device__ constexpr int epi_arrivals(int block_n) { return block_n >= 64 ? EPI_WARPS : 4; }
 template <int S, int MODE>
 __host__ __device__ constexpr int raw_stages(int block_n) {
-  int left = SMEM_LIMIT - 1024 - a_slots(block_n, S, MODE) * A_TILE_BYTES - w_stages(block_n) * block_n * BLOCK_K * 4 -
+  int left = SMEM_LIMIT - 1024 - A_SLOTS * A_TILE_BYTES - w_stages(block_n) * block_n * BLOCK_K * 4 -
              C_STAGING_BYTES - BIAS_STAGING_BYTES - DW_TABLE_BYTES - BARRIER_BYTES;
   int n = left / Raw<S, MODE>::STRIDE;
-  return n > (MODE == MODE_DW ? 4 : 8) ? (MODE == MODE_DW ? 4 : 8) : n;
+  n = n > (MODE == MODE_DW ? 4 : 8) ? (MODE == MODE_DW ? 4 : 8) : n;
+  return n / dw_groups(S, MODE) * dw_groups(S, MODE);  // the same number of stages for every group
 }
 
 struct SepParams {
@@ -138,70 +145,90 @@ __device__ __forceinline__ float dw_activate(float v, float lo, float hi) {
   return v;
 }
 
-// Depthwise 3x3 of one raw stage: thread t computes PIX adjacent output pixels x 4 channels from
-// the window in shared memory and writes them into the A tile.  `table` holds the 9 filter taps
-// and the bias of every channel ([10][C] floats).
+// Depthwise 3x3 of one raw stage by one group of threads: thread t computes a block of TR output
+// rows x TC columns (2 x 4 at stride 1, 1 x 2 at stride 2) x 4 channels from the window in shared
+// memory and writes it into the A tile.  `table` holds the 9 filter taps and the bias of every
+// channel ([10][C] floats).  The block shares window rows between its output rows and filter
+// taps between all its pixels, which is what bounds the kernel: every 16-byte read costs a
+// quarter-warp wavefront of the shared-memory pipe.  The window is walked row by row and entry by
+// entry, so each output still accumulates its taps in the order (wR, wC) ascending.
 template <int S, int ACT>
 __device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t table, int t, int part, int kb,
                                         const SepParams& p, bool has_bias) {
   using R = Raw<S, MODE_DW>;
-  constexpr int GROUPS_PER_ROW = PW / R::PIX;
-  constexpr int WIN = (R::PIX - 1) * S + 3;
+  constexpr int TR = R::TR, TC = R::TC;
+  constexpr int GROUPS_PER_ROW = PW / TC;
+  constexpr int WROWS = (TR - 1) * S + 3, WIN = (TC - 1) * S + 3;
+  static_assert((R::PART_ROWS / TR) * GROUPS_PER_ROW * 8 == R::GROUP_THREADS, "one block per thread");
   const int q = t & 7;                         // channel quad of the k-block
-  const int g = t >> 3;                        // 0..31
-  const int r = g / GROUPS_PER_ROW;            // row inside this part
-  const int c0 = (g % GROUPS_PER_ROW) * R::PIX;
+  const int g = t >> 3;
+  const int r0 = (g / GROUPS_PER_ROW) * TR;    // first output row inside this part
+  const int c0 = (g % GROUPS_PER_ROW) * TC;
   const int ch = kb * BLOCK_K + q * 4;
   // the four channels travel as two packed float pairs: one fma.rn.f32x2 does two of the taps'
   // multiply-adds, each lane rounding exactly like fmaf
-  uint64_t acc[R::PIX][2];
+  uint64_t acc[TR][TC][2];
+  uint64_t f[3][3][2];
 #pragma unroll
-  for (int j = 0; j < R::PIX; j++) acc[j][0] = acc[j][1] = 0ull;
+  for (int o = 0; o < TR; o++)
 #pragma unroll
-  for (int dr = 0; dr < 3; dr++) {
-    const uint32_t row = raw + (uint32_t)(((r * S + dr) * R::COLS + c0 * S) * (BLOCK_K * 4) + q * 16);
-    uint64_t in[WIN][2];
+    for (int j = 0; j < TC; j++) acc[o][j][0] = acc[o][j][1] = 0ull;
 #pragma unroll
-    for (int i = 0; i < WIN; i++) lds128_pairs(row + i * (BLOCK_K * 4), in[i][0], in[i][1]);
+  for (int ir = 0; ir < WROWS; ir++) {
+    if (ir < 3) {
 #pragma unroll
-    for (int wc = 0; wc < 3; wc++) {
-      uint64_t f0, f1;
-      lds128_pairs(table + (uint32_t)(((dr * 3 + wc) * p.C + ch) * 4), f0, f1);
+      for (int wc = 0; wc < 3; wc++)
+        lds128_pairs(table + (uint32_t)(((ir * 3 + wc) * p.C + ch) * 4), f[ir][wc][0], f[ir][wc][1]);
+    }
+    const uint32_t row = raw + (uint32_t)((((r0 * S + ir) * R::COLS) + c0 * S) * (BLOCK_K * 4) + q * 16);
 #pragma unroll
-      for (int j = 0; j < R::PIX; j++) {
-        acc[j][0] = fma_f32x2(in[j * S + wc][0], f0, acc[j][0]);
-        acc[j][1] = fma_f32x2(in[j * S + wc][1], f1, acc[j][1]);
+    for (int i = 0; i < WIN; i++) {
+      uint64_t in0, in1;
+      lds128_pairs(row + i * (BLOCK_K * 4), in0, in1);
+#pragma unroll
+      for (int o = 0; o < TR; o++) {
+        const int dr = ir - o * S;  // filter row of this window row for output row o
+        if (dr < 0 || dr > 2) continue;
+#pragma unroll
+        for (int wc = 2; wc >= 0; wc--) {
+          const int d = i - wc;     // = j * S for the output column j this entry is tap wc of
+          if (d < 0 || d % S != 0 || d / S >= TC) continue;
+          acc[o][d / S][0] = fma_f32x2(in0, f[dr][wc][0], acc[o][d / S][0]);
+          acc[o][d / S][1] = fma_f32x2(in1, f[dr][wc][1], acc[o][d / S][1]);
+        }
       }
     }
   }
   uint64_t b0, b1;
   lds128_pairs(table + (uint32_t)((9 * p.C + ch) * 4), b0, b1);
-  const int m0 = (part * R::PART_ROWS + r) * PW + c0;  // first of this thread's rows of the A tile
 #pragma unroll
-  for (int j = 0; j < R::PIX; j++) {
-    if (has_bias) {
-      acc[j][0] = add_f32x2(acc[j][0], b0);
-      acc[j][1] = add_f32x2(acc[j][1], b1);
+  for (int o = 0; o < TR; o++) {
+    const int m0 = (part * R::PART_ROWS + r0 + o) * PW + c0;  // first of this row's rows of the A tile
+#pragma unroll
+    for (int j = 0; j < TC; j++) {
+      if (has_bias) {
+        acc[o][j][0] = add_f32x2(acc[o][j][0], b0);
+        acc[o][j][1] = add_f32x2(acc[o][j][1], b1);
+      }
+      uint32_t ox, oy, oz, ow;
+      unpack_f32x2(acc[o][j][0], ox, oy);
+      unpack_f32x2(acc[o][j][1], oz, ow);
+      float4 v;
+      v.x = dw_activate<ACT>(__uint_as_float(ox), p.dw_lo, p.dw_hi);
+      v.y = dw_activate<ACT>(__uint_as_float(oy), p.dw_lo, p.dw_hi);
+      v.z = dw_activate<ACT>(__uint_as_float(oz), p.dw_lo, p.dw_hi);
+      v.w = dw_activate<ACT>(__uint_as_float(ow), p.dw_lo, p.dw_hi);
+      sts128(a_tile + swz(m0 + j, q * 16), v);
     }
-    uint32_t ox, oy, oz, ow;
-    unpack_f32x2(acc[j][0], ox, oy);
-    unpack_f32x2(acc[j][1], oz, ow);
-    float4 o;
-    o.x = dw_activate<ACT>(__uint_as_float(ox), p.dw_lo, p.dw_hi);
-    o.y = dw_activate<ACT>(__uint_as_float(oy), p.dw_lo, p.dw_hi);
-    o.z = dw_activate<ACT>(__uint_as_float(oz), p.dw_lo, p.dw_hi);
-    o.w = dw_activate<ACT>(__uint_as_float(ow), p.dw_lo, p.dw_hi);
-    sts128(a_tile + swz(m0 + j, q * 16), o);
   }
 }
 
-// MODE_RGB: thread t < 128 turns the 3 x 9 window floats of output pixel t (3 filter rows of 3 pixels
+// MODE_RGB: thread t of a group turns the 3 x 9 window floats of output pixel t (3 filter rows of 3 pixels
 // x 3 channels, contiguous in the NHWC image) into row t of the A tile, in the K' order the repacked
 // filter uses: floats 10*wr + 3*wc + ci, with zeros at 9, 19 and 29..31.
 template <int S>
 __device__ __forceinline__ void rgb_part(uint32_t raw, uint32_t a_tile, int t, const SepParams& p) {
   using R = Raw<S, MODE_RGB>;
-  if (t >= 128) return;
   const int r = t / PW, c = t % PW;
   float v[3][9];
 #pragma unroll
@@ -226,9 +253,19 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
                        const __grid_constant__ CUtensorMap map_y, SepParams p) {
   using R = Raw<S, MODE>;
   constexpr int W_STAGES = w_stages(BLOCK_N);
-  constexpr int A_SLOTS = a_slots(BLOCK_N, S, MODE);
+  constexpr int GROUPS = dw_groups(S, MODE);
+  constexpr int GROUP_THREADS = DW_THREADS / GROUPS;
   constexpr int RAW_STAGES = raw_stages<S, MODE>(BLOCK_N);
-  static_assert(RAW_STAGES >= 2, "the input ring needs two stages");
+  static_assert(RAW_STAGES >= 2 && RAW_STAGES % GROUPS == 0 && A_SLOTS % GROUPS == 0, "rings split evenly");
+  static_assert(GROUPS == 1 || R::PARTS == 1, "two groups take whole k-blocks of one raw stage each");
+  // Where k-block n of this CTA (counted over all its tiles) lives: with two groups, group n % 2
+  // owns slots / stages [group * size / 2, (group + 1) * size / 2) and cycles through them.
+  auto ring_pos = [](int seq, int size, int& index, uint32_t& phase) {
+    const int per_group = size / GROUPS;
+    const int group = seq % GROUPS, turn = seq / GROUPS;
+    index = group * per_group + turn % per_group;
+    phase = (uint32_t)(turn / per_group) & 1u;
+  };
   constexpr int W_STAGE_BYTES = BLOCK_N * BLOCK_K * 4;
   // Accumulator buffers in tensor memory: two, or four when a tile is only 32 columns wide; then
   // each half of the epilogue warps drains every other tile, so two epilogues run at a time.
@@ -238,7 +275,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   // stage is the A operand itself) the commit of the MMAs that read it
   // (one arrival per warp, by lane 0 after __syncwarp: 256 single-thread arrivals on one barrier
   // serialise in the shared-memory pipe, which is the busiest unit of this kernel)
-  constexpr int RAW_READERS = MODE == MODE_CONV ? 1 : DW_THREADS / 32;
+  constexpr int RAW_READERS = MODE == MODE_CONV ? 1 : GROUP_THREADS / 32;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -273,7 +310,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       mbar_init(smem_u32(&w_empty[s]), 1);
     }
     for (int s = 0; s < A_SLOTS; s++) {
-      mbar_init(smem_u32(&a_full[s]), DW_THREADS / 32);
+      mbar_init(smem_u32(&a_full[s]), GROUP_THREADS / 32);
       mbar_init(smem_u32(&a_empty[s]), 1);
     }
     for (int a = 0; a < NUM_ACC; a++) {
@@ -308,9 +345,15 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 
   if (warp == 8) {
     // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      int rs = 0, ws = 0;
-      uint32_t rphase = 0, wphase = 0;
+    // With two groups: two independent cursors, one over the weight tiles and one over the raw stages,
+    // advanced by polling: a weight stage is only free once the MMAs three k-blocks back have retired, and an
+    // in-order producer would hold the input loads back behind it although the raw ring has room.
+    // The input loads carry the DRAM latency, so they must run as far ahead as their ring allows.
+    // (Prefetching the windows into L2 a few k-blocks ahead as well measured slower on every block.)
+    if (lane == 0 && GROUPS == 1) {
+      // one group of consumers works through both rings at the same pace: plain in-order issue
+      int rn = 0, ws = 0;
+      uint32_t wphase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
         const int b = tile / tiles_per_image;
@@ -323,7 +366,10 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
           mbar_arrive_expect_tx(smem_u32(&w_full[ws]), W_STAGE_BYTES);
           tma_load_2d(smem_u32(w_tiles + ws * W_STAGE_BYTES), &map_w, smem_u32(&w_full[ws]), kb * BLOCK_K, 0);
           if (++ws == W_STAGES) { ws = 0; wphase ^= 1; }
-          for (int part = 0; part < R::PARTS; part++) {
+          for (int part = 0; part < R::PARTS; part++, rn++) {
+            int rs;
+            uint32_t rphase;
+            ring_pos(rn, RAW_STAGES, rs, rphase);
             ok = mbar_wait(smem_u32(&raw_empty[rs]), rphase ^ 1, abort_flag, p.status, 12);
             if (!ok) break;
             mbar_arrive_expect_tx(smem_u32(&raw_full[rs]), R::BYTES);
@@ -332,13 +378,65 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
               const int wr = tap / p.fw, wc = tap - wr * p.fw;
               tma_load_4d(smem_u32(raw + rs * R::STRIDE), &map_x, smem_u32(&raw_full[rs]), cg * BLOCK_K,
                           x0 + wc * p.dil_w, y0 + wr * p.dil_h, b);
-            } else if (MODE == MODE_DW)
+            } else {
               tma_load_4d(smem_u32(raw + rs * R::STRIDE), &map_x, smem_u32(&raw_full[rs]), kb * BLOCK_K, x0,
                           y0 + part * R::PART_ROWS * S, b);
+            }
+          }
+        }
+      }
+    } else if (lane == 0) {
+      int w_tile = blockIdx.x, w_kb = 0, ws = 0;
+      uint32_t wphase = 0;
+      int r_tile = blockIdx.x, r_kb = 0, r_part = 0, rn = 0;  // rn: raw stages requested so far
+      long long t0 = clock64();
+      uint32_t idle = 0;
+      while (w_tile < p.num_tiles || r_tile < p.num_tiles) {
+        bool progressed = false;
+        if (r_tile < p.num_tiles) {
+          int rs;
+          uint32_t rphase;
+          ring_pos(rn, RAW_STAGES, rs, rphase);
+          if (mbar_test_wait(smem_u32(&raw_empty[rs]), rphase ^ 1)) {
+            const int b = r_tile / tiles_per_image;
+            const int rem = r_tile - b * tiles_per_image;
+            const int ty = rem / p.tiles_x, tx = rem - ty * p.tiles_x;
+            const int x0 = tx * PW * S - p.pad_c, y0 = ty * PH * S - p.pad_r;
+            mbar_arrive_expect_tx(smem_u32(&raw_full[rs]), R::BYTES);
+            if (MODE == MODE_DW)
+              tma_load_4d(smem_u32(raw + rs * R::STRIDE), &map_x, smem_u32(&raw_full[rs]), r_kb * BLOCK_K, x0,
+                          y0 + r_part * R::PART_ROWS * S, b);
             else  // image rows as runs of W*3 floats; the copy starts rgb_off floats before the window
               tma_load_3d(smem_u32(raw + rs * R::STRIDE), &map_x, smem_u32(&raw_full[rs]), x0 * 3 - p.rgb_off,
                           y0, b);
-            if (++rs == RAW_STAGES) { rs = 0; rphase ^= 1; }
+            rn++;
+            if (++r_part == R::PARTS) {
+              r_part = 0;
+              if (++r_kb == p.num_k_blocks) { r_kb = 0; r_tile += gridDim.x; }
+            }
+            progressed = true;
+          }
+        }
+        if (w_tile < p.num_tiles && mbar_test_wait(smem_u32(&w_empty[ws]), wphase ^ 1)) {
+          mbar_arrive_expect_tx(smem_u32(&w_full[ws]), W_STAGE_BYTES);
+          tma_load_2d(smem_u32(w_tiles + ws * W_STAGE_BYTES), &map_w, smem_u32(&w_full[ws]), w_kb * BLOCK_K, 0);
+          if (++ws == W_STAGES) { ws = 0; wphase ^= 1; }
+          if (++w_kb == p.num_k_blocks) { w_kb = 0; w_tile += gridDim.x; }
+          progressed = true;
+        }
+        if (progressed) {
+          idle = 0;
+          continue;
+        }
+        // bounded: give up when nothing moved for the wait limit, or another role already gave up
+        __nanosleep(64);  // each poll is a shared-memory access: keep them rare
+        if (++idle == 1) t0 = clock64();
+        if ((idle & 63) == 63) {
+          if (*abort_flag) break;
+          if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            atomicCAS(p.status, 0, 12);
+            break;
           }
         }
       }
@@ -347,8 +445,8 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(128, BLOCK_N);
-      int ws = 0, slot = 0, local = 0, rs = 0;
-      uint32_t wphase = 0, sphase = 0, rphase = 0;
+      int ws = 0, local = 0, n = 0;  // n: k-blocks so far
+      uint32_t wphase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, local++) {
         const int acc = local % NUM_ACC;
@@ -357,7 +455,11 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
-        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+        for (int kb = 0; kb < p.num_k_blocks; kb++, n++) {
+          int slot, rs;
+          uint32_t sphase, rphase;
+          ring_pos(n, A_SLOTS, slot, sphase);
+          ring_pos(n, RAW_STAGES, rs, rphase);  // MODE_CONV: one raw stage per k-block
           ok = mbar_wait(smem_u32(&w_full[ws]), wphase, abort_flag, p.status, 14);
           if (ok && MODE == MODE_CONV) ok = mbar_wait(smem_u32(&raw_full[rs]), rphase, abort_flag, p.status, 15);
           if (ok && MODE != MODE_CONV) ok = mbar_wait(smem_u32(&a_full[slot]), sphase, abort_flag, p.status, 15);
@@ -371,13 +473,10 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
             tcgen05_mma_tf32(tmem_d, make_smem_desc(a_s + k * 32), make_smem_desc(w_s + k * 32), idesc,
                              (kb > 0 || k > 0) ? 1u : 0u);
           tcgen05_commit(smem_u32(&w_empty[ws]));
-          if (MODE == MODE_CONV) {
+          if (MODE == MODE_CONV)
             tcgen05_commit(smem_u32(&raw_empty[rs]));
-            if (++rs == RAW_STAGES) { rs = 0; rphase ^= 1; }
-          } else {
+          else
             tcgen05_commit(smem_u32(&a_empty[slot]));
-            if (++slot == A_SLOTS) { slot = 0; sphase ^= 1; }
-          }
           if (++ws == W_STAGES) { ws = 0; wphase ^= 1; }
         }
         if (ok) tcgen05_commit(smem_u32(&tmem_full_bar[acc]));
@@ -387,18 +486,27 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     // nothing to do: the operands go from TMA to the tensor core
   } else if (warp >= 10) {
     // ---------------- depthwise warps ----------------
-    const int t = threadIdx.x - 320;
+    // With two groups, each takes every other k-block (counted over all the tiles of this CTA), so
+    // that two A tiles are in the making at any time.
+    const int t = (threadIdx.x - 320) % GROUP_THREADS;
+    const int group = (threadIdx.x - 320) / GROUP_THREADS;
     const uint32_t table_s = smem_u32(table);
     const bool has_bias = p.dw_bias != nullptr;
-    int rs = 0, slot = 0;
-    uint32_t rphase = 0, sphase = 0;
+    int n = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-      for (int kb = 0; kb < p.num_k_blocks && ok; kb++) {
+      for (int kb = 0; kb < p.num_k_blocks && ok; kb++, n++) {
+        if (n % GROUPS != group) continue;
+        int slot;
+        uint32_t sphase;
+        ring_pos(n, A_SLOTS, slot, sphase);
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&a_empty[slot]), sphase ^ 1, abort_flag, p.status, 16));
         if (!ok) break;
         const uint32_t a_s = smem_u32(a_tiles + slot * A_TILE_BYTES);
         for (int part = 0; part < R::PARTS; part++) {
+          int rs;
+          uint32_t rphase;
+          ring_pos(n * R::PARTS + part, RAW_STAGES, rs, rphase);
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&raw_full[rs]), rphase, abort_flag, p.status, 17));
           if (!ok) break;
           const uint32_t raw_s = smem_u32(raw + rs * R::STRIDE);
@@ -413,13 +521,11 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
           }
           __syncwarp();  // every lane has read all it needs of the window
           if (lane == 0) mbar_arrive(smem_u32(&raw_empty[rs]));
-          if (++rs == RAW_STAGES) { rs = 0; rphase ^= 1; }
         }
         if (!ok) break;
         fence_proxy_async_smem();  // generic-proxy writes of the A tile -> visible to the tensor core
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&a_full[slot]));
-        if (++slot == A_SLOTS) { slot = 0; sphase ^= 1; }
       }
     }
   } else {
@@ -505,6 +611,11 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     if (lane == 0) tma_store_wait_all();
   }
 
+  // A wait that gave up leaves copies and MMAs of this CTA in flight: give them time to land
+  // before the shared and tensor memory they target is released.
+  if (*abort_flag) {
+    for (int i = 0; i < 100; i++) __nanosleep(1000);
+  }
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 9) {
@@ -518,7 +629,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 template <int BLOCK_N, int S, int MODE>
 int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my,
                    const SepParams& p) {
-  constexpr int smem_bytes = 1024 + a_slots(BLOCK_N, S, MODE) * A_TILE_BYTES + w_stages(BLOCK_N) * BLOCK_N * BLOCK_K * 4 +
+  constexpr int smem_bytes = 1024 + A_SLOTS * A_TILE_BYTES + w_stages(BLOCK_N) * BLOCK_N * BLOCK_K * 4 +
                              C_STAGING_BYTES + raw_stages<S, MODE>(BLOCK_N) * Raw<S, MODE>::STRIDE +
                              DW_TABLE_BYTES + BIAS_STAGING_BYTES + BARRIER_BYTES;
   static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
