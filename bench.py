@@ -272,7 +272,8 @@ KERNEL_FAMILY = {"separableConv2d (fused dw3x3 s1 + pw, TF32)": "separable_fused
                  "conv2d_tcgen05 (TF32)": "conv2d_tcgen05", "conv2d_tcgen05 (3xTF32)": "conv2d_tcgen05",
                  "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32)": "conv2d_tcgen05",
                  "conv2d_tcgen05 (shifted-patch TMA, TF32)": "conv2d_tcgen05",
-                 "depthwiseConv2D (3x3 strip)": "depthwise3x3_strip", "conv2d (stem)": "conv2d_stem",
+                 "depthwiseConv2D (3x3 strip)": "depthwise3x3", "depthwiseConv2D (3x3 image window, TMA)": "depthwise3x3",
+                 "conv2d (stem)": "conv2d_stem",
                  "avgPool (global)": "global_avgpool", "softmax_last": "softmax"}
 
 
@@ -483,7 +484,7 @@ def run_cuda(args):
 # captures summarised under profiles/; it grows in proportion to the batch.
 TRAFFIC_MB_PER_IMAGE_AND_LAUNCH = {"separable_fused": 1779.9 / 4 / 128,
                                    "gemm_tcgen05": 4062.4 / 14 / 256,
-                                   "depthwise3x3_strip": 4638.7 / 13 / 256,
+                                   "depthwise3x3": 4638.7 / 13 / 256,
                                    "conv2d_tcgen05": 502.7 / 256}
 
 

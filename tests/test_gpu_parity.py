@@ -184,6 +184,62 @@ def test_depthwise_shapes(tf, shape, fshape, stride, pad, dil):
     assert ulp_diff(got.dataSync(), want) <= 2
 
 
+@pytest.mark.parametrize("shape,stride,pad", [
+    ((3, 14, 14, 64), 1, "same"),       # MobileNet's 14x14 layers, two channel groups short of a wave
+    ((2, 14, 14, 96), 1, "same"),       # 32-channel groups
+    ((5, 14, 14, 512), 2, "same"),      # 14 -> 7, pad bottom / right only
+    ((2, 7, 7, 1024), 1, "same"),       # the last depthwise layer
+    ((1, 16, 16, 32), 1, "valid"),      # no padding: the window starts inside the image
+    ((1, 9, 9, 128), 1, "valid"),
+    ((170, 7, 7, 128), 1, "same"),      # more items than CTAs: the stage ring wraps
+])
+@pytest.mark.parametrize("epilogue", [None, "bias_relu6", "bias_relu"])
+def test_depthwise_image_window(tf, shape, stride, pad, epilogue):
+    """3x3 depthwise on 14x14 / 7x7 outputs goes through the whole-image TMA kernel; results are
+    those of MathBackendCPU.depthwiseConv2D bit for bit (up to the double rounding), borders included."""
+    from tfjs_core_b200 import conv_util
+    rng = _rng(sum(shape) + stride)
+    C = shape[3]
+    x = rng.uniform(-1, 1, shape).astype(np.float32)
+    w = rng.uniform(-1, 1, (3, 3, C, 1)).astype(np.float32)
+    bias = rng.normal(0, 0.5, C).astype(np.float32)
+    ci = oracle.compute_conv2d_info(shape, w.shape, stride, 1, pad, None, True)
+    want = oracle.depthwise_conv2d(x, w, ci)
+    bk = tf.ENGINE.backend
+    dci = conv_util.compute_conv2d_info(shape, w.shape, stride, 1, pad, None, True)
+    xt, wt = tf.ops.tensor(x), tf.ops.tensor(w)
+    names = []
+    bk.profileBegin(4)
+    if epilogue is None:
+        got = bk.depthwiseConv2D(xt, wt, dci)
+    else:
+        want = oracle.binary("add", want, bias)
+        want = oracle.unary("clip", want, 0, 6) if epilogue == "bias_relu6" else oracle.unary("relu", want)
+        got = bk.fusedDepthwiseConv2D(xt, wt, dci, tf.ops.tensor(bias), epilogue[5:])
+    names = [n for n, _ in bk.profileEnd()]
+    assert any("image window" in n for n in names), names
+    assert got.shape == list(want.shape)
+    assert ulp_diff(got.dataSync(), want) <= 2
+
+
+def test_depthwise_image_window_skips_taps_outside(tf):
+    """A non-finite filter tap must not leak into the outputs whose tap lies outside the image:
+    the reference skips those taps (backend_cpu.ts:2002-2014), it does not multiply them by zero."""
+    rng = _rng(77)
+    x = rng.uniform(-1, 1, (2, 14, 14, 32)).astype(np.float32)
+    w = rng.uniform(-1, 1, (3, 3, 32, 1)).astype(np.float32)
+    w[0, 0, 3, 0] = np.inf      # top-left tap: outside for the first row and the first column
+    w[2, 1, 5, 0] = np.nan      # bottom-centre tap: outside for the last row
+    ci = oracle.compute_conv2d_info(x.shape, w.shape, 1, 1, "same", None, True)
+    want = oracle.depthwise_conv2d(x, w, ci)
+    got = tf.ops.depthwise_conv2d(tf.ops.tensor(x), tf.ops.tensor(w), 1, "same").dataSync().reshape(want.shape)
+    assert np.isfinite(want[:, 0, :, 3]).all() and np.isfinite(want[:, 13, :, 5]).all()
+    np.testing.assert_array_equal(np.isnan(got), np.isnan(want))
+    np.testing.assert_array_equal(np.isinf(got), np.isinf(want))
+    ok = np.isfinite(want)
+    assert ulp_diff(got[ok], want[ok]) <= 2
+
+
 @pytest.mark.parametrize("shape,fshape,stride,pad,dil", [
     ((2, 16, 16, 3), (3, 3, 3, 32), 2, "same", 1),      # stem geometry
     ((1, 15, 17, 3), (3, 3, 3, 32), 2, "same", 1),      # odd input, conv_util_test.ts:82-99

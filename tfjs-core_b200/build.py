@@ -13,7 +13,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libtfjs_cuda.so")
 SOURCES = ["context.cu", "elementwise.cu", "conv.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "api.cu",
-           "no_alloc.cu", "sepconv_tcgen05.cu", "backward.cu"]
+           "no_alloc.cu", "sepconv_tcgen05.cu", "backward.cu", "depthwise_tma.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC"]  # no --use_fast_math: results must match the reference

@@ -272,6 +272,10 @@ int launch_conv_tma_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2
 // conv.cu
 int launch_conv2d_direct(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* y,
                          const tfjs_conv2d_info& ci, const EpilogueArgs& epi);
+// 3x3 depthwise on 14x14 / 7x7 images through whole-image TMA windows (depthwise_tma.cu)
+bool depthwise_image_supported(const tfjs_conv2d_info& ci, int activation);
+int launch_depthwise_image(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* y, const tfjs_conv2d_info& ci,
+                           const EpilogueArgs& epi);
 int launch_depthwise(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* y,
                      const tfjs_conv2d_info& ci, const EpilogueArgs& epi);
 int launch_pool2d(tfjs_cuda_ctx* ctx, const float* x, float* y, const tfjs_conv2d_info& ci,

@@ -531,6 +531,8 @@ int launch_depthwise(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* 
                     ci.inChannels % 4 == 0 && ci.strideHeight == ci.strideWidth &&
                     (ci.strideHeight == 1 || ci.strideHeight == 2) && epi.activation != TFJS_ACT_PRELU &&
                     (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) == 0;
+  if (fast && depthwise_image_supported(ci, epi.activation) && (epi.bias == nullptr || ((uintptr_t)epi.bias & 15) == 0))
+    return launch_depthwise_image(ctx, x, w, y, ci, epi);
   if (fast) {
     const int C4 = ci.inChannels / 4;
     const int cb = C4 < 128 ? C4 : 128;                // channel quads per block

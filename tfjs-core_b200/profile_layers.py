@@ -1,12 +1,14 @@
 #!/usr/bin/env python3
 """Per-layer device times of one fused MobileNetV1 forward on the cuda backend.
 
-    python tfjs-core_b200/profile_layers.py [batch] [tf32|3xtf32] [f|q|q-in-loop] [separable|layerwise]
+    python tfjs-core_b200/profile_layers.py [batch] [tf32|3xtf32] [f|q|q-in-loop] [separable|layerwise|separable-all]
 
 Prints, for each launch of one forward pass (26 with the fused depthwise + pointwise blocks,
 30 with `layerwise`), the kernel name, the best device time over a few passes
 (events recorded between launches on the context's stream), the layer's algorithmic bytes and
-the bandwidth that corresponds to.  `q` stores the filters as uint8 (BASELINE config 5); `q-in-loop` also keeps the GEMM weights uint8 and dequantises them inside the GEMM main loop.  This is
+the bandwidth that corresponds to.  `q` stores the filters as uint8 (BASELINE config 5); `q-in-loop` also keeps the GEMM weights uint8 and dequantises them inside the GEMM main loop;
+`separable-all` fuses every block the fused kernel can take (up to 256 channels), not only those
+where fusion pays.  This is
 also the small-case command the ncu captures summarised under profiles/ were taken with.
 """
 import os
@@ -29,6 +31,8 @@ def main():
     tf.ENGINE.registerBackend("profile-cuda", lambda: bk, 10)
     tf.ENGINE.setBackend("profile-cuda")
     bk.setOption("dequant_in_gemm", 1 if in_loop else 0)
+    if len(sys.argv) > 4 and sys.argv[4] == "separable-all":
+        bk.setOption("fuse_separable", 2)
     params = mobilenet.make_weights(4 if quantized else 3, quantized=quantized, gain=1.5)
     net = mobilenet.MobileNetV1(params, bk)
     forward = net.forward_fused if layerwise else net.forward_separable
