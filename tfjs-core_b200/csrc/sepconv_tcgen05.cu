@@ -10,12 +10,15 @@
 //   warp 8      producer: per 32-channel k-block, TMA-loads the pointwise weight tile
 //               [BLOCK_N x 32] and the input window of the patch ((8-1)*S+3 rows x (16-1)*S+3
 //               columns x 32 channels; in two halves of 4 patch rows for stride 2) through a 4-D
-//               tensor map whose out-of-range reads return zero, which is SAME padding.
-//   warps 10-17 depthwise: each thread owns 4 channels of 4 (stride 1) or 2 (stride 2) adjacent
-//               output pixels, accumulates the 9 taps in the reference's order with one fmaf per
-//               tap, adds the bias, applies the activation and writes 16 bytes of the swizzled
-//               K-major A tile (two slots, so the next k-block is computed while the tensor core
-//               reads the current one).
+//               tensor map whose out-of-range reads return zero, which is SAME padding.  At
+//               stride 1 the two kinds of load advance independently, so that the window loads,
+//               which carry the DRAM latency, are not held back behind the weight ring.
+//   warps 10-17 depthwise: a thread owns 4 channels of a block of output pixels (2 rows x 4
+//               columns at stride 1, where the warps form two groups that take alternate
+//               k-blocks; 2 adjacent pixels at stride 2), accumulates the 9 taps in the
+//               reference's order with one fmaf per tap, adds the bias, applies the activation
+//               and writes 16 bytes per pixel of the swizzled K-major A tile (two slots, so the
+//               next k-block is computed while the tensor core reads the current one).
 //   warp 9      one thread issues tcgen05.mma (M = 128, N = BLOCK_N, K = 8) into one of two TMEM
 //               accumulators and commits the barriers that free the slots.
 //   warps 0-7   epilogue: tcgen05.ld, bias, activation, swizzled staging, 4-D TMA store of
@@ -74,11 +77,15 @@ struct Raw {
   static constexpr int TC = PW * PART_ROWS * 8 / (TR * GROUP_THREADS);  // and columns (4 / 2)
 };
 
-__host__ __device__ constexpr int w_stages(int block_n) { return block_n >= 256 ? 2 : (block_n >= 128 ? 3 : 4); }
+// Weight tiles come from L2 and need little lookahead; at stride 2 and 128 columns two stages
+// instead of three make room for a third 38 KB window stage, and the windows carry the DRAM latency.
+__host__ __device__ constexpr int w_stages(int block_n, int s, int mode) {
+  return block_n >= 256 ? 2 : (block_n >= 128 ? ((mode == 0 && s == 2) ? 2 : 3) : 4);
+}
 __host__ __device__ constexpr int epi_arrivals(int block_n) { return block_n >= 64 ? EPI_WARPS : 4; }
 template <int S, int MODE>
 __host__ __device__ constexpr int raw_stages(int block_n) {
-  int left = SMEM_LIMIT - 1024 - A_SLOTS * A_TILE_BYTES - w_stages(block_n) * block_n * BLOCK_K * 4 -
+  int left = SMEM_LIMIT - 1024 - A_SLOTS * A_TILE_BYTES - w_stages(block_n, S, MODE) * block_n * BLOCK_K * 4 -
              C_STAGING_BYTES - BIAS_STAGING_BYTES - DW_TABLE_BYTES - BARRIER_BYTES;
   int n = left / Raw<S, MODE>::STRIDE;
   n = n > (MODE == MODE_DW ? 4 : 8) ? (MODE == MODE_DW ? 4 : 8) : n;
@@ -252,7 +259,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                        const __grid_constant__ CUtensorMap map_y, SepParams p) {
   using R = Raw<S, MODE>;
-  constexpr int W_STAGES = w_stages(BLOCK_N);
+  constexpr int W_STAGES = w_stages(BLOCK_N, S, MODE);
   constexpr int GROUPS = dw_groups(S, MODE);
   constexpr int GROUP_THREADS = DW_THREADS / GROUPS;
   constexpr int RAW_STAGES = raw_stages<S, MODE>(BLOCK_N);
@@ -629,7 +636,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 template <int BLOCK_N, int S, int MODE>
 int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my,
                    const SepParams& p) {
-  constexpr int smem_bytes = 1024 + A_SLOTS * A_TILE_BYTES + w_stages(BLOCK_N) * BLOCK_N * BLOCK_K * 4 +
+  constexpr int smem_bytes = 1024 + A_SLOTS * A_TILE_BYTES + w_stages(BLOCK_N, S, MODE) * BLOCK_N * BLOCK_K * 4 +
                              C_STAGING_BYTES + raw_stages<S, MODE>(BLOCK_N) * Raw<S, MODE>::STRIDE +
                              DW_TABLE_BYTES + BIAS_STAGING_BYTES + BARRIER_BYTES;
   static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
