@@ -89,6 +89,28 @@ def test_fused_equals_the_two_kernels_and_matches_the_oracle(tf, b, h, w, c, n, 
         bk.setMathMode("3xtf32")
 
 
+@pytest.mark.parametrize("b,h,w,c,n,stride", [
+    (16, 112, 112, 32, 64, 1),    # 1568 patches of one k-block: about 11 per CTA, every ring wraps
+    (24, 56, 56, 128, 128, 1),    # 672 patches of four k-blocks, two depthwise groups
+    (24, 56, 56, 128, 256, 2),    # 192 patches of four k-blocks, two half-windows each
+    (40, 112, 112, 64, 128, 2),   # 1120 patches, three window stages
+])
+def test_fused_many_patches_per_cta(tf, b, h, w, c, n, stride):
+    """Sizes at which every CTA works through several patches, so that the stage rings, the A
+    slots and the tensor-memory accumulators are reused many times: the fused kernel must still
+    equal the two separate kernels bit for bit (the oracle would take minutes at these sizes; the
+    two kernels are checked against it at the small sizes above)."""
+    bk = tf.ENGINE.backend
+    bk.setMathMode("tf32")
+    bk.setOption("fuse_separable", 2)
+    try:
+        _, _, _, _, _, _, got, ref = _case(tf, b, h, w, c, n, stride, seed=b + c + n)
+        assert np.array_equal(got, ref)
+    finally:
+        bk.setOption("fuse_separable", 1)
+        bk.setMathMode("3xtf32")
+
+
 @pytest.mark.parametrize("dw_act,pw_act,bias", [("linear", "linear", False), ("relu", "linear", True),
                                                  (("clip", -0.5, 0.75), "relu", True)])
 def test_fused_epilogue_variants(tf, dw_act, pw_act, bias):
