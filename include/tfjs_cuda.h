@@ -198,7 +198,7 @@ int tfjs_cuda_depthwise_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor
  * kernel that keeps the depthwise result in shared memory; other shapes run the two kernels back
  * to back.  Results are bit-identical to the two separate calls.  Option "fuse_separable": 0
  * forces the two-kernel form, 1 (default) fuses where that is the faster form (up to 128
- * channels), 2 fuses every shape the kernel takes. */
+ * channels, and 256 channels at stride 1), 2 fuses every shape the kernel takes. */
 int tfjs_cuda_separable_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x, tfjs_tensor_id dw_filter,
                                tfjs_tensor_id pw_filter, tfjs_tensor_id out,
                                const tfjs_conv2d_info* dw_info, int32_t out_channels,

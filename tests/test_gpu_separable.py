@@ -185,7 +185,7 @@ def test_mobilenet_with_fused_blocks_equals_the_layerwise_forward(tf):
         b = [t.dataSync() for t in net.forward_separable(x)]
         launches = bk.launchCount() - before
         assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
-        assert launches == 1 + 4 + 2 * 9 + 3, launches  # blocks 1-4 fused by default
+        assert launches == 1 + 5 + 2 * 8 + 3, launches  # blocks 1-5 fused by default
     finally:
         net.dispose()
         bk.setMathMode("3xtf32")

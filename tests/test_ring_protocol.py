@@ -113,6 +113,79 @@ def simulate(ring_pos, groups, raw_stages, a_slots, parts, w_stages, k_blocks, t
         assert steps < 2_000_000, "deadlock"
 
 
+def simulate_in_place(ring_pos, groups, raw_stages, w_stages, k_blocks, tiles, seed):
+    """The 256-column stride-1 variant: a group writes the A tile over its own window, so a raw
+    stage goes TMA -> depthwise group -> MMA and is freed by the MMAs' commit."""
+    rnd = random.Random(seed)
+    warps = 8 // groups
+    raw_full = [Barrier(1) for _ in range(raw_stages)]
+    raw_empty = [Barrier(1) for _ in range(raw_stages)]
+    a_full = [Barrier(warps) for _ in range(raw_stages)]
+    w_full = [Barrier(1) for _ in range(w_stages)]
+    w_empty = [Barrier(1) for _ in range(w_stages)]
+
+    def wait(bar, parity, completions_needed):
+        while not bar.test(parity):
+            yield
+        assert bar.completions >= completions_needed, "a wait passed on the parity of an earlier phase"
+
+    def producer():  # polls both rings; a step advances whichever is free
+        rn = wn = 0
+        total = tiles * k_blocks
+        while rn < total or wn < total:
+            moved = False
+            if rn < total:
+                rs, phase, need = ring_pos(rn, raw_stages, groups)
+                if raw_empty[rs].test(phase ^ 1):
+                    assert raw_empty[rs].completions >= need
+                    raw_full[rs].arrive()
+                    rn += 1
+                    moved = True
+            if wn < total:
+                ws, wturn = wn % w_stages, wn // w_stages
+                if w_empty[ws].test((wturn & 1) ^ 1):
+                    assert w_empty[ws].completions >= wturn
+                    w_full[ws].arrive()
+                    wn += 1
+                    moved = True
+            yield moved
+
+    def mma():
+        for n in range(tiles * k_blocks):
+            rs, phase, need = ring_pos(n, raw_stages, groups)
+            ws, wturn = n % w_stages, n // w_stages
+            yield from wait(a_full[rs], phase, need + 1)
+            yield from wait(w_full[ws], wturn & 1, wturn + 1)
+            yield
+            w_empty[ws].arrive()
+            raw_empty[rs].arrive()
+
+    def depthwise_warp(group):
+        for n in range(tiles * k_blocks):
+            if n % groups != group:
+                continue
+            rs, phase, need = ring_pos(n, raw_stages, groups)
+            yield from wait(raw_full[rs], phase, need + 1)
+            yield
+            a_full[rs].arrive()
+
+    alive = [producer(), mma()] + [depthwise_warp(g) for g in range(groups) for _ in range(warps)]
+    steps = 0
+    while alive:
+        role = rnd.choice(alive)
+        try:
+            next(role)
+        except StopIteration:
+            alive.remove(role)
+        steps += 1
+        assert steps < 2_000_000, "deadlock"
+
+
+def test_in_place_tiles_are_safe():
+    for seed in range(8):
+        simulate_in_place(ring_pos_owned, 2, 4, 2, 8, 5, seed)
+
+
 # (groups, raw stages, A slots, raw stages per k-block, weight stages, k-blocks per tile, tiles per CTA)
 GEOMETRIES = [
     (2, 4, 2, 1, 4, 1, 25),   # block 1: 32 channels, N = 64

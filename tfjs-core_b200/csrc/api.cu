@@ -355,9 +355,11 @@ extern "C" int tfjs_cuda_separable_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_i
   const float* wdf;
   rc = float_view(ctx, wd, &wdf);
   if (rc) return rc;
-  // fuse_separable: 1 fuses where it measures faster than the two kernels (up to 128 channels:
-  // beyond that the fused kernel is bound by shared-memory bandwidth), 2 wherever it can
-  if (ctx->use_tensor_cores && ctx->fuse_separable && (ctx->fuse_separable >= 2 || C <= 128) &&
+  // fuse_separable: 1 fuses where it measures faster than the two kernels (up to 128 channels, and
+  // 256 channels at stride 1; at 256 channels and stride 2 the shared memory left beside the
+  // weight stages holds too few input windows to cover the DRAM latency), 2 wherever it can
+  const bool pays = C <= 128 || (C <= 256 && dw->strideHeight == 1);
+  if (ctx->use_tensor_cores && ctx->fuse_separable && (ctx->fuse_separable >= 2 || pays) &&
       sepconv_tcgen05_supported(*dw, N, de.activation, pe.activation, ctx->math_mode)) {
     PackedWeights pw;
     bool temporary;

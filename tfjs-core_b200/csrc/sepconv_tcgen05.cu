@@ -34,6 +34,19 @@ constexpr int PH = 8, PW = 16;                    // output patch
 constexpr int BLOCK_K = 32;
 constexpr int A_TILE_BYTES = 128 * BLOCK_K * 4;   // 16 KB
 constexpr int A_SLOTS = 2;
+// Stride-1 depthwise blocks of 256 columns build the A tile IN PLACE: a window (10 x 18 x 128 B = 23 KB) is larger
+// than the tile made from it (16 KB), so once the threads of a group have all read their window
+// taps into registers (a named barrier) they write the tile over the start of the same stage, the
+// tensor core reads it there, and the commit of those MMAs frees the stage for the next load.
+// That saves the separate A slots (32 KB), which buys two more window stages: the number of
+// window bytes in flight is what bounds these blocks.
+// (Only at 256 columns, where the 64 KB of weight stages otherwise leave room for two window stages:
+// four in place.  With narrower tiles the ring already holds four, and in place measured slower:
+// a stage then stays occupied until its MMAs retire, and the group barrier costs overlap.)
+__host__ __device__ constexpr bool a_in_place(int block_n, int s, int mode) { return mode == 0 && s == 1 && block_n >= 256; }
+__host__ __device__ constexpr int a_slot_bytes(int block_n, int s, int mode) {
+  return a_in_place(block_n, s, mode) ? 0 : A_SLOTS * A_TILE_BYTES;
+}
 constexpr int EPI_WARPS = 8;
 constexpr int C_CHUNK_BYTES = 32 * 32 * 4;
 constexpr int C_STAGING_BYTES = EPI_WARPS * C_CHUNK_BYTES;
@@ -85,10 +98,11 @@ __host__ __device__ constexpr int w_stages(int block_n, int s, int mode) {
 __host__ __device__ constexpr int epi_arrivals(int block_n) { return block_n >= 64 ? EPI_WARPS : 4; }
 template <int S, int MODE>
 __host__ __device__ constexpr int raw_stages(int block_n) {
-  int left = SMEM_LIMIT - 1024 - A_SLOTS * A_TILE_BYTES - w_stages(block_n, S, MODE) * block_n * BLOCK_K * 4 -
+  int left = SMEM_LIMIT - 1024 - a_slot_bytes(block_n, S, MODE) - w_stages(block_n, S, MODE) * block_n * BLOCK_K * 4 -
              C_STAGING_BYTES - BIAS_STAGING_BYTES - DW_TABLE_BYTES - BARRIER_BYTES;
   int n = left / Raw<S, MODE>::STRIDE;
-  n = n > (MODE == MODE_DW ? 4 : 8) ? (MODE == MODE_DW ? 4 : 8) : n;
+  const int cap = MODE == MODE_DW ? 4 : 8;
+  n = n > cap ? cap : n;
   return n / dw_groups(S, MODE) * dw_groups(S, MODE);  // the same number of stages for every group
 }
 
@@ -161,7 +175,7 @@ __device__ __forceinline__ float dw_activate(float v, float lo, float hi) {
 // entry, so each output still accumulates its taps in the order (wR, wC) ascending.
 template <int S, int ACT>
 __device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t table, int t, int part, int kb,
-                                        const SepParams& p, bool has_bias) {
+                                        const SepParams& p, bool has_bias, int sync_id) {
   using R = Raw<S, MODE_DW>;
   constexpr int TR = R::TR, TC = R::TC;
   constexpr int GROUPS_PER_ROW = PW / TC;
@@ -208,6 +222,9 @@ __device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t 
   }
   uint64_t b0, b1;
   lds128_pairs(table + (uint32_t)((9 * p.C + ch) * 4), b0, b1);
+  // When the tile is written over its own window (sync_id > 0), every thread of the group must
+  // have its window taps in registers first.
+  if (sync_id > 0) asm volatile("bar.sync %0, %1;" ::"r"(sync_id), "n"(R::GROUP_THREADS) : "memory");
 #pragma unroll
   for (int o = 0; o < TR; o++) {
     const int m0 = (part * R::PART_ROWS + r0 + o) * PW + c0;  // first of this row's rows of the A tile
@@ -264,6 +281,9 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   constexpr int GROUP_THREADS = DW_THREADS / GROUPS;
   constexpr int RAW_STAGES = raw_stages<S, MODE>(BLOCK_N);
   static_assert(RAW_STAGES >= 2 && RAW_STAGES % GROUPS == 0 && A_SLOTS % GROUPS == 0, "rings split evenly");
+  constexpr bool IN_PLACE = a_in_place(BLOCK_N, S, MODE);
+  constexpr int NUM_A = IN_PLACE ? RAW_STAGES : A_SLOTS;  // A tiles (and their full barriers)
+  static_assert(!IN_PLACE || (R::BYTES >= A_TILE_BYTES && R::STRIDE % 1024 == 0), "the tile fits its window's stage");
   static_assert(GROUPS == 1 || R::PARTS == 1, "two groups take whole k-blocks of one raw stage each");
   // Where k-block n of this CTA (counted over all its tiles) lives: with two groups, group n % 2
   // owns slots / stages [group * size / 2, (group + 1) * size / 2) and cycles through them.
@@ -286,8 +306,8 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint8_t* a_tiles = smem;                                   // [A_SLOTS][16 KB], SWIZZLE_128B
-  uint8_t* w_tiles = a_tiles + A_SLOTS * A_TILE_BYTES;       // [W_STAGES][BLOCK_N x 128 B]
+  uint8_t* a_tiles = smem;                                   // [A_SLOTS][16 KB], SWIZZLE_128B (none if in place)
+  uint8_t* w_tiles = a_tiles + a_slot_bytes(BLOCK_N, S, MODE);  // [W_STAGES][BLOCK_N x 128 B]
   uint8_t* c_stage = w_tiles + W_STAGES * W_STAGE_BYTES;     // [8 warps][4 KB]
   uint8_t* raw = c_stage + C_STAGING_BYTES;                  // [RAW_STAGES][window]
   uint8_t* table = raw + RAW_STAGES * R::STRIDE;             // [10][C] floats
@@ -297,9 +317,9 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   uint64_t* raw_empty = raw_full + RAW_STAGES;     // [RAW_STAGES] depthwise warps -> TMA
   uint64_t* w_full = raw_empty + RAW_STAGES;       // [W_STAGES] TMA -> MMA
   uint64_t* w_empty = w_full + W_STAGES;           // [W_STAGES] MMA -> TMA
-  uint64_t* a_full = w_empty + W_STAGES;           // [A_SLOTS] depthwise warps -> MMA
-  uint64_t* a_empty = a_full + A_SLOTS;            // [A_SLOTS] MMA -> depthwise warps
-  uint64_t* tmem_full_bar = a_empty + A_SLOTS;           // [NUM_ACC] MMA -> epilogue
+  uint64_t* a_full = w_empty + W_STAGES;           // [NUM_A] depthwise warps -> MMA
+  uint64_t* a_empty = a_full + NUM_A;              // [NUM_A] MMA -> depthwise warps (unused if in place)
+  uint64_t* tmem_full_bar = a_empty + NUM_A;             // [NUM_ACC] MMA -> epilogue
   uint64_t* tmem_empty_bar = tmem_full_bar + NUM_ACC;    // [NUM_ACC] epilogue -> MMA
   uint32_t* tmem_ptr_holder = (uint32_t*)(tmem_empty_bar + NUM_ACC);
   volatile int* abort_flag = (volatile int*)(tmem_ptr_holder + 1);
@@ -310,13 +330,13 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   if (threadIdx.x == 0) {
     for (int s = 0; s < RAW_STAGES; s++) {
       mbar_init(smem_u32(&raw_full[s]), 1);
-      mbar_init(smem_u32(&raw_empty[s]), RAW_READERS);
+      mbar_init(smem_u32(&raw_empty[s]), IN_PLACE ? 1 : RAW_READERS);  // in place: freed by the MMAs' commit
     }
     for (int s = 0; s < W_STAGES; s++) {
       mbar_init(smem_u32(&w_full[s]), 1);
       mbar_init(smem_u32(&w_empty[s]), 1);
     }
-    for (int s = 0; s < A_SLOTS; s++) {
+    for (int s = 0; s < NUM_A; s++) {
       mbar_init(smem_u32(&a_full[s]), GROUP_THREADS / 32);
       mbar_init(smem_u32(&a_empty[s]), 1);
     }
@@ -465,22 +485,27 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
         for (int kb = 0; kb < p.num_k_blocks; kb++, n++) {
           int slot, rs;
           uint32_t sphase, rphase;
-          ring_pos(n, A_SLOTS, slot, sphase);
-          ring_pos(n, RAW_STAGES, rs, rphase);  // MODE_CONV: one raw stage per k-block
+          ring_pos(n, RAW_STAGES, rs, rphase);  // MODE_CONV and in place: one raw stage per k-block
+          if (IN_PLACE) {
+            slot = rs;
+            sphase = rphase;
+          } else {
+            ring_pos(n, A_SLOTS, slot, sphase);
+          }
           ok = mbar_wait(smem_u32(&w_full[ws]), wphase, abort_flag, p.status, 14);
           if (ok && MODE == MODE_CONV) ok = mbar_wait(smem_u32(&raw_full[rs]), rphase, abort_flag, p.status, 15);
           if (ok && MODE != MODE_CONV) ok = mbar_wait(smem_u32(&a_full[slot]), sphase, abort_flag, p.status, 15);
           if (!ok) break;
           tcgen05_fence_after();
-          const uint32_t a_s = MODE == MODE_CONV ? smem_u32(raw + rs * R::STRIDE)
-                                                 : smem_u32(a_tiles + slot * A_TILE_BYTES);
+          const uint32_t a_s = (MODE == MODE_CONV || IN_PLACE) ? smem_u32(raw + rs * R::STRIDE)
+                                                               : smem_u32(a_tiles + slot * A_TILE_BYTES);
           const uint32_t w_s = smem_u32(w_tiles + ws * W_STAGE_BYTES);
 #pragma unroll
           for (int k = 0; k < BLOCK_K / 8; k++)
             tcgen05_mma_tf32(tmem_d, make_smem_desc(a_s + k * 32), make_smem_desc(w_s + k * 32), idesc,
                              (kb > 0 || k > 0) ? 1u : 0u);
           tcgen05_commit(smem_u32(&w_empty[ws]));
-          if (MODE == MODE_CONV)
+          if (MODE == MODE_CONV || IN_PLACE)
             tcgen05_commit(smem_u32(&raw_empty[rs]));
           else
             tcgen05_commit(smem_u32(&a_empty[slot]));
@@ -504,12 +529,15 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
       for (int kb = 0; kb < p.num_k_blocks && ok; kb++, n++) {
         if (n % GROUPS != group) continue;
-        int slot;
-        uint32_t sphase;
-        ring_pos(n, A_SLOTS, slot, sphase);
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&a_empty[slot]), sphase ^ 1, abort_flag, p.status, 16));
-        if (!ok) break;
-        const uint32_t a_s = smem_u32(a_tiles + slot * A_TILE_BYTES);
+        int slot = 0;
+        uint32_t sphase = 0;
+        uint32_t a_s = 0;
+        if (!IN_PLACE) {
+          ring_pos(n, A_SLOTS, slot, sphase);
+          ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&a_empty[slot]), sphase ^ 1, abort_flag, p.status, 16));
+          if (!ok) break;
+          a_s = smem_u32(a_tiles + slot * A_TILE_BYTES);
+        }
         for (int part = 0; part < R::PARTS; part++) {
           int rs;
           uint32_t rphase;
@@ -517,17 +545,25 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&raw_full[rs]), rphase, abort_flag, p.status, 17));
           if (!ok) break;
           const uint32_t raw_s = smem_u32(raw + rs * R::STRIDE);
+          if (IN_PLACE) {  // the tile replaces its own window; the stage's index is the tile's
+            a_s = raw_s;
+            slot = rs;
+          }
           if (MODE == MODE_RGB) {
             rgb_part<S>(raw_s, a_s, t, p);
           } else {
+            // in place: named barrier 1 + group over the group's threads, between reads and writes
+            const int sync_id = IN_PLACE ? 1 + group : 0;
             switch (p.dw_act) {
-              case TFJS_ACT_RELU: dw_part<S, TFJS_ACT_RELU>(raw_s, a_s, table_s, t, part, kb, p, has_bias); break;
-              case TFJS_ACT_CLIP: dw_part<S, TFJS_ACT_CLIP>(raw_s, a_s, table_s, t, part, kb, p, has_bias); break;
-              default: dw_part<S, TFJS_ACT_LINEAR>(raw_s, a_s, table_s, t, part, kb, p, has_bias); break;
+              case TFJS_ACT_RELU: dw_part<S, TFJS_ACT_RELU>(raw_s, a_s, table_s, t, part, kb, p, has_bias, sync_id); break;
+              case TFJS_ACT_CLIP: dw_part<S, TFJS_ACT_CLIP>(raw_s, a_s, table_s, t, part, kb, p, has_bias, sync_id); break;
+              default: dw_part<S, TFJS_ACT_LINEAR>(raw_s, a_s, table_s, t, part, kb, p, has_bias, sync_id); break;
             }
           }
-          __syncwarp();  // every lane has read all it needs of the window
-          if (lane == 0) mbar_arrive(smem_u32(&raw_empty[rs]));
+          if (!IN_PLACE) {
+            __syncwarp();  // every lane has read all it needs of the window
+            if (lane == 0) mbar_arrive(smem_u32(&raw_empty[rs]));
+          }
         }
         if (!ok) break;
         fence_proxy_async_smem();  // generic-proxy writes of the A tile -> visible to the tensor core
@@ -636,7 +672,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 template <int BLOCK_N, int S, int MODE>
 int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my,
                    const SepParams& p) {
-  constexpr int smem_bytes = 1024 + A_SLOTS * A_TILE_BYTES + w_stages(BLOCK_N, S, MODE) * BLOCK_N * BLOCK_K * 4 +
+  constexpr int smem_bytes = 1024 + a_slot_bytes(BLOCK_N, S, MODE) + w_stages(BLOCK_N, S, MODE) * BLOCK_N * BLOCK_K * 4 +
                              C_STAGING_BYTES + raw_stages<S, MODE>(BLOCK_N) * Raw<S, MODE>::STRIDE +
                              DW_TABLE_BYTES + BIAS_STAGING_BYTES + BARRIER_BYTES;
   static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
