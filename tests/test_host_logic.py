@@ -62,9 +62,10 @@ def test_mobilenet_accounting_matches_layer_table():
     assert mobilenet.algorithmic_bytes_per_image() * 64 + mobilenet.weight_bytes() == 2638567840
     assert mobilenet.weight_bytes() == 16884128
     assert mobilenet.flops_per_image() == 1137530880
-    # per-launch accounting: the layer-wise forward has 30 launches; with the first four
-    # depthwise + pointwise pairs fused there are 26, and the four intermediates (1.6 + 0.8 + 1.6 +
-    # 0.4 MB per image, written once and read once) drop out of the byte count
+    # per-launch accounting: the layer-wise forward has 30 launches; with four depthwise +
+    # pointwise pairs fused (the accounting of this example; the default forward fuses five) there
+    # are 26, and the four intermediates (1.6 + 0.8 + 1.6 + 0.4 MB per image, written once and read
+    # once) drop out of the byte count
     layerwise = mobilenet.layer_algorithmic_bytes(64, True)
     names = (["conv2d_tcgen05 (3-channel 3x3, window TMA, TF32)"] +
              ["separableConv2d (fused dw3x3 s1 + pw, TF32)"] * 4 +

@@ -3,7 +3,7 @@
 
     python tfjs-core_b200/profile_layers.py [batch] [tf32|3xtf32] [f|q|q-in-loop] [separable|layerwise|separable-all]
 
-Prints, for each launch of one forward pass (26 with the fused depthwise + pointwise blocks,
+Prints, for each launch of one forward pass (25 with the fused depthwise + pointwise blocks,
 30 with `layerwise`), the kernel name, the best device time over a few passes
 (events recorded between launches on the context's stream), the layer's algorithmic bytes and
 the bandwidth that corresponds to.  `q` stores the filters as uint8 (BASELINE config 5); `q-in-loop` also keeps the GEMM weights uint8 and dequantises them inside the GEMM main loop;
