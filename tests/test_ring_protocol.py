@@ -190,9 +190,8 @@ def test_in_place_tiles_are_safe():
 GEOMETRIES = [
     (2, 4, 2, 1, 4, 1, 25),   # block 1: 32 channels, N = 64
     (2, 4, 2, 1, 3, 4, 9),    # block 3: 128 channels, N = 128
-    (2, 2, 2, 1, 2, 8, 5),    # 256 channels, N = 256, stride 1
     (2, 8, 2, 1, 4, 1, 25),   # the stem (im2col threads instead of depthwise threads)
-    (1, 2, 2, 2, 3, 2, 9),    # block 2: stride 2, one group, two half-windows per k-block
+    (1, 3, 2, 2, 2, 2, 9),    # block 2: stride 2, one group, two half-windows per k-block, three window stages
     (1, 2, 2, 2, 2, 4, 7),    # block 4
 ]
 
