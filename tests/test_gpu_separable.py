@@ -94,6 +94,7 @@ def test_fused_equals_the_two_kernels_and_matches_the_oracle(tf, b, h, w, c, n, 
     (24, 56, 56, 128, 128, 1),    # 672 patches of four k-blocks, two depthwise groups
     (24, 56, 56, 128, 256, 2),    # 192 patches of four k-blocks, two half-windows each
     (40, 112, 112, 64, 128, 2),   # 1120 patches, three window stages
+    (64, 28, 28, 256, 256, 1),    # 512 patches of eight k-blocks, A tiles built in place over their windows
 ])
 def test_fused_many_patches_per_cta(tf, b, h, w, c, n, stride):
     """Sizes at which every CTA works through several patches, so that the stage rings, the A
