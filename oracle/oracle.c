@@ -3,8 +3,11 @@
  * MobileNet inference path (see oracle.h).  The shipped library never calls this.
  *
  * Parity pin: checked against the literal known-answer vectors of the reference's own
- * spec files (transcribed under tests/golden/), and cross-checked against an independent
- * float64 numpy/torch implementation for the shapes the reference's specs do not cover.
+ * spec files (extracted into tests/golden/reference_kats.json, checked by
+ * tests/test_oracle_golden.py), and cross-checked against an independent float64 numpy
+ * implementation (tests/f64_forward.py, by tests/test_oracle_crosscheck.py) on the shapes those
+ * vectors do not cover: stride-2 SAME depthwise, 3x3 SAME convolution over many channels,
+ * matMul beyond one 48-wide block, the whole MobileNetV1 forward.
  */
 #include "oracle.h"
 
