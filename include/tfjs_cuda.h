@@ -103,6 +103,10 @@ typedef struct {
 /* ---- context: the backend factory of tf.registerBackend('cuda', factory)
  *      (tfjs-core/src/engine.ts:220-307) creates one; KernelBackend.dispose() destroys it. */
 int tfjs_cuda_ctx_create(int device_ordinal, tfjs_cuda_ctx** out);
+/* Number of usable CUDA devices (0 when there is none): one context per device is how a batch is
+ * sharded, each registered as its own backend 'cuda:0' ... 'cuda:N-1' (the engine's registry is
+ * keyed by name, tfjs-core/src/engine.ts:132-138, 220-232). */
+int tfjs_cuda_device_count(int* out);
 int tfjs_cuda_ctx_destroy(tfjs_cuda_ctx* ctx);
 const char* tfjs_cuda_last_error(const tfjs_cuda_ctx* ctx);
 /* Flags mirrored from ENV.registerFlag (environment.ts:32-142).  Keys: "math_mode"
@@ -111,7 +115,13 @@ const char* tfjs_cuda_last_error(const tfjs_cuda_ctx* ctx);
  * into cached tf32 planes; 1 keeps them uint8 in device memory and dequantises each tile in
  * shared memory inside the GEMM main loop; the results are bit-identical), "fuse_separable"
  * (see tfjs_cuda_separable_conv2d), "pdl" (1 launches the main kernels with programmatic stream
- * serialization, so that a kernel's prologue overlaps its predecessor's tail; default 0). */
+ * serialization, so that a kernel's prologue overlaps its predecessor's tail; default 0),
+ * "wait_limit_us" (every device-side wait of the kernels is bounded; a wait that runs out makes
+ * the kernel return and the next ctx_sync / tensor_read report TFJS_CUDA_ERR_TIMEOUT, the context
+ * stays usable; default 2 s, per device), "debug_canary" (1: every buffer is followed by a guard
+ * pattern that is verified when the buffer is released; an overwritten guard is reported as
+ * TFJS_CUDA_ERR_CUDA at the next synchronisation), "test_withhold_last_load" (diagnostic: the
+ * tensor-core matMul withholds its last load so that the bounded waits run out). */
 int tfjs_cuda_ctx_set_option(tfjs_cuda_ctx* ctx, const char* key, double value);
 /* Blocks until all enqueued work is done; TFJS_CUDA_ERR_TIMEOUT after timeout_ms (<0: none). */
 int tfjs_cuda_ctx_sync(tfjs_cuda_ctx* ctx, int timeout_ms);

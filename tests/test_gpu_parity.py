@@ -539,3 +539,37 @@ def test_memory_is_recycled(tf):
     assert m1["numTensors"] == m0["numTensors"] and m1["numBytes"] == m0["numBytes"]
     assert m1["numDeviceAllocs"] == m0["numDeviceAllocs"]
     assert m1["numBytesInGPU"] == m0["numBytesInGPU"]
+
+
+def test_graph_capture_refuses_unprepared_weights(tf):
+    """While a graph is captured, kernels are recorded and not run, so a weight layout prepared
+    during capture would be cached without ever having been written.  The first use of a weight
+    tensor inside a capture is therefore an error that says what to do, the context stays usable,
+    and after one eager pass the same capture succeeds and replays to the eager result."""
+    bk = tf.ENGINE.backend
+    rng = _rng(91)
+    x = rng.uniform(-1, 1, (1, 256, 64)).astype(np.float32)
+    q = rng.integers(0, 256, (1, 64, 128), dtype=np.uint8)
+    xt = tf.ops.tensor(x)
+    wq = bk.registerQuantized(list(q.shape), q, 0.01, -1.28)
+    bk.graphBegin()
+    try:
+        with pytest.raises(NotImplementedError, match="eagerly"):
+            bk.fusedBatchMatMul(xt, wq)
+    finally:
+        g = bk.graphEnd()
+        bk.graphDestroy(g)
+    eager = bk.fusedBatchMatMul(xt, wq)           # prepares the tensor-core layout of wq
+    want = eager.dataSync().copy()
+    bk.graphBegin()
+    out = bk.fusedBatchMatMul(xt, wq)
+    g = bk.graphEnd()
+    try:
+        again = bk.fusedBatchMatMul(xt, wq).dataSync()   # an eager call before the first replay
+        assert np.array_equal(again, want)
+        bk.graphLaunch(g)
+        assert np.array_equal(out.dataSync(), want)
+    finally:
+        bk.graphDestroy(g)
+        for t in (eager, out, xt, wq):
+            t.dispose()

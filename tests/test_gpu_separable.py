@@ -260,3 +260,54 @@ def test_conv2d_shifted_patch_tma(tf, b, h, w, cin, n, fh, fw, dil, pad):
         assert rel_err(got.dataSync().reshape(want.shape), want) <= 1e-3
     finally:
         bk.setMathMode("3xtf32")
+
+
+@pytest.mark.parametrize("c,h,stride", [(32, 16, 1), (64, 28, 2), (256, 28, 1)])
+def test_non_finite_filter_taps_at_the_border(tf, c, h, stride):
+    """The reference skips filter taps that fall outside the image (backend_cpu.ts:2002-2014);
+    it does not multiply them by zero, so an inf or NaN tap must not leak into the border
+    outputs.  The fused kernel gets its padding from zero-filled loads (0 * inf = NaN), so a
+    separable call with such a filter must take the depthwise kernels, which skip those taps
+    (strip kernel at 16 and 28 pixels, image kernel at 14 and 7): same NaN / inf pattern as the
+    oracle, finite values within the contraction tolerance."""
+    from tfjs_core_b200 import conv_util
+    bk = tf.ENGINE.backend
+    bk.setMathMode("tf32")
+    bk.setOption("fuse_separable", 2)
+    try:
+        rng = _rng(c + h)
+        n = 64
+        x = rng.uniform(0.1, 1, (2, h, h, c)).astype(np.float32)
+        wd = rng.normal(0, 0.5, (3, 3, c, 1)).astype(np.float32)
+        # SAME padding at stride 2 on an even image pads the bottom and the right only, so the taps
+        # that can fall outside at both strides are those of the last filter row / column
+        wd[2, 2, 3, 0] = np.inf      # bottom-right tap: outside for the last row and the last column
+        wd[2, 1, 5, 0] = np.nan      # bottom-centre tap: outside for the last row
+        wp = np.zeros((1, 1, c, n), np.float32)
+        wp[0, 0, np.arange(c), np.arange(c) % n] = 1.0   # output channel j sums channels j, j+64, ...
+        ci = conv_util.compute_conv2d_info(x.shape, wd.shape, stride, 1, "same", None, True)
+        names_before = bk.launchCount()
+        bk.profileBegin()
+        got = bk.fusedSeparableConv2d(tf.ops.tensor(x), tf.ops.tensor(wd), tf.ops.tensor(wp), ci, None, "linear",
+                                      None, "linear").dataSync()
+        names = [nm for nm, _ in bk.profileEnd()]
+        assert not any("fused" in nm for nm in names), names
+        assert bk.launchCount() > names_before
+        want = _oracle(x, wd, wp, None, None, stride, "linear", "linear")
+        got = got.reshape(want.shape)
+        np.testing.assert_array_equal(np.isnan(got), np.isnan(want))
+        np.testing.assert_array_equal(np.isinf(got), np.isinf(want))
+        # a non-finite channel poisons every output channel of its pixel through the pointwise sum
+        # (0 * inf), so the finite outputs are the pixels of the last row, where both taps are skipped
+        ok = np.isfinite(want)
+        assert ok[:, -1].all() and not ok[:, :-1].any()
+        assert np.abs(got[ok] - want[ok]).max() <= 1e-3 * np.abs(want[ok]).max()
+        # the same filter with the two bad taps made finite runs fused again
+        wd[2, 2, 3, 0] = wd[2, 1, 5, 0] = 0.25
+        bk.profileBegin()
+        bk.fusedSeparableConv2d(tf.ops.tensor(x), tf.ops.tensor(wd), tf.ops.tensor(wp), ci, None, "linear", None,
+                                "linear").dataSync()
+        assert any("fused" in nm for nm, _ in bk.profileEnd())
+    finally:
+        bk.setOption("fuse_separable", 1)
+        bk.setMathMode("3xtf32")

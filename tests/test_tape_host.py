@@ -105,3 +105,34 @@ def test_kernels_without_a_gradient_cannot_be_backpropagated(host):
     # max has no gradient on this path: the tape has no node for it, so y is unreachable
     with pytest.raises((ValueError, AttributeError)):
         ops.grad(lambda v: ops.max(v))(x)
+
+
+def test_grad_does_not_leak_without_a_caller_side_tidy(host):
+    """tf.grad wraps the forward pass in its own scope (engine.ts:737, gradients.ts:68-80): the value
+    of f and every intermediate are disposed, only the gradient survives."""
+    x = ops.tensor(np.array([1.0, -2.0, 3.0], np.float32))
+    before = ENGINE.numTensors
+    g = ops.grad(lambda v: ops.mul(ops.relu(v), ops.exp(v)))(x)
+    assert ENGINE.numTensors == before + 1
+    g.dispose()
+    z = ops.tensor(np.array([2.0, 2.0, 2.0], np.float32))
+    gs = ops.grads(lambda p, q: ops.mul(ops.add(p, q), p))([x, z])
+    assert ENGINE.numTensors == before + 3
+    for t in gs + [z]:
+        t.dispose()
+    assert ENGINE.numTensors == before and ENGINE.activeTape is None
+
+
+def test_second_derivative_through_a_nested_tape(host):
+    """grad(grad(f)): the inner call records onto the outer call's tape (engine.ts:660-665), so the
+    outer call differentiates through the inner backward pass.  f = x^3: f'' = 6x."""
+    x = ops.tensor(np.array([0.5, -1.0, 2.0], np.float32))
+    cube = lambda v: ops.mul(ops.mul(v, v), v)  # noqa: E731
+    before = ENGINE.numTensors
+    first = ops.grad(cube)(x)
+    np.testing.assert_allclose(first.dataSync(), 3 * np.array([0.5, -1.0, 2.0]) ** 2, rtol=1e-6)
+    second = ops.grad(lambda v: ops.grad(cube)(v))(x)
+    np.testing.assert_allclose(second.dataSync(), 6 * np.array([0.5, -1.0, 2.0]), rtol=1e-6)
+    first.dispose()
+    second.dispose()
+    assert ENGINE.numTensors == before and ENGINE.activeTape is None and ENGINE.gradientDepth == 0

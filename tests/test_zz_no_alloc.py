@@ -54,14 +54,42 @@ def _both_ways(tf, m, k, n, seed, activation):
 
 
 def test_static_scratch_matmul_matches_regular_entry_point_twice(tf):
+    # Both entry points run the same two kernels (repack b, tensor-core GEMM) on the same values,
+    # so the results must agree bit for bit, not merely within a tolerance.
     # first call: a 1024-wide b fills the whole fixed array
     want, got = _both_ways(tf, 256, 1024, 1024, seed=1, activation="relu")
-    assert rel_err(got, want) <= 1e-5
+    assert np.array_equal(got, want)
     # second call straight after, smaller operands with a ragged tile edge: the array still
     # holds the first call's planes and must not leak into this result
     want, got = _both_ways(tf, 130, 68, 72, seed=2, activation="relu6")
-    assert rel_err(got, want) <= 1e-5
+    assert np.array_equal(got, want)
     assert np.isfinite(got).all()
+    # and against the CPU oracle, so that the pair is not merely self-consistent
+    import oracle
+    rng = np.random.Generator(np.random.PCG64(2))
+    a = rng.uniform(-1, 1, (1, 130, 68)).astype(np.float32)
+    b = rng.uniform(-1, 1, (1, 68, 72)).astype(np.float32)
+    bias = rng.normal(0, 1, 72).astype(np.float32)
+    ref = oracle.unary("clip", oracle.fused_matmul(a, b, bias=bias)[0], 0.0, 6.0)
+    assert rel_err(got, ref) <= 1e-5
+
+
+def test_static_scratch_matmul_in_tf32_mode(tf):
+    """The entry point follows the context's math mode: one tensor-core pass on operands rounded
+    to tf32, again identical to the regular entry point and within 1e-3 of the oracle."""
+    import oracle
+    bk = tf.ENGINE.backend
+    bk.setMathMode("tf32")
+    try:
+        want, got = _both_ways(tf, 200, 96, 64, seed=3, activation="linear")
+        assert np.array_equal(got, want)
+        rng = np.random.Generator(np.random.PCG64(3))
+        a = rng.uniform(-1, 1, (1, 200, 96)).astype(np.float32)
+        b = rng.uniform(-1, 1, (1, 96, 64)).astype(np.float32)
+        bias = rng.normal(0, 1, 64).astype(np.float32)
+        assert rel_err(got, oracle.fused_matmul(a, b, bias=bias)[0]) <= 1e-3
+    finally:
+        bk.setMathMode("3xtf32")
 
 
 def test_static_scratch_matmul_refuses_oversized_operands(tf):

@@ -9,6 +9,7 @@ there fails loudly (there is no CPU fallback inside it).
 from . import _ffi, conv_util, ops, weights_loader  # noqa: F401
 from .backend_cuda import BackendCuda, CudaError  # noqa: F401
 from .engine import ENGINE, Tensor  # noqa: F401
+from .sharded import ShardedRunner, device_count, run_sharded  # noqa: F401
 
 
 def register_backend(name="cuda", device=0, priority=3, math_mode="3xtf32"):

@@ -53,6 +53,7 @@ _P = C.c_void_p
 _I64P = C.POINTER(C.c_int64)
 SIGNATURES = {
     "tfjs_cuda_ctx_create": (C.c_int, [C.c_int, C.POINTER(_P)]),
+    "tfjs_cuda_device_count": (C.c_int, [C.POINTER(C.c_int)]),
     "tfjs_cuda_ctx_destroy": (C.c_int, [_P]),
     "tfjs_cuda_last_error": (C.c_char_p, [_P]),
     "tfjs_cuda_ctx_set_option": (C.c_int, [_P, C.c_char_p, C.c_double]),

@@ -238,24 +238,22 @@ class BackendCuda:
         q = np.ascontiguousarray(np.asarray(q).reshape(-1), dtype=np.uint8)
         if q.size != size_from_shape(shape):
             raise ValueError("quantised byte count does not match the shape")
-        t = Tensor.__new__(Tensor)
-        t.shape, t.dtype, t.size = [int(s) for s in shape], "float32", q.size
-        from .engine import DataId
-        t.dataId, t.isDisposed = DataId(), False
+        # The engine creates and tracks the tensor like any other backend output (Tensor.make
+        # re-enters register(), which allocates a float32 buffer); that buffer is then swapped
+        # for the uint8 storage, so that id, refcount, scopes and the tape all see a normal tensor.
+        t = Tensor.make([int(s) for s in shape], {}, "float32", self)
+        rec = self._data[t.dataId]
         out = C.c_int64()
-        self._check(self._lib.tfjs_cuda_tensor_register_quantized(
-            self._ctx, C.byref(out), len(shape), _ffi.shape_array(shape),
-            q.ctypes.data_as(C.c_void_p), float(scale), float(min_)))
+        try:
+            self._check(self._lib.tfjs_cuda_tensor_register_quantized(
+                self._ctx, C.byref(out), len(shape), _ffi.shape_array(shape),
+                q.ctypes.data_as(C.c_void_p), float(scale), float(min_)))
+        except Exception:
+            t.dispose()
+            raise
+        self._lib.tfjs_cuda_tensor_dispose(self._ctx, rec["id"])
         self._data[t.dataId] = {"id": out.value, "dtype": "float32", "shape": list(t.shape),
                                 "quantized": True}
-        # make the engine track it like any other tensor, without a second register()
-        ENGINE.tensorInfo[t.dataId] = {"backend": self, "refCount": 1, "shape": t.shape,
-                                       "dtype": "float32", "bytes": q.size}
-        ENGINE.numTensors += 1
-        ENGINE.numDataBuffers += 1
-        ENGINE.numBytes += q.size
-        if ENGINE.scopeStack:
-            ENGINE.scopeStack[-1]["track"].append(t)
         return t
 
     # ---- fused epilogue marshalling ------------------------------------------------------

@@ -4,6 +4,19 @@
 
 namespace {
 
+// The derived forms of a weight tensor (dequantised copy, repacked tf32 planes, K-major bytes)
+// are computed once and cached on the tensor.  While a graph is being captured a kernel is only
+// recorded, not run, so a cache filled during capture would be marked valid without ever having
+// been written: an eager call on the same tensor before the first replay would read garbage, and
+// every replay would redo the repack.  A miss during capture is therefore refused.
+int refuse_miss_during_capture(tfjs_cuda_ctx* ctx, const char* what) {
+  if (!ctx->capturing) return TFJS_CUDA_OK;
+  return set_error(ctx, TFJS_CUDA_ERR_UNSUPPORTED,
+                   "%s of a weight tensor is not prepared yet and cannot be prepared while a graph is being "
+                   "captured: run the same calls once eagerly before tfjs_cuda_graph_begin",
+                   what);
+}
+
 // float32 view of a tensor for kernels that read plain floats; a quantised tensor gets a
 // cached dequantised copy (io_utils.ts:139 arithmetic).
 int float_view(tfjs_cuda_ctx* ctx, TensorEntry* t, const float** out) {
@@ -12,6 +25,8 @@ int float_view(tfjs_cuda_ctx* ctx, TensorEntry* t, const float** out) {
     return TFJS_CUDA_OK;
   }
   if (!t->deq || t->deq_version != t->version) {
+    int miss = refuse_miss_during_capture(ctx, "the dequantised copy");
+    if (miss) return miss;
     if (!t->deq) {
       void* p;
       int rc = ctx_alloc(ctx, (size_t)t->size * 4, &p, &t->deq_capacity);
@@ -40,6 +55,10 @@ int packed_weights(tfjs_cuda_ctx* ctx, TensorEntry* w, int64_t offset_elems, int
       c.transposed_source == source_is_nk && c.row_pad == row_pad) {
     *out = c;
     return TFJS_CUDA_OK;
+  }
+  if (cacheable) {
+    int miss = refuse_miss_during_capture(ctx, "the tensor-core layout");
+    if (miss) return miss;
   }
   PackedWeights fresh;
   fresh.n = N;
@@ -90,7 +109,7 @@ void release_temporary(tfjs_cuda_ctx* ctx, const PackedWeights& p, bool temporar
 // out[M, N] = epi(a[M, K] . w), with w a [K, N] (or [N, K] when source_is_nk) operand.
 int gemm_dispatch(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, TensorEntry* w,
                   int64_t w_offset, bool source_is_nk, bool cacheable, float* out, int64_t N,
-                  const EpilogueArgs& epi) {
+                  const EpilogueArgs& epi, bool a_tf32_exact = false) {
   if (ctx->use_tensor_cores && tcgen05_gemm_supported(M, N, K)) {
     if (ctx->dequant_in_gemm && w->quant.quantized && cacheable && w_offset == 0) {
       // Quantised weights stay uint8 in HBM: a K-major byte copy is cached once and the kernel
@@ -98,6 +117,8 @@ int gemm_dispatch(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, Tens
       const int64_t kq = (K + 15) / 16 * 16;
       if (!w->packed_q || w->packed_q_version != w->version || w->packed_q_n != N ||
           w->packed_q_k != K || w->packed_q_transposed != source_is_nk) {
+        int miss = refuse_miss_during_capture(ctx, "the K-major uint8 layout");
+        if (miss) return miss;
         if (w->packed_q) ctx_free(ctx, w->packed_q, w->packed_q_capacity);
         w->packed_q = nullptr;
         void* p;
@@ -114,13 +135,13 @@ int gemm_dispatch(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, Tens
         w->packed_q_transposed = source_is_nk;
       }
       return launch_gemm_tcgen05_u8(ctx, a, M, K, w->packed_q, kq, w->quant.scale, w->quant.min, out,
-                                    N, epi, ctx->math_mode);
+                                    N, epi, ctx->math_mode, a_tf32_exact);
     }
     PackedWeights pw;
     bool temporary;
     int rc = packed_weights(ctx, w, w_offset, K, N, source_is_nk, cacheable, &pw, &temporary);
     if (rc) return rc;
-    rc = launch_gemm_tcgen05(ctx, a, M, K, pw.hi, pw.lo, pw.kp, out, N, epi, ctx->math_mode);
+    rc = launch_gemm_tcgen05(ctx, a, M, K, pw.hi, pw.lo, pw.kp, out, N, epi, ctx->math_mode, a_tf32_exact);
     release_temporary(ctx, pw, temporary);
     return rc;
   }
@@ -359,7 +380,12 @@ extern "C" int tfjs_cuda_separable_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_i
   // 256 channels at stride 1; at 256 channels and stride 2 the shared memory left beside the
   // weight stages holds too few input windows to cover the DRAM latency), 2 wherever it can
   const bool pays = C <= 128 || (C <= 256 && dw->strideHeight == 1);
-  if (ctx->use_tensor_cores && ctx->fuse_separable && (ctx->fuse_separable >= 2 || pays) &&
+  // The fused kernel gets its SAME padding from the zero fill of its window loads and multiplies
+  // those zeros by the filter taps, where the reference skips taps outside the image
+  // (backend_cpu.ts:2002-2014).  The two agree unless a tap is inf or NaN (0 * inf = NaN), so the
+  // fused kernel is taken only for a filter the host wrote with finite values; any other filter
+  // goes through the depthwise kernels, which skip those taps.
+  if (ctx->use_tensor_cores && ctx->fuse_separable && (ctx->fuse_separable >= 2 || pays) && known_finite(wd) &&
       sepconv_tcgen05_supported(*dw, N, de.activation, pe.activation, ctx->math_mode)) {
     PackedWeights pw;
     bool temporary;
@@ -372,8 +398,15 @@ extern "C" int tfjs_cuda_separable_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_i
   size_t mid_cap;
   rc = ctx_alloc(ctx, (size_t)(pixels * C) * 4, &mid, &mid_cap);
   if (rc) return rc;
+  // The intermediate is private to this call.  When a TF32 tensor-core GEMM reads it, the depthwise
+  // kernel rounds its results to tf32 as it stores them (the fused kernel rounds the same values as
+  // it builds its A tile), so the GEMM needs no rounding pass of its own.
+  const bool round_mid = ctx->use_tensor_cores && ctx->math_mode == TFJS_MATH_TF32 &&
+                         tcgen05_gemm_supported(pixels, N, C);
+  de.round_tf32 = round_mid ? 1 : 0;
   rc = launch_depthwise(ctx, (const float*)x->ptr, wdf, (float*)mid, *dw, de);
-  if (!rc) rc = gemm_dispatch(ctx, (const float*)mid, pixels, C, wp, 0, false, true, (float*)o->ptr, N, pe);
+  if (!rc)
+    rc = gemm_dispatch(ctx, (const float*)mid, pixels, C, wp, 0, false, true, (float*)o->ptr, N, pe, round_mid);
   ctx_free(ctx, mid, mid_cap);
   return rc;
 }

@@ -41,6 +41,9 @@ struct TensorEntry {
   int64_t shape[8] = {0};
   int64_t size = 0;      // element count
   uint64_t version = 0;  // bumped on every write / kernel output
+  // == version when the host wrote the current contents and every value was finite (checked on
+  // small float tensors only): kernels whose padding relies on 0 * tap == 0 need finite taps
+  uint64_t finite_version = ~0ull;
   QuantInfo quant;
   PackedWeights packed;
   // float32 copy of a quantised tensor for the kernels that read plain floats
@@ -100,6 +103,16 @@ struct tfjs_cuda_ctx {
   // with one persistent block per SM the next kernel's blocks cannot become resident before this
   // kernel's blocks retire, and the measured step time is 0.5-3 % worse with it on)
   bool use_pdl = false;
+  // debug_canary: every buffer handed out by the allocator is followed by a 256-byte guard
+  // pattern that is verified when the buffer is released; a kernel that wrote past the end of its
+  // output is then reported through the status word at the next synchronisation (the substitute
+  // for a memory checker on machines where none can run)
+  bool debug_canary = false;
+  std::unordered_map<void*, size_t> canary_offset;  // buffer -> byte offset of its guard
+  // Diagnostic: the tensor-core GEMM withholds the last load of every CTA, so that the bounded
+  // wait of its consumers runs out and the error path (status word, TFJS_CUDA_ERR_TIMEOUT,
+  // context still usable) can be exercised without a fault
+  bool test_withhold_last_load = false;
   // bookkeeping
   int64_t launch_count = 0;
   cudaEvent_t time_start = nullptr, time_stop = nullptr;
@@ -161,6 +174,7 @@ int ctx_alloc(tfjs_cuda_ctx* ctx, size_t nbytes, void** ptr, size_t* capacity);
 void ctx_free(tfjs_cuda_ctx* ctx, void* ptr, size_t capacity);
 
 TensorEntry* find_tensor(tfjs_cuda_ctx* ctx, tfjs_tensor_id id);
+inline bool known_finite(const TensorEntry* t) { return t->finite_version == t->version; }
 // Looks the id up and checks dtype float32 with at least `min_elems` elements.
 int get_f32(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, int64_t min_elems, const char* what,
             TensorEntry** out);
@@ -175,6 +189,10 @@ struct EpilogueArgs {
   const float* prelu = nullptr;
   int prelu_scalar = 0;
   float clip_lo = 0.f, clip_hi = 0.f;
+  // Internal (never set through the C ABI): round the result to the nearest tf32 value before
+  // storing it.  Set for an intermediate tensor whose only reader is a TF32 tensor-core
+  // contraction, which would otherwise truncate it.
+  int round_tf32 = 0;
 };
 int resolve_epilogue(tfjs_cuda_ctx* ctx, const tfjs_epilogue* epi, int64_t channels,
                      EpilogueArgs* out);
@@ -190,6 +208,26 @@ __device__ __forceinline__ float min_nan(float a, float b) {
   float d;
   asm("min.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
   return d;
+}
+
+// Round to the nearest tf32 value (10 mantissa bits, ties away from zero); the low 13 bits of the
+// result are zero, so the tensor core, which reads only the upper 19 bits, takes it exactly.
+__device__ __forceinline__ float round_tf32(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return __uint_as_float(r);
+}
+
+// The same rounding for a value that goes straight to the tensor core, as one integer add: the
+// tensor core reads bits [13, 32) only, so adding half a tf32 unit to the bit pattern and letting
+// it drop the rest is round-to-nearest (ties away from zero).  inf and NaN are left alone (the add
+// would turn inf into NaN).  The low 13 bits of the result are NOT cleared.  cvt.rna.tf32 goes
+// through the conversion unit, whose throughput is a fraction of the integer ALU's; on the stem,
+// which rounds 27 values per output pixel, that difference was 10 % of the kernel.
+__device__ __forceinline__ float round_tf32_for_mma(float v) {
+  uint32_t b = __float_as_uint(v);
+  b += ((b & 0x7f800000u) != 0x7f800000u) ? 0x1000u : 0u;
+  return __uint_as_float(b);
 }
 
 // Programmatic dependent launch.  A kernel launched through launch_ex may start while the
@@ -218,6 +256,7 @@ __device__ __forceinline__ float apply_epilogue(float v, int c, const EpilogueAr
     case TFJS_ACT_CLIP: v = (v > e.clip_hi) ? e.clip_hi : ((v < e.clip_lo) ? e.clip_lo : v); break;
     default: break;
   }
+  if (e.round_tf32) v = round_tf32(v);
   return v;
 }
 
@@ -238,16 +277,24 @@ int launch_pack_u8(tfjs_cuda_ctx* ctx, const uint8_t* src, int64_t K, int64_t N,
                    int64_t n_stride, int64_t kq, uint8_t* dst);
 int launch_dequant(tfjs_cuda_ctx* ctx, const uint8_t* q, float* out, int64_t n, double scale,
                    double min);
+// Limit, in SM clock cycles, of every bounded device-side wait in the three translation units
+// that have such waits (each keeps its own copy of the constant); the device must be current.
+int set_wait_limit_gemm(long long cycles);
+int set_wait_limit_sepconv(long long cycles);
+int set_wait_limit_depthwise_image(long long cycles);
 // gemm_tcgen05.cu
 bool tcgen05_gemm_supported(int64_t M, int64_t N, int64_t K);
+// a_tf32_exact (TF32 mode only): every element of `a` already has its low 13 mantissa bits zero
+// (its producer rounded it), so the kernel may hand the tiles to the tensor core as they are;
+// otherwise it rounds them to nearest in shared memory, because the tensor core truncates.
 int launch_gemm_tcgen05(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K,
                         const float* w_hi, const float* w_lo, int64_t kp, float* out, int64_t N,
-                        const EpilogueArgs& epi, int math_mode);
+                        const EpilogueArgs& epi, int math_mode, bool a_tf32_exact = false);
 // Same contraction with the weights as K-major uint8 [N, kq] (kq a multiple of 16, zero
 // padded): w = q*scale + min is evaluated in shared memory inside the main loop.
 int launch_gemm_tcgen05_u8(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K,
                            const uint8_t* w_q, int64_t kq, double scale, double min, float* out,
-                           int64_t N, const EpilogueArgs& epi, int math_mode);
+                           int64_t N, const EpilogueArgs& epi, int math_mode, bool a_tf32_exact = false);
 // Implicit-GEMM convolution on the tensor cores: mode 0 = not eligible, otherwise the gather
 // flavour; tcgen05_conv_k is the contraction length the packed weights must have.
 int tcgen05_conv_mode(const tfjs_conv2d_info& ci);

@@ -103,11 +103,23 @@ static void release_cached(tfjs_cuda_ctx* ctx) {
   ctx->num_cached = 0;
 }
 
+// ---- guard pattern behind every buffer (option "debug_canary") ------------------------------
+constexpr size_t CANARY_BYTES = 256;
+constexpr uint32_t CANARY_WORD = 0xA5C3F00Du;
+constexpr int STATUS_CANARY = 90;  // device status code: a guard pattern was overwritten
+
+__global__ void canary_fill_kernel(uint32_t* guard) { guard[threadIdx.x] = CANARY_WORD; }
+__global__ void canary_check_kernel(const uint32_t* guard, int* status) {
+  if (guard[threadIdx.x] != CANARY_WORD) atomicCAS(status, 0, STATUS_CANARY);
+}
+
 int ctx_alloc(tfjs_cuda_ctx* ctx, size_t nbytes, void** ptr, size_t* capacity) {
   *ptr = nullptr;
   *capacity = 0;
   if (nbytes == 0) return TFJS_CUDA_OK;
-  const size_t cls = size_class(nbytes);
+  const bool canary = ctx->debug_canary && !ctx->capturing;
+  const size_t guard_at = (nbytes + 15) / 16 * 16;
+  const size_t cls = size_class(canary ? guard_at + CANARY_BYTES : nbytes);
   if (ctx->capturing) {
     // Buffers released earlier in this capture can serve later captured kernels: the graph
     // replays its nodes in the captured order, so the reuse stays stream-ordered.
@@ -145,12 +157,25 @@ int ctx_alloc(tfjs_cuda_ctx* ctx, size_t nbytes, void** ptr, size_t* capacity) {
   }
   *capacity = cls;
   ctx->bytes_in_use += (int64_t)cls;
+  if (canary) {
+    canary_fill_kernel<<<1, CANARY_BYTES / 4, 0, ctx->stream>>>((uint32_t*)((char*)*ptr + guard_at));
+    ctx->canary_offset[*ptr] = guard_at;
+  }
   return TFJS_CUDA_OK;
 }
 
 void ctx_free(tfjs_cuda_ctx* ctx, void* ptr, size_t capacity) {
   if (!ptr) return;
   ctx->bytes_in_use -= (int64_t)capacity;
+  auto guard = ctx->canary_offset.find(ptr);
+  if (guard != ctx->canary_offset.end()) {
+    // stream-ordered after every kernel that wrote the buffer; a mismatch lands in the status
+    // word and surfaces at the next synchronisation
+    if (!ctx->capturing)
+      canary_check_kernel<<<1, CANARY_BYTES / 4, 0, ctx->stream>>>(
+          (const uint32_t*)((const char*)ptr + guard->second), ctx->d_status);
+    ctx->canary_offset.erase(guard);
+  }
   if (ctx->capturing) {
     // A captured graph keeps writing to this buffer on every replay.
     ctx->capturing->held[ptr] = capacity;
@@ -229,6 +254,17 @@ static void free_entry_buffers(tfjs_cuda_ctx* ctx, TensorEntry& t) {
   }
 }
 
+extern "C" int tfjs_cuda_device_count(int* out) {
+  if (!out) return TFJS_CUDA_ERR_INVALID_ARG;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  *out = n;
+  return TFJS_CUDA_OK;
+}
+
 extern "C" int tfjs_cuda_ctx_destroy(tfjs_cuda_ctx* ctx) {
   if (!ctx) return TFJS_CUDA_OK;
   cudaSetDevice(ctx->device);
@@ -271,6 +307,21 @@ extern "C" int tfjs_cuda_ctx_set_option(tfjs_cuda_ctx* ctx, const char* key, dou
     ctx->dequant_in_gemm = value != 0;
   } else if (!strcmp(key, "pdl")) {
     ctx->use_pdl = value != 0;
+  } else if (!strcmp(key, "debug_canary")) {
+    ctx->debug_canary = value != 0;
+  } else if (!strcmp(key, "test_withhold_last_load")) {
+    ctx->test_withhold_last_load = value != 0;
+  } else if (!strcmp(key, "wait_limit_us")) {
+    // bounded device-side waits give up after this long; per device, shared by its contexts
+    TFJS_REQUIRE(ctx, value >= 100 && value <= 60e6, "wait_limit_us must lie between 100 and 60 000 000");
+    cudaSetDevice(ctx->device);
+    int khz = 0;
+    TFJS_CHECK_CUDA(ctx, cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->device));
+    const long long cycles = (long long)(value * 1e-3 * (double)khz);
+    if (set_wait_limit_gemm(cycles) || set_wait_limit_sepconv(cycles) || set_wait_limit_depthwise_image(cycles)) {
+      cudaGetLastError();
+      return set_error(ctx, TFJS_CUDA_ERR_CUDA, "could not set the wait limit");
+    }
   } else if (!strcmp(key, "fuse_separable")) {
     TFJS_REQUIRE(ctx, value == 0 || value == 1 || value == 2, "fuse_separable must be 0, 1 or 2");
     ctx->fuse_separable = (int)value;
@@ -286,6 +337,9 @@ static int check_device_status(tfjs_cuda_ctx* ctx) {
     int code = *ctx->h_status;
     *ctx->h_status = 0;
     cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
+    if (code == STATUS_CANARY)
+      return set_error(ctx, TFJS_CUDA_ERR_CUDA,
+                       "a kernel wrote past the end of a buffer (guard pattern overwritten; device status %d)", code);
     return set_error(ctx, TFJS_CUDA_ERR_TIMEOUT,
                      "a kernel gave up on a bounded wait (device status %d)", code);
   }
@@ -367,6 +421,17 @@ TensorEntry* find_tensor(tfjs_cuda_ctx* ctx, tfjs_tensor_id id) {
 
 static size_t dtype_size(int dtype) { return dtype == TFJS_BOOL ? 1 : 4; }
 
+// Records whether the values the host just handed over are all finite (small float tensors only:
+// filters and biases; an image batch is not scanned).
+static void note_host_values(TensorEntry* t, const void* host) {
+  t->finite_version = ~0ull;
+  if (t->dtype != TFJS_F32 || t->size > 65536 || (t->size > 0 && !host)) return;
+  const uint32_t* bits = (const uint32_t*)host;
+  for (int64_t i = 0; i < t->size; i++)
+    if ((bits[i] & 0x7f800000u) == 0x7f800000u) return;  // inf or NaN
+  t->finite_version = t->version;
+}
+
 static int register_impl(tfjs_cuda_ctx* ctx, tfjs_tensor_id* out_id, int rank, const int64_t* shape,
                          int dtype, size_t elem_size) {
   TFJS_REQUIRE(ctx, out_id != nullptr, "out_id is null");
@@ -412,6 +477,11 @@ extern "C" int tfjs_cuda_tensor_register_quantized(tfjs_cuda_ctx* ctx, tfjs_tens
   if (t->nbytes)
     TFJS_CHECK_CUDA(ctx, cudaMemcpyAsync(t->ptr, q, t->nbytes, cudaMemcpyHostToDevice, ctx->stream));
   t->version++;
+  // q * scale + min over the 256 byte values is finite when both ends are
+  const double w0 = min, w255 = 255.0 * scale + min;
+  if (w0 == w0 && w255 == w255 && w0 - w0 == 0.0 && w255 - w255 == 0.0 && (float)w0 - (float)w0 == 0.f &&
+      (float)w255 - (float)w255 == 0.f)
+    t->finite_version = t->version;
   return TFJS_CUDA_OK;
 }
 
@@ -432,6 +502,7 @@ extern "C" int tfjs_cuda_tensor_write(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, con
   if (nbytes)
     TFJS_CHECK_CUDA(ctx, cudaMemcpyAsync(t->ptr, host, nbytes, cudaMemcpyHostToDevice, ctx->stream));
   t->version++;
+  note_host_values(t, host);
   return TFJS_CUDA_OK;
 }
 
@@ -462,6 +533,7 @@ extern "C" int tfjs_cuda_tensor_write_async(tfjs_cuda_ctx* ctx, tfjs_tensor_id i
   if (!t->copy_event)
     TFJS_CHECK_CUDA(ctx, cudaEventCreateWithFlags(&t->copy_event, cudaEventDisableTiming));
   t->version++;
+  note_host_values(t, host);
   if (!nbytes) return TFJS_CUDA_OK;
   // write-after-read: kernels already enqueued may still read the old contents
   TFJS_CHECK_CUDA(ctx, cudaEventRecord(ctx->compute_mark, ctx->stream));

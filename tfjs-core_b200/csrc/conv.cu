@@ -265,7 +265,7 @@ struct DepthwiseStrip {
   __device__ __forceinline__ void step(int yi, bool more, int64_t row_stride, int in_height, int C4,
                                        const float4* w_s, int cbn, int c_local, float4* yrow,
                                        int cols_left, bool has_bias, const float4& bias4, float lo,
-                                       float hi) {
+                                       float hi, bool round) {
     constexpr int B = (A + 1) % 3, C = (A + 2) % 3;
 #pragma unroll
     for (int j = 0; j < TW; j++) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -284,6 +284,9 @@ struct DepthwiseStrip {
         o.y = activate<ACT>(o.y, lo, hi);
         o.z = activate<ACT>(o.z, lo, hi);
         o.w = activate<ACT>(o.w, lo, hi);
+        if (round) {  // the only reader is a TF32 contraction: round instead of letting it truncate
+          o.x = round_tf32(o.x); o.y = round_tf32(o.y); o.z = round_tf32(o.z); o.w = round_tf32(o.w);
+        }
         yrow[j * C4] = o;
       }
     }
@@ -293,7 +296,7 @@ struct DepthwiseStrip {
   __device__ __forceinline__ void run(const float4* xb, float4* yb, int yo0, int yo1, int xo0, int xi0,
                                       const tfjs_conv2d_info& ci, int C4, const float4* w_s, int cbn,
                                       int c_local, bool has_bias, const float4& bias4, float lo,
-                                      float hi) {
+                                      float hi, bool round) {
     const int64_t row_stride = (int64_t)ci.inWidth * C4;
     const int64_t out_stride = (int64_t)ci.outWidth * C4;
     const int in_height = ci.inHeight;
@@ -318,15 +321,15 @@ struct DepthwiseStrip {
     // bank of the top row: 0, 1, 2, 0, ... for stride 1 and 0, 2, 1, 0, ... for stride 2
     while (true) {
       step<0, INTERIOR>(yi, yo + 1 < yo1, row_stride, in_height, C4, w_s, cbn, c_local, yrow, cols_left,
-                        has_bias, bias4, lo, hi);
+                        has_bias, bias4, lo, hi, round);
       if (++yo >= yo1) break;
       yi += S; yrow += out_stride;
       step<(S == 1 ? 1 : 2), INTERIOR>(yi, yo + 1 < yo1, row_stride, in_height, C4, w_s, cbn, c_local, yrow,
-                                       cols_left, has_bias, bias4, lo, hi);
+                                       cols_left, has_bias, bias4, lo, hi, round);
       if (++yo >= yo1) break;
       yi += S; yrow += out_stride;
       step<(S == 1 ? 2 : 1), INTERIOR>(yi, yo + 1 < yo1, row_stride, in_height, C4, w_s, cbn, c_local, yrow,
-                                       cols_left, has_bias, bias4, lo, hi);
+                                       cols_left, has_bias, bias4, lo, hi, round);
       if (++yo >= yo1) break;
       yi += S; yrow += out_stride;
     }
@@ -390,10 +393,10 @@ depthwise3x3_strip_kernel(const float* __restrict__ x, const float* __restrict__
                           yi_last < ci.inHeight && xo0 + TW <= ci.outWidth;
     if (interior)
       ds.template run<true>(xb, yb, yo0, yo1, xo0, xi0, ci, C4, w_s, cbn, c_local, has_bias, bias4,
-                            epi.clip_lo, epi.clip_hi);
+                            epi.clip_lo, epi.clip_hi, epi.round_tf32 != 0);
     else
       ds.template run<false>(xb, yb, yo0, yo1, xo0, xi0, ci, C4, w_s, cbn, c_local, has_bias, bias4,
-                             epi.clip_lo, epi.clip_hi);
+                             epi.clip_lo, epi.clip_hi, epi.round_tf32 != 0);
   }
 }
 

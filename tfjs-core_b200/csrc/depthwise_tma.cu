@@ -35,6 +35,7 @@ struct ImageParams {
   const float* bias;
   int bias_scalar;
   float lo, hi;
+  int round_tf32;          // round the results to tf32 (their only reader is a TF32 contraction)
   float* y;                // [B, outH, outW, C]
   int* status;
 };
@@ -175,6 +176,9 @@ depthwise3x3_image_kernel(const __grid_constant__ CUtensorMap map_x, ImageParams
         acc.y = act<ACT>(acc.y, p.lo, p.hi);
         acc.z = act<ACT>(acc.z, p.lo, p.hi);
         acc.w = act<ACT>(acc.w, p.lo, p.hi);
+        if (p.round_tf32) {
+          acc.x = round_tf32(acc.x); acc.y = round_tf32(acc.y); acc.z = round_tf32(acc.z); acc.w = round_tf32(acc.w);
+        }
         yp[yo * y_row] = acc;
       }
     }
@@ -215,6 +219,8 @@ int pick_group(const tfjs_conv2d_info& ci) {
 
 }  // namespace
 
+int set_wait_limit_depthwise_image(long long cycles) { return set_wait_limit_here(cycles); }
+
 bool depthwise_image_supported(const tfjs_conv2d_info& ci, int activation) {
   const int S = ci.strideHeight;
   if (!(ci.filterHeight == 3 && ci.filterWidth == 3 && ci.dilationHeight == 1 && ci.dilationWidth == 1 &&
@@ -248,6 +254,7 @@ int launch_depthwise_image(tfjs_cuda_ctx* ctx, const float* x, const float* w, f
   p.bias_scalar = epi.bias_scalar;
   p.lo = epi.clip_lo;
   p.hi = epi.clip_hi;
+  p.round_tf32 = epi.round_tf32;
   p.y = y;
   p.status = ctx->d_status;
   CUtensorMap mx;

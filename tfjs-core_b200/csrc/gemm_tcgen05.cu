@@ -17,6 +17,8 @@
 //               memory and write with TMA stores (which clip the M and N tails).
 // Every mbarrier wait is bounded; a wait that gives up sets the context's status word and the
 // CTA drains and frees its tensor memory.
+#include <atomic>
+
 #include "tcgen05_ptx.cuh"
 
 namespace {
@@ -68,6 +70,9 @@ struct GemmParams {
   // followed by the tf32 rounding gives the same bits as the float64 evaluation
   float q_scale32, q_min32;
   int q_arith;
+  // diagnostic: the producer does not issue the loads of its last k-block, so the consumers'
+  // bounded waits run out (nothing is left in flight, the kernel gives up cleanly)
+  int withhold_last_load;
 };
 
 // How the A operand reaches shared memory.
@@ -83,19 +88,33 @@ constexpr int A_CONV_RGB = 2;   // NHWC image, Cin == 3, 3 columns wide filter: 
 // the tf32 hi (/lo) split straight into the swizzled operand tile the tensor core reads.
 // Threads per CTA: 10 warps, plus 4 converter / gather warps, or 8 converter warps when the
 // weights are dequantised in the loop.
-__host__ __device__ constexpr int cta_threads(bool split, int amode, bool wq) {
-  return wq ? 576 : ((split || amode != A_MATRIX) ? 448 : 320);
+// `converts`: the A stage is rewritten in shared memory before the tensor core reads it (3xTF32
+// split, or round-to-nearest of a TF32 operand), which takes the four helper warps.
+__host__ __device__ constexpr int cta_threads(bool converts, int amode, bool wq) {
+  return wq ? 576 : ((converts || amode != A_MATRIX) ? 448 : 320);
 }
 
-template <int BLOCK_N, bool SPLIT, int AMODE, bool WQ>
-__global__ void __launch_bounds__(cta_threads(SPLIT, AMODE, WQ), 1)
+// How the A operand is prepared for the tensor core, which reads the upper 19 bits of each
+// float32 (sign, exponent, 10 mantissa bits) and so TRUNCATES whatever it is given:
+constexpr int PREC_TF32_ASIS = 0;   // one pass; the caller guarantees A holds tf32-exact values
+                                    // (low 13 mantissa bits zero), e.g. a producer kernel rounded
+                                    // them, or (conv modes) the gather threads round each row
+constexpr int PREC_3XTF32 = 1;      // hi = rna(a), lo = rna(a - hi); three passes
+constexpr int PREC_TF32_ROUND = 2;  // one pass; helper warps round A to nearest (ties away) in
+                                    // shared memory first, so that the operand error is unbiased
+
+template <int BLOCK_N, int PREC, int AMODE, bool WQ>
+__global__ void __launch_bounds__(cta_threads(PREC != PREC_TF32_ASIS, AMODE, WQ), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_w_hi,
                     const __grid_constant__ CUtensorMap map_w_lo,
                     const __grid_constant__ CUtensorMap map_c, GemmParams p) {
   static_assert(!WQ || AMODE == A_MATRIX, "in-loop dequantisation is implemented for the matrix mode");
+  static_assert(PREC != PREC_TF32_ROUND || AMODE == A_MATRIX, "the gather threads of the conv modes round their own rows");
+  constexpr bool SPLIT = PREC == PREC_3XTF32;
+  constexpr bool ROUND = PREC == PREC_TF32_ROUND;
   constexpr int STAGES = num_stages(BLOCK_N, SPLIT, WQ);
-  constexpr int NCONV = cta_threads(SPLIT, AMODE, WQ) - 320;  // converter (or gather) threads
+  constexpr int NCONV = cta_threads(PREC != PREC_TF32_ASIS, AMODE, WQ) - 320;  // converter (or gather) threads
   constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 4;
   constexpr int Q_STAGE_BYTES = BLOCK_N * BLOCK_K;  // uint8 tile
   // Two accumulator buffers (the epilogue drains one while the MMAs fill the other).  In 3xTF32
@@ -217,6 +236,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           }
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 1);
           if (!ok) break;
+          if (p.withhold_last_load && kb + 1 == p.num_k_blocks && tile + (int)gridDim.x >= num_tiles) {
+            ok = false;  // the consumers now wait for a stage that never fills
+            break;
+          }
           const uint32_t bar = smem_u32(&full_bar[stage]);
           mbar_arrive_expect_tx(bar, TX_BYTES);
           if (AMODE == A_MATRIX)
@@ -254,7 +277,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 3);
           if (ok && WQ)
             ok = mbar_wait(smem_u32(&slot_full_bar[slot]), slot_phase, abort_flag, p.status, 4);
-          else if (ok && SPLIT && AMODE == A_MATRIX)
+          else if (ok && (SPLIT || ROUND) && AMODE == A_MATRIX)
             ok = mbar_wait(smem_u32(&conv_bar[stage]), phase, abort_flag, p.status, 4);
           if (!ok) break;
           tcgen05_fence_after();
@@ -314,6 +337,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             l.w = (fabsf(h.w) <= 3.4028234e38f) ? round_tf32(v.w - h.w) : 0.f;
             hi4[i] = h;
             lo4[i] = l;
+          }
+        } else {
+          // TF32: round the row to nearest, the tensor core would truncate it
+          float4* hi4 = reinterpret_cast<float4*>(a_hi + s * A_STAGE_BYTES + t * 128);
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            float4 v = hi4[i];
+            v.x = round_tf32_for_mma(v.x); v.y = round_tf32_for_mma(v.y);
+            v.z = round_tf32_for_mma(v.z); v.w = round_tf32_for_mma(v.w);
+            hi4[i] = v;
           }
         }
         fence_proxy_async_smem();
@@ -384,10 +417,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         if (++hand_stage == STAGES) hand_stage = 0;
         --in_flight;
       }
-    } else if (SPLIT || WQ) {
+    } else if (SPLIT || ROUND || WQ) {
       // ---------------- converter warps (matrix mode) ----------------
-      // 3xTF32: split the A stage in place into tf32 hi / lo.  WQ: dequantise the uint8 weight
-      // tile of the stage into the swizzled tf32 hi (/lo) tile(s).
+      // 3xTF32: split the A stage in place into tf32 hi / lo.  TF32 with rounding: round the A
+      // stage in place.  WQ: dequantise the uint8 weight tile of the stage into the swizzled tf32
+      // hi (/lo) tile(s).
       const int t = threadIdx.x - 320;  // 0..127
       int stage = 0;
       uint32_t phase = 0;
@@ -415,6 +449,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
               l.w = (fabsf(h.w) <= 3.4028234e38f) ? round_tf32(v.w - h.w) : 0.f;
               hi4[idx] = h;
               lo4[idx] = l;
+            }
+          }
+          if (ROUND) {
+            float4* hi4 = reinterpret_cast<float4*>(a_hi + stage * A_STAGE_BYTES);
+#pragma unroll
+            for (int i = 0; i < A_STAGE_BYTES / 16 / NCONV; i++) {
+              const int idx = t + i * NCONV;
+              float4 v = hi4[idx];
+              v.x = round_tf32_for_mma(v.x); v.y = round_tf32_for_mma(v.y);
+              v.z = round_tf32_for_mma(v.z); v.w = round_tf32_for_mma(v.w);
+              hi4[idx] = v;
             }
           }
           if (WQ) {
@@ -602,19 +647,18 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                   CUtensorMapFloatOOBfill);
 
+EncodeTiledFn lookup_encode_fn() {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+      q == cudaDriverEntryPointSuccess)
+    return (EncodeTiledFn)p;
+  cudaGetLastError();
+  return nullptr;
+}
+
 EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-    else
-      cudaGetLastError();
-  }
+  static const EncodeTiledFn fn = lookup_encode_fn();  // initialised once, safely across host threads
   return fn;
 }
 
@@ -632,45 +676,49 @@ bool encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BLOCK_N, bool SPLIT, int AMODE, bool WQ = false>
+template <int BLOCK_N, int PREC, int AMODE, bool WQ = false>
 int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mh, const CUtensorMap& ml,
                    const CUtensorMap& mc, const GemmParams& p) {
+  constexpr bool SPLIT = PREC == PREC_3XTF32;
   constexpr int smem_bytes = wq_ring_bytes(BLOCK_N, SPLIT, WQ) + num_stages(BLOCK_N, SPLIT, WQ) * stage_bytes(BLOCK_N, SPLIT, WQ) + C_STAGING_BYTES +
                              BIAS_STAGING_BYTES + BARRIER_BYTES + 1024;
   static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
-  auto kernel = gemm_tcgen05_kernel<BLOCK_N, SPLIT, AMODE, WQ>;
-  static bool configured[64] = {false};  // the attribute is per device
-  if (!configured[ctx->device & 63]) {
+  auto kernel = gemm_tcgen05_kernel<BLOCK_N, PREC, AMODE, WQ>;
+  // the attribute is per device and per kernel; contexts of several devices may call from several
+  // host threads, so the flags are atomic (setting the attribute twice is harmless)
+  static std::atomic<bool> configured[64];
+  if (!configured[ctx->device & 63].load(std::memory_order_acquire)) {
     TFJS_CHECK_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-    configured[ctx->device & 63] = true;
+    configured[ctx->device & 63].store(true, std::memory_order_release);
   }
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-  launch_ex(ctx, kernel, dim3(grid), dim3(cta_threads(SPLIT, AMODE, WQ)), smem_bytes, ma, mh, ml, mc, p);
+  launch_ex(ctx, kernel, dim3(grid), dim3(cta_threads(PREC != PREC_TF32_ASIS, AMODE, WQ)), smem_bytes, ma, mh, ml, mc, p);
   if (WQ) return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32, uint8 weights)" : "gemm_tcgen05 (TF32, uint8 weights)");
   if (AMODE == A_MATRIX) return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32)" : "gemm_tcgen05 (TF32)");
   return post_launch(ctx, SPLIT ? "conv2d_tcgen05 (3xTF32)" : "conv2d_tcgen05 (TF32)");
 }
 
-template <int AMODE>
-int launch_mode(tfjs_cuda_ctx* ctx, int block_n, bool split, const CUtensorMap& ma, const CUtensorMap& mh,
+// prec: PREC_3XTF32 is limited to 128 columns (two tile pairs fill tensor memory)
+template <int AMODE, bool WQ>
+int launch_mode(tfjs_cuda_ctx* ctx, int block_n, int prec, const CUtensorMap& ma, const CUtensorMap& mh,
                 const CUtensorMap& ml, const CUtensorMap& mc, const GemmParams& p) {
+#define TFJS_GEMM_CASE(BN)                                                                            \
+  case BN:                                                                                            \
+    if (prec == PREC_3XTF32) return launch_variant<BN, PREC_3XTF32, AMODE, WQ>(ctx, ma, mh, ml, mc, p); \
+    if (AMODE == A_MATRIX && prec == PREC_TF32_ROUND)                                                 \
+      return launch_variant<BN, AMODE == A_MATRIX ? PREC_TF32_ROUND : PREC_TF32_ASIS, AMODE, WQ>(ctx, ma, mh, ml, mc, p); \
+    return launch_variant<BN, PREC_TF32_ASIS, AMODE, WQ>(ctx, ma, mh, ml, mc, p);
   switch (block_n) {
-    case 32: return split ? launch_variant<32, true, AMODE>(ctx, ma, mh, ml, mc, p) : launch_variant<32, false, AMODE>(ctx, ma, mh, ml, mc, p);
-    case 64: return split ? launch_variant<64, true, AMODE>(ctx, ma, mh, ml, mc, p) : launch_variant<64, false, AMODE>(ctx, ma, mh, ml, mc, p);
-    case 128: return split ? launch_variant<128, true, AMODE>(ctx, ma, mh, ml, mc, p) : launch_variant<128, false, AMODE>(ctx, ma, mh, ml, mc, p);
-    default: return launch_variant<256, false, AMODE>(ctx, ma, mh, ml, mc, p);
+    TFJS_GEMM_CASE(32)
+    TFJS_GEMM_CASE(64)
+    TFJS_GEMM_CASE(128)
+    default:
+      if (AMODE == A_MATRIX && prec == PREC_TF32_ROUND)
+        return launch_variant<256, AMODE == A_MATRIX ? PREC_TF32_ROUND : PREC_TF32_ASIS, AMODE, WQ>(ctx, ma, mh, ml, mc, p);
+      return launch_variant<256, PREC_TF32_ASIS, AMODE, WQ>(ctx, ma, mh, ml, mc, p);
   }
-}
-
-int launch_quantized(tfjs_cuda_ctx* ctx, int block_n, bool split, const CUtensorMap& ma, const CUtensorMap& mq,
-                     const CUtensorMap& mc, const GemmParams& p) {
-  switch (block_n) {
-    case 32: return split ? launch_variant<32, true, A_MATRIX, true>(ctx, ma, mq, mq, mc, p) : launch_variant<32, false, A_MATRIX, true>(ctx, ma, mq, mq, mc, p);
-    case 64: return split ? launch_variant<64, true, A_MATRIX, true>(ctx, ma, mq, mq, mc, p) : launch_variant<64, false, A_MATRIX, true>(ctx, ma, mq, mq, mc, p);
-    case 128: return split ? launch_variant<128, true, A_MATRIX, true>(ctx, ma, mq, mq, mc, p) : launch_variant<128, false, A_MATRIX, true>(ctx, ma, mq, mq, mc, p);
-    default: return launch_variant<256, false, A_MATRIX, true>(ctx, ma, mq, mq, mc, p);
-  }
+#undef TFJS_GEMM_CASE
 }
 
 // True when, for every byte value q, tf32(fma(float(q), float(scale), float(min))) has the same
@@ -707,9 +755,11 @@ bool encode_2d_u8(CUtensorMap* map, const void* base, uint64_t rows, uint64_t co
 // (A_MATRIX) or null; K is the contraction length as laid out in the packed weights.
 int launch_common(tfjs_cuda_ctx* ctx, int amode, const float* a, const ConvGeom* conv, int64_t M, int64_t K,
                   const float* w_hi, const float* w_lo, int64_t kp, float* out, int64_t N,
-                  const EpilogueArgs& epi, int math_mode, const uint8_t* w_q = nullptr, double q_scale = 0.0,
-                  double q_min = 0.0) {
+                  const EpilogueArgs& epi, int math_mode, bool a_tf32_exact, const uint8_t* w_q = nullptr,
+                  double q_scale = 0.0, double q_min = 0.0) {
   const bool split = math_mode == TFJS_MATH_TF32X3;
+  // TF32: a dense A matrix is rounded to nearest in shared memory unless its producer already did
+  const int prec = split ? PREC_3XTF32 : ((amode == A_MATRIX && !a_tf32_exact) ? PREC_TF32_ROUND : PREC_TF32_ASIS);
   TFJS_REQUIRE(ctx, w_q != nullptr || !split || w_lo != nullptr, "3xTF32 needs the residual weight plane");
   int block_n;
   if (N <= 32) block_n = 32;
@@ -770,15 +820,18 @@ int launch_common(tfjs_cuda_ctx* ctx, int amode, const float* a, const ConvGeom*
   p.q_scale32 = (float)q_scale;
   p.q_min32 = (float)q_min;
   p.q_arith = (w_q && !split && dequant_exact_in_float32(q_scale, q_min)) ? 1 : 0;
-  if (w_q) return launch_quantized(ctx, block_n, split, ma, mh, mc, p);
+  p.withhold_last_load = (ctx->test_withhold_last_load && amode == A_MATRIX) ? 1 : 0;
+  if (w_q) return launch_mode<A_MATRIX, true>(ctx, block_n, prec, ma, mh, mh, mc, p);
   switch (amode) {
-    case A_CONV_VEC: return launch_mode<A_CONV_VEC>(ctx, block_n, split, ma, mh, ml, mc, p);
-    case A_CONV_RGB: return launch_mode<A_CONV_RGB>(ctx, block_n, split, ma, mh, ml, mc, p);
-    default: return launch_mode<A_MATRIX>(ctx, block_n, split, ma, mh, ml, mc, p);
+    case A_CONV_VEC: return launch_mode<A_CONV_VEC, false>(ctx, block_n, prec, ma, mh, ml, mc, p);
+    case A_CONV_RGB: return launch_mode<A_CONV_RGB, false>(ctx, block_n, prec, ma, mh, ml, mc, p);
+    default: return launch_mode<A_MATRIX, false>(ctx, block_n, prec, ma, mh, ml, mc, p);
   }
 }
 
 }  // namespace
+
+int set_wait_limit_gemm(long long cycles) { return set_wait_limit_here(cycles); }
 
 bool tma_encode_tiled(CUtensorMap* map, CUtensorMapDataType dtype, int rank, const void* base,
                       const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
@@ -805,17 +858,17 @@ bool tcgen05_gemm_supported(int64_t M, int64_t N, int64_t K) {
 
 int launch_gemm_tcgen05(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, const float* w_hi,
                         const float* w_lo, int64_t kp, float* out, int64_t N, const EpilogueArgs& epi,
-                        int math_mode) {
-  return launch_common(ctx, A_MATRIX, a, nullptr, M, K, w_hi, w_lo, kp, out, N, epi, math_mode);
+                        int math_mode, bool a_tf32_exact) {
+  return launch_common(ctx, A_MATRIX, a, nullptr, M, K, w_hi, w_lo, kp, out, N, epi, math_mode, a_tf32_exact);
 }
 
 // Matrix-mode GEMM whose weights are raw uint8 bytes, K-major [N, kq] (kq a multiple of 16),
 // dequantised inside the main loop.
 int launch_gemm_tcgen05_u8(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, const uint8_t* w_q,
                            int64_t kq, double scale, double min, float* out, int64_t N,
-                           const EpilogueArgs& epi, int math_mode) {
-  return launch_common(ctx, A_MATRIX, a, nullptr, M, K, nullptr, nullptr, kq, out, N, epi, math_mode, w_q,
-                       scale, min);
+                           const EpilogueArgs& epi, int math_mode, bool a_tf32_exact) {
+  return launch_common(ctx, A_MATRIX, a, nullptr, M, K, nullptr, nullptr, kq, out, N, epi, math_mode,
+                       a_tf32_exact, w_q, scale, min);
 }
 
 // Which implicit-GEMM gather, if any, can take this convolution (0 = none).
@@ -846,5 +899,5 @@ int launch_conv_tcgen05(tfjs_cuda_ctx* ctx, int mode, const float* x, const tfjs
   g.padT = ci.padTop; g.padL = ci.padLeft; g.fH = ci.filterHeight; g.fW = ci.filterWidth;
   const int64_t M = (int64_t)ci.batchSize * ci.outHeight * ci.outWidth;
   return launch_common(ctx, mode, nullptr, &g, M, tcgen05_conv_k(ci, mode), w_hi, w_lo, kp, out,
-                       ci.outChannels, epi, math_mode);
+                       ci.outChannels, epi, math_mode, false);
 }

@@ -22,6 +22,8 @@
 //    array: serialise them;
 //  - the first call on a device resolves the array's device address (cudaGetSymbolAddress, with
 //    that device current).  Make that first call before any stream capture is started.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace {
@@ -33,12 +35,14 @@ constexpr int64_t kStaticPlaneFloats = 1 << 20;  // 1 Mi floats = 4 MiB per plan
 static __device__ __align__(256) float g_static_planes[2 * kStaticPlaneFloats];
 
 constexpr int kMaxDevices = 64;
-float* g_planes_addr[kMaxDevices] = {nullptr};  // resolved device address, per device ordinal
+// resolved device address, per device ordinal; atomic because contexts of different devices may
+// be driven from different host threads (two threads resolving the same device store the same value)
+std::atomic<float*> g_planes_addr[kMaxDevices];
 
 // Once per device, with that device current.
 int resolve_planes(tfjs_cuda_ctx* ctx, float** out) {
   TFJS_REQUIRE(ctx, ctx->device >= 0 && ctx->device < kMaxDevices, "device ordinal out of range");
-  if (!g_planes_addr[ctx->device]) {
+  if (!g_planes_addr[ctx->device].load(std::memory_order_acquire)) {
     TFJS_CHECK_CUDA(ctx, cudaSetDevice(ctx->device));
     float* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&p, g_static_planes);
@@ -47,9 +51,9 @@ int resolve_planes(tfjs_cuda_ctx* ctx, float** out) {
       return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cudaGetSymbolAddress(static scratch) failed: %s",
                        cudaGetErrorString(e));
     }
-    g_planes_addr[ctx->device] = p;
+    g_planes_addr[ctx->device].store(p, std::memory_order_release);
   }
-  *out = g_planes_addr[ctx->device];
+  *out = g_planes_addr[ctx->device].load(std::memory_order_acquire);
   return TFJS_CUDA_OK;
 }
 
@@ -66,7 +70,8 @@ extern "C" int tfjs_cuda_matmul_static_scratch(tfjs_cuda_ctx* ctx, const float* 
                "activation must be linear, relu or clip");
   if (m * n == 0) return TFJS_CUDA_OK;
   TFJS_REQUIRE(ctx, a && b && out, "a, b and out must be device pointers");
-  TFJS_REQUIRE(ctx, !ctx->capturing || g_planes_addr[ctx->device & (kMaxDevices - 1)],
+  TFJS_REQUIRE(ctx, ctx->device >= 0 && ctx->device < kMaxDevices, "device ordinal out of range");
+  TFJS_REQUIRE(ctx, !ctx->capturing || g_planes_addr[ctx->device].load(std::memory_order_acquire),
                "make the first call on a device before starting a stream capture");
   const int64_t kp = (k + 3) / 4 * 4;
   if (n * kp > kStaticPlaneFloats)

@@ -26,6 +26,8 @@
 //               the image).
 // The arithmetic is that of the two separate kernels, operation for operation, so the results are
 // bit-identical to running them back to back.  Every mbarrier wait is bounded.
+#include <atomic>
+
 #include "tcgen05_ptx.cuh"
 
 namespace {
@@ -237,11 +239,13 @@ __device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t 
       uint32_t ox, oy, oz, ow;
       unpack_f32x2(acc[o][j][0], ox, oy);
       unpack_f32x2(acc[o][j][1], oz, ow);
+      // rounded to the nearest tf32 value: the tensor core reads the upper 19 bits only, and
+      // truncating these (non-negative, after relu6) values would bias every sum downwards
       float4 v;
-      v.x = dw_activate<ACT>(__uint_as_float(ox), p.dw_lo, p.dw_hi);
-      v.y = dw_activate<ACT>(__uint_as_float(oy), p.dw_lo, p.dw_hi);
-      v.z = dw_activate<ACT>(__uint_as_float(oz), p.dw_lo, p.dw_hi);
-      v.w = dw_activate<ACT>(__uint_as_float(ow), p.dw_lo, p.dw_hi);
+      v.x = round_tf32_for_mma(dw_activate<ACT>(__uint_as_float(ox), p.dw_lo, p.dw_hi));
+      v.y = round_tf32_for_mma(dw_activate<ACT>(__uint_as_float(oy), p.dw_lo, p.dw_hi));
+      v.z = round_tf32_for_mma(dw_activate<ACT>(__uint_as_float(oz), p.dw_lo, p.dw_hi));
+      v.w = round_tf32_for_mma(dw_activate<ACT>(__uint_as_float(ow), p.dw_lo, p.dw_hi));
       sts128(a_tile + swz(m0 + j, q * 16), v);
     }
   }
@@ -259,7 +263,7 @@ __device__ __forceinline__ void rgb_part(uint32_t raw, uint32_t a_tile, int t, c
   for (int dr = 0; dr < 3; dr++) {
     const uint32_t row = raw + (uint32_t)(((r * S + dr) * R::ROW_FLOATS + p.rgb_off + c * S * 3) * 4);
 #pragma unroll
-    for (int j = 0; j < 9; j++) v[dr][j] = lds32(row + j * 4);
+    for (int j = 0; j < 9; j++) v[dr][j] = round_tf32_for_mma(lds32(row + j * 4));  // the tensor core would truncate
   }
   sts128(a_tile + swz(t, 0), make_float4(v[0][0], v[0][1], v[0][2], v[0][3]));
   sts128(a_tile + swz(t, 16), make_float4(v[0][4], v[0][5], v[0][6], v[0][7]));
@@ -282,7 +286,10 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   constexpr int RAW_STAGES = raw_stages<S, MODE>(BLOCK_N);
   static_assert(RAW_STAGES >= 2 && RAW_STAGES % GROUPS == 0 && A_SLOTS % GROUPS == 0, "rings split evenly");
   constexpr bool IN_PLACE = a_in_place(BLOCK_N, S, MODE);
-  constexpr int NUM_A = IN_PLACE ? RAW_STAGES : A_SLOTS;  // A tiles (and their full barriers)
+  // MODE_CONV: the stage the TMA load filled IS the A tile; the helper warps only round it to tf32
+  // in place before the tensor core reads it
+  constexpr bool STAGE_IS_A = IN_PLACE || MODE == MODE_CONV;
+  constexpr int NUM_A = STAGE_IS_A ? RAW_STAGES : A_SLOTS;  // A tiles (and their full barriers)
   static_assert(!IN_PLACE || (R::BYTES >= A_TILE_BYTES && R::STRIDE % 1024 == 0), "the tile fits its window's stage");
   static_assert(GROUPS == 1 || R::PARTS == 1, "two groups take whole k-blocks of one raw stage each");
   // Where k-block n of this CTA (counted over all its tiles) lives: with two groups, group n % 2
@@ -493,11 +500,11 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
             ring_pos(n, A_SLOTS, slot, sphase);
           }
           ok = mbar_wait(smem_u32(&w_full[ws]), wphase, abort_flag, p.status, 14);
-          if (ok && MODE == MODE_CONV) ok = mbar_wait(smem_u32(&raw_full[rs]), rphase, abort_flag, p.status, 15);
+          if (ok && MODE == MODE_CONV) ok = mbar_wait(smem_u32(&a_full[rs]), rphase, abort_flag, p.status, 15);
           if (ok && MODE != MODE_CONV) ok = mbar_wait(smem_u32(&a_full[slot]), sphase, abort_flag, p.status, 15);
           if (!ok) break;
           tcgen05_fence_after();
-          const uint32_t a_s = (MODE == MODE_CONV || IN_PLACE) ? smem_u32(raw + rs * R::STRIDE)
+          const uint32_t a_s = STAGE_IS_A ? smem_u32(raw + rs * R::STRIDE)
                                                                : smem_u32(a_tiles + slot * A_TILE_BYTES);
           const uint32_t w_s = smem_u32(w_tiles + ws * W_STAGE_BYTES);
 #pragma unroll
@@ -505,7 +512,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
             tcgen05_mma_tf32(tmem_d, make_smem_desc(a_s + k * 32), make_smem_desc(w_s + k * 32), idesc,
                              (kb > 0 || k > 0) ? 1u : 0u);
           tcgen05_commit(smem_u32(&w_empty[ws]));
-          if (MODE == MODE_CONV || IN_PLACE)
+          if (STAGE_IS_A)
             tcgen05_commit(smem_u32(&raw_empty[rs]));
           else
             tcgen05_commit(smem_u32(&a_empty[slot]));
@@ -515,7 +522,33 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
       }
     }
   } else if (warp >= 10 && MODE == MODE_CONV) {
-    // nothing to do: the operands go from TMA to the tensor core
+    // ---------------- rounding warps ----------------
+    // The A tile arrives from TMA in the layout the tensor core reads, as raw float32.  The tensor
+    // core would truncate it to tf32; these 256 threads round it to nearest in place (element-wise,
+    // so the swizzled placement is untouched) and hand the stage on.
+    const int t = threadIdx.x - 320;
+    int n = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      for (int kb = 0; kb < p.num_k_blocks && ok; kb++, n++) {
+        int rs;
+        uint32_t rphase;
+        ring_pos(n, RAW_STAGES, rs, rphase);
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&raw_full[rs]), rphase, abort_flag, p.status, 17));
+        if (!ok) break;
+        float4* tile4 = reinterpret_cast<float4*>(raw + rs * R::STRIDE);
+#pragma unroll
+        for (int i = 0; i < A_TILE_BYTES / 16 / DW_THREADS; i++) {
+          float4 v = tile4[t + i * DW_THREADS];
+          v.x = round_tf32_for_mma(v.x); v.y = round_tf32_for_mma(v.y);
+          v.z = round_tf32_for_mma(v.z); v.w = round_tf32_for_mma(v.w);
+          tile4[t + i * DW_THREADS] = v;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&a_full[rs]));
+      }
+    }
   } else if (warp >= 10) {
     // ---------------- depthwise warps ----------------
     // With two groups, each takes every other k-block (counted over all the tiles of this CTA), so
@@ -677,10 +710,12 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap&
                              DW_TABLE_BYTES + BIAS_STAGING_BYTES + BARRIER_BYTES;
   static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
   auto kernel = sepconv_tcgen05_kernel<BLOCK_N, S, MODE>;
-  static bool configured[8] = {false};
-  if (!configured[ctx->device & 7]) {
+  // per device and per kernel; atomic because contexts of several devices may call from several
+  // host threads (setting the attribute twice is harmless)
+  static std::atomic<bool> configured[64];
+  if (!configured[ctx->device & 63].load(std::memory_order_acquire)) {
     TFJS_CHECK_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-    configured[ctx->device & 7] = true;
+    configured[ctx->device & 63].store(true, std::memory_order_release);
   }
   const int grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
   launch_ex(ctx, kernel, dim3(grid), dim3(THREADS), smem_bytes, mx, mw, my, p);
@@ -704,6 +739,8 @@ int launch_stride(tfjs_cuda_ctx* ctx, int block_n, const CUtensorMap& mx, const 
 }
 
 }  // namespace
+
+int set_wait_limit_sepconv(long long cycles) { return set_wait_limit_here(cycles); }
 
 // Depthwise 3x3 (stride 1 or 2, dilation 1, channel multiplier 1, C a multiple of 32 up to 256)
 // feeding a pointwise convolution with 8..256 output channels, in TF32.

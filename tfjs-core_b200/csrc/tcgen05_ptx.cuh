@@ -8,7 +8,15 @@
 
 namespace {
 
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // ~2 s at 1.9 GHz
+// Upper bound of every mbarrier wait, in SM clock cycles (~2 s at 1.9 GHz by default).  The
+// context option "wait_limit_us" rewrites it; each translation unit that includes this header has
+// its own copy, set through set_wait_limit_here().
+__constant__ long long g_wait_limit_cycles = 4000000000LL;
+#define WAIT_LIMIT_CYCLES g_wait_limit_cycles
+
+inline int set_wait_limit_here(long long cycles) {
+  return cudaMemcpyToSymbol(g_wait_limit_cycles, &cycles, sizeof(cycles)) == cudaSuccess ? 0 : -1;
+}
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -156,12 +164,6 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
 // [24,29).
 __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ float round_tf32(float v) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
-  return __uint_as_float(r);
 }
 
 // Bias and activation of one 32x32 output chunk in registers: thread `lane` owns row `lane`,

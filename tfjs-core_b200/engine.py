@@ -5,7 +5,8 @@ KernelBackend; it cannot run here (no JavaScript toolchain), so this module repl
 calling sequence against the same backend interface: backend registry with priorities and
 fallback on failed initialisation (engine.ts:220-359), tensor registry with per-dataId
 reference counts (engine.ts:502-572), tidy scopes (engine.ts:365-399, 675-718) and the
-runKernel dispatcher (engine.ts:435-498).  No autograd: the path is inference.
+runKernel dispatcher (engine.ts:435-498), the gradient tape (engine.ts:660-669, 726-774;
+tape.ts) including nested tapes for higher-order gradients.
 """
 import warnings
 
@@ -45,9 +46,11 @@ class Tensor:
     _next_id = 0
 
     def clone(self):
-        """A second Tensor over the same storage (engine.ts clone: shares the dataId)."""
+        """A second Tensor over the same storage (shares the dataId).  While a tape records, the
+        clone is a node of it (identity, gradient dy), so that gradients flow through clones."""
         self._throw_if_disposed()
-        return Tensor(self.shape, self.dtype, None, self.dataId)
+        return ENGINE.runKernel(lambda backend: Tensor(self.shape, self.dtype, None, self.dataId), "clone",
+                                {"x": self}, lambda dy, saved: {"x": lambda: dy.clone()})
 
     @staticmethod
     def make(shape, data=None, dtype="float32", backend=None):
@@ -251,13 +254,17 @@ class Engine:
         with respect to each input.  While a tape records (engine.gradients), a node with the
         inputs, the output and the gradient function is appended to it; `save(tensors)` keeps
         clones of the tensors the gradient needs, so the caller may dispose its own handles."""
+        # engine.ts:427-429 isTapeOn: only kernels called directly from user code are recorded,
+        # not the kernels a kernel calls, and only while some gradients() scope is open
+        tape_on = self.gradientDepth > 0 and self.kernelDepth == 0
         self.kernelDepth += 1
         saved = []
 
         def save(tensors):
-            if self.activeTape is not None and self.kernelDepth == 1:
+            # not saved unless recording: nothing would ever dispose the kept clones
+            if tape_on:
                 for t in tensors:
-                    saved.append(self.keep(t.clone()))
+                    saved.append(self.keep(self._clone_on_tape(t)))
         try:
             if name:
                 self.kernelNames.append(name)
@@ -268,12 +275,22 @@ class Engine:
             result = forward(self.backend, save) if takes_save else forward(self.backend)
         finally:
             self.kernelDepth -= 1
-        if self.activeTape is not None and self.kernelDepth == 0 and inputs and backward is not None:
+        if tape_on and inputs and backward is not None:
             self.nextTapeNodeId += 1
             self.activeTape.append({"id": self.nextTapeNodeId, "name": name, "inputs": dict(inputs),
                                     "outputs": [result], "saved": saved,
                                     "gradient": (lambda dy, _s=saved: backward(dy, _s))})
         return result
+
+    def _clone_on_tape(self, x):
+        """engine.ts:401-409 clone(): an alias of x recorded on the tape as an identity node.  The
+        saved tensors of a kernel are such clones; the node keeps them connected to x, which is
+        what lets an outer gradients() differentiate through an inner backward pass."""
+        y = Tensor(x.shape, x.dtype, None, x.dataId)
+        self.nextTapeNodeId += 1
+        self.activeTape.append({"id": self.nextTapeNodeId, "name": "clone", "inputs": {"x": x}, "outputs": [y],
+                                "saved": [], "gradient": (lambda dy: {"x": lambda: dy.clone()})})
+        return y
 
     def keep(self, t):
         """tf.keep (engine.ts:720-731): the tensor survives the enclosing tidy scopes."""
@@ -288,26 +305,34 @@ class Engine:
         assert xs, "gradients() received an empty list of xs."
         if dy is not None and dy.dtype != "float32":
             raise ValueError(f"dy must have 'float32' dtype, but has '{dy.dtype}'")
-        outer_tape = self.activeTape
-        self.activeTape = []
+        # engine.ts:660-669 startTape / endTape: a fresh tape only for the outermost gradients();
+        # a nested call records onto the same tape, so that the outer call can differentiate
+        # through the inner call's backward pass (higher-order gradients)
+        if self.gradientDepth == 0:
+            self.activeTape = []
         self.gradientDepth += 1
         try:
-            y = f()
-            if not isinstance(y, Tensor):
-                raise ValueError("The result y returned by f() must be a tensor.")
-            tape = self.activeTape
+            y = self.tidy(f)   # engine.ts:737: the forward pass runs in its own scope
         finally:
             self.gradientDepth -= 1
-            self.activeTape = outer_tape
+        if not isinstance(y, Tensor):
+            if self.gradientDepth == 0:
+                self._dispose_tape(self.activeTape)
+                self.activeTape = None
+            raise ValueError("The result y returned by f() must be a tensor.")
+        tape = self.activeTape
         filtered = get_filtered_nodes_x_to_y(tape, xs, y)
         if not filtered and xs:
-            self._dispose_tape(tape)
+            if self.gradientDepth == 0:
+                self._dispose_tape(tape)
+                self.activeTape = None
             raise ValueError("Cannot compute gradient of y=f(x) with respect to x. Make sure that the f "
                              "you passed encloses all operations that lead from x to y.")
         # Back-propagation runs in its own scope: every temporary it creates (clones, masks,
         # partial sums, the gradients of intermediates) is disposed when the scope ends, only the
-        # gradients of xs survive (engine.ts:764-779 wraps this in tidy).
-        self.startScope("backprop")
+        # gradients of xs survive (engine.ts:751-773 wraps this in tidy).  With an outer
+        # gradients() still open (gradientDepth > 0) these kernels are recorded too.
+        self.startScope("backward")
         grads = None
         try:
             acc = {y.id: dy if dy is not None else ops.tensor(np.ones(y.shape, np.float32), y.shape)}
@@ -322,7 +347,10 @@ class Engine:
                 grads.append(g)
         finally:
             self.endScope(grads)
-            self._dispose_tape(tape)
+            if self.gradientDepth == 0:
+                # not computing higher-order gradients: the tape can go (engine.ts:762-771)
+                self._dispose_tape(tape)
+                self.activeTape = None
         return y, grads
 
     @staticmethod

@@ -663,8 +663,11 @@ def grad(f):
     """tf.grad(f)(x, dy?) -> df/dx."""
     def g(x, dy=None):
         x = _convert(x, "x", "tf.grad")
-        _, grads = ENGINE.gradients(lambda: f(x), [x], dy)
-        return grads[0]
+
+        def run():   # gradients.ts:68-80: tidy, so that the value of f and its temporaries go
+            _, grads = ENGINE.gradients(lambda: f(x), [x], dy)
+            return grads[0]
+        return ENGINE.tidy(run)
     return g
 
 
@@ -672,8 +675,11 @@ def grads(f):
     """tf.grads(f)([x1, x2, ...], dy?) -> [df/dx1, ...]."""
     def g(xs, dy=None):
         xs = [_convert(x, "args", "tf.grads") for x in xs]
-        _, out = ENGINE.gradients(lambda: f(*xs), xs, dy)
-        return out
+
+        def run():   # gradients.ts:117-127
+            _, out = ENGINE.gradients(lambda: f(*xs), xs, dy)
+            return out
+        return ENGINE.tidy(run)
     return g
 
 
