@@ -7,14 +7,19 @@
 One process per GPU (torchrun sets RANK / LOCAL_RANK / WORLD_SIZE for N > 1).  The workload is
 BASELINE config 5: MobileNetV1-1.0-224 with every filter stored as uint8 affine-quantised
 bytes, one global batch of 1024 synthetic images sharded by batch over the N GPUs (strong
-scaling, no collective on the data path; torch.distributed is used only for the barrier and
+scaling, no collective on the data path; torch.distributed over gloo serves only the barrier and
 the max-over-ranks of the timings).  `--workload cfg4` runs config 4 instead (float32 weights,
 batch 64 per GPU).
 
-A step is one forward pass over the rank's shard: 26 kernel launches (30 with --forward
-layerwise) replayed from a CUDA graph.  `value` is images/s with the images resident in device memory; `e2e` repeats the
-measurement through the public API with the shard in pinned host memory, copying it to the
-device and reading the probabilities back inside every timed step.
+A step is one forward pass over the rank's shard: 25 kernel launches (30 with --forward
+layerwise, 77 with --forward reference-api) replayed from a CUDA graph.  Before anything is timed
+the same code path is checked against the CPU oracle on a few images (`parity_check`).  `value`
+is images/s with the images resident in device memory; `e2e` repeats the measurement through the
+public API with the shard in pinned host memory, copying it to the device and reading the
+probabilities back inside every timed step, and states the host-to-device copy rate of the same
+buffers without any kernel as its ceiling.  With N > 1 rank 0 afterwards also times the library's
+own in-process runner (one context and one host thread per device, host-side gather) over the
+same global batch (`e2e_in_process`).
 """
 import argparse
 import json
@@ -45,10 +50,14 @@ def parse_args():
     ap.add_argument("--dequant", default="cached", choices=["cached", "in-loop"],
                     help="uint8 weights of the GEMM layers: expanded once into cached tf32 planes, or "
                          "kept uint8 and dequantised in shared memory inside the GEMM main loop")
-    ap.add_argument("--forward", default="separable", choices=["separable", "layerwise"],
+    ap.add_argument("--forward", default="separable", choices=["separable", "layerwise", "reference-api"],
                     help="separable: each depthwise + pointwise pair is one fusedSeparableConv2d call (the "
                          "first five pairs then run as single kernels that keep the depthwise result on "
-                         "chip); layerwise: one kernel per layer (30 launches)")
+                         "chip); layerwise: one kernel per layer (30 launches); reference-api: the network "
+                         "as unmodified tf.* code expresses it (77 backend calls: conv -> add -> clipByValue, "
+                         "the 8-kernel softmax chain)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the extra measurements (in-loop dequantisation, in-process sharded runner)")
     ap.add_argument("--global-batch", type=int, default=0, help="override the workload's batch")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a graph")
     ap.add_argument("--pdl", action="store_true", help="programmatic dependent launch instead of plain stream order")
@@ -62,8 +71,10 @@ def workload_config(args, world):
     if args.workload == "cfg5":
         gb = args.global_batch or 1024
         assert gb % world == 0, "the global batch must divide evenly over the GPUs"
-        return dict(name="cfg5: MobileNetV1-1.0-224, uint8 affine-quantised filters dequantised on "
-                         "device, global batch %d sharded by batch" % gb,
+        how = ("inside the GEMM main loop" if args.dequant == "in-loop"
+               else "once on device into cached tf32 planes")
+        return dict(name="cfg5: MobileNetV1-1.0-224, uint8 affine-quantised filters dequantised %s, "
+                         "global batch %d sharded by batch" % (how, gb),
                     global_batch=gb, per_gpu=gb // world, quantized=True, seed=4, gain=1.0,
                     scaling="strong")
     per = args.global_batch or 64
@@ -273,14 +284,69 @@ KERNEL_FAMILY = {"separableConv2d (fused dw3x3 s1 + pw, TF32)": "separable_fused
                  "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32)": "conv2d_tcgen05",
                  "conv2d_tcgen05 (shifted-patch TMA, TF32)": "conv2d_tcgen05",
                  "depthwiseConv2D (3x3 strip)": "depthwise3x3", "depthwiseConv2D (3x3 image window, TMA)": "depthwise3x3",
-                 "conv2d (stem)": "conv2d_stem",
+                 "conv2d (stem)": "conv2d_stem", "binary (vectorised)": "binary", "binary (general)": "binary",
+                 "unary": "unary", "reduce_last": "reduce_last", "pool2d": "pool2d", "pool2d (128-bit)": "pool2d",
                  "avgPool (global)": "global_avgpool", "softmax_last": "softmax"}
+
+
+def load_measured_traffic():
+    """DRAM bytes per image and launch of each kernel family, from the table of ncu captures in
+    profiles/dram_traffic_per_launch.md (rows `| family | MB per image per launch | batch | ... |`)."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic_per_launch.md")
+    table = {}
+    if os.path.exists(path):
+        for line in open(path):
+            cells = [c.strip() for c in line.strip().strip("|").split("|")]
+            if len(cells) >= 3 and cells[0] in set(KERNEL_FAMILY.values()):
+                try:
+                    table[cells[0]] = (float(cells[1]), int(cells[2]))
+                except ValueError:
+                    continue
+    return table
+
+
+def pick_forward(net, args):
+    return {"separable": net.forward_separable, "layerwise": net.forward_fused,
+            "reference-api": net.forward_reference_api}[args.forward]
+
+
+def parity_check(bk, args, images=4):
+    """The timed code path (same forward, math mode and uint8 weight handling) on a network whose
+    logits mean something -- Glorot weights, stored uint8 when the workload is quantised -- against
+    the CPU oracle, before anything is timed.  BASELINE config 5's own weights make a chaotic
+    network (the oracle itself is 1e-2 away from exact arithmetic on it), so they cannot serve."""
+    import oracle
+    from oracle import mobilenet as oracle_net
+    from tfjs_core_b200 import mobilenet, ops
+    oracle.build()
+    params = mobilenet.make_weights(3, gain=1.5)
+    if args.workload == "cfg5":
+        params = mobilenet.quantize_params(params)
+    x = mobilenet.make_input(3, images)
+    net = mobilenet.MobileNetV1(params, bk)
+    try:
+        logits, probs = pick_forward(net, args)(ops.tensor(x))
+        got = logits.dataSync().reshape(images, -1)
+        logits.dispose()
+        probs.dispose()
+    finally:
+        net.dispose()
+    want = np.concatenate([oracle_net.forward(x[i:i + 1], params)[0] for i in range(images)], 0)
+    err = float(np.abs(got - want).max() / np.abs(want).max())
+    tol = 1e-3 if args.math == "tf32" else 1e-4
+    same = bool((got.argmax(1) == want.argmax(1)).all())
+    assert err <= tol, f"parity check failed: logits differ from the oracle by {err:.2e} (> {tol})"
+    assert same, "parity check failed: argmax differs from the oracle"
+    return {"images": images,
+            "weights": "Glorot (gain 1.5), stored %s" % ("uint8" if args.workload == "cfg5" else "float32"),
+            "against": "CPU oracle (restated MathBackendCPU)", "max_rel_err_logits": err, "tolerance": tol,
+            "argmax_identical": same}
 
 
 def run_cuda(args):
     from tfjs_core_b200 import BackendCuda, ENGINE, mobilenet, ops
 
-    d = Dist("nccl")
+    d = Dist("gloo")
     cfg = workload_config(args, d.world)
     per = cfg["per_gpu"]
     bk = BackendCuda(d.local_rank, args.math)
@@ -289,10 +355,12 @@ def run_cuda(args):
     bk.setOption("dequant_in_gemm", 1 if args.dequant == "in-loop" else 0)
     bk.setOption("pdl", 1 if args.pdl else 0)
 
+    parity = parity_check(bk, args) if d.rank == 0 else None
+
     params = mobilenet.make_weights(cfg["seed"], quantized=cfg["quantized"], gain=cfg["gain"])
     net = mobilenet.MobileNetV1(params, bk)
-    forward = net.forward_separable if args.forward == "separable" else net.forward_fused
-    x_host = mobilenet.make_input(cfg["seed"], per, offset=0 if d.world == 1 else 0)
+    forward = pick_forward(net, args)
+    x_host = mobilenet.make_input(cfg["seed"], per)
     # every rank draws its own slice of the global batch: different seeds per rank keep the
     # generation cheap (skipping d.rank * per images of one stream would cost minutes)
     if d.world > 1:
@@ -363,8 +431,11 @@ def run_cuda(args):
         lg.dispose()
         pr.dispose()
     rows = bk.profileEnd()
-    layer_bytes = mobilenet.launch_algorithmic_bytes(per, cfg["quantized"],
-                                                     [name for name, _ in rows[:launches_per_step]])
+    names = [name for name, _ in rows[:launches_per_step]]
+    if args.forward == "reference-api":
+        layer_bytes = mobilenet.reference_api_launch_bytes(per, cfg["quantized"], names)
+    else:
+        layer_bytes = mobilenet.launch_algorithmic_bytes(per, cfg["quantized"], names)
     fam = {}
     for i, (name, ms) in enumerate(rows):
         f = KERNEL_FAMILY.get(name, name)
@@ -381,16 +452,22 @@ def run_cuda(args):
     hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
     peak_kind = "measured" if peaks else "fallback"
     achieved = fam[top]["bytes"] / (fam[top]["ms"] * 1e-3) / 1e9
+    measured_traffic = load_measured_traffic()
+    traffic, traffic_from = None, None
+    if top in measured_traffic:
+        mb, at_batch = measured_traffic[top]
+        traffic = mb * 1e6 * per
+        traffic_from = f"ncu capture at batch {at_batch}, scaled to batch {per} (traffic grows with the batch)"
     roofline = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                 "frac": achieved / hbm_peak, "peak_source": peak_kind,
                 "launches_per_step": fam[top]["launches"] // prof_steps,
                 "avg_launch_ms": fam[top]["ms"] / fam[top]["launches"],
                 "share_of_step": fam[top]["ms"] / total_ms,
-                "traffic": (TRAFFIC_MB_PER_IMAGE_AND_LAUNCH[top] * 1e6 * per
-                            if top in TRAFFIC_MB_PER_IMAGE_AND_LAUNCH else None)}
+                "traffic": traffic, "traffic_source": traffic_from}
     kernels = {k: {"ms_per_step": v["ms"] / prof_steps, "share": v["ms"] / total_ms,
                    "launches_per_step": v["launches"] // prof_steps,
-                   "achieved_gbs": v["bytes"] / (v["ms"] * 1e-3) / 1e9} for k, v in fam.items()}
+                   "achieved_gbs": v["bytes"] / (v["ms"] * 1e-3) / 1e9,
+                   "frac_of_hbm_peak": v["bytes"] / (v["ms"] * 1e-3) / 1e9 / hbm_peak} for k, v in fam.items()}
     step_bytes = sum(layer_bytes)
     net_gbs = step_bytes / (ms_per_step * 1e-3) / 1e9
 
@@ -414,13 +491,15 @@ def run_cuda(args):
         graphs.append(bk.graphEnd())
         outs.append(pr2)
 
-    def e2e_run(n):
+    def e2e_run(n, kernels_too=True):
         res = None
         bk.writeAsync(xs[0].dataId, pinned, nbytes)
         for i in range(n):
             cur = i % 2
             if i + 1 < n:
                 bk.writeAsync(xs[1 - cur].dataId, pinned, nbytes)
+            if not kernels_too:
+                continue
             if graph is not None:
                 bk.graphLaunch(graphs[cur], inputs=[xs[cur]])
                 res = outs[cur].dataSync()
@@ -441,9 +520,55 @@ def run_cuda(args):
     d.barrier()
     assert np.isfinite(res).all() and np.allclose(res, first, rtol=0, atol=1e-6)
     e2e_value = cfg["global_batch"] * args.steps / e2e_s
+    # the ceiling of that number: the same uploads from the same pinned buffer with no kernel and
+    # no read in between (all ranks at once, as in the run above: GPUs share host uplinks)
+
+    def wait_uploads():
+        for t_in in xs:
+            lib.tfjs_cuda_tensor_wait(bk._ctx, bk._rec(t_in.dataId)["id"])
+        bk.sync()
+
+    e2e_run(2, kernels_too=False)
+    wait_uploads()
+    d.barrier()
+    t0 = time.perf_counter()
+    e2e_run(args.steps, kernels_too=False)
+    wait_uploads()
+    copy_s = d.max(time.perf_counter() - t0)
+    d.barrier()
+    h2d_gbs_per_gpu = nbytes * args.steps / copy_s / 1e9
+    h2d_ceiling_value = cfg["global_batch"] * args.steps / copy_s
     lib.tfjs_cuda_host_free(pinned)
     if len(graphs) > 1:
         bk.graphDestroy(graphs[1])
+
+    # ---- extra: the same step with the uint8 weights dequantised inside the GEMM main loop ----
+    extras = {}
+    if cfg["quantized"] and args.dequant == "cached" and graph is not None and not args.no_extras:
+        bk.setOption("dequant_in_gemm", 1)
+        lg, pr = forward(x)          # prepares the K-major uint8 layouts
+        lg.dispose()
+        pr.dispose()
+        bk.graphBegin()
+        lg_q, pr_q = forward(x)
+        g_q = bk.graphEnd()
+        for _ in range(3):
+            bk.graphLaunch(g_q)
+        bk.sync()
+        d.barrier()
+        n_q = max(3, args.steps // 2)
+        tq = bk.time(lambda: [bk.graphLaunch(g_q) for _ in range(n_q)])
+        ms_q = d.max(tq["kernelMs"]) / n_q
+        same_q = bool(np.array_equal(pr_q.dataSync(), first))
+        bk.graphDestroy(g_q)
+        lg_q.dispose()
+        pr_q.dispose()
+        bk.setOption("dequant_in_gemm", 0)
+        extras["dequant_in_gemm_main_loop"] = {
+            "value": cfg["global_batch"] / (ms_q * 1e-3), "unit": UNIT, "ms_per_step": ms_q,
+            "bit_identical_to_cached_planes": same_q,
+            "note": "uint8 filters of the GEMM layers stay uint8 in device memory and are dequantised in "
+                    "shared memory inside the main loop"}
 
     # ---- CPU baseline beside it (rank 0, N = 1 only) ----
     cpu_baseline = None
@@ -456,6 +581,12 @@ def run_cuda(args):
                         "sample": f"first {n} images of the batch, {secs:.1f} s, restated MathBackendCPU "
                                   "(C, unfused passes), 1 thread as the JavaScript original is single-threaded"}
 
+    # ---- extra: the library's in-process runner over all N devices (rank 0, the other ranks idle) ----
+    d.barrier()
+    if d.rank == 0 and d.world > 1 and not args.no_extras and not args.no_graph:
+        extras["e2e_in_process"] = in_process_e2e(args, cfg, params, d.world)
+    d.barrier()
+
     if d.rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": d.world, "steps": args.steps,
@@ -464,13 +595,20 @@ def run_cuda(args):
             "data": "synthetic",
             "config": {"workload": cfg["name"], "global_batch": cfg["global_batch"], "per_gpu_batch": per,
                        "math_mode": args.math, "dequant": args.dequant, "forward": args.forward,
-                       "launches_per_step": int(launches_per_step), "launch": "eager" if graph is None else "cuda-graph replay",
+                       "launches_per_step": int(launches_per_step),
+                       "launch": "eager" if graph is None else "cuda-graph replay",
                        "l2": "every step streams %.1f GB of activations per GPU (> 126 MB L2) between reuses"
                              % (step_bytes / 1e9)},
+            "parity_check": parity,
             "roofline": roofline, "net_hbm": {"algorithmic_gb_per_step": step_bytes / 1e9,
                                               "achieved_gbs": net_gbs, "frac": net_gbs / hbm_peak},
             "kernels": kernels, "cpu_baseline": cpu_baseline,
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": out_bytes},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": out_bytes,
+                    "h2d_ceiling_gbs_per_gpu": h2d_gbs_per_gpu, "h2d_ceiling_value": h2d_ceiling_value,
+                    "frac_of_h2d_ceiling": e2e_value / h2d_ceiling_value,
+                    "note": "float32 images, 602 KB each; the ceiling is the measured rate of the same uploads "
+                            "with no kernel in between"},
+            "extras": extras,
             "gpu_launches": int(gpu_launches), "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
@@ -479,13 +617,32 @@ def run_cuda(args):
     d.close()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel family, averaged over
-# the family's launches of one forward pass, from the batch-256 (fused blocks: batch-128) ncu
-# captures summarised under profiles/; it grows in proportion to the batch.
-TRAFFIC_MB_PER_IMAGE_AND_LAUNCH = {"separable_fused": 1934.3 / 5 / 128,
-                                   "gemm_tcgen05": 4062.4 / 14 / 256,
-                                   "depthwise3x3": 4638.7 / 13 / 256,
-                                   "conv2d_tcgen05": 502.7 / 256}
+def in_process_e2e(args, cfg, params, n_devices):
+    """End to end through the library's own multi-device entry point: one process, one context and
+    one host thread per device, uploads from one pinned buffer, host-side gather of the
+    [batch, 1000] probabilities into one pinned buffer."""
+    from tfjs_core_b200 import ShardedRunner, mobilenet
+    batch = cfg["global_batch"]
+    options = {"dequant_in_gemm": 1 if args.dequant == "in-loop" else 0}
+    runner = ShardedRunner(lambda backend: mobilenet.MobileNetV1(params, backend),
+                           lambda net, x: pick_forward(net, args)(x), batch, (224, 224, 3),
+                           devices=list(range(n_devices)), math_mode=args.math, options=options)
+    try:
+        rng = np.random.Generator(np.random.PCG64([cfg["seed"], 777]))
+        for slot in runner.input_slots:
+            slot[...] = rng.random(size=slot.shape, dtype=np.float32) * 2.0 - 1.0
+        runner.run_pipelined(2)
+        seen = []
+        t0 = time.perf_counter()
+        runner.run_pipelined(args.steps, consume=lambda k, res: seen.append(float(res[0].sum())))
+        dt = time.perf_counter() - t0
+        assert len(seen) == args.steps and all(abs(v - 1.0) < 1e-3 for v in seen), "gathered probabilities are off"
+        return {"value": batch * args.steps / dt, "unit": UNIT, "devices": n_devices,
+                "host_threads": n_devices, "h2d_bytes_per_step": int(batch * 224 * 224 * 3 * 4),
+                "d2h_bytes_per_step": int(batch * 1000 * 4),
+                "note": "ShardedRunner.run_pipelined: wall clock of this one process over all devices"}
+    finally:
+        runner.dispose()
 
 
 def main():

@@ -1,20 +1,20 @@
 #!/usr/bin/env python3
 """Per-layer device times of one fused MobileNetV1 forward on the cuda backend.
 
-    python tfjs-core_b200/profile_layers.py [batch] [tf32|3xtf32] [f|q|q-in-loop] [separable|layerwise|separable-all]
+    python profile_layers.py [batch] [tf32|3xtf32] [f|q|q-in-loop] [separable|layerwise|separable-all]
 
 Prints, for each launch of one forward pass (25 with the fused depthwise + pointwise blocks,
 30 with `layerwise`), the kernel name, the best device time over a few passes
 (events recorded between launches on the context's stream), the layer's algorithmic bytes and
 the bandwidth that corresponds to.  `q` stores the filters as uint8 (BASELINE config 5); `q-in-loop` also keeps the GEMM weights uint8 and dequantises them inside the GEMM main loop;
 `separable-all` fuses every block the fused kernel can take (up to 256 channels), not only those
-where fusion pays.  This is
-also the small-case command the ncu captures summarised under profiles/ were taken with.
+where fusion pays.  At a small batch this is also a convenient command to capture single
+kernels of the network with ncu.
 """
 import os
 import sys
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 import tfjs_core_b200 as tf  # noqa: E402
 from tfjs_core_b200 import mobilenet, ops  # noqa: E402

@@ -11,10 +11,10 @@ import bench  # noqa: E402
 
 def main():
     d = bench.Dist("gloo")
-    args = argparse.Namespace(workload="cfg5", global_batch=0)
+    args = argparse.Namespace(workload="cfg5", global_batch=0, dequant="cached")
     cfg = bench.workload_config(args, d.world)
     assert cfg["global_batch"] == 1024 and cfg["per_gpu"] == 1024 // d.world and cfg["scaling"] == "strong"
-    cfg4 = bench.workload_config(argparse.Namespace(workload="cfg4", global_batch=0), d.world)
+    cfg4 = bench.workload_config(argparse.Namespace(workload="cfg4", global_batch=0, dequant="cached"), d.world)
     assert cfg4["per_gpu"] == 64 and cfg4["global_batch"] == 64 * d.world and cfg4["scaling"] == "weak"
     d.barrier()
     # the slowest rank defines the step time

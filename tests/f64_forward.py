@@ -115,21 +115,7 @@ def forward(x, params, chunk=8):
     return logits, softmax(logits)
 
 
-def quantize_affine_u8(w):
-    """Per-tensor uint8 affine quantisation of a float filter, the way a tfjs converter stores
-    it: scale = (max - min) / 255, q = round((w - min) / scale) (io/io_utils.ts:122-146 is the
-    inverse).  Returns (q, scale, min)."""
-    w = np.asarray(w, np.float64)
-    lo, hi = float(w.min()), float(w.max())
-    scale = (hi - lo) / 255.0 if hi > lo else 1.0
-    q = np.clip(np.rint((w - lo) / scale), 0, 255).astype(np.uint8)
-    return q, scale, lo
-
-
 def quantize_params(params):
-    """The uint8-stored form of a float parameter dict (filters only; biases stay float32)."""
-    out = {}
-    for name, p in params.items():
-        q, scale, lo = quantize_affine_u8(p["w"])
-        out[name] = {"w": None, "q": q, "scale": scale, "min": lo, "b": p["b"]}
-    return out
+    """The uint8-stored form of a float parameter dict (the product's own helper)."""
+    from tfjs_core_b200 import mobilenet
+    return mobilenet.quantize_params(params)

@@ -65,3 +65,27 @@ def test_sharded_result_matches_the_oracle(tf):
     assert np.abs(got - want).max() <= 1e-5
     assert (got.argmax(1) == want.argmax(1)).all()
     assert tf.set_backend("cuda")
+
+
+def test_pipelined_stream_equals_batch_by_batch(tf):
+    """run_pipelined: five different batches through two slots per device (upload of the next batch
+    overlapping the kernels of the current one) give, batch for batch, what run() gives."""
+    from tfjs_core_b200 import ShardedRunner, device_count, mobilenet
+    n_dev = device_count()
+    params = mobilenet.make_weights(3, gain=1.5)
+    build, forward = _build_and_forward(params)
+    batch, steps = 4, 5
+    batches = [mobilenet.make_input(20 + k, batch) for k in range(steps)]
+    runner = ShardedRunner(build, forward, batch, batches[0].shape[1:], devices=[k % n_dev for k in range(2)],
+                           math_mode="tf32")
+    try:
+        want = [runner.run(b).copy() for b in batches]
+        got = {}
+        runner.run_pipelined(steps, fill=lambda k, buf: np.copyto(buf, batches[k]),
+                             consume=lambda k, res: got.__setitem__(k, res.copy()))
+        assert sorted(got) == list(range(steps))
+        for k in range(steps):
+            assert np.array_equal(got[k], want[k]), k
+    finally:
+        runner.dispose()
+    assert tf.set_backend("cuda")

@@ -437,6 +437,58 @@ __global__ void pool2d_kernel(const float* __restrict__ x, float* __restrict__ y
   }
 }
 
+// The same pool for C % 4 == 0 and 16-byte aligned tensors: a thread owns 4 channels of one output
+// pixel and reads its window with 128-bit loads; consecutive threads take consecutive channel
+// quads, so a warp reads whole 512-byte runs of the NHWC image per tap.  Windows of neighbouring
+// output pixels overlap (by (f - s) rows and columns); those re-reads are served by L1 / L2 (the
+// loads go through the read-only path), DRAM sees every input line once.  Same arithmetic as
+// above: float64 sum over the in-bounds taps in row-major order for avg, `p > cur` for max.
+template <bool IS_AVG>
+__global__ void __launch_bounds__(256)
+pool2d_vec4_kernel(const float4* __restrict__ x, float4* __restrict__ y, tfjs_conv2d_info ci) {
+  const int C4 = ci.inChannels >> 2;
+  const int64_t total = (int64_t)ci.batchSize * ci.outHeight * ci.outWidth * C4;
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total;
+       t += (int64_t)gridDim.x * blockDim.x) {
+    const int d = (int)(t % C4);
+    int64_t pix = t / C4;
+    const int yc = (int)(pix % ci.outWidth);
+    pix /= ci.outWidth;
+    const int yr = (int)(pix % ci.outHeight);
+    const int b = (int)(pix / ci.outHeight);
+    const int xr_corner = yr * ci.strideHeight - ci.padTop;
+    const int xc_corner = yc * ci.strideWidth - ci.padLeft;
+    const int xr_min = max(0, xr_corner), xr_max = min(ci.inHeight, ci.effectiveFilterHeight + xr_corner);
+    const int xc_min = max(0, xc_corner), xc_max = min(ci.inWidth, ci.effectiveFilterWidth + xc_corner);
+    float4 mm = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+    int count = 0;
+    const float4* img = x + (int64_t)b * ci.inHeight * ci.inWidth * C4 + d;
+    for (int xr = xr_min; xr < xr_max; xr += ci.dilationHeight) {
+      const float4* row = img + (int64_t)xr * ci.inWidth * C4;
+      for (int xc = xc_min; xc < xc_max; xc += ci.dilationWidth) {
+        const float4 p = __ldg(row + (int64_t)xc * C4);
+        if (IS_AVG) {
+          s0 += (double)p.x; s1 += (double)p.y; s2 += (double)p.z; s3 += (double)p.w;
+          count++;
+        } else {
+          if (p.x > mm.x) mm.x = p.x;
+          if (p.y > mm.y) mm.y = p.y;
+          if (p.z > mm.z) mm.z = p.z;
+          if (p.w > mm.w) mm.w = p.w;
+        }
+      }
+    }
+    if (IS_AVG) {
+      const double n = (double)count;
+      mm = make_float4((float)(s0 / n), (float)(s1 / n), (float)(s2 / n), (float)(s3 / n));
+    }
+    y[t] = mm;
+  }
+}
+
 // Global average pool (window = whole image, VALID, stride 1): MobileNet's 7x7x1024 -> 1024.
 // One thread per (image, channel); taps are summed in the reference's order (row-major) in
 // float64, so the result is bit-identical.  Reads are coalesced over channels.
@@ -655,6 +707,14 @@ int launch_pool2d(tfjs_cuda_ctx* ctx, const float* x, float* y, const tfjs_conv2
     global_avgpool_kernel<<<grid_1d(total, 128, ctx->sm_count, 16), 128, 0, ctx->stream>>>(
         x, y, ci.batchSize, ci.inHeight * ci.inWidth, ci.inChannels);
     return post_launch(ctx, "avgPool (global)");
+  }
+  if (ci.inChannels % 4 == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0) {
+    const dim3 grid(grid_1d(total / 4, 256, ctx->sm_count, 8));
+    if (is_avg)
+      launch_ex(ctx, pool2d_vec4_kernel<true>, grid, dim3(256), 0, (const float4*)x, (float4*)y, ci);
+    else
+      launch_ex(ctx, pool2d_vec4_kernel<false>, grid, dim3(256), 0, (const float4*)x, (float4*)y, ci);
+    return post_launch(ctx, "pool2d (128-bit)");
   }
   pool2d_kernel<<<grid_1d(total, 256, ctx->sm_count, 8), 256, 0, ctx->stream>>>(x, y, ci, is_avg);
   return post_launch(ctx, "pool2d");

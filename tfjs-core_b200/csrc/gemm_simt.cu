@@ -17,7 +17,7 @@ gemm_simt_kernel(const float* __restrict__ a, const float* __restrict__ b, float
   __shared__ float as[TK][TM + 1];
   __shared__ float bs[TK][TN + 1];
   const int bz = blockIdx.z;
-  const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+  const int m0 = blockIdx.x * TM, n0 = blockIdx.y * TN;  // M tiles on x: up to 2^31 - 1 of them
   const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
   const float* ab = a + bz * a_batch;
   const float* bb = b + bz * b_batch;
@@ -62,12 +62,6 @@ gemm_simt_kernel(const float* __restrict__ a, const float* __restrict__ b, float
       if (gn < N) ob[(int64_t)gm * N + gn] = apply_epilogue(acc[i][j], gn, epi);
     }
   }
-}
-
-__device__ __forceinline__ float round_tf32(float v) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
-  return __uint_as_float(r);
 }
 
 // ---- weight repacking ------------------------------------------------------------------------
@@ -168,7 +162,9 @@ int launch_gemm_simt(tfjs_cuda_ctx* ctx, const float* a, const float* b, float* 
                      int M, int N, int K, int64_t a_batch, int64_t a_row, int64_t a_col,
                      int64_t b_batch, int64_t b_row, int64_t b_col, const EpilogueArgs& epi) {
   if ((int64_t)batch * M * N == 0) return TFJS_CUDA_OK;
-  dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM, batch);
+  // row tiles on grid.x (a pointwise convolution over a large batch has millions of rows: M / 64
+  // exceeds the 65535 limit of grid.y), column tiles on grid.y
+  dim3 grid((M + TM - 1) / TM, (N + TN - 1) / TN, batch);
   if (grid.y > 65535 || grid.z > 65535)
     return set_error(ctx, TFJS_CUDA_ERR_UNSUPPORTED, "matrix too large for the CUDA-core GEMM");
   gemm_simt_kernel<<<grid, 256, 0, ctx->stream>>>(a, b, out, M, N, K, a_batch, a_row, a_col, b_batch,

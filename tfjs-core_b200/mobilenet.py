@@ -60,6 +60,21 @@ def make_weights(seed, quantized=False, gain=1.0):
     return params
 
 
+def quantize_params(params):
+    """The uint8-stored form of a float parameter dict, the way a tfjs converter stores a trained
+    model: per tensor scale = (max - min) / 255, q = round((w - min) / scale), so that
+    decodeWeights' w = q * scale + min (io/io_utils.ts:122-146) restores the filter to within half
+    a step.  Biases stay float32."""
+    out = {}
+    for name, p in params.items():
+        w = np.asarray(p["w"], np.float64)
+        lo, hi = float(w.min()), float(w.max())
+        scale = (hi - lo) / 255.0 if hi > lo else 1.0
+        q = np.clip(np.rint((w - lo) / scale), 0, 255).astype(np.uint8)
+        out[name] = {"w": None, "q": q, "scale": scale, "min": lo, "b": p["b"]}
+    return out
+
+
 def write_manifest(params, directory, shard_bytes=1 << 20):
     """Saves `params` (the dict make_weights returns) as a tfjs weights manifest: one group,
     entries `<layer>/filter` (uint8-quantised with the layer's scale / min when the layer has
@@ -265,6 +280,41 @@ def launch_algorithmic_bytes(batch, quantized, kernel_names):
             out.append(per_layer[i])
             i += 1
     assert i == len(per_layer), "kernel list does not cover the network"
+    return out
+
+
+def reference_api_launch_bytes(batch, quantized, kernel_names):
+    """Algorithmic bytes of each launch of forward_reference_api (the network as unmodified tf.*
+    code runs it), in launch order: every contraction / depthwise / pooling launch counts its
+    layer once; every element-wise pass (the bias `add`, `clipByValue`, the stages of the softmax
+    chain) reads and writes the activation it touches, which is what the unfused form costs."""
+    per_layer = layer_algorithmic_bytes(batch, quantized)
+    specs = layer_specs()
+    sizes = []
+    h = w = 224
+    c = 3
+    for name, kind, shape, s in specs[:-1]:
+        ho, wo = -(-h // s), -(-w // s)
+        co = c if kind == "dw" else shape[3]
+        sizes.append(ho * wo * co)
+        h, w, c = ho, wo, co
+    sizes += [c, NUM_CLASSES]                      # global average pool, classifier
+    out, layer, cur = [], 0, 0
+    tail = None
+    for name in kernel_names:
+        heavy = name.startswith(("conv2d", "gemm_tcgen05", "depthwiseConv2D", "batchMatMul", "avgPool", "pool2d"))
+        if heavy and layer < len(sizes):
+            out.append(per_layer[layer])
+            cur = sizes[layer]
+            layer += 1
+            if layer == len(sizes):
+                n = NUM_CLASSES                     # the 8 stages of tf.softmax (ops/softmax.ts:57-63)
+                tail = [n + 1, 2 * n + 1, 2 * n, n + 1, 2, 3, 2 * n + 1, 2 * n]
+        elif tail:
+            out.append(4 * batch * tail.pop(0))
+        else:
+            out.append(8 * batch * cur)            # add(bias) or clipByValue: one read, one write
+    assert layer == len(sizes) and not tail, "kernel list does not cover the network"
     return out
 
 

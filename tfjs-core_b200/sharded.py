@@ -11,7 +11,8 @@ Set-up (model building, one eager pass that prepares the tensor-core layouts of 
 CUDA-graph capture) runs on the calling thread, device by device, because the engine is a
 single-threaded object exactly as in JavaScript.  A step then runs on one host thread per
 device: upload of the device's slice from the pinned input buffer, graph replay, asynchronous
-read into the output buffer, wait for that read.  Those calls go straight to the C ABI of the
+read into the output buffer, wait for that read (run_pipelined streams batches through two
+slots so that the upload of the next batch overlaps the kernels of the current one).  Those calls go straight to the C ABI of the
 device's own context (ctypes releases the GIL), touch no engine state, and contexts are
 independent of each other, so the threads need no lock.
 
@@ -70,10 +71,13 @@ class _Shard:
     def __init__(self, backend, name, first, rows):
         self.backend, self.name, self.first, self.rows = backend, name, first, rows
         self.net = None
-        self.input = None     # device tensor [rows, *image_shape]
-        self.output = None    # device tensor [rows, classes], rewritten by every replay
-        self.logits = None
-        self.graph = None
+        # Two slots, so that the upload of batch k + 1 overlaps the kernels of batch k: each has
+        # its own input tensor, captured graph and output tensor (a graph is tied to the buffers
+        # it was captured with).
+        self.inputs = [None, None]    # device tensors [rows, *image_shape]
+        self.outputs = [None, None]   # device tensors [rows, classes], rewritten by every replay
+        self.graphs = [None, None]
+        self.forward = None           # eager forward of slot 0 (no graph capture)
 
 
 class ShardedRunner:
@@ -94,7 +98,7 @@ class ShardedRunner:
         self.plan = plan_shards(batch, len(devices))
         self.batch, self.image_shape = batch, tuple(image_shape)
         self.shards, self.classes = [], None
-        self.pinned_in = self.pinned_out = None
+        self.pinned_in, self.pinned_out = [], []
         self._errors = []
         make = backend_factory or (lambda dev: BackendCuda(dev, math_mode))
         previous = ENGINE.backendName
@@ -109,6 +113,8 @@ class ShardedRunner:
                     backend = ENGINE.registry[name]
                 else:
                     ENGINE.setBackend(name)
+                    if hasattr(backend, "setMathMode"):
+                        backend.setMathMode(math_mode)
                 for key, value in (options or {}).items():
                     backend.setOption(key, value)
                 shard = _Shard(backend, name, first, rows)
@@ -122,9 +128,9 @@ class ShardedRunner:
                 ENGINE.setBackend(previous)
         self._lib = getattr(self.shards[0].backend, "_lib", None)
         if self._lib is not None:
-            self.pinned_in = _PinnedBuffer(self._lib, (batch,) + self.image_shape)
-            self.pinned_out = _PinnedBuffer(self._lib, (batch, self.classes))
-            self.input = self.pinned_in.array
+            self.pinned_in = [_PinnedBuffer(self._lib, (batch,) + self.image_shape) for _ in range(2)]
+            self.pinned_out = [_PinnedBuffer(self._lib, (batch, self.classes)) for _ in range(2)]
+            self.input = self.pinned_in[0].array
         else:  # a host-memory fake backend: plain arrays
             self.input = np.zeros((batch,) + self.image_shape, np.float32)
             self._out = np.zeros((batch, self.classes), np.float32)
@@ -134,67 +140,95 @@ class ShardedRunner:
         from . import ops
         bk = shard.backend
         shard.net = build(bk)
-        shard.input = ops.tensor(np.zeros((shard.rows,) + self.image_shape, np.float32))
 
-        def run():
-            out = forward(shard.net, shard.input)
+        def run(x):
+            out = forward(shard.net, x)
             outs = list(out) if isinstance(out, (tuple, list)) else [out]
             for t in outs[:-1]:
                 t.dispose()
             return outs[-1]
 
-        warm = run()                      # eager: prepares the weights' tensor-core layouts
+        graphs = use_graph and hasattr(bk, "graphBegin")
+        for slot in range(2 if graphs else 1):
+            shard.inputs[slot] = ops.tensor(np.zeros((shard.rows,) + self.image_shape, np.float32))
+        warm = run(shard.inputs[0])       # eager: prepares the weights' tensor-core layouts
         classes = int(np.prod(warm.shape[1:]))
         if self.classes not in (None, classes):
             raise ValueError("the model returns different shapes on different devices")
         self.classes = classes
-        if use_graph and hasattr(bk, "graphBegin"):
+        if graphs:
             warm.dispose()
-            bk.graphBegin()
-            shard.output = run()
-            shard.graph = bk.graphEnd()
+            for slot in range(2):
+                bk.graphBegin()
+                shard.outputs[slot] = run(shard.inputs[slot])
+                shard.graphs[slot] = bk.graphEnd()
         else:
-            shard.output = warm
-            shard.forward = run
+            shard.outputs[0] = warm
+            shard.forward = lambda: run(shard.inputs[0])
 
-    # ---- one step ---------------------------------------------------------------------------
+    # ---- the calls of one step, each of which only enqueues ----------------------------------
+    def _check(self, shard, rc):
+        if rc:
+            raise CudaError(f"shard {shard.name}: " + self._lib.tfjs_cuda_last_error(shard.backend._ctx).decode())
+
+    def _upload(self, shard, slot):
+        bk, lib = shard.backend, self._lib
+        buf = self.pinned_in[slot]
+        self._check(shard, lib.tfjs_cuda_tensor_write_async(
+            bk._ctx, bk._rec(shard.inputs[slot].dataId)["id"], buf.address(shard.first),
+            shard.rows * buf.array.strides[0]))
+
+    def _launch(self, shard, slot):
+        bk, lib = shard.backend, self._lib
+        self._check(shard, lib.tfjs_cuda_tensor_wait(bk._ctx, bk._rec(shard.inputs[slot].dataId)["id"]))
+        self._check(shard, lib.tfjs_cuda_graph_launch(bk._ctx, shard.graphs[slot]))
+
+    def _read(self, shard, slot, out_tensor=None):
+        """Enqueues the copy of the shard's result into its rows of the gather buffer."""
+        bk, lib = shard.backend, self._lib
+        out = out_tensor if out_tensor is not None else shard.outputs[slot]
+        ev = C.c_void_p()
+        self._check(shard, lib.tfjs_cuda_tensor_read_async(
+            bk._ctx, bk._rec(out.dataId)["id"], self.pinned_out[slot].address(shard.first),
+            shard.rows * self.classes * 4, C.byref(ev)))
+        return ev
+
+    def _wait(self, shard, ev):
+        rc = self._lib.tfjs_cuda_event_wait(ev, -1)
+        self._lib.tfjs_cuda_event_destroy(ev)
+        if rc:
+            raise CudaError(f"read of shard {shard.name} failed with status {rc}")
+
     def _step_on(self, shard):
         bk = shard.backend
         try:
             if self._lib is None:         # fake backend: synchronous host arrays
-                bk.write(shard.input.dataId, self.input[shard.first:shard.first + shard.rows])
-                out = shard.forward() if shard.graph is None else None
-                res = out if out is not None else shard.output
-                self._out[shard.first:shard.first + shard.rows] = res.dataSync().reshape(shard.rows, -1)
-                if out is not None and out is not shard.output:
-                    out.dispose()
-                return
-            lib, ctx = self._lib, bk._ctx
-            in_id = bk._rec(shard.input.dataId)["id"]
-            nbytes_in = shard.rows * self.pinned_in.array.strides[0]
-            rc = lib.tfjs_cuda_tensor_write_async(ctx, in_id, self.pinned_in.address(shard.first), nbytes_in)
-            if rc == 0 and shard.graph is not None:
-                rc = lib.tfjs_cuda_tensor_wait(ctx, in_id)
-                rc = rc or lib.tfjs_cuda_graph_launch(ctx, shard.graph)
-            if rc:
-                raise CudaError(lib.tfjs_cuda_last_error(ctx).decode())
-            out = shard.output
-            if shard.graph is None:       # eager: a fresh result tensor every step
+                bk.write(shard.inputs[0].dataId, self.input[shard.first:shard.first + shard.rows])
                 out = shard.forward()
-            out_id = bk._rec(out.dataId)["id"]
-            ev = C.c_void_p()
-            rc = lib.tfjs_cuda_tensor_read_async(ctx, out_id, self.pinned_out.address(shard.first),
-                                                 shard.rows * self.classes * 4, C.byref(ev))
-            if rc:
-                raise CudaError(lib.tfjs_cuda_last_error(ctx).decode())
-            rc = lib.tfjs_cuda_event_wait(ev, -1)
-            lib.tfjs_cuda_event_destroy(ev)
-            if out is not shard.output:
+                self._out[shard.first:shard.first + shard.rows] = out.dataSync().reshape(shard.rows, -1)
                 out.dispose()
-            if rc:
-                raise CudaError(f"read of shard {shard.name} failed with status {rc}")
+                return
+            self._upload(shard, 0)
+            if shard.graphs[0] is not None:
+                self._launch(shard, 0)
+                self._wait(shard, self._read(shard, 0))
+            else:                         # eager: a fresh result tensor every step
+                out = shard.forward()
+                self._wait(shard, self._read(shard, 0, out))
+                out.dispose()
         except Exception as err:  # surfaced by run() on the calling thread
             self._errors.append((shard.name, err))
+
+    def _threaded(self):
+        # Threads only for graph replays, which touch nothing but their own context.  An eager
+        # forward goes through the engine (scopes, tensor registry), which is single-threaded.
+        return (self._lib is not None and len(self.shards) > 1 and
+                all(s.graphs[0] is not None for s in self.shards))
+
+    def _raise_errors(self):
+        if self._errors:
+            name, err = self._errors[0]
+            raise CudaError(f"shard {name}: {err}") from err
 
     def run(self, images=None):
         """Runs one batch.  `images` ([batch, *image_shape] float32) is copied into the pinned
@@ -204,13 +238,10 @@ class ShardedRunner:
         if images is not None:
             np.copyto(self.input, np.asarray(images, np.float32).reshape(self.input.shape))
         self._errors = []
-        # Threads only for graph replays, which touch nothing but their own context.  An eager
-        # forward goes through the engine (scopes, tensor registry), which is single-threaded.
-        threaded = self._lib is not None and len(self.shards) > 1 and all(s.graph is not None for s in self.shards)
-        if not threaded:
+        if not self._threaded():
             previous = ENGINE.backendName
             for s in self.shards:
-                if s.graph is None:
+                if s.graphs[0] is None:
                     ENGINE.setBackend(s.name)  # an eager forward may create tensors through the op layer
                 self._step_on(s)
             if previous is not None and previous != ENGINE.backendName and previous in ENGINE.registryFactory:
@@ -221,28 +252,85 @@ class ShardedRunner:
                 t.start()
             for t in threads:
                 t.join()
-        if self._errors:
-            name, err = self._errors[0]
-            raise CudaError(f"shard {name}: {err}") from err
-        return self.pinned_out.array if self._lib is not None else self._out
+        self._raise_errors()
+        return self.pinned_out[0].array if self._lib is not None else self._out
+
+    def run_pipelined(self, num_batches, fill=None, consume=None):
+        """Streams `num_batches` batches through the devices with the upload of batch k + 1
+        overlapping the kernels of batch k.
+
+        fill(k, buffer): write batch k into `buffer` ([batch, *image_shape], pinned); called on
+        the calling thread before the batch is uploaded.  Without it the slots' current contents
+        are used (self.input_slots).  consume(k, result): called with the gathered
+        [batch, classes] result of batch k (a view that is overwritten two batches later).
+        Needs captured graphs (use_graph=True on a real backend)."""
+        if self._lib is None or any(g is None for s in self.shards for g in s.graphs):
+            raise CudaError("run_pipelined needs captured graphs on every device")
+        if num_batches < 1:
+            return
+        self._errors = []
+        n = len(self.shards)
+        ready = threading.Barrier(n + 1)   # calling thread + one thread per device
+        done = threading.Barrier(n + 1)
+
+        def device_loop(shard):
+            try:
+                self._upload(shard, 0)
+                for k in range(num_batches):
+                    ready.wait()                       # batch k + 1 is in its pinned slot
+                    if k + 1 < num_batches:
+                        self._upload(shard, (k + 1) % 2)   # issued BEFORE the kernels of batch k, so it overlaps them
+                    self._launch(shard, k % 2)
+                    self._wait(shard, self._read(shard, k % 2))
+                    done.wait()
+            except Exception as err:
+                self._errors.append((shard.name, err))
+                ready.abort()
+                done.abort()
+
+        if fill is not None:
+            fill(0, self.pinned_in[0].array)
+        threads = [threading.Thread(target=device_loop, args=(s,)) for s in self.shards]
+        for t in threads:
+            t.start()
+        try:
+            for k in range(num_batches):
+                if fill is not None and k + 1 < num_batches:
+                    # slot (k + 1) % 2 is free: batch k - 1, its last user, has been computed
+                    fill(k + 1, self.pinned_in[(k + 1) % 2].array)
+                ready.wait()
+                done.wait()
+                if consume is not None:
+                    consume(k, self.pinned_out[k % 2].array)
+        except threading.BrokenBarrierError:
+            pass
+        for t in threads:
+            t.join()
+        self._raise_errors()
+
+    @property
+    def input_slots(self):
+        """The two pinned input buffers of run_pipelined (batch k uses slot k % 2)."""
+        return [b.array for b in self.pinned_in]
 
     def dispose(self):
         for s in self.shards:
             bk = s.backend
-            if s.graph is not None:
-                bk.graphDestroy(s.graph)
-                s.graph = None
-            for t in (s.input, s.output):
+            for slot in range(2):
+                if s.graphs[slot] is not None:
+                    bk.graphDestroy(s.graphs[slot])
+                    s.graphs[slot] = None
+            for t in s.inputs + s.outputs:
                 if t is not None and not t.isDisposed:
                     t.dispose()
             if s.net is not None and hasattr(s.net, "dispose"):
                 s.net.dispose()
-            s.net = s.input = s.output = None
+            s.net = None
+            s.inputs, s.outputs = [None, None], [None, None]
         self.shards = []
-        for buf in (self.pinned_in, self.pinned_out):
-            if buf is not None:
-                buf.free()
-        self.pinned_in = self.pinned_out = None
+        for buf in list(self.pinned_in) + list(self.pinned_out):
+            buf.free()
+        self.pinned_in, self.pinned_out = [], []
 
 
 def run_sharded(build, forward, images, devices=None, **kwargs):
