@@ -58,6 +58,10 @@ def parse_args():
                          "the 8-kernel softmax chain)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the extra measurements (in-loop dequantisation, in-process sharded runner)")
+    ap.add_argument("--activations", default="f32", choices=["f32", "f16"],
+                    help="f16: activations are stored as IEEE half between the layers (the reference's 16-bit "
+                         "precision class); a SEPARATE configuration with its own algorithmic-bytes figure, "
+                         "never the headline")
     ap.add_argument("--global-batch", type=int, default=0, help="override the workload's batch")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a graph")
     ap.add_argument("--pdl", action="store_true", help="programmatic dependent launch instead of plain stream order")
@@ -73,8 +77,10 @@ def workload_config(args, world):
         assert gb % world == 0, "the global batch must divide evenly over the GPUs"
         how = ("inside the GEMM main loop" if args.dequant == "in-loop"
                else "once on device into cached tf32 planes")
+        half = ", float16 activation storage (16-bit precision class: separate configuration)" \
+            if getattr(args, "activations", "f32") == "f16" else ""
         return dict(name="cfg5: MobileNetV1-1.0-224, uint8 affine-quantised filters dequantised %s, "
-                         "global batch %d sharded by batch" % (how, gb),
+                         "global batch %d sharded by batch%s" % (how, gb, half),
                     global_batch=gb, per_gpu=gb // world, quantized=True, seed=4, gain=1.0,
                     scaling="strong")
     per = args.global_batch or 64
@@ -275,7 +281,13 @@ def run_reference(args):
 
 
 # ---- this backend -------------------------------------------------------------------------------
-KERNEL_FAMILY = {"separableConv2d (fused dw3x3 s1 + pw, TF32)": "separable_fused",
+KERNEL_FAMILY = {"separableConv2d (fused dw3x3 s1 + pw, TF32, float16)": "separable_fused",
+                 "separableConv2d (fused dw3x3 s2 + pw, TF32, float16)": "separable_fused",
+                 "gemm_tcgen05 (F16)": "gemm_tcgen05",
+                 "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32, float16 out)": "conv2d_tcgen05",
+                 "depthwiseConv2D (3x3 image window, TMA, float16)": "depthwise3x3",
+                 "avgPool (global, float16 in)": "global_avgpool",
+                 "separableConv2d (fused dw3x3 s1 + pw, TF32)": "separable_fused",
                  "separableConv2d (fused dw3x3 s2 + pw, TF32)": "separable_fused",
                  "gemm_tcgen05 (TF32)": "gemm_tcgen05", "gemm_tcgen05 (3xTF32)": "gemm_tcgen05",
                  "gemm_tcgen05 (TF32, uint8 weights)": "gemm_tcgen05",
@@ -334,6 +346,8 @@ def parity_check(bk, args, images=4):
     want = np.concatenate([oracle_net.forward(x[i:i + 1], params)[0] for i in range(images)], 0)
     err = float(np.abs(got - want).max() / np.abs(want).max())
     tol = 1e-3 if args.math == "tf32" else 1e-4
+    if args.activations == "f16":
+        tol = 5e-3   # 16-bit precision class (the reference's own tolerance there is 1e-1)
     same = bool((got.argmax(1) == want.argmax(1)).all())
     assert err <= tol, f"parity check failed: logits differ from the oracle by {err:.2e} (> {tol})"
     assert same, "parity check failed: argmax differs from the oracle"
@@ -354,6 +368,11 @@ def run_cuda(args):
     assert ENGINE.setBackend("bench-cuda")
     bk.setOption("dequant_in_gemm", 1 if args.dequant == "in-loop" else 0)
     bk.setOption("pdl", 1 if args.pdl else 0)
+    half = args.activations == "f16"
+    if half:
+        assert args.math == "tf32" and args.forward != "reference-api", \
+            "float16 activation storage goes with --math tf32 and the fused forwards"
+        bk.setActivationStorage("float16")
 
     parity = parity_check(bk, args) if d.rank == 0 else None
 
@@ -435,7 +454,7 @@ def run_cuda(args):
     if args.forward == "reference-api":
         layer_bytes = mobilenet.reference_api_launch_bytes(per, cfg["quantized"], names)
     else:
-        layer_bytes = mobilenet.launch_algorithmic_bytes(per, cfg["quantized"], names)
+        layer_bytes = mobilenet.launch_algorithmic_bytes(per, cfg["quantized"], names, half)
     fam = {}
     for i, (name, ms) in enumerate(rows):
         f = KERNEL_FAMILY.get(name, name)
@@ -544,7 +563,7 @@ def run_cuda(args):
 
     # ---- extra: the same step with the uint8 weights dequantised inside the GEMM main loop ----
     extras = {}
-    if cfg["quantized"] and args.dequant == "cached" and graph is not None and not args.no_extras:
+    if cfg["quantized"] and args.dequant == "cached" and graph is not None and not args.no_extras and not half:
         bk.setOption("dequant_in_gemm", 1)
         lg, pr = forward(x)          # prepares the K-major uint8 layouts
         lg.dispose()
@@ -583,7 +602,7 @@ def run_cuda(args):
 
     # ---- extra: the library's in-process runner over all N devices (rank 0, the other ranks idle) ----
     d.barrier()
-    if d.rank == 0 and d.world > 1 and not args.no_extras and not args.no_graph:
+    if d.rank == 0 and d.world > 1 and not args.no_extras and not args.no_graph and not half:
         extras["e2e_in_process"] = in_process_e2e(args, cfg, params, d.world)
     d.barrier()
 
@@ -591,10 +610,12 @@ def run_cuda(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": d.world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": cfg["scaling"], "vs_baseline": None, "dtype": "tf32" if args.math == "tf32" else "3xtf32",
+            "scaling": cfg["scaling"], "vs_baseline": None,
+            "dtype": ("tf32 (float16 activation storage)" if half else "tf32") if args.math == "tf32" else "3xtf32",
             "data": "synthetic",
             "config": {"workload": cfg["name"], "global_batch": cfg["global_batch"], "per_gpu_batch": per,
                        "math_mode": args.math, "dequant": args.dequant, "forward": args.forward,
+                       "activation_storage": "float16" if half else "float32",
                        "launches_per_step": int(launches_per_step),
                        "launch": "eager" if graph is None else "cuda-graph replay",
                        "l2": "every step streams %.1f GB of activations per GPU (> 126 MB L2) between reuses"

@@ -45,8 +45,14 @@ typedef enum {
   TFJS_CUDA_ERR_NOT_FOUND = -6
 } tfjs_cuda_status;
 
-/* DataType subset the path stores; numbering of tfjs-backend-wasm/src/lib.cc:26-30. */
-typedef enum { TFJS_F32 = 0, TFJS_I32 = 1, TFJS_BOOL = 2 } tfjs_dtype;
+/* DataType subset the path stores; numbering of tfjs-backend-wasm/src/lib.cc:26-30.
+ * TFJS_F16 is an extension: a float32 tensor whose STORAGE is IEEE half precision (2 bytes per
+ * element).  It is the storage of activations in the 16-bit precision class of the reference
+ * (KernelBackend.floatPrecision() == 16, backends/backend.ts:120-126; the WebGL backend on
+ * devices with half-float textures): tensor_write takes and tensor_read returns float32 values,
+ * the convolution, separable-convolution, depthwise and pooling entry points read and write it
+ * natively, every other kernel takes it after tfjs_cuda_cast to TFJS_F32. */
+typedef enum { TFJS_F32 = 0, TFJS_I32 = 1, TFJS_BOOL = 2, TFJS_F16 = 3 } tfjs_dtype;
 
 /* Activation of fused ops.  linear/relu/prelu are tfjs-core/src/ops/fused_util.ts:20;
  * CLIP is an extension (relu6 = clip(0, 6), i.e. tf.clipByValue fused into the producer). */

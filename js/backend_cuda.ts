@@ -30,6 +30,7 @@ const EPSILON_FLOAT16 = 1e-4;   // backends/backend.ts:24
 
 // enums of include/tfjs_cuda.h
 const DTYPE: {[d: string]: number} = {float32: 0, int32: 1, bool: 2};
+const STORAGE_F16 = 3;   // TFJS_F16: a float32 tensor stored as IEEE half
 const ACT: {[a: string]: number} = {linear: 0, relu: 1, prelu: 2, clip: 3};
 const MATH: {[m: string]: number} = {'3xtf32': 0, tf32: 1};
 const BINARY = {add: 0, sub: 1, mul: 2, div: 3, prelu: 4, notEqual: 5};
@@ -40,6 +41,7 @@ const ERR_UNSUPPORTED = -5;
 interface TensorRecord {
   id: number;             // tfjs_tensor_id
   dtype: DataType;        // dtype the storage was registered with
+  half?: boolean;         // float32 values stored as IEEE half (16-bit activation storage)
   shape: number[];
   quantized?: boolean;    // uint8 bytes + scale/min (registerQuantized)
 }
@@ -57,6 +59,8 @@ export class BackendCuda extends KernelBackend {
    * memory (backends/backend.ts:47-70, engine.ts:361-363). */
   private data: DataStorage<TensorRecord>;
   mathMode: '3xtf32'|'tf32' = '3xtf32';
+  activationStorage: 'float32'|'float16' = 'float32';
+  private pendingStorage: 'float32'|'float16'|null = null;
 
   constructor(readonly device = 0, mathMode: '3xtf32'|'tf32' = '3xtf32') {
     super();
@@ -90,10 +94,17 @@ export class BackendCuda extends KernelBackend {
    * then a converted temporary is returned as the second element and must be freed. */
   private id(t: Tensor, want: DataType = 'float32'): [number, number|null] {
     const rec = this.data.get(t.dataId);
-    if (rec.dtype === want) return [rec.id, null];
+    if (rec.dtype === want && !rec.half) return [rec.id, null];
     const tmp = this.newId(t.shape, want);
     this.check(binding.cast(this.ctx, rec.id, tmp));
     return [tmp, tmp];
+  }
+
+  /** Device id of an activation operand for the kernels that read float32 and half storage alike. */
+  private activationId(t: Tensor): [number, number|null] {
+    const rec = this.data.get(t.dataId);
+    if (rec.half) return [rec.id, null];
+    return this.id(t);
   }
 
   private freeTmp(...ids: Array<number|null>): void {
@@ -104,6 +115,17 @@ export class BackendCuda extends KernelBackend {
 
   private makeOutput<T extends Tensor>(shape: number[], dtype: DataType = 'float32'): T {
     return Tensor.make(shape, {}, dtype, this) as T;   // re-enters register()
+  }
+
+  /** Output of a convolution: float32 values whose storage follows the activation-storage mode
+   * (or `storage` when the caller names one). */
+  private makeActivation<T extends Tensor>(shape: number[], storage?: 'float32'|'float16'): T {
+    this.pendingStorage = storage || this.activationStorage;
+    try {
+      return Tensor.make(shape, {}, 'float32', this) as T;
+    } finally {
+      this.pendingStorage = null;
+    }
   }
 
   private outId(t: Tensor): number {
@@ -122,6 +144,13 @@ export class BackendCuda extends KernelBackend {
   register(dataId: DataId, shape: number[], dtype: DataType): void {
     if (this.data.has(dataId)) {
       throw new Error('Data buffer is already registered');   // backend_cpu.ts:119-121
+    }
+    if (this.pendingStorage === 'float16' && dtype === 'float32') {
+      // a float32 tensor stored as IEEE half: the native library converts on write / read
+      const r = binding.tensorRegister(this.ctx, shape.length, shape, STORAGE_F16);
+      this.check(r.status);
+      this.data.set(dataId, {id: r.out_id, dtype, shape: shape.slice(), half: true});
+      return;
     }
     this.data.set(dataId, {id: this.newId(shape, dtype), dtype, shape: shape.slice()});
   }
@@ -157,7 +186,7 @@ export class BackendCuda extends KernelBackend {
   readSync(dataId: DataId): backend_util.BackendValues {
     const rec = this.data.get(dataId);
     const out = typedArrayFor(rec.quantized ? 'float32' : rec.dtype, util.sizeFromShape(rec.shape));
-    this.check(binding.tensorRead(this.ctx, rec.id, out));
+    this.check(binding.tensorRead(this.ctx, rec.id, out));   // half storage arrives as float32
     return out;
   }
 
@@ -203,8 +232,9 @@ export class BackendCuda extends KernelBackend {
     return {kernelMs: r.kernel_ms, getExtraProfileInfo: () => `${r.num_launches} kernel launches`};
   }
 
+  /** backend.ts:120-126: 16 while activations are stored as IEEE half, else 32. */
   floatPrecision(): 16|32 {
-    return 32;
+    return this.activationStorage === 'float16' ? 16 : 32;
   }
 
   epsilon(): number {
@@ -227,6 +257,14 @@ export class BackendCuda extends KernelBackend {
   setMathMode(mode: '3xtf32'|'tf32'): void {
     this.mathMode = mode;
     this.check(binding.ctxSetOption(this.ctx, 'math_mode', MATH[mode]));
+  }
+
+  /** Extension: 'float32' (default) or 'float16'.  With 'float16' the outputs of the convolution
+   * methods are stored as IEEE half, which halves the bytes every layer moves; the arithmetic
+   * stays float32 / tf32 with float32 accumulation.  This is the reference's 16-bit precision
+   * class (floatPrecision() == 16, test tolerance 1e-1: test_util.ts:23-39). */
+  setActivationStorage(storage: 'float32'|'float16'): void {
+    this.activationStorage = storage;
   }
 
   setOption(key: string, value: number): void {
@@ -395,12 +433,12 @@ export class BackendCuda extends KernelBackend {
 
   /** backend.ts:414-418; CPU backend_cpu.ts:1536-1616. */
   fusedConv2d(x: Tensor4D, filter: Tensor4D, convInfo: Conv2DInfo, bias?: Tensor, activation?: CudaActivation,
-              preluActivationWeights?: Tensor): Tensor4D {
+              preluActivationWeights?: Tensor, outputStorage?: 'float32'|'float16'): Tensor4D {
     this.assertNumeric([x, filter, bias], 'conv2d');
     const {epi, tmps, compose} = this.epilogue(bias, activation, preluActivationWeights, convInfo.outChannels);
-    const [xid, tx] = this.id(x);
+    const [xid, tx] = this.activationId(x);
     const [fid, tf] = this.id(filter);
-    let out = this.makeOutput<Tensor4D>(convInfo.outShape);
+    let out = this.makeActivation<Tensor4D>(convInfo.outShape, outputStorage);
     this.check(binding.conv2d(this.ctx, xid, fid, this.outId(out), convInfo, epi));
     this.freeTmp(tx, tf, ...tmps);
     if (compose) out = this.composeEpilogue(out, bias, activation, preluActivationWeights);
@@ -417,9 +455,9 @@ export class BackendCuda extends KernelBackend {
                        activation?: CudaActivation): Tensor4D {
     this.assertNumeric([x, filter, bias], 'depthwiseConv2D');
     const {epi, tmps, compose} = this.epilogue(bias, activation, undefined, convInfo.outChannels);
-    const [xid, tx] = this.id(x);
+    const [xid, tx] = this.activationId(x);
     const [fid, tf] = this.id(filter);
-    let out = this.makeOutput<Tensor4D>(convInfo.outShape);
+    let out = this.makeActivation<Tensor4D>(convInfo.outShape);
     this.check(binding.depthwiseConv2d(this.ctx, xid, fid, this.outId(out), convInfo, epi));
     this.freeTmp(tx, tf, ...tmps);
     if (compose) out = this.composeEpilogue(out, bias, activation, undefined);
@@ -452,10 +490,10 @@ export class BackendCuda extends KernelBackend {
       mid.dispose();
       return out;
     }
-    const [xid, tx] = this.id(x);
+    const [xid, tx] = this.activationId(x);
     const [did, td] = this.id(depthwiseFilter);
     const [pid, tp] = this.id(pointwiseFilter);
-    const out = this.makeOutput<Tensor4D>([convInfo.batchSize, convInfo.outHeight, convInfo.outWidth, outDepth]);
+    const out = this.makeActivation<Tensor4D>([convInfo.batchSize, convInfo.outHeight, convInfo.outWidth, outDepth]);
     this.check(binding.separableConv2d(this.ctx, xid, did, pid, this.outId(out), convInfo, outDepth, dw.epi, pw.epi));
     this.freeTmp(tx, td, tp, ...dw.tmps, ...pw.tmps);
     return out;
@@ -464,7 +502,7 @@ export class BackendCuda extends KernelBackend {
   // ---- pooling (backend.ts:453-466) --------------------------------------------------------------
   private pool(x: Tensor4D, convInfo: Conv2DInfo, isAvg: boolean): Tensor4D {
     this.assertNumeric([x], 'pool');
-    const [xid, tx] = this.id(x);
+    const [xid, tx] = this.activationId(x);
     const out = this.makeOutput<Tensor4D>(convInfo.outShape);
     this.check(binding.pool2d(this.ctx, xid, this.outId(out), convInfo, isAvg ? 1 : 0));
     this.freeTmp(tx);

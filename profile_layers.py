@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Per-layer device times of one fused MobileNetV1 forward on the cuda backend.
 
-    python profile_layers.py [batch] [tf32|3xtf32] [f|q|q-in-loop] [separable|layerwise|separable-all]
+    python profile_layers.py [batch] [tf32|3xtf32] [f|q|q-in-loop] [separable|layerwise|separable-all] [f32|f16]
 
 Prints, for each launch of one forward pass (25 with the fused depthwise + pointwise blocks,
 30 with `layerwise`), the kernel name, the best device time over a few passes
@@ -26,11 +26,14 @@ def main():
     quantized = len(sys.argv) > 3 and sys.argv[3] in ("q", "q-in-loop")
     in_loop = len(sys.argv) > 3 and sys.argv[3] == "q-in-loop"
     layerwise = len(sys.argv) > 4 and sys.argv[4] == "layerwise"
+    half = len(sys.argv) > 5 and sys.argv[5] == "f16"   # activations stored as IEEE half
     reps = 4
     bk = tf.BackendCuda(0, mode)
     tf.ENGINE.registerBackend("profile-cuda", lambda: bk, 10)
     tf.ENGINE.setBackend("profile-cuda")
     bk.setOption("dequant_in_gemm", 1 if in_loop else 0)
+    if half:
+        bk.setActivationStorage("float16")
     if len(sys.argv) > 4 and sys.argv[4] == "separable-all":
         bk.setOption("fuse_separable", 2)
     params = mobilenet.make_weights(4 if quantized else 3, quantized=quantized, gain=1.5)
@@ -51,7 +54,7 @@ def main():
         probs.dispose()
     rows = bk.profileEnd()
     kernel_names = [name for name, _ in rows[:n]]
-    layer_bytes = mobilenet.launch_algorithmic_bytes(batch, quantized, kernel_names)
+    layer_bytes = mobilenet.launch_algorithmic_bytes(batch, quantized, kernel_names, half)
     names = [s[0] for s in mobilenet.layer_specs()][:-1] + ["avgpool", "fc", "softmax"]
     total, layer = 0.0, 0
     for i in range(n):
@@ -60,7 +63,7 @@ def main():
         fused = kernel_names[i].startswith("separableConv2d (fused")
         label = names[layer] + "+" + names[layer + 1] if fused else names[layer]
         layer += 2 if fused else 1
-        print(f"{label:9s} {kernel_names[i]:44s} {ms * 1e3:9.1f} us {layer_bytes[i] / 1e6:9.1f} MB "
+        print(f"{label:9s} {kernel_names[i]:62s} {ms * 1e3:9.1f} us {layer_bytes[i] / 1e6:9.1f} MB "
               f"{layer_bytes[i] / ms / 1e6:7.0f} GB/s")
     print(f"total {total:.3f} ms  {batch / total * 1e3:.0f} img/s  "
           f"{sum(layer_bytes) / total / 1e6:.0f} GB/s algorithmic")

@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(_HERE, "libtfjs_cuda.so")
 
 OK = 0
 ERR_INVALID_ARG, ERR_OOM, ERR_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_NOT_FOUND = -1, -2, -3, -4, -5, -6
-F32, I32, BOOL = 0, 1, 2
+F32, I32, BOOL, F16 = 0, 1, 2, 3
 ACT = {None: 0, "linear": 0, "relu": 1, "prelu": 2, "clip": 3}
 MATH = {"3xtf32": 0, "tf32": 1}
 BINARY = {"add": 0, "sub": 1, "mul": 2, "div": 3, "prelu": 4, "notEqual": 5}

@@ -21,7 +21,10 @@ from . import _ffi
 from .engine import ENGINE, NP_DTYPE, Tensor, size_from_shape
 
 EPSILON_FLOAT32 = 1e-7  # backends/backend.ts:23
-_DTYPE_CODE = {"float32": _ffi.F32, "int32": _ffi.I32, "bool": _ffi.BOOL}
+EPSILON_FLOAT16 = 1e-4  # backends/backend.ts:24
+_DTYPE_CODE = {"float32": _ffi.F32, "int32": _ffi.I32, "bool": _ffi.BOOL, "float16": _ffi.F16}
+# host-side element type per STORAGE dtype: half-stored tensors travel as float32 (the library converts)
+_HOST_DTYPE = dict(NP_DTYPE, float16=np.float32)
 
 
 class CudaError(RuntimeError):
@@ -65,6 +68,8 @@ class BackendCuda:
         self._ctx = ctx
         self.device = int(device)
         self._data = weakref.WeakKeyDictionary()  # DataStorage (backend.ts:47-70): dataId -> record
+        self.activation_storage = "float32"
+        self._pending_storage = None
         self.setMathMode(math_mode)
 
     # ---- helpers -------------------------------------------------------------------------
@@ -108,6 +113,23 @@ class BackendCuda:
     def _out(self, shape, dtype="float32"):
         return Tensor.make(shape, {}, dtype, self)
 
+    def _out_activation(self, shape, storage=None):
+        """Output of a convolution: a float32 tensor whose storage follows the activation-storage
+        mode (or `storage` when the caller names one)."""
+        self._pending_storage = storage or self.activation_storage
+        try:
+            return Tensor.make(shape, {}, "float32", self)
+        finally:
+            self._pending_storage = None
+
+    def _activation_id(self, t):
+        """Device id of an activation operand for the kernels that read float32 and half storage
+        alike; any other storage is converted to float32 first."""
+        rec = self._rec(t.dataId)
+        if rec["dtype"] in ("float32", "float16"):
+            return rec["id"], None
+        return self._id(t)
+
     @staticmethod
     def _assert_numeric(tensors, op):
         for t in tensors if isinstance(tensors, (list, tuple)) else [tensors]:
@@ -120,14 +142,17 @@ class BackendCuda:
             raise ValueError("Data buffer is already registered")  # backend_cpu.ts:119-121
         if dtype not in _DTYPE_CODE:
             raise ValueError(f"cuda backend does not support dtype {dtype}")
-        self._data[dataId] = {"id": self._new_id(shape, dtype), "dtype": dtype,
+        storage = dtype
+        if self._pending_storage == "float16" and dtype == "float32":
+            storage = "float16"   # a float32 tensor stored as IEEE half (16-bit activation storage)
+        self._data[dataId] = {"id": self._new_id(shape, storage), "dtype": storage,
                               "shape": list(shape)}
 
     def write(self, dataId, values):
         if values is None:
             raise ValueError("MathBackendCUDA.write(): values can not be null")
         rec = self._rec(dataId)
-        arr = np.ascontiguousarray(np.asarray(values).reshape(-1), dtype=NP_DTYPE[rec["dtype"]])
+        arr = np.ascontiguousarray(np.asarray(values).reshape(-1), dtype=_HOST_DTYPE[rec["dtype"]])
         self._check(self._lib.tfjs_cuda_tensor_write(self._ctx, rec["id"], arr.ctypes.data_as(C.c_void_p),
                                                      arr.nbytes))
 
@@ -145,14 +170,14 @@ class BackendCuda:
     def readSync(self, dataId):
         rec = self._rec(dataId)
         n = size_from_shape(rec["shape"])
-        out = np.empty(n, dtype=np.float32 if rec.get("quantized") else NP_DTYPE[rec["dtype"]])
+        out = np.empty(n, dtype=np.float32 if rec.get("quantized") else _HOST_DTYPE[rec["dtype"]])
         self._check(self._lib.tfjs_cuda_tensor_read(self._ctx, rec["id"], out.ctypes.data_as(C.c_void_p),
                                                     out.nbytes))
         return out
 
     def read(self, dataId):
         rec = self._rec(dataId)
-        dtype = np.float32 if rec.get("quantized") else NP_DTYPE[rec["dtype"]]
+        dtype = np.float32 if rec.get("quantized") else _HOST_DTYPE[rec["dtype"]]
         nbytes = size_from_shape(rec["shape"]) * np.dtype(dtype).itemsize
         host = C.c_void_p()
         if self._lib.tfjs_cuda_host_alloc(C.byref(host), nbytes) != 0:
@@ -184,10 +209,11 @@ class BackendCuda:
                 "getExtraProfileInfo": lambda: f"{n.value} kernel launches"}
 
     def floatPrecision(self):
-        return 32
+        """backend.ts:120-126: 16 while activations are stored as IEEE half, else 32."""
+        return 16 if self.activation_storage == "float16" else 32
 
     def epsilon(self):
-        return EPSILON_FLOAT32
+        return EPSILON_FLOAT32 if self.floatPrecision() == 32 else EPSILON_FLOAT16
 
     def dispose(self):
         if self._ctx:
@@ -203,6 +229,16 @@ class BackendCuda:
         """'3xtf32' (default, float32-level accuracy) or 'tf32' (one tensor-core pass)."""
         self.math_mode = mode
         self._check(self._lib.tfjs_cuda_ctx_set_option(self._ctx, b"math_mode", float(_ffi.MATH[mode])))
+
+    def setActivationStorage(self, storage):
+        """Extension: 'float32' (default) or 'float16'.  With 'float16' the outputs of the
+        convolution methods (fusedConv2d, fusedDepthwiseConv2D, fusedSeparableConv2d) are stored as
+        IEEE half, which halves the bytes every layer moves; the arithmetic stays float32 /
+        tf32 with float32 accumulation.  This is the reference's 16-bit precision class
+        (floatPrecision() == 16, test tolerance 1e-1: test_util.ts:23-39)."""
+        if storage not in ("float32", "float16"):
+            raise ValueError("activation storage must be 'float32' or 'float16'")
+        self.activation_storage = storage
 
     def setOption(self, key, value):
         self._check(self._lib.tfjs_cuda_ctx_set_option(self._ctx, key.encode(), float(value)))
@@ -347,13 +383,15 @@ class BackendCuda:
     def conv2d(self, x, filter, convInfo):
         return self.fusedConv2d(x, filter, convInfo)
 
-    def fusedConv2d(self, x, filter, convInfo, bias=None, activation=None, preluActivationWeights=None):
-        """backend.ts:414-418; CPU backend_cpu.ts:1536-1616."""
+    def fusedConv2d(self, x, filter, convInfo, bias=None, activation=None, preluActivationWeights=None,
+                    outputStorage=None):
+        """backend.ts:414-418; CPU backend_cpu.ts:1536-1616.  `outputStorage` (extension) overrides
+        the activation-storage mode for this result, e.g. 'float32' for a network's logits."""
         self._assert_numeric([x, filter, bias], "conv2d")
         epi, tmps, compose = self._epilogue(bias, activation, preluActivationWeights, convInfo.outChannels)
-        xid, tx = self._id(x)
+        xid, tx = self._activation_id(x)
         fid, tf_ = self._id(filter)
-        out = self._out(convInfo.outShape)
+        out = self._out_activation(convInfo.outShape, outputStorage)
         oid = self._rec(out.dataId)["id"]
         self._check(self._lib.tfjs_cuda_conv2d(self._ctx, xid, fid, oid, C.byref(convInfo),
                                                C.byref(epi) if epi is not None else None))
@@ -370,9 +408,9 @@ class BackendCuda:
         """Extension: depthwiseConv2D + add(bias) + activation in one kernel."""
         self._assert_numeric([x, filter, bias], "depthwiseConv2D")
         epi, tmps, compose = self._epilogue(bias, activation, None, convInfo.outChannels)
-        xid, tx = self._id(x)
+        xid, tx = self._activation_id(x)
         fid, tf_ = self._id(filter)
-        out = self._out(convInfo.outShape)
+        out = self._out_activation(convInfo.outShape)
         oid = self._rec(out.dataId)["id"]
         self._check(self._lib.tfjs_cuda_depthwise_conv2d(self._ctx, xid, fid, oid, C.byref(convInfo),
                                                          C.byref(epi) if epi is not None else None))
@@ -404,10 +442,10 @@ class BackendCuda:
             out = self.fusedConv2d(mid, pointwiseFilter, ci, pwBias, pwActivation)
             mid.dispose()
             return out
-        xid, tx = self._id(x)
+        xid, tx = self._activation_id(x)
         did, td = self._id(depthwiseFilter)
         pid, tp = self._id(pointwiseFilter)
-        out = self._out([convInfo.batchSize, convInfo.outHeight, convInfo.outWidth, out_depth])
+        out = self._out_activation([convInfo.batchSize, convInfo.outHeight, convInfo.outWidth, out_depth])
         oid = self._rec(out.dataId)["id"]
         self._check(self._lib.tfjs_cuda_separable_conv2d(
             self._ctx, xid, did, pid, oid, C.byref(convInfo), int(out_depth), C.byref(dw_epi), C.byref(pw_epi)))
@@ -417,7 +455,7 @@ class BackendCuda:
     # ---- pooling -------------------------------------------------------------------------
     def _pool(self, x, convInfo, is_avg):
         self._assert_numeric(x, "pool")
-        xid, tx = self._id(x)
+        xid, tx = self._activation_id(x)
         out = self._out(convInfo.outShape)
         self._check(self._lib.tfjs_cuda_pool2d(self._ctx, xid, self._rec(out.dataId)["id"],
                                                C.byref(convInfo), int(is_avg)))

@@ -100,6 +100,88 @@ int packed_weights(tfjs_cuda_ctx* ctx, TensorEntry* w, int64_t offset_elems, int
   return TFJS_CUDA_OK;
 }
 
+// ---- 16-bit activation storage --------------------------------------------------------------
+// An activation tensor may be stored as IEEE half (TFJS_F16).  Kernels with a native half path
+// take it as it is; every other kernel sees a float32 temporary (converted before, and for an
+// output converted back after), so that any call works on any storage and only the hot path
+// needs half-aware kernels.  Temporaries are stream-ordered like every other buffer.
+struct F32View {
+  const float* ptr = nullptr;
+  void* tmp = nullptr;
+  size_t cap = 0;
+};
+int view_as_f32(tfjs_cuda_ctx* ctx, TensorEntry* t, F32View* v) {
+  if (t->dtype != TFJS_F16) {
+    v->ptr = (const float*)t->ptr;
+    return TFJS_CUDA_OK;
+  }
+  int rc = ctx_alloc(ctx, (size_t)t->size * 4, &v->tmp, &v->cap);
+  if (rc) return rc;
+  v->ptr = (const float*)v->tmp;
+  return launch_convert(ctx, t->ptr, TFJS_F16, v->tmp, TFJS_F32, t->size);
+}
+void release_view(tfjs_cuda_ctx* ctx, F32View* v) {
+  if (v->tmp) ctx_free(ctx, v->tmp, v->cap);
+  v->tmp = nullptr;
+}
+struct F32Out {
+  float* ptr = nullptr;
+  void* tmp = nullptr;
+  size_t cap = 0;
+  TensorEntry* dst = nullptr;
+};
+int out_as_f32(tfjs_cuda_ctx* ctx, TensorEntry* o, F32Out* v) {
+  v->dst = o;
+  if (o->dtype != TFJS_F16) {
+    v->ptr = (float*)o->ptr;
+    return TFJS_CUDA_OK;
+  }
+  int rc = ctx_alloc(ctx, (size_t)o->size * 4, &v->tmp, &v->cap);
+  if (rc) return rc;
+  v->ptr = (float*)v->tmp;
+  return TFJS_CUDA_OK;
+}
+// Converts the float32 temporary into the half tensor (when there is one) and frees it.
+int finish_out(tfjs_cuda_ctx* ctx, F32Out* v, int rc) {
+  if (v->tmp) {
+    if (!rc) rc = launch_convert(ctx, v->tmp, TFJS_F32, v->dst->ptr, TFJS_F16, v->dst->size);
+    ctx_free(ctx, v->tmp, v->cap);
+    v->tmp = nullptr;
+  }
+  return rc;
+}
+
+// K-major IEEE half plane [N, kp] of a [K, N] contraction operand, cached on the tensor.
+int half_weights(tfjs_cuda_ctx* ctx, TensorEntry* w, int64_t K, int64_t N, const void** plane, int64_t* kp_out) {
+  const int64_t kp = (K + 7) / 8 * 8;
+  if (!w->w16 || w->w16_version != w->version || w->w16_n != N || w->w16_k != K) {
+    int miss = refuse_miss_during_capture(ctx, "the half-precision tensor-core layout");
+    if (miss) return miss;
+    if (w->w16) ctx_free(ctx, w->w16, w->w16_capacity);
+    w->w16 = nullptr;
+    int rc = ctx_alloc(ctx, (size_t)(N * kp) * 2, &w->w16, &w->w16_capacity);
+    if (rc) return rc;
+    rc = launch_pack_weights_f16(ctx, w->ptr, w->quant.quantized, w->quant.scale, w->quant.min, K, N, N, 1, kp,
+                                 w->w16);
+    if (rc) return rc;
+    w->w16_version = w->version;
+    w->w16_n = N;
+    w->w16_k = K;
+    w->w16_kp = kp;
+  }
+  *plane = w->w16;
+  *kp_out = kp;
+  return TFJS_CUDA_OK;
+}
+
+// Whether the whole-image depthwise kernel takes this call on half storage.
+bool depthwise_half_native(const tfjs_conv2d_info& ci, const EpilogueArgs& e, const void* x, const float* w,
+                           const void* y) {
+  return ci.inChannels % 4 == 0 && depthwise_image_supported(ci, e.activation, true) &&
+         (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) == 0 &&
+         (e.bias == nullptr || ((uintptr_t)e.bias & 15) == 0);
+}
+
 void release_temporary(tfjs_cuda_ctx* ctx, const PackedWeights& p, bool temporary) {
   if (!temporary) return;
   ctx_free(ctx, p.hi, p.capacity);
@@ -231,14 +313,13 @@ extern "C" int tfjs_cuda_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_te
   if (rc) return rc;
   const int64_t pixels = (int64_t)ci->batchSize * ci->outHeight * ci->outWidth;
   TensorEntry *x, *w, *o;
-  rc = get_f32(ctx, x_id, (int64_t)ci->batchSize * ci->inHeight * ci->inWidth * ci->inChannels, "x", &x);
+  rc = get_activation(ctx, x_id, (int64_t)ci->batchSize * ci->inHeight * ci->inWidth * ci->inChannels, "x", &x);
   if (rc) return rc;
   rc = get_f32(ctx, w_id, (int64_t)ci->filterHeight * ci->filterWidth * ci->inChannels * ci->outChannels,
                "filter", &w);
   if (rc) return rc;
-  rc = get_f32(ctx, out_id, pixels * ci->outChannels, "conv2d output", &o);
+  rc = get_activation(ctx, out_id, pixels * ci->outChannels, "conv2d output", &o);
   if (rc) return rc;
-  TFJS_REQUIRE(ctx, !x->quant.quantized && !o->quant.quantized, "only the filter may be quantised");
   EpilogueArgs e;
   rc = resolve_epilogue(ctx, epi, ci->outChannels, &e);
   if (rc) return rc;
@@ -249,30 +330,54 @@ extern "C" int tfjs_cuda_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_te
   const bool pointwise = ci->filterHeight == 1 && ci->filterWidth == 1 && ci->strideHeight == 1 &&
                          ci->strideWidth == 1 && ci->padTop == 0 && ci->padLeft == 0 &&
                          ci->outHeight == ci->inHeight && ci->outWidth == ci->inWidth;
-  if (pointwise && ci->inChannels > 0)
-    return gemm_dispatch(ctx, (const float*)x->ptr, pixels, ci->inChannels, w, 0, false, true,
-                         (float*)o->ptr, ci->outChannels, e);
-  // Everything else with Cin % 4 == 0 (or the 3-channel, 3-wide stem) is an implicit GEMM: the
-  // A tile is gathered from the image by the kernel itself, K = fH * fW * Cin.
+  const bool x16 = x->dtype == TFJS_F16, o16 = o->dtype == TFJS_F16;
+  // Half-precision activations: the pointwise convolution runs on the tensor cores' f16 path,
+  // reading x (and writing out, if it is half too) as stored.
+  if (x16 && pointwise && ci->inChannels > 0 && ctx->use_tensor_cores && e.activation != TFJS_ACT_PRELU &&
+      tcgen05_gemm_f16_supported(pixels, ci->outChannels, ci->inChannels, o16)) {
+    const void* plane;
+    int64_t kp;
+    rc = half_weights(ctx, w, ci->inChannels, ci->outChannels, &plane, &kp);
+    if (rc) return rc;
+    return launch_gemm_tcgen05_f16(ctx, x->ptr, pixels, ci->inChannels, plane, kp, o->ptr, o16, ci->outChannels, e);
+  }
   // The 3-channel 3x3 stem: the image window of a patch arrives by TMA and is rearranged into
-  // im2col rows in shared memory (TF32; other modes take the gather path below).
-  if (ctx->use_tensor_cores && conv_rgb_tcgen05_supported(*ci, e.activation, ctx->math_mode)) {
+  // im2col rows in shared memory (TF32; other modes take the gather path below).  It can store
+  // its result as half directly.
+  if (!x16 && ctx->use_tensor_cores && conv_rgb_tcgen05_supported(*ci, e.activation, ctx->math_mode)) {
     PackedWeights pw;
     bool temporary;
     rc = packed_weights(ctx, w, 0, 27, ci->outChannels, false, true, &pw, &temporary, 9, 10, 32);
     if (rc) return rc;
-    return launch_conv_rgb_tcgen05(ctx, (const float*)x->ptr, *ci, pw.hi, pw.kp, (float*)o->ptr, e);
+    return launch_conv_rgb_tcgen05(ctx, (const float*)x->ptr, *ci, pw.hi, pw.kp, o->ptr, e, o16);
   }
+  // Every other kernel computes on float32 storage.
+  F32View xv;
+  F32Out ov;
+  rc = view_as_f32(ctx, x, &xv);
+  if (!rc) rc = out_as_f32(ctx, o, &ov);
+  if (rc) {
+    release_view(ctx, &xv);
+    return finish_out(ctx, &ov, rc);
+  }
+  auto done = [&](int status) {
+    release_view(ctx, &xv);
+    return finish_out(ctx, &ov, status);
+  };
+  if (pointwise && ci->inChannels > 0)
+    return done(gemm_dispatch(ctx, xv.ptr, pixels, ci->inChannels, w, 0, false, true, ov.ptr, ci->outChannels, e));
   // Cin a multiple of 32 at stride 1: each filter tap's A tile is one TMA load of the shifted
-  // output patch, no gather threads (TF32; 3xTF32 and strided shapes take the gather path below).
+  // output patch (TF32; 3xTF32 and strided shapes take the gather path below).
   if (ctx->use_tensor_cores && conv_tma_tcgen05_supported(*ci, e.activation, ctx->math_mode)) {
     PackedWeights pw;
     bool temporary;
     rc = packed_weights(ctx, w, 0, (int64_t)ci->filterHeight * ci->filterWidth * ci->inChannels,
                         ci->outChannels, false, true, &pw, &temporary);
-    if (rc) return rc;
-    return launch_conv_tma_tcgen05(ctx, (const float*)x->ptr, *ci, pw.hi, pw.kp, (float*)o->ptr, e);
+    if (rc) return done(rc);
+    return done(launch_conv_tma_tcgen05(ctx, xv.ptr, *ci, pw.hi, pw.kp, ov.ptr, e));
   }
+  // Everything else with Cin % 4 == 0 (or a 3-channel, 3-wide filter) is an implicit GEMM: the
+  // A tile is gathered from the image by the kernel itself, K = fH * fW * Cin.
   const int mode = ctx->use_tensor_cores ? tcgen05_conv_mode(*ci) : 0;
   if (mode) {
     const int64_t K = (int64_t)ci->filterHeight * ci->filterWidth * ci->inChannels;
@@ -282,14 +387,13 @@ extern "C" int tfjs_cuda_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_te
     rc = packed_weights(ctx, w, 0, K, ci->outChannels, false, true, &pw, &temporary,
                         rgb ? ci->filterWidth * ci->inChannels : 0, rgb ? 10 : 0,
                         rgb ? tcgen05_conv_k(*ci, mode) : 0);
-    if (rc) return rc;
-    return launch_conv_tcgen05(ctx, mode, (const float*)x->ptr, *ci, pw.hi, pw.lo, pw.kp, (float*)o->ptr, e,
-                               ctx->math_mode);
+    if (rc) return done(rc);
+    return done(launch_conv_tcgen05(ctx, mode, xv.ptr, *ci, pw.hi, pw.lo, pw.kp, ov.ptr, e, ctx->math_mode));
   }
   const float* wf;
   rc = float_view(ctx, w, &wf);
-  if (rc) return rc;
-  return launch_conv2d_direct(ctx, (const float*)x->ptr, wf, (float*)o->ptr, *ci, e);
+  if (rc) return done(rc);
+  return done(launch_conv2d_direct(ctx, xv.ptr, wf, ov.ptr, *ci, e));
 }
 
 extern "C" int tfjs_cuda_depthwise_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_tensor_id w_id,
@@ -302,13 +406,12 @@ extern "C" int tfjs_cuda_depthwise_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_i
                "depthwise outChannels must be a multiple of inChannels");
   const int64_t out_n = (int64_t)ci->batchSize * ci->outHeight * ci->outWidth * ci->outChannels;
   TensorEntry *x, *w, *o;
-  rc = get_f32(ctx, x_id, (int64_t)ci->batchSize * ci->inHeight * ci->inWidth * ci->inChannels, "x", &x);
+  rc = get_activation(ctx, x_id, (int64_t)ci->batchSize * ci->inHeight * ci->inWidth * ci->inChannels, "x", &x);
   if (rc) return rc;
   rc = get_f32(ctx, w_id, (int64_t)ci->filterHeight * ci->filterWidth * ci->outChannels, "filter", &w);
   if (rc) return rc;
-  rc = get_f32(ctx, out_id, out_n, "depthwiseConv2D output", &o);
+  rc = get_activation(ctx, out_id, out_n, "depthwiseConv2D output", &o);
   if (rc) return rc;
-  TFJS_REQUIRE(ctx, !x->quant.quantized && !o->quant.quantized, "only the filter may be quantised");
   EpilogueArgs e;
   rc = resolve_epilogue(ctx, epi, ci->outChannels, &e);
   if (rc) return rc;
@@ -318,7 +421,15 @@ extern "C" int tfjs_cuda_depthwise_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_i
   const float* wf;
   rc = float_view(ctx, w, &wf);
   if (rc) return rc;
-  return launch_depthwise(ctx, (const float*)x->ptr, wf, (float*)o->ptr, *ci, e);
+  if (x->dtype == TFJS_F16 && o->dtype == TFJS_F16 && depthwise_half_native(*ci, e, x->ptr, wf, o->ptr))
+    return launch_depthwise_image(ctx, x->ptr, wf, o->ptr, *ci, e, true);
+  F32View xv;
+  F32Out ov;
+  rc = view_as_f32(ctx, x, &xv);
+  if (!rc) rc = out_as_f32(ctx, o, &ov);
+  if (!rc) rc = launch_depthwise(ctx, xv.ptr, wf, ov.ptr, *ci, e);
+  release_view(ctx, &xv);
+  return finish_out(ctx, &ov, rc);
 }
 
 extern "C" int tfjs_cuda_pool2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_tensor_id out_id,
@@ -328,15 +439,23 @@ extern "C" int tfjs_cuda_pool2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_te
   if (rc) return rc;
   const int64_t out_n = (int64_t)ci->batchSize * ci->outHeight * ci->outWidth * ci->inChannels;
   TensorEntry *x, *o;
-  rc = get_f32(ctx, x_id, (int64_t)ci->batchSize * ci->inHeight * ci->inWidth * ci->inChannels, "x", &x);
+  rc = get_activation(ctx, x_id, (int64_t)ci->batchSize * ci->inHeight * ci->inWidth * ci->inChannels, "x", &x);
   if (rc) return rc;
-  rc = get_f32(ctx, out_id, out_n, "pool output", &o);
+  rc = get_activation(ctx, out_id, out_n, "pool output", &o);
   if (rc) return rc;
-  TFJS_REQUIRE(ctx, !x->quant.quantized, "pooling takes float tensors");
   o->version++;
   if (out_n == 0) return TFJS_CUDA_OK;
   cudaSetDevice(ctx->device);
-  return launch_pool2d(ctx, (const float*)x->ptr, (float*)o->ptr, *ci, is_avg);
+  // the network's global average pool reads half storage directly (its result is float32)
+  if (x->dtype == TFJS_F16 && o->dtype == TFJS_F32 && global_avgpool_half_supported(*ci, is_avg, x->ptr, o->ptr))
+    return launch_global_avgpool_half(ctx, x->ptr, (float*)o->ptr, *ci);
+  F32View xv;
+  F32Out ov;
+  rc = view_as_f32(ctx, x, &xv);
+  if (!rc) rc = out_as_f32(ctx, o, &ov);
+  if (!rc) rc = launch_pool2d(ctx, xv.ptr, ov.ptr, *ci, is_avg);
+  release_view(ctx, &xv);
+  return finish_out(ctx, &ov, rc);
 }
 
 // y = pw_act(conv1x1(dw_act(depthwise(x, dw_filter) + dw_bias), pw_filter) + pw_bias).  Shapes the
@@ -356,15 +475,14 @@ extern "C" int tfjs_cuda_separable_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_i
   const int64_t pixels = (int64_t)dw->batchSize * dw->outHeight * dw->outWidth;
   const int64_t C = dw->outChannels, N = out_channels;
   TensorEntry *x, *wd, *wp, *o;
-  rc = get_f32(ctx, x_id, (int64_t)dw->batchSize * dw->inHeight * dw->inWidth * dw->inChannels, "x", &x);
+  rc = get_activation(ctx, x_id, (int64_t)dw->batchSize * dw->inHeight * dw->inWidth * dw->inChannels, "x", &x);
   if (rc) return rc;
   rc = get_f32(ctx, dw_filter_id, (int64_t)dw->filterHeight * dw->filterWidth * C, "depthwise filter", &wd);
   if (rc) return rc;
   rc = get_f32(ctx, pw_filter_id, C * N, "pointwise filter", &wp);
   if (rc) return rc;
-  rc = get_f32(ctx, out_id, pixels * N, "separableConv2d output", &o);
+  rc = get_activation(ctx, out_id, pixels * N, "separableConv2d output", &o);
   if (rc) return rc;
-  TFJS_REQUIRE(ctx, !x->quant.quantized && !o->quant.quantized, "only the filters may be quantised");
   EpilogueArgs de, pe;
   rc = resolve_epilogue(ctx, dw_epi, C, &de);
   if (rc) return rc;
@@ -376,6 +494,8 @@ extern "C" int tfjs_cuda_separable_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_i
   const float* wdf;
   rc = float_view(ctx, wd, &wdf);
   if (rc) return rc;
+  TFJS_REQUIRE(ctx, C > 0, "separableConv2d needs at least one channel");
+  const bool half = x->dtype == TFJS_F16 && o->dtype == TFJS_F16;
   // fuse_separable: 1 fuses where it measures faster than the two kernels (up to 128 channels, and
   // 256 channels at stride 1; at 256 channels and stride 2 the shared memory left beside the
   // weight stages holds too few input windows to cover the DRAM latency), 2 wherever it can
@@ -385,28 +505,68 @@ extern "C" int tfjs_cuda_separable_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_i
   // (backend_cpu.ts:2002-2014).  The two agree unless a tap is inf or NaN (0 * inf = NaN), so the
   // fused kernel is taken only for a filter the host wrote with finite values; any other filter
   // goes through the depthwise kernels, which skip those taps.
-  if (ctx->use_tensor_cores && ctx->fuse_separable && (ctx->fuse_separable >= 2 || pays) && known_finite(wd) &&
-      sepconv_tcgen05_supported(*dw, N, de.activation, pe.activation, ctx->math_mode)) {
+  // With half storage the arithmetic is TF32 whatever the math mode says: 16-bit storage is the
+  // 16-bit precision class.
+  const int fused_math = half ? TFJS_MATH_TF32 : ctx->math_mode;
+  if ((half || (x->dtype == TFJS_F32 && o->dtype == TFJS_F32)) && ctx->use_tensor_cores && ctx->fuse_separable &&
+      (ctx->fuse_separable >= 2 || pays) && known_finite(wd) &&
+      sepconv_tcgen05_supported(*dw, N, de.activation, pe.activation, fused_math)) {
     PackedWeights pw;
     bool temporary;
     rc = packed_weights(ctx, wp, 0, C, N, false, true, &pw, &temporary);
     if (rc) return rc;
-    return launch_sepconv_tcgen05(ctx, (const float*)x->ptr, *dw, wdf, de, pw.hi, pw.kp, (float*)o->ptr, N, pe);
+    return launch_sepconv_tcgen05(ctx, x->ptr, *dw, wdf, de, pw.hi, pw.kp, o->ptr, N, pe, half);
   }
-  TFJS_REQUIRE(ctx, C > 0, "separableConv2d needs at least one channel");
-  void* mid;
-  size_t mid_cap;
-  rc = ctx_alloc(ctx, (size_t)(pixels * C) * 4, &mid, &mid_cap);
-  if (rc) return rc;
-  // The intermediate is private to this call.  When a TF32 tensor-core GEMM reads it, the depthwise
-  // kernel rounds its results to tf32 as it stores them (the fused kernel rounds the same values as
-  // it builds its A tile), so the GEMM needs no rounding pass of its own.
-  const bool round_mid = ctx->use_tensor_cores && ctx->math_mode == TFJS_MATH_TF32 &&
-                         tcgen05_gemm_supported(pixels, N, C);
-  de.round_tf32 = round_mid ? 1 : 0;
-  rc = launch_depthwise(ctx, (const float*)x->ptr, wdf, (float*)mid, *dw, de);
-  if (!rc)
-    rc = gemm_dispatch(ctx, (const float*)mid, pixels, C, wp, 0, false, true, (float*)o->ptr, N, pe, round_mid);
-  ctx_free(ctx, mid, mid_cap);
-  return rc;
+  // Half storage, two kernels: whole-image depthwise into a half intermediate, f16 tensor-core GEMM.
+  if (half && ctx->use_tensor_cores && pe.activation != TFJS_ACT_PRELU &&
+      tcgen05_gemm_f16_supported(pixels, N, C, true)) {
+    void* mid;
+    size_t mid_cap;
+    rc = ctx_alloc(ctx, (size_t)(pixels * C) * 2, &mid, &mid_cap);
+    if (rc) return rc;
+    if (depthwise_half_native(*dw, de, x->ptr, wdf, mid)) {
+      rc = launch_depthwise_image(ctx, x->ptr, wdf, mid, *dw, de, true);
+    } else {
+      // no half depthwise kernel for this shape: float32 depthwise on a converted copy
+      F32View xv;
+      void* mid32 = nullptr;
+      size_t mid32_cap = 0;
+      rc = view_as_f32(ctx, x, &xv);
+      if (!rc) rc = ctx_alloc(ctx, (size_t)(pixels * C) * 4, &mid32, &mid32_cap);
+      if (!rc) rc = launch_depthwise(ctx, xv.ptr, wdf, (float*)mid32, *dw, de);
+      if (!rc) rc = launch_convert(ctx, mid32, TFJS_F32, mid, TFJS_F16, pixels * C);
+      release_view(ctx, &xv);
+      if (mid32) ctx_free(ctx, mid32, mid32_cap);
+    }
+    if (!rc) {
+      const void* plane;
+      int64_t kp;
+      rc = half_weights(ctx, wp, C, N, &plane, &kp);
+      if (!rc) rc = launch_gemm_tcgen05_f16(ctx, mid, pixels, C, plane, kp, o->ptr, true, N, pe);
+    }
+    ctx_free(ctx, mid, mid_cap);
+    return rc;
+  }
+  // float32 storage (or a mix of storages, through converted temporaries)
+  F32View xv;
+  F32Out ov;
+  rc = view_as_f32(ctx, x, &xv);
+  if (!rc) rc = out_as_f32(ctx, o, &ov);
+  void* mid = nullptr;
+  size_t mid_cap = 0;
+  if (!rc) rc = ctx_alloc(ctx, (size_t)(pixels * C) * 4, &mid, &mid_cap);
+  if (!rc) {
+    // The intermediate is private to this call.  When a TF32 tensor-core GEMM reads it, the depthwise
+    // kernel rounds its results to tf32 as it stores them (the fused kernel rounds the same values as
+    // it builds its A tile), so the GEMM needs no rounding pass of its own.
+    const bool round_mid = ctx->use_tensor_cores && ctx->math_mode == TFJS_MATH_TF32 &&
+                           tcgen05_gemm_supported(pixels, N, C);
+    de.round_tf32 = round_mid ? 1 : 0;
+    rc = launch_depthwise(ctx, xv.ptr, wdf, (float*)mid, *dw, de);
+    if (!rc)
+      rc = gemm_dispatch(ctx, (const float*)mid, pixels, C, wp, 0, false, true, ov.ptr, N, pe, round_mid);
+  }
+  if (mid) ctx_free(ctx, mid, mid_cap);
+  release_view(ctx, &xv);
+  return finish_out(ctx, &ov, rc);
 }

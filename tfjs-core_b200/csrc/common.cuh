@@ -57,6 +57,12 @@ struct TensorEntry {
   int64_t packed_q_n = 0, packed_q_k = 0, packed_q_kq = 0;
   uint64_t packed_q_version = 0;
   bool packed_q_transposed = false;
+  // K-major IEEE half plane [N, kp] of a contraction operand, for the kind::f16 kernel that
+  // serves 16-bit activation storage
+  void* w16 = nullptr;
+  size_t w16_capacity = 0;
+  int64_t w16_n = 0, w16_k = 0, w16_kp = 0;
+  uint64_t w16_version = ~0ull;
   // asynchronous upload in flight on the copy stream (tensor_write_async)
   cudaEvent_t copy_event = nullptr;
   bool copy_pending = false;
@@ -179,6 +185,12 @@ inline bool known_finite(const TensorEntry* t) { return t->finite_version == t->
 int get_f32(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, int64_t min_elems, const char* what,
             TensorEntry** out);
 
+// An activation operand: float32 or half-precision storage.
+int get_activation(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, int64_t min_elems, const char* what,
+                   TensorEntry** out);
+// elementwise.cu: dst[i] = convert(src[i]) between the storage dtypes (float32, int32, bool, float16)
+int launch_convert(tfjs_cuda_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n);
+
 static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 // Epilogue resolved to device pointers, passed by value to kernels.
@@ -290,6 +302,15 @@ bool tcgen05_gemm_supported(int64_t M, int64_t N, int64_t K);
 int launch_gemm_tcgen05(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K,
                         const float* w_hi, const float* w_lo, int64_t kp, float* out, int64_t N,
                         const EpilogueArgs& epi, int math_mode, bool a_tf32_exact = false);
+// The contraction on IEEE half operands (16-bit activation storage): a is [M, K] half, w16 the
+// K-major half plane [N, kp] (kp a multiple of 8, zero padded), out is float32 or half.
+bool tcgen05_gemm_f16_supported(int64_t M, int64_t N, int64_t K, bool out16);
+int launch_gemm_tcgen05_f16(tfjs_cuda_ctx* ctx, const void* a, int64_t M, int64_t K, const void* w16, int64_t kp,
+                            void* out, bool out16, int64_t N, const EpilogueArgs& epi);
+// K-major half plane [N, kp] of a [K, N] operand addressed through strides (float32 or uint8 source)
+int launch_pack_weights_f16(tfjs_cuda_ctx* ctx, const void* src, bool src_is_u8, double scale, double min,
+                            int64_t K, int64_t N, int64_t src_k_stride, int64_t src_n_stride, int64_t kp,
+                            void* dst);
 // Same contraction with the weights as K-major uint8 [N, kq] (kq a multiple of 16, zero
 // padded): w = q*scale + min is evaluated in shared memory inside the main loop.
 int launch_gemm_tcgen05_u8(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K,
@@ -307,12 +328,13 @@ int launch_conv_tcgen05(tfjs_cuda_ctx* ctx, int mode, const float* x, const tfjs
 // the two kernels back to back).
 bool sepconv_tcgen05_supported(const tfjs_conv2d_info& dw, int64_t N, int dw_activation, int pw_activation,
                                int math_mode);
-int launch_sepconv_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& dw, const float* dw_filter,
-                           const EpilogueArgs& dw_epi, const float* w_hi, int64_t kp, float* y, int64_t N,
-                           const EpilogueArgs& pw_epi);
+// half: x and y are stored as IEEE half (16-bit activation storage); weights and biases are float32
+int launch_sepconv_tcgen05(tfjs_cuda_ctx* ctx, const void* x, const tfjs_conv2d_info& dw, const float* dw_filter,
+                           const EpilogueArgs& dw_epi, const float* w_hi, int64_t kp, void* y, int64_t N,
+                           const EpilogueArgs& pw_epi, bool half = false);
 bool conv_rgb_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode);
 int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& ci, const float* w_hi,
-                            int64_t kp, float* y, const EpilogueArgs& epi);
+                            int64_t kp, void* y, const EpilogueArgs& epi, bool out_half = false);
 bool conv_tma_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode);
 int launch_conv_tma_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& ci, const float* w_hi,
                             int64_t kp, float* y, const EpilogueArgs& epi);
@@ -320,10 +342,14 @@ int launch_conv_tma_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2
 int launch_conv2d_direct(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* y,
                          const tfjs_conv2d_info& ci, const EpilogueArgs& epi);
 // 3x3 depthwise on 14x14 / 7x7 images through whole-image TMA windows (depthwise_tma.cu)
-bool depthwise_image_supported(const tfjs_conv2d_info& ci, int activation);
-int launch_depthwise_image(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* y, const tfjs_conv2d_info& ci,
-                           const EpilogueArgs& epi);
+// half: x and y are stored as IEEE half (16-bit activation storage); the filter and bias stay float32
+bool depthwise_image_supported(const tfjs_conv2d_info& ci, int activation, bool half = false);
+int launch_depthwise_image(tfjs_cuda_ctx* ctx, const void* x, const float* w, void* y, const tfjs_conv2d_info& ci,
+                           const EpilogueArgs& epi, bool half = false);
 int launch_depthwise(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* y,
                      const tfjs_conv2d_info& ci, const EpilogueArgs& epi);
 int launch_pool2d(tfjs_cuda_ctx* ctx, const float* x, float* y, const tfjs_conv2d_info& ci,
                   int is_avg);
+// global average pool (window = whole image) of a half-stored image into float32
+bool global_avgpool_half_supported(const tfjs_conv2d_info& ci, int is_avg, const void* x, const void* y);
+int launch_global_avgpool_half(tfjs_cuda_ctx* ctx, const void* x, float* y, const tfjs_conv2d_info& ci);

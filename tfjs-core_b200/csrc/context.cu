@@ -245,6 +245,8 @@ static void free_entry_buffers(tfjs_cuda_ctx* ctx, TensorEntry& t) {
   t.deq = nullptr;
   if (t.packed_q) ctx_free(ctx, t.packed_q, t.packed_q_capacity);
   t.packed_q = nullptr;
+  if (t.w16) ctx_free(ctx, t.w16, t.w16_capacity);
+  t.w16 = nullptr;
   if (t.copy_event) {
     // the buffer goes back to the pool: later users are ordered on the compute stream only
     if (t.copy_pending) cudaStreamWaitEvent(ctx->stream, t.copy_event, 0);
@@ -419,7 +421,7 @@ TensorEntry* find_tensor(tfjs_cuda_ctx* ctx, tfjs_tensor_id id) {
   return it == ctx->tensors.end() ? nullptr : &it->second;
 }
 
-static size_t dtype_size(int dtype) { return dtype == TFJS_BOOL ? 1 : 4; }
+static size_t dtype_size(int dtype) { return dtype == TFJS_BOOL ? 1 : (dtype == TFJS_F16 ? 2 : 4); }
 
 // Records whether the values the host just handed over are all finite (small float tensors only:
 // filters and biases; an image batch is not scanned).
@@ -436,7 +438,7 @@ static int register_impl(tfjs_cuda_ctx* ctx, tfjs_tensor_id* out_id, int rank, c
                          int dtype, size_t elem_size) {
   TFJS_REQUIRE(ctx, out_id != nullptr, "out_id is null");
   TFJS_REQUIRE(ctx, rank >= 0 && rank <= 8, "rank %d out of range", rank);
-  TFJS_REQUIRE(ctx, dtype == TFJS_F32 || dtype == TFJS_I32 || dtype == TFJS_BOOL,
+  TFJS_REQUIRE(ctx, dtype == TFJS_F32 || dtype == TFJS_I32 || dtype == TFJS_BOOL || dtype == TFJS_F16,
                "unsupported dtype %d", dtype);
   TensorEntry t;
   t.dtype = dtype;
@@ -493,12 +495,30 @@ extern "C" int tfjs_cuda_tensor_write(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, con
   // backend_cpu.ts:125-127: writing null throws
   TFJS_REQUIRE(ctx, host != nullptr || nbytes == 0, "MathBackendCUDA.write(): values cannot be null");
   TFJS_REQUIRE(ctx, !t->quant.quantized, "cannot write float values into a quantised tensor");
-  TFJS_REQUIRE(ctx, nbytes == t->nbytes, "write: %zu bytes given, tensor holds %zu", nbytes, t->nbytes);
   cudaSetDevice(ctx->device);
   if (t->copy_pending) {  // an earlier asynchronous upload must not land after this one
     TFJS_CHECK_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, t->copy_event, 0));
     t->copy_pending = false;
   }
+  if (t->dtype == TFJS_F16) {
+    // half-precision storage: the host hands over float32 values, converted on the device
+    TFJS_REQUIRE(ctx, nbytes == (size_t)t->size * 4, "write: %zu bytes given, tensor holds %zu float32 values",
+                 nbytes, (size_t)t->size);
+    if (nbytes) {
+      void* tmp;
+      size_t cap;
+      int rc = ctx_alloc(ctx, nbytes, &tmp, &cap);
+      if (rc) return rc;
+      cudaError_t e = cudaMemcpyAsync(tmp, host, nbytes, cudaMemcpyHostToDevice, ctx->stream);
+      rc = e == cudaSuccess ? launch_convert(ctx, tmp, TFJS_F32, t->ptr, TFJS_F16, t->size)
+                            : set_error(ctx, TFJS_CUDA_ERR_CUDA, "write failed: %s", cudaGetErrorString(e));
+      ctx_free(ctx, tmp, cap);
+      if (rc) return rc;
+    }
+    t->version++;
+    return TFJS_CUDA_OK;
+  }
+  TFJS_REQUIRE(ctx, nbytes == t->nbytes, "write: %zu bytes given, tensor holds %zu", nbytes, t->nbytes);
   if (nbytes)
     TFJS_CHECK_CUDA(ctx, cudaMemcpyAsync(t->ptr, host, nbytes, cudaMemcpyHostToDevice, ctx->stream));
   t->version++;
@@ -523,6 +543,7 @@ extern "C" int tfjs_cuda_tensor_write_async(tfjs_cuda_ctx* ctx, tfjs_tensor_id i
   if (!t) return set_error(ctx, TFJS_CUDA_ERR_NOT_FOUND, "write: unknown tensor id %lld", (long long)id);
   TFJS_REQUIRE(ctx, host != nullptr || nbytes == 0, "MathBackendCUDA.write(): values cannot be null");
   TFJS_REQUIRE(ctx, !t->quant.quantized, "cannot write float values into a quantised tensor");
+  TFJS_REQUIRE(ctx, t->dtype != TFJS_F16, "asynchronous writes need float32 storage (use tensor_write)");
   TFJS_REQUIRE(ctx, nbytes == t->nbytes, "write: %zu bytes given, tensor holds %zu", nbytes, t->nbytes);
   TFJS_REQUIRE(ctx, !ctx->capturing, "asynchronous writes cannot be captured into a graph");
   cudaSetDevice(ctx->device);
@@ -555,7 +576,8 @@ extern "C" int tfjs_cuda_tensor_wait(tfjs_cuda_ctx* ctx, tfjs_tensor_id id) {
 static int enqueue_read(tfjs_cuda_ctx* ctx, TensorEntry* t, void* host, size_t nbytes) {
   int wrc = wait_for_upload(ctx, t);
   if (wrc) return wrc;
-  if (t->quant.quantized) {
+  if (t->quant.quantized || t->dtype == TFJS_F16) {
+    // stored narrower than float32: the host gets float32 values, expanded on the device
     TFJS_REQUIRE(ctx, nbytes == (size_t)t->size * 4, "read: %zu bytes asked, tensor holds %zu",
                  nbytes, (size_t)t->size * 4);
     if (!nbytes) return TFJS_CUDA_OK;
@@ -563,7 +585,9 @@ static int enqueue_read(tfjs_cuda_ctx* ctx, TensorEntry* t, void* host, size_t n
     size_t cap;
     int rc = ctx_alloc(ctx, nbytes, &tmp, &cap);
     if (rc) return rc;
-    rc = launch_dequant(ctx, (const uint8_t*)t->ptr, (float*)tmp, t->size, t->quant.scale, t->quant.min);
+    rc = t->quant.quantized
+             ? launch_dequant(ctx, (const uint8_t*)t->ptr, (float*)tmp, t->size, t->quant.scale, t->quant.min)
+             : launch_convert(ctx, t->ptr, TFJS_F16, tmp, TFJS_F32, t->size);
     if (!rc) {
       cudaError_t e = cudaMemcpyAsync(host, tmp, nbytes, cudaMemcpyDeviceToHost, ctx->stream);
       if (e != cudaSuccess) rc = set_error(ctx, TFJS_CUDA_ERR_CUDA, "read failed: %s", cudaGetErrorString(e));
@@ -687,6 +711,20 @@ int get_f32(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, int64_t min_elems, const char
                (long long)t->size, (long long)min_elems);
   *out = t;
   return wait_for_upload(ctx, t);  // kernels that take this operand run after its upload
+}
+
+// Same for an activation operand, which may be stored as float32 or as half precision.
+int get_activation(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, int64_t min_elems, const char* what,
+                   TensorEntry** out) {
+  TensorEntry* t = find_tensor(ctx, id);
+  if (!t) return set_error(ctx, TFJS_CUDA_ERR_NOT_FOUND, "%s: unknown tensor id %lld", what, (long long)id);
+  TFJS_REQUIRE(ctx, t->dtype == TFJS_F32 || t->dtype == TFJS_F16,
+               "%s must be stored as float32 or float16 (cast it first)", what);
+  TFJS_REQUIRE(ctx, !t->quant.quantized, "%s cannot be a quantised tensor", what);
+  TFJS_REQUIRE(ctx, t->size >= min_elems, "%s holds %lld elements, %lld needed", what,
+               (long long)t->size, (long long)min_elems);
+  *out = t;
+  return wait_for_upload(ctx, t);
 }
 
 int resolve_epilogue(tfjs_cuda_ctx* ctx, const tfjs_epilogue* epi, int64_t channels,

@@ -6,6 +6,8 @@
 // float32 (fmaf), which reproduces `y[i] += x * w` on a Float32Array except for rare
 // double-rounding cases.  The results are therefore (almost always) bit-identical to the
 // reference's.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace {
@@ -482,8 +484,15 @@ pool2d_vec4_kernel(const float4* __restrict__ x, float4* __restrict__ y, tfjs_co
       }
     }
     if (IS_AVG) {
-      const double n = (double)count;
-      mm = make_float4((float)(s0 / n), (float)(s1 / n), (float)(s2 / n), (float)(s3 / n));
+      if ((count & (count - 1)) == 0) {
+        // 1, 2, 4, 8 ... taps: the reciprocal is a power of two, so multiplying by it is the exact
+        // float64 quotient the reference computes, without the long division sequence
+        const double r = 1.0 / (double)count;
+        mm = make_float4((float)(s0 * r), (float)(s1 * r), (float)(s2 * r), (float)(s3 * r));
+      } else {
+        const double n = (double)count;
+        mm = make_float4((float)(s0 / n), (float)(s1 / n), (float)(s2 / n), (float)(s3 / n));
+      }
     }
     y[t] = mm;
   }
@@ -648,6 +657,30 @@ int launch_depthwise(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* 
   return post_launch(ctx, "depthwiseConv2D (generic)");
 }
 
+// The same pool over an image stored as IEEE half: a thread owns 4 channels (8 bytes per tap),
+// sums tap by tap in float64 in the reference's order, and writes float32.
+__global__ void global_avgpool_half_kernel(const uint2* __restrict__ x, float4* __restrict__ y, int batch, int hw,
+                                           int C4) {
+  const int64_t total = (int64_t)batch * C4;
+  pdl_wait();
+  pdl_launch_dependents();
+  for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total;
+       t += (int64_t)gridDim.x * blockDim.x) {
+    const int d = (int)(t % C4);
+    const int b = (int)(t / C4);
+    const uint2* p = x + (int64_t)b * hw * C4 + d;
+    double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+    for (int i = 0; i < hw; i++) {
+      const uint2 h = __ldg(p + (int64_t)i * C4);
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&h.x));
+      const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&h.y));
+      s0 += (double)a.x; s1 += (double)a.y; s2 += (double)c.x; s3 += (double)c.y;
+    }
+    const double n = (double)hw;
+    y[t] = make_float4((float)(s0 / n), (float)(s1 / n), (float)(s2 / n), (float)(s3 / n));
+  }
+}
+
 // Global average pool through shared memory: a block stages the hw x 256-channel slab of one image
 // with 16-byte asynchronous copies (every copy of the block in flight at once, which is what a
 // small batch needs to cover the memory latency), then thread c sums channel c tap by tap in
@@ -679,6 +712,19 @@ __global__ void __launch_bounds__(AVG_SLAB_CH) global_avgpool_slab_kernel(const 
     for (int i = 0; i < hw; i++) s += (double)slab[i * AVG_SLAB_CH + threadIdx.x];
     y[(int64_t)b * C + c0 + threadIdx.x] = (float)(s / (double)hw);
   }
+}
+
+bool global_avgpool_half_supported(const tfjs_conv2d_info& ci, int is_avg, const void* x, const void* y) {
+  return is_avg && ci.outHeight == 1 && ci.outWidth == 1 && ci.padTop == 0 && ci.padLeft == 0 &&
+         ci.dilationHeight == 1 && ci.dilationWidth == 1 && ci.filterHeight == ci.inHeight &&
+         ci.filterWidth == ci.inWidth && ci.inChannels % 4 == 0 && ((uintptr_t)x & 7) == 0 && ((uintptr_t)y & 15) == 0;
+}
+
+int launch_global_avgpool_half(tfjs_cuda_ctx* ctx, const void* x, float* y, const tfjs_conv2d_info& ci) {
+  const int64_t total = (int64_t)ci.batchSize * (ci.inChannels / 4);
+  launch_ex(ctx, global_avgpool_half_kernel, dim3(grid_1d(total, 64, ctx->sm_count, 32)), dim3(64), 0,
+            (const uint2*)x, (float4*)y, ci.batchSize, ci.inHeight * ci.inWidth, ci.inChannels / 4);
+  return post_launch(ctx, "avgPool (global, float16 in)");
 }
 
 int launch_pool2d(tfjs_cuda_ctx* ctx, const float* x, float* y, const tfjs_conv2d_info& ci,

@@ -4,6 +4,8 @@
 // are single float32 operations (a float64 op on two float32 values, rounded once, is the
 // float32 op); exp/log are evaluated in float64 and rounded once, like Math.exp/Math.log
 // stored into a Float32Array; sum accumulates in float64.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace {
@@ -134,11 +136,32 @@ __global__ void cast_kernel(const void* __restrict__ src, int src_dtype, void* _
        i += (int64_t)gridDim.x * blockDim.x) {
     float v;
     if (src_dtype == TFJS_F32) v = ((const float*)src)[i];
+    else if (src_dtype == TFJS_F16) v = __half2float(((const __half*)src)[i]);
     else if (src_dtype == TFJS_I32) v = (float)((const int32_t*)src)[i];
     else v = ((const uint8_t*)src)[i] ? 1.f : 0.f;
     if (dst_dtype == TFJS_F32) ((float*)dst)[i] = v;
+    else if (dst_dtype == TFJS_F16) ((__half*)dst)[i] = __float2half_rn(v);
     else if (dst_dtype == TFJS_I32) ((int32_t*)dst)[i] = (src_dtype == TFJS_F32) ? (int32_t)v : (int32_t)v;
     else ((uint8_t*)dst)[i] = (v != 0.f) ? 1 : 0;
+  }
+}
+
+// float32 <-> float16, 8 elements (16 / 32 bytes) per thread step
+__global__ void convert_half_kernel(const void* __restrict__ src, void* __restrict__ dst, int to_half, int64_t n8) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    if (to_half) {
+      const float4 a = ((const float4*)src)[2 * i], b = ((const float4*)src)[2 * i + 1];
+      __half2 h[4] = {__floats2half2_rn(a.x, a.y), __floats2half2_rn(a.z, a.w), __floats2half2_rn(b.x, b.y),
+                      __floats2half2_rn(b.z, b.w)};
+      ((uint4*)dst)[i] = *reinterpret_cast<uint4*>(h);
+    } else {
+      uint4 raw = ((const uint4*)src)[i];
+      const __half2* h = reinterpret_cast<const __half2*>(&raw);
+      const float2 p0 = __half22float2(h[0]), p1 = __half22float2(h[1]), p2 = __half22float2(h[2]),
+                   p3 = __half22float2(h[3]);
+      ((float4*)dst)[2 * i] = make_float4(p0.x, p0.y, p1.x, p1.y);
+      ((float4*)dst)[2 * i + 1] = make_float4(p2.x, p2.y, p3.x, p3.y);
+    }
   }
 }
 
@@ -443,6 +466,18 @@ extern "C" int tfjs_cuda_unary(tfjs_cuda_ctx* ctx, int op, tfjs_tensor_id x_id,
   return post_launch(ctx, "unary");
 }
 
+int launch_convert(tfjs_cuda_ctx* ctx, const void* src, int src_dtype, void* dst, int dst_dtype, int64_t n) {
+  if (n == 0) return TFJS_CUDA_OK;
+  const bool halves = (src_dtype == TFJS_F32 && dst_dtype == TFJS_F16) || (src_dtype == TFJS_F16 && dst_dtype == TFJS_F32);
+  if (halves && n % 8 == 0 && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
+    convert_half_kernel<<<grid_for(n / 8, ctx->sm_count), kThreads, 0, ctx->stream>>>(src, dst, dst_dtype == TFJS_F16,
+                                                                                    n / 8);
+    return post_launch(ctx, "cast (float16)");
+  }
+  cast_kernel<<<grid_for(n, ctx->sm_count), kThreads, 0, ctx->stream>>>(src, src_dtype, dst, dst_dtype, n);
+  return post_launch(ctx, "cast");
+}
+
 extern "C" int tfjs_cuda_cast(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_tensor_id out_id) {
   if (!ctx) return TFJS_CUDA_ERR_INVALID_ARG;
   TensorEntry* x = find_tensor(ctx, x_id);
@@ -458,9 +493,7 @@ extern "C" int tfjs_cuda_cast(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_tens
     return launch_dequant(ctx, (const uint8_t*)x->ptr, (float*)o->ptr, x->size, x->quant.scale,
                           x->quant.min);
   }
-  cast_kernel<<<grid_for(x->size, ctx->sm_count), kThreads, 0, ctx->stream>>>(
-      x->ptr, x->dtype, o->ptr, o->dtype, x->size);
-  return post_launch(ctx, "cast");
+  return launch_convert(ctx, x->ptr, x->dtype, o->ptr, o->dtype, x->size);
 }
 
 extern "C" int tfjs_cuda_reduce_last(tfjs_cuda_ctx* ctx, int op, tfjs_tensor_id x_id,

@@ -1,5 +1,7 @@
 // CUDA-core GEMM for shapes the tensor-core kernel does not take, plus the operand
 // preparation kernels (weight repacking with tf32 hi/lo split, batched transpose).
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace {
@@ -98,6 +100,30 @@ __global__ void pack_weights_kernel(const void* __restrict__ src, int src_is_u8,
   }
 }
 
+// The same source as one K-major IEEE half plane [N, kp] (round to nearest even), for the
+// kind::f16 tensor-core kernel.
+__global__ void pack_weights_f16_kernel(const void* __restrict__ src, int src_is_u8, double scale, double mn,
+                                        int K, int N, int64_t k_stride, int64_t n_stride, int kp,
+                                        __half* __restrict__ dst) {
+  __shared__ float tile[32][33];
+  const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    int k, n;
+    if (n_stride == 1) { k = k0 + r; n = n0 + threadIdx.x; } else { n = n0 + r; k = k0 + threadIdx.x; }
+    float v = 0.f;
+    if (k < K && n < N) {
+      const int64_t off = k * k_stride + n * n_stride;
+      v = src_is_u8 ? (float)((double)((const uint8_t*)src)[off] * scale + mn) : ((const float*)src)[off];
+    }
+    tile[k - k0][n - n0] = v;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int n = n0 + r, k = k0 + threadIdx.x;
+    if (n < N && k < kp) dst[(int64_t)n * kp + k] = __float2half_rn(tile[threadIdx.x][r]);
+  }
+}
+
 // Repack for the Cin == 3 implicit-GEMM gather: destination column k' = wr * row_pad + j holds
 // source row k = wr * row_len + j for j < row_len and zero otherwise (each filter row of
 // row_len = fW * Cin values is padded to row_pad).  The operand is tiny (27 x N), one thread per
@@ -170,6 +196,16 @@ int launch_gemm_simt(tfjs_cuda_ctx* ctx, const float* a, const float* b, float* 
   gemm_simt_kernel<<<grid, 256, 0, ctx->stream>>>(a, b, out, M, N, K, a_batch, a_row, a_col, b_batch,
                                                   b_row, b_col, epi);
   return post_launch(ctx, "batchMatMul (CUDA cores)");
+}
+
+int launch_pack_weights_f16(tfjs_cuda_ctx* ctx, const void* src, bool src_is_u8, double scale, double mn,
+                            int64_t K, int64_t N, int64_t src_k_stride, int64_t src_n_stride, int64_t kp,
+                            void* dst) {
+  if (N * kp == 0) return TFJS_CUDA_OK;
+  dim3 grid((unsigned)ceil_div64(N, 32), (unsigned)ceil_div64(kp, 32));
+  pack_weights_f16_kernel<<<grid, dim3(32, 8), 0, ctx->stream>>>(src, src_is_u8 ? 1 : 0, scale, mn, (int)K, (int)N,
+                                                                 src_k_stride, src_n_stride, (int)kp, (__half*)dst);
+  return post_launch(ctx, "pack_weights (float16)");
 }
 
 int launch_pack_weights(tfjs_cuda_ctx* ctx, const void* src, bool src_is_u8, double scale,

@@ -102,19 +102,29 @@ constexpr int PREC_TF32_ASIS = 0;   // one pass; the caller guarantees A holds t
 constexpr int PREC_3XTF32 = 1;      // hi = rna(a), lo = rna(a - hi); three passes
 constexpr int PREC_TF32_ROUND = 2;  // one pass; helper warps round A to nearest (ties away) in
                                     // shared memory first, so that the operand error is unbiased
+constexpr int PREC_F16 = 3;         // A and W are IEEE half matrices (16-bit activation storage): one
+                                    // kind::f16 pass, a k-block is 64 elements (the same 128-byte rows)
 
-template <int BLOCK_N, int PREC, int AMODE, bool WQ>
-__global__ void __launch_bounds__(cta_threads(PREC != PREC_TF32_ASIS, AMODE, WQ), 1)
+// cta_threads' first argument: does the variant rewrite its A stages in shared memory
+__host__ __device__ constexpr bool converts_a(int prec) { return prec == PREC_3XTF32 || prec == PREC_TF32_ROUND; }
+
+// OUT16: the result is stored as IEEE half (rows of a 32-column chunk are 64 bytes, unswizzled)
+template <int BLOCK_N, int PREC, int AMODE, bool WQ, bool OUT16 = false>
+__global__ void __launch_bounds__(cta_threads(converts_a(PREC), AMODE, WQ), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_w_hi,
                     const __grid_constant__ CUtensorMap map_w_lo,
                     const __grid_constant__ CUtensorMap map_c, GemmParams p) {
   static_assert(!WQ || AMODE == A_MATRIX, "in-loop dequantisation is implemented for the matrix mode");
   static_assert(PREC != PREC_TF32_ROUND || AMODE == A_MATRIX, "the gather threads of the conv modes round their own rows");
+  static_assert(PREC != PREC_F16 || (AMODE == A_MATRIX && !WQ), "half operands: dense matrix mode only");
+  static_assert(!OUT16 || PREC == PREC_F16, "half output goes with half operands");
   constexpr bool SPLIT = PREC == PREC_3XTF32;
   constexpr bool ROUND = PREC == PREC_TF32_ROUND;
+  constexpr bool HALF = PREC == PREC_F16;
+  constexpr int KB_ELEMS = HALF ? 64 : BLOCK_K;  // elements per k-block: 128 bytes either way
   constexpr int STAGES = num_stages(BLOCK_N, SPLIT, WQ);
-  constexpr int NCONV = cta_threads(PREC != PREC_TF32_ASIS, AMODE, WQ) - 320;  // converter (or gather) threads
+  constexpr int NCONV = cta_threads(converts_a(PREC), AMODE, WQ) - 320;  // converter (or gather) threads
   constexpr int B_STAGE_BYTES = BLOCK_N * BLOCK_K * 4;
   constexpr int Q_STAGE_BYTES = BLOCK_N * BLOCK_K;  // uint8 tile
   // Two accumulator buffers (the epilogue drains one while the MMAs fill the other).  In 3xTF32
@@ -223,7 +233,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                : 0;
       int ptile = blockIdx.x, pkb = 0;
       for (int i = 0; i < PREFETCH && ptile < num_tiles; i++) {
-        tma_prefetch_2d(&map_a, pkb * BLOCK_K, (ptile / p.num_n_tiles) * BLOCK_M);
+        tma_prefetch_2d(&map_a, pkb * KB_ELEMS, (ptile / p.num_n_tiles) * BLOCK_M);
         if (++pkb == p.num_k_blocks) { pkb = 0; ptile += gridDim.x; }
       }
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -231,7 +241,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         const int n0 = (tile % p.num_n_tiles) * BLOCK_N;
         for (int kb = 0; kb < p.num_k_blocks; kb++) {
           if (PREFETCH > 0 && ptile < num_tiles) {
-            tma_prefetch_2d(&map_a, pkb * BLOCK_K, (ptile / p.num_n_tiles) * BLOCK_M);
+            tma_prefetch_2d(&map_a, pkb * KB_ELEMS, (ptile / p.num_n_tiles) * BLOCK_M);
             if (++pkb == p.num_k_blocks) { pkb = 0; ptile += gridDim.x; }
           }
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 1);
@@ -243,11 +253,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           const uint32_t bar = smem_u32(&full_bar[stage]);
           mbar_arrive_expect_tx(bar, TX_BYTES);
           if (AMODE == A_MATRIX)
-            tma_load_2d(smem_u32(a_hi + stage * A_STAGE_BYTES), &map_a, bar, kb * BLOCK_K, m0);
+            tma_load_2d(smem_u32(a_hi + stage * A_STAGE_BYTES), &map_a, bar, kb * KB_ELEMS, m0);
           if (WQ) {
             tma_load_2d(smem_u32(b_q + stage * Q_STAGE_BYTES), &map_w_hi, bar, kb * BLOCK_K, n0);
           } else {
-            tma_load_2d(smem_u32(b_hi + stage * B_STAGE_BYTES), &map_w_hi, bar, kb * BLOCK_K, n0);
+            tma_load_2d(smem_u32(b_hi + stage * B_STAGE_BYTES), &map_w_hi, bar, kb * KB_ELEMS, n0);
             if (SPLIT)
               tma_load_2d(smem_u32(b_lo + stage * B_STAGE_BYTES), &map_w_lo, bar, kb * BLOCK_K, n0);
           }
@@ -258,7 +268,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   } else if (warp == 9) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BLOCK_M, BLOCK_N);
+      constexpr uint32_t idesc = HALF ? make_idesc_f16(BLOCK_M, BLOCK_N) : make_idesc(BLOCK_M, BLOCK_N);
       int stage = 0;
       uint32_t phase = 0;
       int slot = 0;  // WQ: position in the ring of dequantised weight tiles
@@ -294,6 +304,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
               tcgen05_mma_tf32(tmem_corr, make_smem_desc(a_lo_s + koff), make_smem_desc(b_hi_s + koff), idesc, accum);
               tcgen05_mma_tf32(tmem_corr, make_smem_desc(a_hi_s + koff), make_smem_desc(b_lo_s + koff), idesc, 1u);
               tcgen05_mma_tf32(tmem_d, make_smem_desc(a_hi_s + koff), make_smem_desc(b_hi_s + koff), idesc, accum);
+            } else if (HALF) {  // 16 halves = the same 32 bytes per instruction
+              tcgen05_mma_f16(tmem_d, make_smem_desc(a_hi_s + koff), make_smem_desc(b_hi_s + koff), idesc, accum);
             } else {
               tcgen05_mma_tf32(tmem_d, make_smem_desc(a_hi_s + koff), make_smem_desc(b_hi_s + koff), idesc, accum);
             }
@@ -541,6 +553,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       const bool has_bias = p.epi.bias != nullptr;
       const bool has_alpha = p.epi.activation == TFJS_ACT_PRELU;
       int local = 0;
+      int store_parity = 0;  // OUT16: which half of the staging buffer the next chunk uses
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
         const int m0 = (tile / p.num_n_tiles) * BLOCK_M;
@@ -599,20 +612,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             case TFJS_ACT_CLIP: finish_chunk<TFJS_ACT_CLIP>(v, has_bias, bias_s, alpha_s, p.epi); break;
             default: finish_chunk<TFJS_ACT_LINEAR>(v, has_bias, bias_s, alpha_s, p.epi); break;
           }
-          // the staging buffer must have been read by this warp's previous TMA store
-          if (lane == 0) tma_store_wait_read<0>();
+          // the staging buffer must have been read by this warp's previous TMA store (a half
+          // chunk is 2 KB of the 4 KB buffer: its two halves alternate and one store may be pending)
+          if (lane == 0) {
+            if (OUT16) tma_store_wait_read<1>(); else tma_store_wait_read<0>();
+          }
           __syncwarp();
-          // SWIZZLE_128B placement expected by the store's tensor map: 16-byte chunk j of row
-          // `lane` lives at chunk (j ^ (lane & 7)).
-          uint8_t* dst = stage_buf + lane * 128;
+          if (OUT16) {
+            // half output: 32 columns are 64 bytes per row, stored unswizzled
+            store_parity ^= 1;
+            uint8_t* dst = stage_buf + store_parity * 2048 + lane * 64;
 #pragma unroll
-          for (int j = 0; j < 8; j++)
-            *reinterpret_cast<float4*>(dst + ((j ^ (lane & 7)) << 4)) =
-                make_float4(v[j * 4 + 0], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+            for (int j = 0; j < 4; j++)
+              *reinterpret_cast<uint4*>(dst + (j << 4)) =
+                  make_uint4(pack_half2(v[j * 8 + 0], v[j * 8 + 1]), pack_half2(v[j * 8 + 2], v[j * 8 + 3]),
+                             pack_half2(v[j * 8 + 4], v[j * 8 + 5]), pack_half2(v[j * 8 + 6], v[j * 8 + 7]));
+          } else {
+            // SWIZZLE_128B placement expected by the store's tensor map: 16-byte chunk j of row
+            // `lane` lives at chunk (j ^ (lane & 7)).
+            uint8_t* dst = stage_buf + lane * 128;
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+              *reinterpret_cast<float4*>(dst + ((j ^ (lane & 7)) << 4)) =
+                  make_float4(v[j * 4 + 0], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+          }
           fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA engine
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&map_c, smem_u32(stage_buf), c0, m0 + quarter * 32);
+            tma_store_2d(&map_c, smem_u32(stage_buf + (OUT16 ? store_parity * 2048 : 0)), c0, m0 + quarter * 32);
             tma_store_commit();
           }
         }
@@ -662,28 +689,30 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D row-major float32 matrix [rows, cols] (cols contiguous), box [box_rows, box_cols].
+// 2-D row-major matrix [rows, cols] (cols contiguous) of float32 or IEEE half, box [box_rows,
+// box_cols]; SWIZZLE_128B unless `plain`.
 bool encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
-               uint32_t box_cols) {
+               uint32_t box_cols, bool half = false, bool plain = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 4};
+  cuuint64_t strides[1] = {cols * (half ? 2 : 4)};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  return fn(map, half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            plain ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BLOCK_N, int PREC, int AMODE, bool WQ = false>
+template <int BLOCK_N, int PREC, int AMODE, bool WQ = false, bool OUT16 = false>
 int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mh, const CUtensorMap& ml,
                    const CUtensorMap& mc, const GemmParams& p) {
   constexpr bool SPLIT = PREC == PREC_3XTF32;
   constexpr int smem_bytes = wq_ring_bytes(BLOCK_N, SPLIT, WQ) + num_stages(BLOCK_N, SPLIT, WQ) * stage_bytes(BLOCK_N, SPLIT, WQ) + C_STAGING_BYTES +
                              BIAS_STAGING_BYTES + BARRIER_BYTES + 1024;
   static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
-  auto kernel = gemm_tcgen05_kernel<BLOCK_N, PREC, AMODE, WQ>;
+  auto kernel = gemm_tcgen05_kernel<BLOCK_N, PREC, AMODE, WQ, OUT16>;
   // the attribute is per device and per kernel; contexts of several devices may call from several
   // host threads, so the flags are atomic (setting the attribute twice is harmless)
   static std::atomic<bool> configured[64];
@@ -693,7 +722,8 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtensorMap&
   }
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-  launch_ex(ctx, kernel, dim3(grid), dim3(cta_threads(PREC != PREC_TF32_ASIS, AMODE, WQ)), smem_bytes, ma, mh, ml, mc, p);
+  launch_ex(ctx, kernel, dim3(grid), dim3(cta_threads(converts_a(PREC), AMODE, WQ)), smem_bytes, ma, mh, ml, mc, p);
+  if (PREC == PREC_F16) return post_launch(ctx, "gemm_tcgen05 (F16)");
   if (WQ) return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32, uint8 weights)" : "gemm_tcgen05 (TF32, uint8 weights)");
   if (AMODE == A_MATRIX) return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32)" : "gemm_tcgen05 (TF32)");
   return post_launch(ctx, SPLIT ? "conv2d_tcgen05 (3xTF32)" : "conv2d_tcgen05 (TF32)");
@@ -829,6 +859,58 @@ int launch_common(tfjs_cuda_ctx* ctx, int amode, const float* a, const ConvGeom*
   }
 }
 
+// A and W as IEEE half matrices (K-major W [N, kp], kp a multiple of 8); out is float32 or half.
+int launch_half(tfjs_cuda_ctx* ctx, const void* a, int64_t M, int64_t K, const void* w16, int64_t kp, void* out,
+                bool out16, int64_t N, const EpilogueArgs& epi) {
+  int block_n = N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : ((N % 256 == 0 || N > 512) ? 256 : 128)));
+  const int64_t m_tiles = ceil_div64(M, BLOCK_M);
+  if (m_tiles * ceil_div64(N, block_n) < 2 * (int64_t)ctx->sm_count) {
+    // the same waves x (k-blocks x operand bytes + epilogue) model as the float32 kernel
+    const int64_t k_blocks = ceil_div64(K, 64);
+    auto cost = [&](int bn) {
+      const int64_t waves = ceil_div64(m_tiles * ceil_div64(N, bn), ctx->sm_count);
+      return (double)waves * ((double)k_blocks * 2.9 * (BLOCK_M + bn) + 6.0 * bn + 600.0);
+    };
+    int best = block_n;
+    double best_cost = cost(block_n);
+    for (int bn = block_n / 2; bn >= 32; bn /= 2)
+      if (cost(bn) < 0.9 * best_cost) {
+        best = bn;
+        best_cost = cost(bn);
+      }
+    block_n = best;
+  }
+  CUtensorMap ma, mw, mc;
+  const bool ok = encode_2d(&ma, a, (uint64_t)M, (uint64_t)K, BLOCK_M, 64, true) &&
+                  encode_2d(&mw, w16, (uint64_t)N, (uint64_t)kp, (uint32_t)block_n, 64, true) &&
+                  (out16 ? encode_2d(&mc, out, (uint64_t)M, (uint64_t)N, 32, 32, true, true)
+                         : encode_2d(&mc, out, (uint64_t)M, (uint64_t)N, 32, 32));
+  if (!ok) return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = (int)M;
+  p.N = (int)N;
+  p.K = (int)K;
+  p.num_m_tiles = (int)m_tiles;
+  p.num_n_tiles = (int)ceil_div64(N, block_n);
+  p.num_k_blocks = (int)ceil_div64(K, 64);
+  p.status = ctx->d_status;
+  p.epi = epi;
+#define TFJS_HALF_CASE(BN)                                                                       \
+  case BN:                                                                                       \
+    return out16 ? launch_variant<BN, PREC_F16, A_MATRIX, false, true>(ctx, ma, mw, mw, mc, p)   \
+                 : launch_variant<BN, PREC_F16, A_MATRIX, false, false>(ctx, ma, mw, mw, mc, p);
+  switch (block_n) {
+    TFJS_HALF_CASE(32)
+    TFJS_HALF_CASE(64)
+    TFJS_HALF_CASE(128)
+    default:
+      return out16 ? launch_variant<256, PREC_F16, A_MATRIX, false, true>(ctx, ma, mw, mw, mc, p)
+                   : launch_variant<256, PREC_F16, A_MATRIX, false, false>(ctx, ma, mw, mw, mc, p);
+  }
+#undef TFJS_HALF_CASE
+}
+
 }  // namespace
 
 int set_wait_limit_gemm(long long cycles) { return set_wait_limit_here(cycles); }
@@ -860,6 +942,17 @@ int launch_gemm_tcgen05(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K
                         const float* w_lo, int64_t kp, float* out, int64_t N, const EpilogueArgs& epi,
                         int math_mode, bool a_tf32_exact) {
   return launch_common(ctx, A_MATRIX, a, nullptr, M, K, w_hi, w_lo, kp, out, N, epi, math_mode, a_tf32_exact);
+}
+
+bool tcgen05_gemm_f16_supported(int64_t M, int64_t N, int64_t K, bool out16) {
+  // TMA needs 16-byte row strides: 8 halves per row of A, W and (if half) the output
+  return M >= 1 && N >= 8 && K >= 8 && K % 8 == 0 && N % (out16 ? 8 : 4) == 0 && M < (1ll << 31) &&
+         N < (1ll << 31) && K < (1ll << 31) && get_encode_fn() != nullptr;
+}
+
+int launch_gemm_tcgen05_f16(tfjs_cuda_ctx* ctx, const void* a, int64_t M, int64_t K, const void* w16, int64_t kp,
+                            void* out, bool out16, int64_t N, const EpilogueArgs& epi) {
+  return launch_half(ctx, a, M, K, w16, kp, out, out16, N, epi);
 }
 
 // Matrix-mode GEMM whose weights are raw uint8 bytes, K-major [N, kq] (kq a multiple of 16),

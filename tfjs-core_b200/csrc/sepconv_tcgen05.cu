@@ -45,9 +45,12 @@ constexpr int A_SLOTS = 2;
 // (Only at 256 columns, where the 64 KB of weight stages otherwise leave room for two window stages:
 // four in place.  With narrower tiles the ring already holds four, and in place measured slower:
 // a stage then stays occupied until its MMAs retire, and the group barrier costs overlap.)
-__host__ __device__ constexpr bool a_in_place(int block_n, int s, int mode) { return mode == 0 && s == 1 && block_n >= 256; }
-__host__ __device__ constexpr int a_slot_bytes(int block_n, int s, int mode) {
-  return a_in_place(block_n, s, mode) ? 0 : A_SLOTS * A_TILE_BYTES;
+// (Not with half input: its 11.5 KB window is smaller than the 16 KB tile, and four of them fit anyway.)
+__host__ __device__ constexpr bool a_in_place(int block_n, int s, int mode, bool in16 = false) {
+  return mode == 0 && s == 1 && block_n >= 256 && !in16;
+}
+__host__ __device__ constexpr int a_slot_bytes(int block_n, int s, int mode, bool in16 = false) {
+  return a_in_place(block_n, s, mode, in16) ? 0 : A_SLOTS * A_TILE_BYTES;
 }
 constexpr int EPI_WARPS = 8;
 constexpr int C_CHUNK_BYTES = 32 * 32 * 4;
@@ -76,8 +79,12 @@ constexpr int MODE_CONV = 2; // dense convolution, Cin a multiple of 32, stride 
                              // tap, loaded by TMA straight into the swizzled layout the tensor core reads;
                              // no thread touches the operands (zero fill of the load is the padding)
 
-template <int S, int MODE>
+// IN16: the input image is stored as IEEE half (16-bit activation storage): a pixel of a k-block
+// is a 64-byte line, a window stage half as large.
+template <int S, int MODE, bool IN16 = false>
 struct Raw {
+  static constexpr int ELEM = IN16 ? 2 : 4;
+  static constexpr int PIX_BYTES = BLOCK_K * ELEM;       // one pixel of a 32-channel k-block (MODE_DW)
   static constexpr int PARTS = MODE == MODE_DW ? S : 1;  // raw stages per k-block
   static constexpr int PART_ROWS = PH / PARTS;           // patch rows per raw stage
   static constexpr int ROWS = (PART_ROWS - 1) * S + 3;
@@ -85,7 +92,7 @@ struct Raw {
   // floats per window row: 32 channels per pixel, or (RGB) 3 per pixel plus up to 3 floats of
   // slack in front so that the copy can start on a 16-byte boundary, rounded up to 16 bytes
   static constexpr int ROW_FLOATS = MODE == MODE_DW ? COLS * BLOCK_K : (COLS * 3 + 3 + 3) / 4 * 4;
-  static constexpr int BYTES = MODE == MODE_CONV ? A_TILE_BYTES : ROWS * ROW_FLOATS * 4;
+  static constexpr int BYTES = MODE == MODE_CONV ? A_TILE_BYTES : ROWS * ROW_FLOATS * ELEM;
   static constexpr int STRIDE = (BYTES + 1023) / 1024 * 1024;
   static constexpr int GROUP_THREADS = DW_THREADS / dw_groups(S, MODE);
   static constexpr int TR = S == 1 ? 2 : 1;                            // a thread's block of outputs: rows
@@ -98,12 +105,14 @@ __host__ __device__ constexpr int w_stages(int block_n, int s, int mode) {
   return block_n >= 256 ? 2 : (block_n >= 128 ? ((mode == 0 && s == 2) ? 2 : 3) : 4);
 }
 __host__ __device__ constexpr int epi_arrivals(int block_n) { return block_n >= 64 ? EPI_WARPS : 4; }
-template <int S, int MODE>
+template <int S, int MODE, bool IN16 = false>
 __host__ __device__ constexpr int raw_stages(int block_n) {
-  int left = SMEM_LIMIT - 1024 - a_slot_bytes(block_n, S, MODE) - w_stages(block_n, S, MODE) * block_n * BLOCK_K * 4 -
+  int left = SMEM_LIMIT - 1024 - a_slot_bytes(block_n, S, MODE, IN16) - w_stages(block_n, S, MODE) * block_n * BLOCK_K * 4 -
              C_STAGING_BYTES - BIAS_STAGING_BYTES - DW_TABLE_BYTES - BARRIER_BYTES;
-  int n = left / Raw<S, MODE>::STRIDE;
-  const int cap = MODE == MODE_DW ? 4 : 8;
+  int n = left / Raw<S, MODE, IN16>::STRIDE;
+  // Window loads carry the DRAM latency: about 90 KB must be in flight per SM to keep the memory
+  // system busy (four 23 KB float32 windows; with half-size windows that takes eight stages).
+  const int cap = (MODE == MODE_DW && !IN16) ? 4 : 8;
   n = n > cap ? cap : n;
   return n / dw_groups(S, MODE) * dw_groups(S, MODE);  // the same number of stages for every group
 }
@@ -161,6 +170,23 @@ __device__ __forceinline__ void sts128(uint32_t addr, const float4& v) {
   asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
                : "memory");
 }
+// Four channels of a window pixel as two packed float pairs, from float32 (16 bytes) or IEEE half
+// (8 bytes, converted exactly).
+template <bool IN16>
+__device__ __forceinline__ void lds_quad_pairs(uint32_t addr, uint64_t& lo, uint64_t& hi) {
+  if (!IN16) {
+    lds128_pairs(addr, lo, hi);
+  } else {
+    uint32_t a, b;
+    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "r"(addr));
+    float x, y, z, w;
+    unpack_half2(a, x, y);
+    unpack_half2(b, z, w);
+    lo = pack_f32x2(__float_as_uint(x), __float_as_uint(y));
+    hi = pack_f32x2(__float_as_uint(z), __float_as_uint(w));
+  }
+}
+
 template <int ACT>
 __device__ __forceinline__ float dw_activate(float v, float lo, float hi) {
   if (ACT == TFJS_ACT_RELU) return max_nan(v, 0.f);
@@ -175,10 +201,10 @@ __device__ __forceinline__ float dw_activate(float v, float lo, float hi) {
 // taps between all its pixels, which is what bounds the kernel: every 16-byte read costs a
 // quarter-warp wavefront of the shared-memory pipe.  The window is walked row by row and entry by
 // entry, so each output still accumulates its taps in the order (wR, wC) ascending.
-template <int S, int ACT>
+template <int S, int ACT, bool IN16>
 __device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t table, int t, int part, int kb,
                                         const SepParams& p, bool has_bias, int sync_id) {
-  using R = Raw<S, MODE_DW>;
+  using R = Raw<S, MODE_DW, IN16>;
   constexpr int TR = R::TR, TC = R::TC;
   constexpr int GROUPS_PER_ROW = PW / TC;
   constexpr int WROWS = (TR - 1) * S + 3, WIN = (TC - 1) * S + 3;
@@ -203,11 +229,11 @@ __device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t 
       for (int wc = 0; wc < 3; wc++)
         lds128_pairs(table + (uint32_t)(((ir * 3 + wc) * p.C + ch) * 4), f[ir][wc][0], f[ir][wc][1]);
     }
-    const uint32_t row = raw + (uint32_t)((((r0 * S + ir) * R::COLS) + c0 * S) * (BLOCK_K * 4) + q * 16);
+    const uint32_t row = raw + (uint32_t)((((r0 * S + ir) * R::COLS) + c0 * S) * R::PIX_BYTES + q * 4 * R::ELEM);
 #pragma unroll
     for (int i = 0; i < WIN; i++) {
       uint64_t in0, in1;
-      lds128_pairs(row + i * (BLOCK_K * 4), in0, in1);
+      lds_quad_pairs<IN16>(row + i * R::PIX_BYTES, in0, in1);
 #pragma unroll
       for (int o = 0; o < TR; o++) {
         const int dr = ir - o * S;  // filter row of this window row for output row o
@@ -275,17 +301,22 @@ __device__ __forceinline__ void rgb_part(uint32_t raw, uint32_t a_tile, int t, c
   sts128(a_tile + swz(t, 112), make_float4(v[2][8], 0.f, 0.f, 0.f));
 }
 
-template <int BLOCK_N, int S, int MODE>
+// HALF: 16-bit activation storage.  The output is stored as IEEE half, and in MODE_DW the input
+// is read as IEEE half; the stem (MODE_RGB) keeps its float32 input image.  The arithmetic does not
+// change: float32 depthwise taps, tf32 tensor-core products, float32 accumulators and epilogue.
+template <int BLOCK_N, int S, int MODE, bool HALF = false>
 __global__ void __launch_bounds__(THREADS, 1)
 sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                        const __grid_constant__ CUtensorMap map_y, SepParams p) {
-  using R = Raw<S, MODE>;
+  constexpr bool IN16 = HALF && MODE == MODE_DW;
+  constexpr bool OUT16 = HALF;
+  using R = Raw<S, MODE, IN16>;
   constexpr int W_STAGES = w_stages(BLOCK_N, S, MODE);
   constexpr int GROUPS = dw_groups(S, MODE);
   constexpr int GROUP_THREADS = DW_THREADS / GROUPS;
-  constexpr int RAW_STAGES = raw_stages<S, MODE>(BLOCK_N);
+  constexpr int RAW_STAGES = raw_stages<S, MODE, IN16>(BLOCK_N);
   static_assert(RAW_STAGES >= 2 && RAW_STAGES % GROUPS == 0 && A_SLOTS % GROUPS == 0, "rings split evenly");
-  constexpr bool IN_PLACE = a_in_place(BLOCK_N, S, MODE);
+  constexpr bool IN_PLACE = a_in_place(BLOCK_N, S, MODE, IN16);
   // MODE_CONV: the stage the TMA load filled IS the A tile; the helper warps only round it to tf32
   // in place before the tensor core reads it
   constexpr bool STAGE_IS_A = IN_PLACE || MODE == MODE_CONV;
@@ -314,7 +345,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* a_tiles = smem;                                   // [A_SLOTS][16 KB], SWIZZLE_128B (none if in place)
-  uint8_t* w_tiles = a_tiles + a_slot_bytes(BLOCK_N, S, MODE);  // [W_STAGES][BLOCK_N x 128 B]
+  uint8_t* w_tiles = a_tiles + a_slot_bytes(BLOCK_N, S, MODE, IN16);  // [W_STAGES][BLOCK_N x 128 B]
   uint8_t* c_stage = w_tiles + W_STAGES * W_STAGE_BYTES;     // [8 warps][4 KB]
   uint8_t* raw = c_stage + C_STAGING_BYTES;                  // [RAW_STAGES][window]
   uint8_t* table = raw + RAW_STAGES * R::STRIDE;             // [10][C] floats
@@ -588,9 +619,9 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
             // in place: named barrier 1 + group over the group's threads, between reads and writes
             const int sync_id = IN_PLACE ? 1 + group : 0;
             switch (p.dw_act) {
-              case TFJS_ACT_RELU: dw_part<S, TFJS_ACT_RELU>(raw_s, a_s, table_s, t, part, kb, p, has_bias, sync_id); break;
-              case TFJS_ACT_CLIP: dw_part<S, TFJS_ACT_CLIP>(raw_s, a_s, table_s, t, part, kb, p, has_bias, sync_id); break;
-              default: dw_part<S, TFJS_ACT_LINEAR>(raw_s, a_s, table_s, t, part, kb, p, has_bias, sync_id); break;
+              case TFJS_ACT_RELU: dw_part<S, TFJS_ACT_RELU, IN16>(raw_s, a_s, table_s, t, part, kb, p, has_bias, sync_id); break;
+              case TFJS_ACT_CLIP: dw_part<S, TFJS_ACT_CLIP, IN16>(raw_s, a_s, table_s, t, part, kb, p, has_bias, sync_id); break;
+              default: dw_part<S, TFJS_ACT_LINEAR, IN16>(raw_s, a_s, table_s, t, part, kb, p, has_bias, sync_id); break;
             }
           }
           if (!IN_PLACE) {
@@ -617,6 +648,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     float* bias_s = reinterpret_cast<float*>(bias_stage + warp * 128);
     const bool has_bias = p.epi.bias != nullptr;
     int local = 0;
+    int store_parity = 0;  // OUT16: which half of the staging buffer the next chunk uses
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, local++) {
       const int b = tile / tiles_per_image;
@@ -662,18 +694,35 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
           case TFJS_ACT_CLIP: finish_chunk<TFJS_ACT_CLIP>(v, has_bias, bias_s, bias_s, p.epi); break;
           default: finish_chunk<TFJS_ACT_LINEAR>(v, has_bias, bias_s, bias_s, p.epi); break;
         }
-        if (lane == 0) tma_store_wait_read<0>();
+        // A half chunk is 2 KB of the warp's 4 KB staging buffer: the two halves alternate, so one
+        // store may still be reading its half while the next chunk is written (stores in flight
+        // are what bounds the write rate of the narrow layers).
+        if (lane == 0) {
+          if (OUT16) tma_store_wait_read<1>(); else tma_store_wait_read<0>();
+        }
         __syncwarp();
-        uint8_t* dst = stage_buf + lane * 128;
+        if (OUT16) {
+          // half output: a pixel's 32 channels are 64 bytes, stored unswizzled
+          store_parity ^= 1;
+          uint8_t* dst = stage_buf + store_parity * 2048 + lane * 64;
 #pragma unroll
-        for (int j = 0; j < 8; j++)
-          *reinterpret_cast<float4*>(dst + ((j ^ (lane & 7)) << 4)) =
-              make_float4(v[j * 4 + 0], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+          for (int j = 0; j < 4; j++)
+            *reinterpret_cast<uint4*>(dst + (j << 4)) =
+                make_uint4(pack_half2(v[j * 8 + 0], v[j * 8 + 1]), pack_half2(v[j * 8 + 2], v[j * 8 + 3]),
+                           pack_half2(v[j * 8 + 4], v[j * 8 + 5]), pack_half2(v[j * 8 + 6], v[j * 8 + 7]));
+        } else {
+          uint8_t* dst = stage_buf + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; j++)
+            *reinterpret_cast<float4*>(dst + ((j ^ (lane & 7)) << 4)) =
+                make_float4(v[j * 4 + 0], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+        }
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
           // lanes 0-15 hold patch row 2*quarter, lanes 16-31 the next one: a [2 x 16 x 32] box
-          tma_store_4d(&map_y, smem_u32(stage_buf), c0, tx * PW, ty * PH + quarter * 2, b);
+          tma_store_4d(&map_y, smem_u32(stage_buf + (OUT16 ? store_parity * 2048 : 0)), c0, tx * PW,
+                       ty * PH + quarter * 2, b);
           tma_store_commit();
         }
       }
@@ -702,14 +751,15 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   }
 }
 
-template <int BLOCK_N, int S, int MODE>
+template <int BLOCK_N, int S, int MODE, bool HALF = false>
 int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my,
                    const SepParams& p) {
-  constexpr int smem_bytes = 1024 + a_slot_bytes(BLOCK_N, S, MODE) + w_stages(BLOCK_N, S, MODE) * BLOCK_N * BLOCK_K * 4 +
-                             C_STAGING_BYTES + raw_stages<S, MODE>(BLOCK_N) * Raw<S, MODE>::STRIDE +
+  constexpr bool IN16 = HALF && MODE == MODE_DW;
+  constexpr int smem_bytes = 1024 + a_slot_bytes(BLOCK_N, S, MODE, IN16) + w_stages(BLOCK_N, S, MODE) * BLOCK_N * BLOCK_K * 4 +
+                             C_STAGING_BYTES + raw_stages<S, MODE, IN16>(BLOCK_N) * Raw<S, MODE, IN16>::STRIDE +
                              DW_TABLE_BYTES + BIAS_STAGING_BYTES + BARRIER_BYTES;
   static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
-  auto kernel = sepconv_tcgen05_kernel<BLOCK_N, S, MODE>;
+  auto kernel = sepconv_tcgen05_kernel<BLOCK_N, S, MODE, HALF>;
   // per device and per kernel; atomic because contexts of several devices may call from several
   // host threads (setting the attribute twice is harmless)
   static std::atomic<bool> configured[64];
@@ -719,22 +769,27 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap&
   }
   const int grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
   launch_ex(ctx, kernel, dim3(grid), dim3(THREADS), smem_bytes, mx, mw, my, p);
-  if (MODE == MODE_RGB) return post_launch(ctx, "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32)");
+  if (MODE == MODE_RGB)
+    return post_launch(ctx, HALF ? "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32, float16 out)"
+                                 : "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32)");
   if (MODE == MODE_CONV) return post_launch(ctx, "conv2d_tcgen05 (shifted-patch TMA, TF32)");
+  if (HALF)
+    return post_launch(ctx, S == 1 ? "separableConv2d (fused dw3x3 s1 + pw, TF32, float16)"
+                                   : "separableConv2d (fused dw3x3 s2 + pw, TF32, float16)");
   return post_launch(ctx, S == 1 ? "separableConv2d (fused dw3x3 s1 + pw, TF32)"
                                  : "separableConv2d (fused dw3x3 s2 + pw, TF32)");
 }
 
-template <int S, int MODE>
+template <int S, int MODE, bool HALF = false>
 int launch_stride(tfjs_cuda_ctx* ctx, int block_n, const CUtensorMap& mx, const CUtensorMap& mw,
                   const CUtensorMap& my, const SepParams& p) {
   switch (block_n) {
     case 32:
-      if (MODE != MODE_DW) return launch_variant<32, S, MODE == MODE_DW ? MODE_RGB : MODE>(ctx, mx, mw, my, p);
+      if (MODE != MODE_DW) return launch_variant<32, S, MODE == MODE_DW ? MODE_RGB : MODE, HALF>(ctx, mx, mw, my, p);
       // depthwise mode has no 32-wide variant: falls through
-    case 64: return launch_variant<64, S, MODE>(ctx, mx, mw, my, p);
-    case 128: return launch_variant<128, S, MODE>(ctx, mx, mw, my, p);
-    default: return launch_variant<256, S, MODE>(ctx, mx, mw, my, p);
+    case 64: return launch_variant<64, S, MODE, HALF>(ctx, mx, mw, my, p);
+    case 128: return launch_variant<128, S, MODE, HALF>(ctx, mx, mw, my, p);
+    default: return launch_variant<256, S, MODE, HALF>(ctx, mx, mw, my, p);
   }
 }
 
@@ -756,27 +811,29 @@ bool sepconv_tcgen05_supported(const tfjs_conv2d_info& dw, int64_t N, int dw_act
          tcgen05_gemm_supported(128, N, dw.inChannels);
 }
 
-int launch_sepconv_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& dw, const float* dw_filter,
-                           const EpilogueArgs& dw_epi, const float* w_hi, int64_t kp, float* y, int64_t N,
-                           const EpilogueArgs& pw_epi) {
+int launch_sepconv_tcgen05(tfjs_cuda_ctx* ctx, const void* x, const tfjs_conv2d_info& dw, const float* dw_filter,
+                           const EpilogueArgs& dw_epi, const float* w_hi, int64_t kp, void* y, int64_t N,
+                           const EpilogueArgs& pw_epi, bool half) {
   const int S = dw.strideHeight;
   const int C = dw.inChannels;
   const int block_n = N <= 64 ? 64 : (N <= 128 ? 128 : 256);
+  const uint64_t el = half ? 2 : 4;  // bytes per stored activation
+  const CUtensorMapDataType act_type = half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   CUtensorMap mx, mw, my;
   const uint64_t xd[4] = {(uint64_t)C, (uint64_t)dw.inWidth, (uint64_t)dw.inHeight, (uint64_t)dw.batchSize};
-  const uint64_t xs[3] = {(uint64_t)C * 4, (uint64_t)dw.inWidth * C * 4, (uint64_t)dw.inHeight * dw.inWidth * C * 4};
+  const uint64_t xs[3] = {(uint64_t)C * el, (uint64_t)dw.inWidth * C * el, (uint64_t)dw.inHeight * dw.inWidth * C * el};
   const uint32_t xb1[4] = {BLOCK_K, (uint32_t)Raw<1, MODE_DW>::COLS, (uint32_t)Raw<1, MODE_DW>::ROWS, 1};
   const uint32_t xb2[4] = {BLOCK_K, (uint32_t)Raw<2, MODE_DW>::COLS, (uint32_t)Raw<2, MODE_DW>::ROWS, 1};
   const uint64_t wd[2] = {(uint64_t)kp, (uint64_t)N};
   const uint64_t ws[1] = {(uint64_t)kp * 4};
   const uint32_t wb[2] = {BLOCK_K, (uint32_t)block_n};
   const uint64_t yd[4] = {(uint64_t)N, (uint64_t)dw.outWidth, (uint64_t)dw.outHeight, (uint64_t)dw.batchSize};
-  const uint64_t ys[3] = {(uint64_t)N * 4, (uint64_t)dw.outWidth * N * 4, (uint64_t)dw.outHeight * dw.outWidth * N * 4};
+  const uint64_t ys[3] = {(uint64_t)N * el, (uint64_t)dw.outWidth * N * el, (uint64_t)dw.outHeight * dw.outWidth * N * el};
   const uint32_t yb[4] = {32, PW, 2, 1};
   const bool ok =
-      tma_encode_tiled(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, x, xd, xs, S == 1 ? xb1 : xb2, CU_TENSOR_MAP_SWIZZLE_NONE) &&
+      tma_encode_tiled(&mx, act_type, 4, x, xd, xs, S == 1 ? xb1 : xb2, CU_TENSOR_MAP_SWIZZLE_NONE) &&
       tma_encode_tiled(&mw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, w_hi, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B) &&
-      tma_encode_tiled(&my, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, y, yd, ys, yb, CU_TENSOR_MAP_SWIZZLE_128B);
+      tma_encode_tiled(&my, act_type, 4, y, yd, ys, yb, half ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ok) return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
   SepParams p;
   p.B = dw.batchSize;
@@ -801,6 +858,9 @@ int launch_sepconv_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d
   p.epi = pw_epi;
   p.status = ctx->d_status;
   p.rgb_off = 0;
+  if (half)
+    return S == 1 ? launch_stride<1, MODE_DW, true>(ctx, block_n, mx, mw, my, p)
+                  : launch_stride<2, MODE_DW, true>(ctx, block_n, mx, mw, my, p);
   return S == 1 ? launch_stride<1, MODE_DW>(ctx, block_n, mx, mw, my, p)
                 : launch_stride<2, MODE_DW>(ctx, block_n, mx, mw, my, p);
 }
@@ -818,9 +878,10 @@ bool conv_rgb_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int 
 }
 
 int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& ci, const float* w_hi,
-                            int64_t kp, float* y, const EpilogueArgs& epi) {
+                            int64_t kp, void* y, const EpilogueArgs& epi, bool out_half) {
   const int S = ci.strideHeight;
   const int64_t N = ci.outChannels;
+  const uint64_t el = out_half ? 2 : 4;
   const int block_n = N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256));
   CUtensorMap mx, mw, my;
   const uint64_t xd[3] = {(uint64_t)ci.inWidth * 3, (uint64_t)ci.inHeight, (uint64_t)ci.batchSize};
@@ -831,12 +892,13 @@ int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2
   const uint64_t ws[1] = {(uint64_t)kp * 4};
   const uint32_t wb[2] = {BLOCK_K, (uint32_t)block_n};
   const uint64_t yd[4] = {(uint64_t)N, (uint64_t)ci.outWidth, (uint64_t)ci.outHeight, (uint64_t)ci.batchSize};
-  const uint64_t ys[3] = {(uint64_t)N * 4, (uint64_t)ci.outWidth * N * 4, (uint64_t)ci.outHeight * ci.outWidth * N * 4};
+  const uint64_t ys[3] = {(uint64_t)N * el, (uint64_t)ci.outWidth * N * el, (uint64_t)ci.outHeight * ci.outWidth * N * el};
   const uint32_t yb[4] = {32, PW, 2, 1};
   const bool ok =
       tma_encode_tiled(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, x, xd, xs, S == 1 ? xb1 : xb2, CU_TENSOR_MAP_SWIZZLE_NONE) &&
       tma_encode_tiled(&mw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, w_hi, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B) &&
-      tma_encode_tiled(&my, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, y, yd, ys, yb, CU_TENSOR_MAP_SWIZZLE_128B);
+      tma_encode_tiled(&my, out_half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, y, yd, ys, yb,
+                       out_half ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ok) return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
   SepParams p;
   memset(&p, 0, sizeof(p));
@@ -858,6 +920,9 @@ int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2
   // multiple of 4, so the distance to the 16-byte boundary below it is the same for every patch
   p.rgb_off = ((-3 * ci.padLeft) % 4 + 4) % 4;
   p.status = ctx->d_status;
+  if (out_half)
+    return S == 1 ? launch_stride<1, MODE_RGB, true>(ctx, block_n, mx, mw, my, p)
+                  : launch_stride<2, MODE_RGB, true>(ctx, block_n, mx, mw, my, p);
   return S == 1 ? launch_stride<1, MODE_RGB>(ctx, block_n, mx, mw, my, p)
                 : launch_stride<2, MODE_RGB>(ctx, block_n, mx, mw, my, p);
 }

@@ -128,6 +128,16 @@ __device__ __forceinline__ void tcgen05_mma_tf32(uint32_t tmem_d, uint64_t adesc
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same with IEEE half inputs: A and B tiles hold 16-bit elements, K = 16 per instruction.
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -166,6 +176,12 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Instruction descriptor for kind::f16 with IEEE half operands: D format f32 (1) in [4,6), A and B
+// format f16 (0) in [7,10) and [10,13), both K-major, N >> 3 in [17,23), M >> 4 in [24,29).
+__host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n) {
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
 // Bias and activation of one 32x32 output chunk in registers: thread `lane` owns row `lane`,
 // v[] holds its 32 accumulator columns.  Arithmetic order follows MathBackendCPU's unfused
 // passes: float32(acc) + bias, then the activation (backend_cpu.ts:542-555).  relu is
@@ -198,6 +214,19 @@ __device__ __forceinline__ void finish_chunk(float (&v)[32], bool has_bias, cons
       if (ACT == TFJS_ACT_CLIP) v[j * 4 + i] = min_nan(max_nan(v[j * 4 + i], e.clip_lo), e.clip_hi);
     }
   }
+}
+
+// Two float32 -> one word of two IEEE halves (round to nearest even), low half first.
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// One word of two IEEE halves -> two float32 (exact).
+__device__ __forceinline__ void unpack_half2(uint32_t h, float& lo, float& hi) {
+  asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.f32.f16 %0, a;\n\tcvt.f32.f16 %1, b;\n\t}"
+      : "=f"(lo), "=f"(hi)
+      : "r"(h));
 }
 
 __device__ __forceinline__ void cp_async_16_zfill(uint32_t dst, const void* src, bool valid) {

@@ -194,7 +194,7 @@ class MobileNetV1:
             h = then(bk.avgPool(h, ci), h)
             w, b = self.params["fc"]
             ci = conv_util.compute_conv2d_info(h.shape, w.shape, 1, 1, "same")
-            h = then(bk.fusedConv2d(h, w, ci, b, "linear"), h)
+            h = then(bk.fusedConv2d(h, w, ci, b, "linear", None, "float32"), h)   # logits stay float32
             logits = then(bk.reshape(h, [h.shape[0], NUM_CLASSES]), h)
             return logits, bk.softmax(logits)
         return ENGINE.tidy(body)
@@ -224,7 +224,7 @@ def _forward_separable(self, x):
         h = then(bk.avgPool(h, ci), h)
         w, b = self.params["fc"]
         ci = conv_util.compute_conv2d_info(h.shape, w.shape, 1, 1, "same")
-        h = then(bk.fusedConv2d(h, w, ci, b, "linear"), h)
+        h = then(bk.fusedConv2d(h, w, ci, b, "linear", None, "float32"), h)   # logits stay float32
         logits = then(bk.reshape(h, [h.shape[0], NUM_CLASSES]), h)
         return logits, bk.softmax(logits)
     return ENGINE.tidy(body)
@@ -233,37 +233,42 @@ def _forward_separable(self, x):
 MobileNetV1.forward_separable = _forward_separable
 
 
-def layer_algorithmic_bytes(batch, quantized):
+def layer_algorithmic_bytes(batch, quantized, half=False):
     """Algorithmic bytes of each of the 30 launches of the fused forward, in launch order:
-    4*(|x| + |y|) + filter bytes + 4*|bias| with every tensor counted once."""
+    |x| + |y| at their stored width + filter bytes + 4*|bias| with every tensor counted once.
+    `half`: activations are stored as IEEE half (2 bytes) between the stem and the global pool;
+    the input image, the pooled features, the logits and the probabilities stay float32."""
     out = []
     h = w = 224
     c = 3
     wb = 1 if quantized else 4
+    ab = 2 if half else 4
     for name, kind, shape, s in layer_specs():
         if name == "fc":
-            out.append(4 * batch * (7 * 7 * c + c))
+            out.append(batch * (ab * 7 * 7 * c + 4 * c))
             out.append(4 * batch * (c + 1000) + wb * c * 1000 + 4 * 1000)
             out.append(4 * batch * 2000)
             break
         ho, wo = -(-h // s), -(-w // s)
         co = c if kind == "dw" else shape[3]
-        out.append(4 * batch * (h * w * c + ho * wo * co) + wb * int(np.prod(shape)) + 4 * co)
+        in_b = 4 if name == "stem" else ab
+        out.append(batch * (in_b * h * w * c + ab * ho * wo * co) + wb * int(np.prod(shape)) + 4 * co)
         h, w, c = ho, wo, co
     return out
 
 
 
-def launch_algorithmic_bytes(batch, quantized, kernel_names):
+def launch_algorithmic_bytes(batch, quantized, kernel_names, half=False):
     """Algorithmic bytes of each launch of one forward pass given the names of the kernels it
     launched, in order: a launch whose name starts with 'separableConv2d (fused' covers a
     depthwise + pointwise pair and counts the pair's input, output, filters and biases (the
     intermediate tensor does not exist); every other launch counts its own layer."""
-    per_layer = layer_algorithmic_bytes(batch, quantized)
+    per_layer = layer_algorithmic_bytes(batch, quantized, half)
     specs = layer_specs()
     out, i = [], 0
     h = w = 224
     c = 3
+    ab = 2 if half else 4
     sizes = []  # (in elements, out elements) per image for the 27 conv layers
     for name, kind, shape, s in specs[:-1]:
         ho, wo = -(-h // s), -(-w // s)
@@ -274,7 +279,7 @@ def launch_algorithmic_bytes(batch, quantized, kernel_names):
         if name.startswith("separableConv2d (fused"):
             assert specs[i][1] == "dw" and specs[i + 1][1] == "conv", "fused launch out of place"
             mid = sizes[i][1]
-            out.append(per_layer[i] + per_layer[i + 1] - 2 * 4 * batch * mid)
+            out.append(per_layer[i] + per_layer[i + 1] - 2 * ab * batch * mid)
             i += 2
         else:
             out.append(per_layer[i])
