@@ -62,6 +62,10 @@ def parse_args():
                     help="f16: activations are stored as IEEE half between the layers (the reference's 16-bit "
                          "precision class); a SEPARATE configuration with its own algorithmic-bytes figure, "
                          "never the headline")
+    ap.add_argument("--input", default="float32", choices=["float32", "uint8"],
+                    help="uint8: the images are pixel bytes (tf.browser.fromPixels) registered as a quantised "
+                         "tensor x = q / 127.5 - 1 and decoded by the stem kernel on chip: 4x fewer host-to-device "
+                         "bytes; a SEPARATE configuration, never the headline")
     ap.add_argument("--global-batch", type=int, default=0, help="override the workload's batch")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a graph")
     ap.add_argument("--pdl", action="store_true", help="programmatic dependent launch instead of plain stream order")
@@ -79,6 +83,8 @@ def workload_config(args, world):
                else "once on device into cached tf32 planes")
         half = ", float16 activation storage (16-bit precision class: separate configuration)" \
             if getattr(args, "activations", "f32") == "f16" else ""
+        if getattr(args, "input", "float32") == "uint8":
+            half += ", images as uint8 pixels decoded in the stem (separate configuration)"
         return dict(name="cfg5: MobileNetV1-1.0-224, uint8 affine-quantised filters dequantised %s, "
                          "global batch %d sharded by batch%s" % (how, gb, half),
                     global_batch=gb, per_gpu=gb // world, quantized=True, seed=4, gain=1.0,
@@ -285,6 +291,8 @@ KERNEL_FAMILY = {"separableConv2d (fused dw3x3 s1 + pw, TF32, float16)": "separa
                  "separableConv2d (fused dw3x3 s2 + pw, TF32, float16)": "separable_fused",
                  "gemm_tcgen05 (F16)": "gemm_tcgen05",
                  "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32, float16 out)": "conv2d_tcgen05",
+                 "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32, uint8 in)": "conv2d_tcgen05",
+                 "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32, uint8 in, float16 out)": "conv2d_tcgen05",
                  "depthwiseConv2D (3x3 image window, TMA, float16)": "depthwise3x3",
                  "avgPool (global, float16 in)": "global_avgpool",
                  "separableConv2d (fused dw3x3 s1 + pw, TF32)": "separable_fused",
@@ -385,7 +393,17 @@ def run_cuda(args):
     if d.world > 1:
         rng = np.random.Generator(np.random.PCG64([cfg["seed"], 12345, d.rank]))
         x_host = (rng.random(size=x_host.shape, dtype=np.float32) * 2.0 - 1.0).astype(np.float32)
-    x = ops.tensor(x_host)
+    pixels = args.input == "uint8"
+    if pixels:
+        assert args.forward != "reference-api", "pixel input goes with the fused forwards"
+        # the same images as bytes: q = round((x + 1) * 127.5), x' = q / 127.5 - 1
+        q_host = np.clip(np.rint((x_host + 1.0) * 127.5), 0, 255).astype(np.uint8)
+        x_float = (q_host.astype(np.float64) / 127.5 - 1.0).astype(np.float32)   # what the device decodes
+        x_host = q_host
+        x = bk.registerQuantized(list(q_host.shape), q_host, 1.0 / 127.5, -1.0)
+    else:
+        x_float = x_host
+        x = ops.tensor(x_host)
 
     # eager pass: fills the weight-repack cache and the allocator's free lists
     logits, probs = forward(x)
@@ -455,6 +473,8 @@ def run_cuda(args):
         layer_bytes = mobilenet.reference_api_launch_bytes(per, cfg["quantized"], names)
     else:
         layer_bytes = mobilenet.launch_algorithmic_bytes(per, cfg["quantized"], names, half)
+        if pixels:
+            layer_bytes[0] -= 3 * per * 224 * 224 * 3   # the stem reads one byte per value instead of four
     fam = {}
     for i, (name, ms) in enumerate(rows):
         f = KERNEL_FAMILY.get(name, name)
@@ -502,7 +522,7 @@ def run_cuda(args):
     assert lib.tfjs_cuda_host_alloc(C.byref(pinned), nbytes) == 0
     C.memmove(pinned, x_host.ctypes.data, nbytes)
     out_bytes = per * 1000 * 4
-    xs = [x, ops.tensor(x_host)]
+    xs = [x, bk.registerQuantized(list(x_host.shape), x_host, 1.0 / 127.5, -1.0) if pixels else ops.tensor(x_host)]
     graphs, outs = [graph], [probs if graph is not None else None]
     if graph is not None:
         bk.graphBegin()
@@ -563,7 +583,8 @@ def run_cuda(args):
 
     # ---- extra: the same step with the uint8 weights dequantised inside the GEMM main loop ----
     extras = {}
-    if cfg["quantized"] and args.dequant == "cached" and graph is not None and not args.no_extras and not half:
+    if cfg["quantized"] and args.dequant == "cached" and graph is not None and not args.no_extras and not half \
+            and not pixels:
         bk.setOption("dequant_in_gemm", 1)
         lg, pr = forward(x)          # prepares the K-major uint8 layouts
         lg.dispose()
@@ -595,15 +616,18 @@ def run_cuda(args):
         import oracle
         oracle.build()
         n = args.cpu_sample
-        ips, secs = cpu_forward_images_per_second(params, x_host[:n], 1)
+        ips, secs = cpu_forward_images_per_second(params, x_float[:n], 1)
         cpu_baseline = {"value": ips, "unit": UNIT, "cores": 1, "kind": "port",
                         "sample": f"first {n} images of the batch, {secs:.1f} s, restated MathBackendCPU "
                                   "(C, unfused passes), 1 thread as the JavaScript original is single-threaded"}
 
     # ---- extra: the library's in-process runner over all N devices (rank 0, the other ranks idle) ----
     d.barrier()
-    if d.rank == 0 and d.world > 1 and not args.no_extras and not args.no_graph and not half:
-        extras["e2e_in_process"] = in_process_e2e(args, cfg, params, d.world)
+    if d.rank == 0 and d.world > 1 and not args.no_extras and not args.no_graph and not half and not pixels:
+        try:
+            extras["e2e_in_process"] = in_process_e2e(args, cfg, params, d.world)
+        except Exception as err:  # an extra must never cost the bench line
+            extras["e2e_in_process"] = {"error": f"{type(err).__name__}: {err}"}
     d.barrier()
 
     if d.rank == 0:
@@ -615,7 +639,7 @@ def run_cuda(args):
             "data": "synthetic",
             "config": {"workload": cfg["name"], "global_batch": cfg["global_batch"], "per_gpu_batch": per,
                        "math_mode": args.math, "dequant": args.dequant, "forward": args.forward,
-                       "activation_storage": "float16" if half else "float32",
+                       "activation_storage": "float16" if half else "float32", "input": args.input,
                        "launches_per_step": int(launches_per_step),
                        "launch": "eager" if graph is None else "cuda-graph replay",
                        "l2": "every step streams %.1f GB of activations per GPU (> 126 MB L2) between reuses"
@@ -627,8 +651,8 @@ def run_cuda(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": out_bytes,
                     "h2d_ceiling_gbs_per_gpu": h2d_gbs_per_gpu, "h2d_ceiling_value": h2d_ceiling_value,
                     "frac_of_h2d_ceiling": e2e_value / h2d_ceiling_value,
-                    "note": "float32 images, 602 KB each; the ceiling is the measured rate of the same uploads "
-                            "with no kernel in between"},
+                    "note": ("uint8 pixels, 150 KB per image" if pixels else "float32 images, 602 KB each") +
+                            "; the ceiling is the measured rate of the same uploads with no kernel in between"},
             "extras": extras,
             "gpu_launches": int(gpu_launches), "clocks": clocks,
         }

@@ -161,6 +161,11 @@ export class BackendCuda extends KernelBackend {
     }
     const rec = this.data.get(dataId);
     let host = values as backend_util.TypedArray;
+    if (rec.quantized) {
+      // a quantised tensor is refilled with its raw bytes (e.g. the next batch of pixels)
+      this.check(binding.tensorWrite(this.ctx, rec.id, host as Uint8Array));
+      return;
+    }
     const want = typedArrayFor(rec.dtype, 0).constructor;
     if (host.constructor !== want) {
       const conv = typedArrayFor(rec.dtype, host.length);

@@ -360,6 +360,32 @@ def test_pooling(tf):
         assert np.array_equal(got.dataSync().reshape(ci.outShape), oracle.pool(x2, ci, kind)), kind
 
 
+@pytest.mark.parametrize("shape,fsize,stride,pad", [
+    ((2, 13, 17, 8), [3, 3], 2, "same"),       # overlapping windows, ragged borders
+    ((1, 112, 112, 64), [3, 3], 2, "same"),    # MobileNet-sized plane
+    ((3, 10, 12, 16), [2, 2], 2, "valid"),     # four taps: the exact-reciprocal branch of the average
+    ((2, 9, 9, 4), [3, 3], 1, "same"),         # border windows of 4 and 6 taps, interior of 9
+    ((1, 8, 8, 12), [2, 3], 1, 1),             # numeric padding
+])
+def test_pooling_128_bit_kernel(tf, shape, fsize, stride, pad):
+    """Channel counts that are multiples of four take the 128-bit pooling kernel: bit-identical to
+    the oracle (float64 sum over the in-bounds taps in row-major order, divided by their count;
+    max ignores NaN, avg propagates it, backend_cpu.ts:2299-2339)."""
+    bk = tf.ENGINE.backend
+    rng = _rng(shape[1] * shape[3])
+    x = rng.normal(0, 1, shape).astype(np.float32)
+    x[0, 1, 2, 1] = np.nan
+    ci = oracle.compute_pool2d_info(x.shape, fsize, stride, 1, pad)
+    for kind, op in (("max", tf.ops.max_pool), ("avg", tf.ops.avg_pool)):
+        bk.profileBegin()
+        got = op(tf.ops.tensor(x), fsize, stride, pad).dataSync().reshape(ci.outShape)
+        assert any("128-bit" in n for n, _ in bk.profileEnd())
+        want = oracle.pool(x, ci, kind)
+        np.testing.assert_array_equal(np.isnan(got), np.isnan(want))
+        ok = ~np.isnan(want)
+        assert np.array_equal(got[ok], want[ok]), kind
+
+
 # ---- quantised weights ----------------------------------------------------------------------
 def test_quantized_weights_pointwise_and_depthwise(tf):
     rng = _rng(61)

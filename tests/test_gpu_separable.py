@@ -311,3 +311,49 @@ def test_non_finite_filter_taps_at_the_border(tf, c, h, stride):
     finally:
         bk.setOption("fuse_separable", 1)
         bk.setMathMode("3xtf32")
+
+
+@pytest.mark.parametrize("b,h,w,n,stride,pad,native", [
+    (2, 224, 224, 32, 2, "same", True),    # the network's stem on pixels
+    (1, 32, 48, 40, 1, "same", True),      # pad left 1: the window starts 13 bytes past a 16-byte boundary
+    (3, 17, 16, 8, 2, "valid", True),
+    (1, 20, 24, 32, 2, "same", False),     # rows of 72 bytes cannot be a tensor-map stride: decoded float32 copy
+])
+@pytest.mark.parametrize("out_storage", ["float32", "float16"])
+def test_rgb_stem_conv_on_pixel_bytes(tf, b, h, w, n, stride, pad, native, out_storage):
+    """fromPixels-style input: the image is a quantised tensor (one byte per value, x = q / 127.5 - 1)
+    and the stem decodes it on chip.  The decoded values are exactly those of the float32 image
+    decodeWeights' formula gives, so the result must equal, bit for bit, the same kernel fed that
+    float32 image; refilling the tensor with new bytes (the next batch) must be seen."""
+    from tfjs_core_b200 import conv_util
+    bk = tf.ENGINE.backend
+    bk.setMathMode("tf32")
+    try:
+        rng = _rng(b * h + w + n)
+        q = rng.integers(0, 256, (b, h, w, 3), dtype=np.uint8)
+        scale, mn = 1.0 / 127.5, -1.0
+        x = oracle.dequant_u8(q, scale, mn)
+        wt = rng.normal(0, 0.3, (3, 3, 3, n)).astype(np.float32)
+        bias = rng.normal(0, 0.1, n).astype(np.float32)
+        ci = conv_util.compute_conv2d_info(x.shape, wt.shape, stride, 1, pad)
+        wt_t, bias_t = tf.ops.tensor(wt), tf.ops.tensor(bias)
+        xq = bk.registerQuantized(list(q.shape), q, scale, mn)
+        bk.profileBegin()
+        got = bk.fusedConv2d(xq, wt_t, ci, bias_t, "relu6", None, out_storage)
+        names = [nm for nm, _ in bk.profileEnd()]
+        assert any("uint8 in" in nm for nm in names) == native, names
+        ref = bk.fusedConv2d(tf.ops.tensor(x), wt_t, ci, bias_t, "relu6", None, out_storage)
+        assert np.array_equal(got.dataSync(), ref.dataSync())
+        oci = oracle.compute_conv2d_info(x.shape, wt.shape, stride, 1, pad)
+        want = oracle.unary("clip", oracle.binary("add", oracle.conv2d(x, wt, oci), bias), 0, 6)
+        assert rel_err(got.dataSync().reshape(want.shape), want) <= (2e-3 if out_storage == "float16" else 1e-3)
+        # the next batch of pixels into the same tensor
+        q2 = rng.integers(0, 256, q.shape, dtype=np.uint8)
+        bk.write(xq.dataId, q2)
+        got2 = bk.fusedConv2d(xq, wt_t, ci, bias_t, "relu6", None, out_storage)
+        ref2 = bk.fusedConv2d(tf.ops.tensor(oracle.dequant_u8(q2, scale, mn)), wt_t, ci, bias_t, "relu6", None,
+                              out_storage)
+        assert np.array_equal(got2.dataSync(), ref2.dataSync())
+        assert not np.array_equal(got2.dataSync(), got.dataSync())
+    finally:
+        bk.setMathMode("3xtf32")

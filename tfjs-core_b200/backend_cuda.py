@@ -152,7 +152,9 @@ class BackendCuda:
         if values is None:
             raise ValueError("MathBackendCUDA.write(): values can not be null")
         rec = self._rec(dataId)
-        arr = np.ascontiguousarray(np.asarray(values).reshape(-1), dtype=_HOST_DTYPE[rec["dtype"]])
+        # a quantised tensor is refilled with its raw bytes (e.g. the next batch of pixels)
+        host_dtype = np.uint8 if rec.get("quantized") else _HOST_DTYPE[rec["dtype"]]
+        arr = np.ascontiguousarray(np.asarray(values).reshape(-1), dtype=host_dtype)
         self._check(self._lib.tfjs_cuda_tensor_write(self._ctx, rec["id"], arr.ctypes.data_as(C.c_void_p),
                                                      arr.nbytes))
 

@@ -313,7 +313,14 @@ extern "C" int tfjs_cuda_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_te
   if (rc) return rc;
   const int64_t pixels = (int64_t)ci->batchSize * ci->outHeight * ci->outWidth;
   TensorEntry *x, *w, *o;
-  rc = get_activation(ctx, x_id, (int64_t)ci->batchSize * ci->inHeight * ci->inWidth * ci->inChannels, "x", &x);
+  // x may also be a quantised tensor (uint8 bytes with scale / min): image pixels, decoded by the
+  // stem kernel on chip, or through a float32 copy by every other kernel
+  TensorEntry* xq = find_tensor(ctx, x_id);
+  if (xq && xq->quant.quantized) {
+    rc = get_f32(ctx, x_id, (int64_t)ci->batchSize * ci->inHeight * ci->inWidth * ci->inChannels, "x", &x);
+  } else {
+    rc = get_activation(ctx, x_id, (int64_t)ci->batchSize * ci->inHeight * ci->inWidth * ci->inChannels, "x", &x);
+  }
   if (rc) return rc;
   rc = get_f32(ctx, w_id, (int64_t)ci->filterHeight * ci->filterWidth * ci->inChannels * ci->outChannels,
                "filter", &w);
@@ -344,17 +351,24 @@ extern "C" int tfjs_cuda_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_te
   // The 3-channel 3x3 stem: the image window of a patch arrives by TMA and is rearranged into
   // im2col rows in shared memory (TF32; other modes take the gather path below).  It can store
   // its result as half directly.
-  if (!x16 && ctx->use_tensor_cores && conv_rgb_tcgen05_supported(*ci, e.activation, ctx->math_mode)) {
+  const bool x8 = x->quant.quantized;
+  if (!x16 && ctx->use_tensor_cores &&
+      (x8 ? conv_rgb_u8_tcgen05_supported(*ci, e.activation, ctx->math_mode)
+          : conv_rgb_tcgen05_supported(*ci, e.activation, ctx->math_mode))) {
     PackedWeights pw;
     bool temporary;
     rc = packed_weights(ctx, w, 0, 27, ci->outChannels, false, true, &pw, &temporary, 9, 10, 32);
     if (rc) return rc;
-    return launch_conv_rgb_tcgen05(ctx, (const float*)x->ptr, *ci, pw.hi, pw.kp, o->ptr, e, o16);
+    return launch_conv_rgb_tcgen05(ctx, x->ptr, *ci, pw.hi, pw.kp, o->ptr, e, o16, x8, x->quant.scale, x->quant.min);
   }
   // Every other kernel computes on float32 storage.
   F32View xv;
   F32Out ov;
-  rc = view_as_f32(ctx, x, &xv);
+  if (x8) {  // decoded copy (cached on the tensor until its bytes change)
+    rc = float_view(ctx, x, &xv.ptr);
+  } else {
+    rc = view_as_f32(ctx, x, &xv);
+  }
   if (!rc) rc = out_as_f32(ctx, o, &ov);
   if (rc) {
     release_view(ctx, &xv);

@@ -202,8 +202,9 @@ struct EpilogueArgs {
   int prelu_scalar = 0;
   float clip_lo = 0.f, clip_hi = 0.f;
   // Internal (never set through the C ABI): round the result to the nearest tf32 value before
-  // storing it.  Set for an intermediate tensor whose only reader is a TF32 tensor-core
-  // contraction, which would otherwise truncate it.
+  // storing it (as far as the tensor core can tell: the low 13 bits may be left as they fall).
+  // Set for a private intermediate whose only reader is a TF32 tensor-core contraction, which
+  // would otherwise truncate it.
   int round_tf32 = 0;
 };
 int resolve_epilogue(tfjs_cuda_ctx* ctx, const tfjs_epilogue* epi, int64_t channels,
@@ -333,8 +334,11 @@ int launch_sepconv_tcgen05(tfjs_cuda_ctx* ctx, const void* x, const tfjs_conv2d_
                            const EpilogueArgs& dw_epi, const float* w_hi, int64_t kp, void* y, int64_t N,
                            const EpilogueArgs& pw_epi, bool half = false);
 bool conv_rgb_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode);
-int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& ci, const float* w_hi,
-                            int64_t kp, void* y, const EpilogueArgs& epi, bool out_half = false);
+// in_u8: x holds one unsigned byte per value (image pixels), decoded on chip as q * q_scale + q_min
+bool conv_rgb_u8_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode);
+int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const void* x, const tfjs_conv2d_info& ci, const float* w_hi,
+                            int64_t kp, void* y, const EpilogueArgs& epi, bool out_half = false, bool in_u8 = false,
+                            double q_scale = 0.0, double q_min = 0.0);
 bool conv_tma_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode);
 int launch_conv_tma_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& ci, const float* w_hi,
                             int64_t kp, float* y, const EpilogueArgs& epi);

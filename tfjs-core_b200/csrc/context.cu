@@ -426,6 +426,10 @@ static size_t dtype_size(int dtype) { return dtype == TFJS_BOOL ? 1 : (dtype == 
 // Records whether the values the host just handed over are all finite (small float tensors only:
 // filters and biases; an image batch is not scanned).
 static void note_host_values(TensorEntry* t, const void* host) {
+  if (t->quant.quantized) {  // raw bytes: every decoded value q * scale + min stays as finite as before
+    if (t->finite_version + 1 == t->version) t->finite_version = t->version;
+    return;
+  }
   t->finite_version = ~0ull;
   if (t->dtype != TFJS_F32 || t->size > 65536 || (t->size > 0 && !host)) return;
   const uint32_t* bits = (const uint32_t*)host;
@@ -494,7 +498,9 @@ extern "C" int tfjs_cuda_tensor_write(tfjs_cuda_ctx* ctx, tfjs_tensor_id id, con
   if (!t) return set_error(ctx, TFJS_CUDA_ERR_NOT_FOUND, "write: unknown tensor id %lld", (long long)id);
   // backend_cpu.ts:125-127: writing null throws
   TFJS_REQUIRE(ctx, host != nullptr || nbytes == 0, "MathBackendCUDA.write(): values cannot be null");
-  TFJS_REQUIRE(ctx, !t->quant.quantized, "cannot write float values into a quantised tensor");
+  // a quantised tensor is refilled with raw bytes (one per element), e.g. the next batch of pixels
+  TFJS_REQUIRE(ctx, !t->quant.quantized || nbytes == t->nbytes,
+               "a quantised tensor takes its %zu raw bytes, not float values", t->nbytes);
   cudaSetDevice(ctx->device);
   if (t->copy_pending) {  // an earlier asynchronous upload must not land after this one
     TFJS_CHECK_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, t->copy_event, 0));
@@ -542,7 +548,8 @@ extern "C" int tfjs_cuda_tensor_write_async(tfjs_cuda_ctx* ctx, tfjs_tensor_id i
   TensorEntry* t = find_tensor(ctx, id);
   if (!t) return set_error(ctx, TFJS_CUDA_ERR_NOT_FOUND, "write: unknown tensor id %lld", (long long)id);
   TFJS_REQUIRE(ctx, host != nullptr || nbytes == 0, "MathBackendCUDA.write(): values cannot be null");
-  TFJS_REQUIRE(ctx, !t->quant.quantized, "cannot write float values into a quantised tensor");
+  TFJS_REQUIRE(ctx, !t->quant.quantized || nbytes == t->nbytes,
+               "a quantised tensor takes its %zu raw bytes, not float values", t->nbytes);
   TFJS_REQUIRE(ctx, t->dtype != TFJS_F16, "asynchronous writes need float32 storage (use tensor_write)");
   TFJS_REQUIRE(ctx, nbytes == t->nbytes, "write: %zu bytes given, tensor holds %zu", nbytes, t->nbytes);
   TFJS_REQUIRE(ctx, !ctx->capturing, "asynchronous writes cannot be captured into a graph");

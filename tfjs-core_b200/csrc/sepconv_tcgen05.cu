@@ -81,9 +81,11 @@ constexpr int MODE_CONV = 2; // dense convolution, Cin a multiple of 32, stride 
 
 // IN16: the input image is stored as IEEE half (16-bit activation storage): a pixel of a k-block
 // is a 64-byte line, a window stage half as large.
-template <int S, int MODE, bool IN16 = false>
+// IN8 (MODE_RGB only): the image is stored as one unsigned byte per value (pixels), decoded on chip
+// as q * scale + min through a 256-entry table; ROW_FLOATS then counts bytes.
+template <int S, int MODE, bool IN16 = false, bool IN8 = false>
 struct Raw {
-  static constexpr int ELEM = IN16 ? 2 : 4;
+  static constexpr int ELEM = IN8 ? 1 : (IN16 ? 2 : 4);
   static constexpr int PIX_BYTES = BLOCK_K * ELEM;       // one pixel of a 32-channel k-block (MODE_DW)
   static constexpr int PARTS = MODE == MODE_DW ? S : 1;  // raw stages per k-block
   static constexpr int PART_ROWS = PH / PARTS;           // patch rows per raw stage
@@ -91,7 +93,8 @@ struct Raw {
   static constexpr int COLS = (PW - 1) * S + 3;
   // floats per window row: 32 channels per pixel, or (RGB) 3 per pixel plus up to 3 floats of
   // slack in front so that the copy can start on a 16-byte boundary, rounded up to 16 bytes
-  static constexpr int ROW_FLOATS = MODE == MODE_DW ? COLS * BLOCK_K : (COLS * 3 + 3 + 3) / 4 * 4;
+  static constexpr int ROW_FLOATS = MODE == MODE_DW ? COLS * BLOCK_K
+                                    : (IN8 ? (COLS * 3 + 15 + 15) / 16 * 16 : (COLS * 3 + 3 + 3) / 4 * 4);
   static constexpr int BYTES = MODE == MODE_CONV ? A_TILE_BYTES : ROWS * ROW_FLOATS * ELEM;
   static constexpr int STRIDE = (BYTES + 1023) / 1024 * 1024;
   static constexpr int GROUP_THREADS = DW_THREADS / dw_groups(S, MODE);
@@ -105,11 +108,11 @@ __host__ __device__ constexpr int w_stages(int block_n, int s, int mode) {
   return block_n >= 256 ? 2 : (block_n >= 128 ? ((mode == 0 && s == 2) ? 2 : 3) : 4);
 }
 __host__ __device__ constexpr int epi_arrivals(int block_n) { return block_n >= 64 ? EPI_WARPS : 4; }
-template <int S, int MODE, bool IN16 = false>
+template <int S, int MODE, bool IN16 = false, bool IN8 = false>
 __host__ __device__ constexpr int raw_stages(int block_n) {
   int left = SMEM_LIMIT - 1024 - a_slot_bytes(block_n, S, MODE, IN16) - w_stages(block_n, S, MODE) * block_n * BLOCK_K * 4 -
              C_STAGING_BYTES - BIAS_STAGING_BYTES - DW_TABLE_BYTES - BARRIER_BYTES;
-  int n = left / Raw<S, MODE, IN16>::STRIDE;
+  int n = left / Raw<S, MODE, IN16, IN8>::STRIDE;
   // Window loads carry the DRAM latency: about 90 KB must be in flight per SM to keep the memory
   // system busy (four 23 KB float32 windows; with half-size windows that takes eight stages).
   const int cap = (MODE == MODE_DW && !IN16) ? 4 : 8;
@@ -127,7 +130,8 @@ struct SepParams {
   int dw_act;
   float dw_lo, dw_hi;
   EpilogueArgs epi;                 // of the pointwise convolution
-  int rgb_off;                      // MODE_RGB: floats between the 16-byte aligned copy start and the window
+  int rgb_off;                      // MODE_RGB: floats (bytes for byte input) between the 16-byte aligned copy start and the window
+  double q_scale, q_min;            // MODE_RGB with byte input: value = q * q_scale + q_min
   int fh, fw, dil_h, dil_w, cin_groups;  // MODE_CONV: filter size, dilation, Cin / 32
   int* status;
 };
@@ -280,16 +284,34 @@ __device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t 
 // MODE_RGB: thread t of a group turns the 3 x 9 window floats of output pixel t (3 filter rows of 3 pixels
 // x 3 channels, contiguous in the NHWC image) into row t of the A tile, in the K' order the repacked
 // filter uses: floats 10*wr + 3*wc + ci, with zeros at 9, 19 and 29..31.
-template <int S>
-__device__ __forceinline__ void rgb_part(uint32_t raw, uint32_t a_tile, int t, const SepParams& p) {
-  using R = Raw<S, MODE_RGB>;
+// (y0, x0): input row / column of the tile's first window element.  Byte input only: the zero fill
+// of a load outside the image is the BYTE 0, which decodes to `min`, not to the 0.0 that padding
+// means, so taps outside the image are set to zero here.
+template <int S, bool IN8>
+__device__ __forceinline__ void rgb_part(uint32_t raw, uint32_t a_tile, int t, const SepParams& p, uint32_t lut,
+                                         int y0, int x0) {
+  using R = Raw<S, MODE_RGB, false, IN8>;
   const int r = t / PW, c = t % PW;
   float v[3][9];
 #pragma unroll
   for (int dr = 0; dr < 3; dr++) {
-    const uint32_t row = raw + (uint32_t)(((r * S + dr) * R::ROW_FLOATS + p.rgb_off + c * S * 3) * 4);
+    if (IN8) {
+      // pixel bytes -> float through the table of decoded (and tf32-rounded) values
+      const uint32_t row = raw + (uint32_t)((r * S + dr) * R::ROW_FLOATS + p.rgb_off + c * S * 3);
+      const int yi = y0 + r * S + dr;
+      const bool row_in = yi >= 0 && yi < p.inH;
 #pragma unroll
-    for (int j = 0; j < 9; j++) v[dr][j] = round_tf32_for_mma(lds32(row + j * 4));  // the tensor core would truncate
+      for (int j = 0; j < 9; j++) {
+        uint32_t q;
+        asm volatile("ld.shared.u8 %0, [%1];" : "=r"(q) : "r"(row + j));
+        const int xi = x0 + c * S + j / 3;
+        v[dr][j] = (row_in && xi >= 0 && xi < p.inW) ? lds32(lut + q * 4) : 0.f;
+      }
+    } else {
+      const uint32_t row = raw + (uint32_t)(((r * S + dr) * R::ROW_FLOATS + p.rgb_off + c * S * 3) * 4);
+#pragma unroll
+      for (int j = 0; j < 9; j++) v[dr][j] = round_tf32_for_mma(lds32(row + j * 4));  // the tensor core would truncate
+    }
   }
   sts128(a_tile + swz(t, 0), make_float4(v[0][0], v[0][1], v[0][2], v[0][3]));
   sts128(a_tile + swz(t, 16), make_float4(v[0][4], v[0][5], v[0][6], v[0][7]));
@@ -304,17 +326,19 @@ __device__ __forceinline__ void rgb_part(uint32_t raw, uint32_t a_tile, int t, c
 // HALF: 16-bit activation storage.  The output is stored as IEEE half, and in MODE_DW the input
 // is read as IEEE half; the stem (MODE_RGB) keeps its float32 input image.  The arithmetic does not
 // change: float32 depthwise taps, tf32 tensor-core products, float32 accumulators and epilogue.
-template <int BLOCK_N, int S, int MODE, bool HALF = false>
+// IN8 (MODE_RGB): the input image is stored as bytes and decoded on chip as q * q_scale + q_min.
+template <int BLOCK_N, int S, int MODE, bool HALF = false, bool IN8 = false>
 __global__ void __launch_bounds__(THREADS, 1)
 sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                        const __grid_constant__ CUtensorMap map_y, SepParams p) {
+  static_assert(!IN8 || MODE == MODE_RGB, "byte input is the 3-channel stem's");
   constexpr bool IN16 = HALF && MODE == MODE_DW;
   constexpr bool OUT16 = HALF;
-  using R = Raw<S, MODE, IN16>;
+  using R = Raw<S, MODE, IN16, IN8>;
   constexpr int W_STAGES = w_stages(BLOCK_N, S, MODE);
   constexpr int GROUPS = dw_groups(S, MODE);
   constexpr int GROUP_THREADS = DW_THREADS / GROUPS;
-  constexpr int RAW_STAGES = raw_stages<S, MODE, IN16>(BLOCK_N);
+  constexpr int RAW_STAGES = raw_stages<S, MODE, IN16, IN8>(BLOCK_N);
   static_assert(RAW_STAGES >= 2 && RAW_STAGES % GROUPS == 0 && A_SLOTS % GROUPS == 0, "rings split evenly");
   constexpr bool IN_PLACE = a_in_place(BLOCK_N, S, MODE, IN16);
   // MODE_CONV: the stage the TMA load filled IS the A tile; the helper warps only round it to tf32
@@ -401,6 +425,13 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     for (int i = threadIdx.x; i < 9 * p.C; i += THREADS) tab[i] = __ldg(p.dw_filter + i);
     for (int i = threadIdx.x; i < p.C; i += THREADS)
       tab[9 * p.C + i] = p.dw_bias ? __ldg(p.dw_bias + (p.dw_bias_scalar ? 0 : i)) : 0.f;
+  }
+  if (IN8) {
+    // the 256 byte values decoded once per CTA, q * scale + min in float64 as decodeWeights does
+    // (io_utils.ts:139), already rounded for the tensor core
+    float* lut = reinterpret_cast<float*>(table);
+    for (int q = threadIdx.x; q < 256; q += THREADS)
+      lut[q] = round_tf32_for_mma((float)((double)q * p.q_scale + p.q_min));
   }
   tcgen05_fence_before();
   __syncthreads();
@@ -614,7 +645,10 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
             slot = rs;
           }
           if (MODE == MODE_RGB) {
-            rgb_part<S>(raw_s, a_s, t, p);
+            const int img = tile / tiles_per_image;
+            const int rem = tile - img * tiles_per_image;
+            const int ty = rem / p.tiles_x, tx = rem - ty * p.tiles_x;
+            rgb_part<S, IN8>(raw_s, a_s, t, p, table_s, ty * PH * S - p.pad_r, tx * PW * S - p.pad_c);
           } else {
             // in place: named barrier 1 + group over the group's threads, between reads and writes
             const int sync_id = IN_PLACE ? 1 + group : 0;
@@ -751,15 +785,15 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   }
 }
 
-template <int BLOCK_N, int S, int MODE, bool HALF = false>
+template <int BLOCK_N, int S, int MODE, bool HALF = false, bool IN8 = false>
 int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my,
                    const SepParams& p) {
   constexpr bool IN16 = HALF && MODE == MODE_DW;
   constexpr int smem_bytes = 1024 + a_slot_bytes(BLOCK_N, S, MODE, IN16) + w_stages(BLOCK_N, S, MODE) * BLOCK_N * BLOCK_K * 4 +
-                             C_STAGING_BYTES + raw_stages<S, MODE, IN16>(BLOCK_N) * Raw<S, MODE, IN16>::STRIDE +
+                             C_STAGING_BYTES + raw_stages<S, MODE, IN16, IN8>(BLOCK_N) * Raw<S, MODE, IN16, IN8>::STRIDE +
                              DW_TABLE_BYTES + BIAS_STAGING_BYTES + BARRIER_BYTES;
   static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
-  auto kernel = sepconv_tcgen05_kernel<BLOCK_N, S, MODE, HALF>;
+  auto kernel = sepconv_tcgen05_kernel<BLOCK_N, S, MODE, HALF, IN8>;
   // per device and per kernel; atomic because contexts of several devices may call from several
   // host threads (setting the attribute twice is harmless)
   static std::atomic<bool> configured[64];
@@ -769,6 +803,9 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap&
   }
   const int grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
   launch_ex(ctx, kernel, dim3(grid), dim3(THREADS), smem_bytes, mx, mw, my, p);
+  if (MODE == MODE_RGB && IN8)
+    return post_launch(ctx, HALF ? "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32, uint8 in, float16 out)"
+                                 : "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32, uint8 in)");
   if (MODE == MODE_RGB)
     return post_launch(ctx, HALF ? "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32, float16 out)"
                                  : "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32)");
@@ -780,16 +817,17 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap&
                                  : "separableConv2d (fused dw3x3 s2 + pw, TF32)");
 }
 
-template <int S, int MODE, bool HALF = false>
+template <int S, int MODE, bool HALF = false, bool IN8 = false>
 int launch_stride(tfjs_cuda_ctx* ctx, int block_n, const CUtensorMap& mx, const CUtensorMap& mw,
                   const CUtensorMap& my, const SepParams& p) {
   switch (block_n) {
     case 32:
-      if (MODE != MODE_DW) return launch_variant<32, S, MODE == MODE_DW ? MODE_RGB : MODE, HALF>(ctx, mx, mw, my, p);
+      if (MODE != MODE_DW)
+        return launch_variant<32, S, MODE == MODE_DW ? MODE_RGB : MODE, HALF, IN8>(ctx, mx, mw, my, p);
       // depthwise mode has no 32-wide variant: falls through
-    case 64: return launch_variant<64, S, MODE, HALF>(ctx, mx, mw, my, p);
-    case 128: return launch_variant<128, S, MODE, HALF>(ctx, mx, mw, my, p);
-    default: return launch_variant<256, S, MODE, HALF>(ctx, mx, mw, my, p);
+    case 64: return launch_variant<64, S, MODE, HALF, IN8>(ctx, mx, mw, my, p);
+    case 128: return launch_variant<128, S, MODE, HALF, IN8>(ctx, mx, mw, my, p);
+    default: return launch_variant<256, S, MODE, HALF, IN8>(ctx, mx, mw, my, p);
   }
 }
 
@@ -858,6 +896,7 @@ int launch_sepconv_tcgen05(tfjs_cuda_ctx* ctx, const void* x, const tfjs_conv2d_
   p.epi = pw_epi;
   p.status = ctx->d_status;
   p.rgb_off = 0;
+  p.q_scale = p.q_min = 0.0;
   if (half)
     return S == 1 ? launch_stride<1, MODE_DW, true>(ctx, block_n, mx, mw, my, p)
                   : launch_stride<2, MODE_DW, true>(ctx, block_n, mx, mw, my, p);
@@ -877,17 +916,26 @@ bool conv_rgb_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int 
          tcgen05_gemm_supported(128, ci.outChannels, 32);
 }
 
-int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& ci, const float* w_hi,
-                            int64_t kp, void* y, const EpilogueArgs& epi, bool out_half) {
+// Byte input also needs image rows of a multiple of 16 bytes (the row stride of the tensor map).
+bool conv_rgb_u8_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode) {
+  return conv_rgb_tcgen05_supported(ci, activation, math_mode) && (ci.inWidth * 3) % 16 == 0;
+}
+
+int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const void* x, const tfjs_conv2d_info& ci, const float* w_hi,
+                            int64_t kp, void* y, const EpilogueArgs& epi, bool out_half, bool in_u8, double q_scale,
+                            double q_min) {
   const int S = ci.strideHeight;
   const int64_t N = ci.outChannels;
   const uint64_t el = out_half ? 2 : 4;
   const int block_n = N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256));
   CUtensorMap mx, mw, my;
+  const uint64_t xel = in_u8 ? 1 : 4;
   const uint64_t xd[3] = {(uint64_t)ci.inWidth * 3, (uint64_t)ci.inHeight, (uint64_t)ci.batchSize};
-  const uint64_t xs[2] = {(uint64_t)ci.inWidth * 12, (uint64_t)ci.inHeight * ci.inWidth * 12};
-  const uint32_t xb1[3] = {(uint32_t)Raw<1, MODE_RGB>::ROW_FLOATS, (uint32_t)Raw<1, MODE_RGB>::ROWS, 1};
-  const uint32_t xb2[3] = {(uint32_t)Raw<2, MODE_RGB>::ROW_FLOATS, (uint32_t)Raw<2, MODE_RGB>::ROWS, 1};
+  const uint64_t xs[2] = {(uint64_t)ci.inWidth * 3 * xel, (uint64_t)ci.inHeight * ci.inWidth * 3 * xel};
+  const uint32_t xb1[3] = {(uint32_t)(in_u8 ? Raw<1, MODE_RGB, false, true>::ROW_FLOATS : Raw<1, MODE_RGB>::ROW_FLOATS),
+                           (uint32_t)Raw<1, MODE_RGB>::ROWS, 1};
+  const uint32_t xb2[3] = {(uint32_t)(in_u8 ? Raw<2, MODE_RGB, false, true>::ROW_FLOATS : Raw<2, MODE_RGB>::ROW_FLOATS),
+                           (uint32_t)Raw<2, MODE_RGB>::ROWS, 1};
   const uint64_t wd[2] = {(uint64_t)kp, (uint64_t)N};
   const uint64_t ws[1] = {(uint64_t)kp * 4};
   const uint32_t wb[2] = {BLOCK_K, (uint32_t)block_n};
@@ -895,7 +943,8 @@ int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2
   const uint64_t ys[3] = {(uint64_t)N * el, (uint64_t)ci.outWidth * N * el, (uint64_t)ci.outHeight * ci.outWidth * N * el};
   const uint32_t yb[4] = {32, PW, 2, 1};
   const bool ok =
-      tma_encode_tiled(&mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, x, xd, xs, S == 1 ? xb1 : xb2, CU_TENSOR_MAP_SWIZZLE_NONE) &&
+      tma_encode_tiled(&mx, in_u8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, x, xd, xs,
+                       S == 1 ? xb1 : xb2, CU_TENSOR_MAP_SWIZZLE_NONE) &&
       tma_encode_tiled(&mw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, w_hi, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B) &&
       tma_encode_tiled(&my, out_half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, y, yd, ys, yb,
                        out_half ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B);
@@ -918,7 +967,17 @@ int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2
   p.epi = epi;
   // the window of a patch starts at float (tx*16*S - padLeft)*3 of its image row; 16*S*3 is a
   // multiple of 4, so the distance to the 16-byte boundary below it is the same for every patch
-  p.rgb_off = ((-3 * ci.padLeft) % 4 + 4) % 4;
+  // (bytes: the distance to the 16-byte boundary counts bytes, and 16*S*3 bytes is a multiple of 16 too)
+  p.rgb_off = in_u8 ? ((-3 * ci.padLeft) % 16 + 16) % 16 : ((-3 * ci.padLeft) % 4 + 4) % 4;
+  p.q_scale = q_scale;
+  p.q_min = q_min;
+  if (in_u8) {
+    if (out_half)
+      return S == 1 ? launch_stride<1, MODE_RGB, true, true>(ctx, block_n, mx, mw, my, p)
+                    : launch_stride<2, MODE_RGB, true, true>(ctx, block_n, mx, mw, my, p);
+    return S == 1 ? launch_stride<1, MODE_RGB, false, true>(ctx, block_n, mx, mw, my, p)
+                  : launch_stride<2, MODE_RGB, false, true>(ctx, block_n, mx, mw, my, p);
+  }
   p.status = ctx->d_status;
   if (out_half)
     return S == 1 ? launch_stride<1, MODE_RGB, true>(ctx, block_n, mx, mw, my, p)
