@@ -243,6 +243,19 @@ __device__ __forceinline__ float round_tf32_for_mma(float v) {
   return __uint_as_float(b);
 }
 
+// The same for a value that float32 arithmetic on this device has just produced (an fma chain, a
+// max.NaN / min.NaN clamp): two instructions instead of three.  Such a value is finite, +-inf or
+// the canonical NaN 0x7fffffff.  inf + 0x1000 still reads as inf in the 19 bits the tensor core
+// takes; for the NaN the add wraps to a negative integer and the signed max keeps the NaN.  (A
+// NaN with the sign bit and all of the top 11 mantissa bits set, which no arithmetic instruction
+// returns, would come out as a tiny positive number: operands that arrive from the caller go
+// through round_tf32_for_mma instead.)
+__device__ __forceinline__ float round_tf32_after_arith(float v) {
+  const int b = __float_as_int(v);
+  const int t = (int)((uint32_t)b + 0x1000u);
+  return __int_as_float(max(t, b));
+}
+
 // Programmatic dependent launch.  A kernel launched through launch_ex may start while the
 // kernel before it on the stream is still running; pdl_wait() blocks until that kernel (and
 // therefore everything before it) has completed and its writes are visible, and must precede

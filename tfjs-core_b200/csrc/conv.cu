@@ -287,8 +287,8 @@ struct DepthwiseStrip {
         o.z = activate<ACT>(o.z, lo, hi);
         o.w = activate<ACT>(o.w, lo, hi);
         if (round) {  // the only reader is a TF32 contraction: round instead of letting it truncate
-          o.x = round_tf32_for_mma(o.x); o.y = round_tf32_for_mma(o.y);
-          o.z = round_tf32_for_mma(o.z); o.w = round_tf32_for_mma(o.w);
+          o.x = round_tf32_after_arith(o.x); o.y = round_tf32_after_arith(o.y);
+          o.z = round_tf32_after_arith(o.z); o.w = round_tf32_after_arith(o.w);
         }
         yrow[j * C4] = o;
       }

@@ -197,8 +197,8 @@ depthwise3x3_image_kernel(const __grid_constant__ CUtensorMap map_x, ImageParams
         acc.w = act<ACT>(acc.w, p.lo, p.hi);
         if (p.round_tf32) {
           // (the integer form: cvt.rna.tf32 runs at a fraction of the ALU rate and cost 10 % of this kernel)
-          acc.x = round_tf32_for_mma(acc.x); acc.y = round_tf32_for_mma(acc.y);
-          acc.z = round_tf32_for_mma(acc.z); acc.w = round_tf32_for_mma(acc.w);
+          acc.x = round_tf32_after_arith(acc.x); acc.y = round_tf32_after_arith(acc.y);
+          acc.z = round_tf32_after_arith(acc.z); acc.w = round_tf32_after_arith(acc.w);
         }
         if (HALF)
           yp16[yo * y_row] = make_uint2(pack_half2(acc.x, acc.y), pack_half2(acc.z, acc.w));

@@ -272,10 +272,10 @@ __device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t 
       // rounded to the nearest tf32 value: the tensor core reads the upper 19 bits only, and
       // truncating these (non-negative, after relu6) values would bias every sum downwards
       float4 v;
-      v.x = round_tf32_for_mma(dw_activate<ACT>(__uint_as_float(ox), p.dw_lo, p.dw_hi));
-      v.y = round_tf32_for_mma(dw_activate<ACT>(__uint_as_float(oy), p.dw_lo, p.dw_hi));
-      v.z = round_tf32_for_mma(dw_activate<ACT>(__uint_as_float(oz), p.dw_lo, p.dw_hi));
-      v.w = round_tf32_for_mma(dw_activate<ACT>(__uint_as_float(ow), p.dw_lo, p.dw_hi));
+      v.x = round_tf32_after_arith(dw_activate<ACT>(__uint_as_float(ox), p.dw_lo, p.dw_hi));
+      v.y = round_tf32_after_arith(dw_activate<ACT>(__uint_as_float(oy), p.dw_lo, p.dw_hi));
+      v.z = round_tf32_after_arith(dw_activate<ACT>(__uint_as_float(oz), p.dw_lo, p.dw_hi));
+      v.w = round_tf32_after_arith(dw_activate<ACT>(__uint_as_float(ow), p.dw_lo, p.dw_hi));
       sts128(a_tile + swz(m0 + j, q * 16), v);
     }
   }
