@@ -298,6 +298,7 @@ KERNEL_FAMILY = {"separableConv2d (fused dw3x3 s1 + pw, TF32, float16)": "separa
                  "separableConv2d (fused dw3x3 s1 + pw, TF32)": "separable_fused",
                  "separableConv2d (fused dw3x3 s2 + pw, TF32)": "separable_fused",
                  "gemm_tcgen05 (TF32)": "gemm_tcgen05", "gemm_tcgen05 (3xTF32)": "gemm_tcgen05",
+                 "gemm_tcgen05 (TF32, CTA pairs)": "gemm_tcgen05",
                  "gemm_tcgen05 (TF32, uint8 weights)": "gemm_tcgen05",
                  "gemm_tcgen05 (3xTF32, uint8 weights)": "gemm_tcgen05",
                  "conv2d_tcgen05 (TF32)": "conv2d_tcgen05", "conv2d_tcgen05 (3xTF32)": "conv2d_tcgen05",

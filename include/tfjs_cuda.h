@@ -120,7 +120,9 @@ const char* tfjs_cuda_last_error(const tfjs_cuda_ctx* ctx);
  * "dequant_in_gemm" (quantised matMul / 1x1 conv2d weights: 0, the default, expands them once
  * into cached tf32 planes; 1 keeps them uint8 in device memory and dequantises each tile in
  * shared memory inside the GEMM main loop; the results are bit-identical), "fuse_separable"
- * (see tfjs_cuda_separable_conv2d), "pdl" (1 launches the main kernels with programmatic stream
+ * (see tfjs_cuda_separable_conv2d), "gemm_pair" (TF32 matMul / 1x1 conv2d on pairs of CTAs that
+ * share each weight tile: 1, the default, where the problem is large enough to pay; 0 never; 2
+ * wherever the shape allows; the results are bit-identical either way), "pdl" (1 launches the main kernels with programmatic stream
  * serialization, so that a kernel's prologue overlaps its predecessor's tail; default 0),
  * "wait_limit_us" (every device-side wait of the kernels is bounded; a wait that runs out makes
  * the kernel return and the next ctx_sync / tensor_read report TFJS_CUDA_ERR_TIMEOUT, the context

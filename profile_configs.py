@@ -4,6 +4,8 @@ operators of the unfused tf.* path.
 
     python profile_configs.py [tf32|3xtf32]          # configs 1-3
     python profile_configs.py ops [batch] [reps]     # add / clip / exp / sum / max / pooling
+    python profile_configs.py block B HW C N [stride] [key=value ...]
+                                                     # one depthwise 3x3 + pointwise block on its own
 
 For each config: the device time of one call launched eagerly and replayed from a CUDA graph, and
 the bandwidth / FLOP rate the algorithmic figures correspond to (parity with the CPU oracle is
@@ -90,7 +92,45 @@ def run_ops(batch, reps=5):
         print(f"{name:42s} {rows[0][0]:24s} {best * 1e3:9.1f} us  {nbytes / best / 1e6:8.0f} GB/s", flush=True)
 
 
+def run_block(batch, hw, c, n, stride, options, reps=5):
+    """One separable block (depthwise 3x3 + bias + relu6, pointwise + bias + relu6) of a MobileNet
+    layer's shape, alone on the device: input, intermediate and output are the only large buffers
+    (1.2 GB for pw7-pw11 at batch 1024), which keeps a profiler capture of a full-size launch small.
+    `options` are context options (e.g. gemm_pair=0, fuse_separable=0)."""
+    bk = tf.BackendCuda(0, "tf32")
+    tf.ENGINE.registerBackend("profile-cuda", lambda: bk, 10)
+    tf.ENGINE.setBackend("profile-cuda")
+    for key, value in options.items():
+        bk.setOption(key, value)
+    r = rng(21)
+    x = ops.tensor(r.uniform(0, 6, (batch, hw, hw, c)).astype(np.float32))
+    wd = ops.tensor(r.normal(0, 0.5, (3, 3, c, 1)).astype(np.float32))
+    wp = ops.tensor((r.uniform(-1, 1, (1, 1, c, n)) / np.sqrt(c)).astype(np.float32))
+    bd = ops.tensor(r.normal(0, 0.3, c).astype(np.float32))
+    bp = ops.tensor(r.normal(0, 0.3, n).astype(np.float32))
+    ci = conv_util.compute_conv2d_info(x.shape, wd.shape, stride, 1, "same", None, True)
+    call = lambda: bk.fusedSeparableConv2d(x, wd, wp, ci, bd, "relu6", bp, "relu6")  # noqa: E731
+    call().dispose()
+    bk.profileBegin(4 * reps)
+    for _ in range(reps):
+        call().dispose()
+    rows = bk.profileEnd()
+    per_call = len(rows) // reps
+    out_pixels = batch * ci.outHeight * ci.outWidth
+    nbytes = {"depthwise": 4 * (x.size + out_pixels * c), "pointwise": 4 * out_pixels * (c + n),
+              "fused": 4 * (x.size + out_pixels * n)}
+    for i in range(per_call):
+        name = rows[i][0]
+        best = min(rows[i + k * per_call][1] for k in range(reps))
+        kind = "fused" if name.startswith("separableConv2d") else ("depthwise" if name.startswith("depthwise") else "pointwise")
+        print(f"{name:62s} {best * 1e3:9.1f} us {nbytes[kind] / 1e6:9.1f} MB {nbytes[kind] / best / 1e6:7.0f} GB/s", flush=True)
+
+
 def main():
+    if len(sys.argv) > 1 and sys.argv[1] == "block":
+        nums = [int(a) for a in sys.argv[2:] if "=" not in a]
+        options = {a.split("=")[0]: int(a.split("=")[1]) for a in sys.argv[2:] if "=" in a}
+        return run_block(nums[0], nums[1], nums[2], nums[3], nums[4] if len(nums) > 4 else 1, options)
     if len(sys.argv) > 1 and sys.argv[1] == "ops":
         return run_ops(int(sys.argv[2]) if len(sys.argv) > 2 else 64, int(sys.argv[3]) if len(sys.argv) > 3 else 5)
     mode = sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("-") else "tf32"

@@ -1,0 +1,115 @@
+"""The TF32 GEMM on pairs of CTAs (256 x 256 tiles, tcgen05 cta_group::2).
+
+It serves the pointwise convolution of a separable block whose depthwise result has already been
+rounded to tf32 (KernelBackend.fusedConv2d with a 1x1 filter, tfjs-core/src/backends/backend.ts:
+414-418).  The pair kernel issues the same tensor-core instructions over the same k-slices as the
+single-CTA kernel, so the two must agree bit for bit; against the CPU oracle the block is held to
+the TF32 tolerance.  Shapes cover whole tiles, a last row tile whose second CTA lies entirely
+beyond M, one and several column tiles, one to many k-blocks, and every epilogue.
+"""
+import numpy as np
+import pytest
+
+import oracle
+from gpu_util import rel_err, tf  # noqa: F401
+
+pytestmark = pytest.mark.gpu
+
+
+def _block(tf, b, h, w, c, n, seed, pw_act, bias, pair):
+    """depthwise 3x3 + pointwise through fusedSeparableConv2d's two-kernel form."""
+    from tfjs_core_b200 import conv_util
+    bk = tf.ENGINE.backend
+    rng = np.random.Generator(np.random.PCG64(seed))
+    x = rng.uniform(-1, 1, (b, h, w, c)).astype(np.float32)
+    wd = rng.normal(0, 0.5, (3, 3, c, 1)).astype(np.float32)
+    wp = (rng.uniform(-1, 1, (1, 1, c, n)) / np.sqrt(c)).astype(np.float32)
+    bd = rng.normal(0, 0.3, c).astype(np.float32)
+    bp = rng.normal(0, 0.3, n).astype(np.float32) if bias else None
+    ci = conv_util.compute_conv2d_info(x.shape, wd.shape, 1, 1, "same", None, True)
+    t = lambda a: None if a is None else tf.ops.tensor(a)  # noqa: E731
+    bk.setOption("gemm_pair", pair)
+    before = bk.launchCount()
+    y = bk.fusedSeparableConv2d(t(x), t(wd), t(wp), ci, t(bd), "relu6", t(bp), pw_act)
+    out = y.dataSync().reshape(y.shape)
+    return x, wd, wp, bd, bp, out, bk.launchCount() - before
+
+
+def _oracle_block(x, wd, wp, bd, bp, pw_act):
+    ci = oracle.compute_conv2d_info(x.shape, wd.shape, 1, 1, "same", None, True)
+    mid = oracle.unary("clip", oracle.binary("add", oracle.depthwise_conv2d(x, wd, ci), bd), 0, 6)
+    ci2 = oracle.compute_conv2d_info(mid.shape, wp.shape, 1, 1, "valid")
+    y = oracle.conv2d(mid, wp, ci2)
+    if bp is not None:
+        y = oracle.binary("add", y, bp)
+    if pw_act == "relu6":
+        y = oracle.unary("clip", y, 0, 6)
+    elif pw_act == "relu":
+        y = oracle.unary("relu", y)
+    return y
+
+
+SHAPES = [
+    # b, h, w, c (= K), n, pointwise activation, bias
+    (8, 14, 14, 512, 512, "relu6", True),    # M = 1568: 6 whole row tiles + 32 rows, two column tiles
+    (3, 14, 14, 512, 256, "relu", True),     # M = 588: the last tile's second CTA is all padding
+    (2, 16, 16, 288, 1024, "linear", False), # M = 512: whole tiles, 9 k-blocks, four column tiles
+    (6, 7, 7, 1024, 1024, "relu6", True),    # M = 294: one tile and a sliver, 32 k-blocks
+    (4, 16, 16, 128, 256, "linear", True),   # 4 k-blocks: shorter than the ring
+]
+
+
+@pytest.mark.parametrize("b,h,w,c,n,act,bias", SHAPES)
+def test_pair_kernel_equals_single_cta_kernel_and_matches_the_oracle(tf, b, h, w, c, n, act, bias):
+    bk = tf.ENGINE.backend
+    bk.setMathMode("tf32")
+    bk.setOption("fuse_separable", 0)
+    try:
+        seed = b * 1000 + c + n
+        x, wd, wp, bd, bp, single, _ = _block(tf, b, h, w, c, n, seed, act, bias, pair=0)
+        bk.profileBegin(16)
+        _, _, _, _, _, paired, _ = _block(tf, b, h, w, c, n, seed, act, bias, pair=2)
+        names = [name for name, _ in bk.profileEnd()]
+        assert any("CTA pairs" in name for name in names), names   # the pair kernel did run
+        assert np.array_equal(paired, single)
+        want = _oracle_block(x, wd, wp, bd, bp, act)
+        assert rel_err(paired, want) <= 1e-3   # TF32 contraction tolerance
+    finally:
+        bk.setOption("gemm_pair", 1)
+        bk.setOption("fuse_separable", 1)
+        bk.setMathMode("3xtf32")
+
+
+def test_pair_kernel_twice_in_a_row_and_after_other_kernels(tf):
+    """Tensor memory and barriers are set up per launch: back-to-back launches with different
+    shapes, with a single-CTA tensor-core kernel in between, leave nothing behind."""
+    bk = tf.ENGINE.backend
+    bk.setMathMode("tf32")
+    bk.setOption("fuse_separable", 0)
+    try:
+        outs = []
+        for rep in range(2):
+            for (b, h, w, c, n, act, bias) in (SHAPES[0], SHAPES[1]):
+                outs.append(_block(tf, b, h, w, c, n, 7, act, bias, pair=2)[5])
+                _block(tf, 2, 8, 8, 64, 64, 8, "relu", True, pair=0)
+        assert np.array_equal(outs[0], outs[2]) and np.array_equal(outs[1], outs[3])
+    finally:
+        bk.setOption("gemm_pair", 1)
+        bk.setOption("fuse_separable", 1)
+        bk.setMathMode("3xtf32")
+
+
+def test_default_dispatch_takes_the_pair_kernel_only_for_large_problems(tf):
+    bk = tf.ENGINE.backend
+    bk.setMathMode("tf32")
+    try:
+        bk.profileBegin(16)
+        _block(tf, 2, 14, 14, 512, 512, 1, "relu6", True, pair=1)        # 2 x 2 tiles: single-CTA kernel
+        small = [name for name, _ in bk.profileEnd()]
+        bk.profileBegin(16)
+        _block(tf, 128, 14, 14, 512, 512, 1, "relu6", True, pair=1)      # 98 x 2 tiles: pairs
+        large = [name for name, _ in bk.profileEnd()]
+        assert not any("CTA pairs" in name for name in small), small
+        assert any("CTA pairs" in name for name in large), large
+    finally:
+        bk.setMathMode("3xtf32")

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libtfjs_cuda.so")
-SOURCES = ["context.cu", "elementwise.cu", "conv.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "api.cu",
+SOURCES = ["context.cu", "elementwise.cu", "conv.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "gemm_tcgen05_pair.cu", "api.cu",
            "no_alloc.cu", "sepconv_tcgen05.cu", "backward.cu", "depthwise_tma.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

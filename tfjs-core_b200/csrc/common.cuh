@@ -105,6 +105,7 @@ struct tfjs_cuda_ctx {
   // separable_conv2d: 0 = always two kernels, 1 = one fused kernel where that is faster,
   // 2 = fused wherever the kernel takes the shape
   int fuse_separable = 1;
+  int gemm_pair = 1;  // 0: never use the CTA-pair GEMM, 1: where it pays, 2: wherever its shape rules allow
   // launch the kernels that support it with programmatic stream serialization (off by default:
   // with one persistent block per SM the next kernel's blocks cannot become resident before this
   // kernel's blocks retire, and the measured step time is 0.5-3 % worse with it on)
@@ -308,6 +309,11 @@ int launch_dequant(tfjs_cuda_ctx* ctx, const uint8_t* q, float* out, int64_t n, 
 int set_wait_limit_gemm(long long cycles);
 int set_wait_limit_sepconv(long long cycles);
 int set_wait_limit_depthwise_image(long long cycles);
+int set_wait_limit_gemm_pair(long long cycles);
+// gemm_tcgen05_pair.cu: the 256 x 256 tile on a pair of CTAs (tcgen05 cta_group::2); TF32, A tf32-exact
+bool gemm_pair_supported(const tfjs_cuda_ctx* ctx, int64_t M, int64_t K, int64_t N);
+int launch_gemm_tcgen05_pair(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, const float* w_hi, int64_t kp,
+                             float* out, int64_t N, const EpilogueArgs& epi);
 // gemm_tcgen05.cu
 bool tcgen05_gemm_supported(int64_t M, int64_t N, int64_t K);
 // a_tf32_exact (TF32 mode only): every element of `a` already has its low 13 mantissa bits zero

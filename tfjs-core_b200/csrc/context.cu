@@ -107,6 +107,7 @@ static void release_cached(tfjs_cuda_ctx* ctx) {
 constexpr size_t CANARY_BYTES = 256;
 constexpr uint32_t CANARY_WORD = 0xA5C3F00Du;
 constexpr int STATUS_CANARY = 90;  // device status code: a guard pattern was overwritten
+constexpr int STATUS_SMEM_LAYOUT = 91;  // a kernel's dynamic shared-memory window did not start 1024-aligned
 
 __global__ void canary_fill_kernel(uint32_t* guard) { guard[threadIdx.x] = CANARY_WORD; }
 __global__ void canary_check_kernel(const uint32_t* guard, int* status) {
@@ -320,10 +321,14 @@ extern "C" int tfjs_cuda_ctx_set_option(tfjs_cuda_ctx* ctx, const char* key, dou
     int khz = 0;
     TFJS_CHECK_CUDA(ctx, cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->device));
     const long long cycles = (long long)(value * 1e-3 * (double)khz);
-    if (set_wait_limit_gemm(cycles) || set_wait_limit_sepconv(cycles) || set_wait_limit_depthwise_image(cycles)) {
+    if (set_wait_limit_gemm(cycles) || set_wait_limit_sepconv(cycles) || set_wait_limit_depthwise_image(cycles) ||
+        set_wait_limit_gemm_pair(cycles)) {
       cudaGetLastError();
       return set_error(ctx, TFJS_CUDA_ERR_CUDA, "could not set the wait limit");
     }
+  } else if (!strcmp(key, "gemm_pair")) {
+    TFJS_REQUIRE(ctx, value == 0 || value == 1 || value == 2, "gemm_pair must be 0, 1 or 2");
+    ctx->gemm_pair = (int)value;
   } else if (!strcmp(key, "fuse_separable")) {
     TFJS_REQUIRE(ctx, value == 0 || value == 1 || value == 2, "fuse_separable must be 0, 1 or 2");
     ctx->fuse_separable = (int)value;
@@ -342,6 +347,9 @@ static int check_device_status(tfjs_cuda_ctx* ctx) {
     if (code == STATUS_CANARY)
       return set_error(ctx, TFJS_CUDA_ERR_CUDA,
                        "a kernel wrote past the end of a buffer (guard pattern overwritten; device status %d)", code);
+    if (code == STATUS_SMEM_LAYOUT)
+      return set_error(ctx, TFJS_CUDA_ERR_CUDA,
+                       "a kernel found its shared-memory window misaligned and did not run (device status %d)", code);
     return set_error(ctx, TFJS_CUDA_ERR_TIMEOUT,
                      "a kernel gave up on a bounded wait (device status %d)", code);
   }

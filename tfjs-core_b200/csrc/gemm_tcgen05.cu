@@ -45,11 +45,22 @@ __host__ __device__ constexpr int stage_bytes(int block_n, bool split, bool wq =
 __host__ __device__ constexpr int wq_ring_bytes(int block_n, bool split, bool wq) {
   return wq ? WQ_SLOTS * block_n * BLOCK_K * 4 * (split ? 2 : 1) + LUT_BYTES : 0;
 }
+// The ring takes everything the 227 KB allow.  No room is set aside for aligning the dynamic
+// shared-memory window to 1024 bytes (which SWIZZLE_128B tiles need): the window of a kernel
+// without static shared memory starts 1024-aligned, the launch asks for up to 1 KB of slack where
+// the layout leaves it, and a CTA that finds it would not fit reports STATUS_SMEM_LAYOUT and
+// returns before touching anything.  At BLOCK_N = 256 this is the difference between 3 and 4
+// stages of 48 KB, i.e. a third more bytes in flight on the layers that are bound by load latency.
 __host__ __device__ constexpr int num_stages(int block_n, bool split, bool wq = false) {
-  int s = (SMEM_LIMIT - C_STAGING_BYTES - BIAS_STAGING_BYTES - BARRIER_BYTES - 1024 -
+  int s = (SMEM_LIMIT - C_STAGING_BYTES - BIAS_STAGING_BYTES - BARRIER_BYTES -
            wq_ring_bytes(block_n, split, wq)) / stage_bytes(block_n, split, wq);
   return s > 8 ? 8 : s;
 }
+__host__ __device__ constexpr int layout_bytes(int block_n, bool split, bool wq) {
+  return wq_ring_bytes(block_n, split, wq) + num_stages(block_n, split, wq) * stage_bytes(block_n, split, wq) +
+         C_STAGING_BYTES + BIAS_STAGING_BYTES + BARRIER_BYTES;
+}
+constexpr int STATUS_SMEM_LAYOUT = 91;  // device status code: the shared-memory window is not aligned as assumed
 
 // Geometry of an implicit-GEMM convolution: row m of the A matrix is output pixel
 // (b, yo, xo) = unflatten(m), column kk is filter tap (wr, wc) and input channel ci.
@@ -142,7 +153,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment by an offset on the __shared__ array itself: the pointers derived from
   // it stay in the shared address space (an integer round trip would make every access generic)
-  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const uint32_t align_pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
+  {
+    uint32_t window;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(window));
+    if (align_pad + (uint32_t)layout_bytes(BLOCK_N, SPLIT, WQ) > window) {  // uniform over the CTA
+      if (threadIdx.x == 0) atomicCAS(p.status, 0, STATUS_SMEM_LAYOUT);
+      return;
+    }
+  }
+  uint8_t* smem = smem_raw + align_pad;
   uint8_t* a_hi = smem;
   uint8_t* a_lo = a_hi + STAGES * A_STAGE_BYTES;  // SPLIT only
   // tf32 weight tiles: one per stage, or (WQ) a ring of WQ_SLOTS tiles filled by the converters
@@ -227,7 +247,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       // (Only where an A tile is worked on for long: K >= 512, or K >= 256 with two or more column
       // tiles.  On the other short-K layers, which run at the DRAM roofline anyway, the extra
       // requests measured slower.)
-      const int PREFETCH = (AMODE == A_MATRIX && STAGES < 6 &&
+      const int PREFETCH = (AMODE == A_MATRIX && STAGES <= 6 &&
                             (p.num_k_blocks >= 16 || (p.num_k_blocks >= 8 && p.num_n_tiles >= 2)))
                                ? 8
                                : 0;
@@ -709,9 +729,9 @@ template <int BLOCK_N, int PREC, int AMODE, bool WQ = false, bool OUT16 = false>
 int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mh, const CUtensorMap& ml,
                    const CUtensorMap& mc, const GemmParams& p) {
   constexpr bool SPLIT = PREC == PREC_3XTF32;
-  constexpr int smem_bytes = wq_ring_bytes(BLOCK_N, SPLIT, WQ) + num_stages(BLOCK_N, SPLIT, WQ) * stage_bytes(BLOCK_N, SPLIT, WQ) + C_STAGING_BYTES +
-                             BIAS_STAGING_BYTES + BARRIER_BYTES + 1024;
-  static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
+  constexpr int layout = layout_bytes(BLOCK_N, SPLIT, WQ);
+  static_assert(layout <= SMEM_LIMIT, "shared memory budget exceeded");
+  constexpr int smem_bytes = layout + 1024 <= SMEM_LIMIT ? layout + 1024 : SMEM_LIMIT;
   auto kernel = gemm_tcgen05_kernel<BLOCK_N, PREC, AMODE, WQ, OUT16>;
   // the attribute is per device and per kernel; contexts of several devices may call from several
   // host threads, so the flags are atomic (setting the attribute twice is harmless)
@@ -791,6 +811,11 @@ int launch_common(tfjs_cuda_ctx* ctx, int amode, const float* a, const ConvGeom*
   // TF32: a dense A matrix is rounded to nearest in shared memory unless its producer already did
   const int prec = split ? PREC_3XTF32 : ((amode == A_MATRIX && !a_tf32_exact) ? PREC_TF32_ROUND : PREC_TF32_ASIS);
   TFJS_REQUIRE(ctx, w_q != nullptr || !split || w_lo != nullptr, "3xTF32 needs the residual weight plane");
+  // Large TF32 problems whose A is already tf32-exact go to the CTA-pair kernel (256 x 256 tiles,
+  // half of the weight tile per SM).
+  if (amode == A_MATRIX && prec == PREC_TF32_ASIS && !w_q && ctx->gemm_pair && kp == K &&
+      gemm_pair_supported(ctx, M, K, N))
+    return launch_gemm_tcgen05_pair(ctx, a, M, K, w_hi, kp, out, N, epi);
   int block_n;
   if (N <= 32) block_n = 32;
   else if (N <= 64) block_n = 64;

@@ -1,0 +1,408 @@
+// Tensor-core GEMM on CTA pairs (tcgen05 cta_group::2): out[M, N] = act(A[M, K] * W[K, N] + bias[N])
+// for the deep pointwise convolutions (tfjs-core/src/backends/backend.ts:414-418 fusedConv2d with a
+// 1x1 filter, :134-138 fusedBatchMatMul), float32 in and out, one TF32 pass.
+//
+// Why pairs.  The single-CTA kernel computes a 128 x 256 tile per SM and has to bring 128 rows of A
+// and 256 rows of W into its shared memory per k-block: 48 KB for 128 x 256 x 32 multiply-adds.  Its
+// main loop runs at about 2.9 cycles per 128-byte operand row, i.e. it is bound by the bytes that
+// arrive in (and are read back out of) the SM's shared memory, with the tensor pipe half idle.  A
+// pair of CTAs on the two SMs of a cluster computes a 256 x 256 tile together: each CTA supplies its
+// own 128 rows of A and only HALF of the W tile (128 rows), and the tensor cores of both SMs read
+// both halves.  That is 32 KB per SM and k-block for the same 128 x 256 x 32 multiply-adds per SM,
+// the W traffic out of L2 halves, and the shared memory holds 6 stages instead of 4.
+//
+// Structure (both CTAs of a pair run the same code; rank 0 is the leader):
+//   warp 8      TMA producer, in each CTA: its A tile [128 x 32] and its half of the W tile
+//               [128 x 32] per k-block into a ring of local stages.  The loads of both CTAs complete
+//               on the LEADER's full barrier (cp.async.bulk.tensor with .cta_group::2, no multicast).
+//   warp 9      MMA issuer, leader only: one thread issues tcgen05.mma.cta_group::2 (M = 256,
+//               N = 256, K = 8) per 32-byte k-step and commits stage-release and accumulator-ready
+//               barriers in both CTAs (one tcgen05.commit per barrier; the peer's through its
+//               shared::cluster address).
+//   warps 0-7   epilogue, in each CTA: its 128 rows x 256 columns of the accumulator (two buffers
+//               of 256 tensor-memory columns, so the next tile's MMAs overlap), bias, activation,
+//               swizzled staging, 128-bit row stores.  Both CTAs hand the buffer back on the leader's barrier.
+// Every mbarrier wait is bounded.  A wait that gives up sets the status word; the CTA leaves its
+// loops and still takes part in the two cluster barriers, so its peer (whose own waits then run out
+// as well) is not left behind, and the pair frees its tensor memory.
+#include <atomic>
+
+#include "tcgen05_ptx.cuh"
+
+namespace {
+
+constexpr int CTA_M = 128;    // rows of A (and of the output) per CTA
+constexpr int PAIR_M = 256;   // rows per pair tile
+constexpr int TILE_N = 256;   // columns per pair tile
+constexpr int HALF_N = 128;   // rows of the K-major W tile that each CTA stages
+constexpr int BLOCK_K = 32;   // 32 fp32 = 128 bytes = one swizzle row
+constexpr int A_BYTES = CTA_M * BLOCK_K * 4;   // 16 KB
+constexpr int B_BYTES = HALF_N * BLOCK_K * 4;  // 16 KB
+constexpr int STAGE_TX = A_BYTES + B_BYTES;    // bytes one CTA's loads deposit per stage
+constexpr int STAGES = 6;
+constexpr int EPI_WARPS = 8;
+constexpr int C_CHUNK_BYTES = 32 * 32 * 4;
+constexpr int C_STAGING_BYTES = EPI_WARPS * C_CHUNK_BYTES;
+constexpr int BIAS_STAGING_BYTES = EPI_WARPS * 256;
+constexpr int BARRIER_BYTES = 1024;
+constexpr int LAYOUT_BYTES = STAGES * (A_BYTES + B_BYTES) + C_STAGING_BYTES + BIAS_STAGING_BYTES + BARRIER_BYTES;
+constexpr int SMEM_LIMIT = 232448;  // 227 KB
+static_assert(LAYOUT_BYTES <= SMEM_LIMIT, "shared memory budget exceeded");
+constexpr int THREADS = 320;
+constexpr uint32_t ACC_COLS = TILE_N;        // tensor-memory columns per accumulator buffer
+constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;  // all 512
+constexpr int STATUS_SMEM_LAYOUT = 91;
+
+struct PairParams {
+  int M, N, K;
+  int num_m_tiles, num_n_tiles, num_k_blocks;
+  float* out;
+  int* status;
+  EpilogueArgs epi;
+};
+
+// ---- cluster-level PTX -----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
+               "r"(bytes)
+               : "memory");
+}
+// TMA load whose completion is counted on a barrier that may live in the peer CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y)
+      : "memory");
+}
+// one barrier (anywhere in the cluster) arrives once all MMAs issued so far by this thread are done
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar)
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_tf32_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                      uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                         PairParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t align_pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
+  uint32_t window;
+  asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(window));
+  // the same in both CTAs of a pair; a pair that cannot lay out its stages does nothing but the
+  // two cluster barriers
+  const bool layout_ok = align_pad + (uint32_t)LAYOUT_BYTES <= window;
+  uint8_t* smem = smem_raw + align_pad;
+  uint8_t* a_st = smem;
+  uint8_t* b_st = a_st + STAGES * A_BYTES;
+  uint8_t* c_stage = b_st + STAGES * B_BYTES;
+  uint8_t* bias_stage = c_stage + C_STAGING_BYTES;
+  uint64_t* bars = (uint64_t*)(bias_stage + BIAS_STAGING_BYTES);
+  uint64_t* full_bar = bars;                     // [STAGES] leader's: both CTAs' loads -> MMA
+  uint64_t* empty_bar = bars + STAGES;           // [STAGES] in each CTA: MMA -> local producer
+  uint64_t* tmem_full_bar = bars + 2 * STAGES;   // [2] in each CTA: MMA -> local epilogue
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;  // [2] leader's: both CTAs' epilogues -> MMA
+  uint32_t* tmem_ptr_holder = (uint32_t*)(tmem_empty_bar + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_ptr_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+
+  if (layout_ok) {
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < STAGES; s++) {
+        mbar_init(smem_u32(&full_bar[s]), 2);  // one arrive.expect_tx from the producer of each CTA
+        mbar_init(smem_u32(&empty_bar[s]), 1);
+      }
+      for (int a = 0; a < 2; a++) {
+        mbar_init(smem_u32(&tmem_full_bar[a]), 1);
+        mbar_init(smem_u32(&tmem_empty_bar[a]), 2 * EPI_WARPS);
+      }
+      *abort_flag = 0;
+      fence_barrier_init();
+    }
+    if (warp == 9) {
+      // Tensor memory of both SMs: warp 9 of each CTA takes part in the allocation, and the same
+      // warps free it at the end.
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(tmem_ptr_holder)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+  } else if (threadIdx.x == 0) {
+    atomicCAS(p.status, 0, STATUS_SMEM_LAYOUT);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+  tcgen05_fence_after();
+  const uint32_t tmem_base = layout_ok ? *tmem_ptr_holder : 0u;
+  // everything above touched only shared and tensor memory; global memory from here on
+  pdl_wait();
+  pdl_launch_dependents();
+
+  if (!layout_ok) {
+    // nothing to do
+  } else if (warp == 8) {
+    // ---------------- TMA producer (each CTA loads its own operands) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      // (No L2 prefetch cursor ahead of the loads, unlike the single-CTA kernel: with six stages in
+      // flight it measured 6-12 % slower, its requests compete with the loads.)
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m0 = (tile / p.num_n_tiles) * PAIR_M + (int)rank * CTA_M;
+        const int n0 = (tile % p.num_n_tiles) * TILE_N + (int)rank * HALF_N;
+        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+          ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 31);
+          if (!ok) break;
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          mbar_arrive_expect_tx_cluster(bar, STAGE_TX);
+          tma_load_2d_pair(smem_u32(a_st + stage * A_BYTES), &map_a, bar, kb * BLOCK_K, m0);
+          tma_load_2d_pair(smem_u32(b_st + stage * B_BYTES), &map_w, bar, kb * BLOCK_K, n0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ---------------- MMA issuer (leader only) ----------------
+    if (rank == 0 && lane == 0) {
+      constexpr uint32_t idesc = make_idesc(PAIR_M, TILE_N);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, local++) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status, 32);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * ACC_COLS;
+        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+          ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 33);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t a_s = smem_u32(a_st + stage * A_BYTES);
+          const uint32_t b_s = smem_u32(b_st + stage * B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / 8; k++) {
+            const uint32_t koff = k * 32;  // 8 tf32 = 32 bytes inside the 128-byte swizzle row
+            tcgen05_mma_tf32_pair(tmem_d, make_smem_desc(a_s + koff), make_smem_desc(b_s + koff), idesc,
+                                  (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          // the stage is free in both CTAs once these MMAs have read it
+          const uint32_t eb = smem_u32(&empty_bar[stage]);
+          tcgen05_commit_pair(eb);
+          tcgen05_commit_pair(map_to_cta(eb, 1));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) {  // accumulator complete: wake the epilogue of both CTAs
+          const uint32_t fb = smem_u32(&tmem_full_bar[acc]);
+          tcgen05_commit_pair(fb);
+          tcgen05_commit_pair(map_to_cta(fb, 1));
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue warps 0-7 (each CTA: its 128 rows, all 256 columns) ----------------
+    // Warps w and w+4 share TMEM lane quarter w%4 and split the eight 32-column chunks: warp half h
+    // takes chunks h, h+2, h+4, h+6.
+    constexpr int MY_CHUNKS = TILE_N / 64;
+    const int quarter = warp & 3;
+    const int half = warp >> 2;
+    uint8_t* stage_buf = c_stage + warp * C_CHUNK_BYTES;
+    float* bias_s = reinterpret_cast<float*>(bias_stage + warp * 256);
+    float* alpha_s = bias_s + 32;
+    const bool has_bias = p.epi.bias != nullptr;
+    const bool has_alpha = p.epi.activation == TFJS_ACT_PRELU;
+    int local = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, local++) {
+      const int m0 = (tile / p.num_n_tiles) * PAIR_M + (int)rank * CTA_M;
+      const int n0 = (tile % p.num_n_tiles) * TILE_N;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      float bias_l[MY_CHUNKS], alpha_l[MY_CHUNKS];
+#pragma unroll
+      for (int i = 0; i < MY_CHUNKS; i++) {
+        const int cl = n0 + (2 * i + half) * 32 + lane;
+        bias_l[i] = 0.f;
+        alpha_l[i] = 0.f;
+        if (has_bias) bias_l[i] = p.epi.bias_scalar ? __ldg(p.epi.bias) : (cl < p.N ? __ldg(p.epi.bias + cl) : 0.f);
+        if (has_alpha) alpha_l[i] = p.epi.prelu_scalar ? __ldg(p.epi.prelu) : (cl < p.N ? __ldg(p.epi.prelu + cl) : 0.f);
+      }
+      ok = mbar_wait(smem_u32(&tmem_full_bar[acc]), acc_phase, abort_flag, p.status, 34);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      // TMEM address: lane in bits [16,32), column in [0,16)
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * ACC_COLS;
+#pragma unroll
+      for (int i = 0; i < MY_CHUNKS; i++) {
+        const int chunk = 2 * i + half;
+        const int c0 = n0 + chunk * 32;
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + chunk * 32, r);
+        __syncwarp();
+        bias_s[lane] = bias_l[i];
+        if (has_alpha) alpha_s[lane] = alpha_l[i];
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int k = 0; k < 32; k++) v[k] = __uint_as_float(r[k]);
+        __syncwarp();
+        if (i == MY_CHUNKS - 1) {
+          // this warp's last read of the accumulator: hand it back to the leader's MMA warp
+          tcgen05_fence_before();
+          if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
+        }
+        switch (p.epi.activation) {
+          case TFJS_ACT_RELU: finish_chunk<TFJS_ACT_RELU>(v, has_bias, bias_s, alpha_s, p.epi); break;
+          case TFJS_ACT_PRELU: finish_chunk<TFJS_ACT_PRELU>(v, has_bias, bias_s, alpha_s, p.epi); break;
+          case TFJS_ACT_CLIP: finish_chunk<TFJS_ACT_CLIP>(v, has_bias, bias_s, alpha_s, p.epi); break;
+          default: finish_chunk<TFJS_ACT_LINEAR>(v, has_bias, bias_s, alpha_s, p.epi); break;
+        }
+        // Through the warp's staging buffer (rows of 128 bytes, 16-byte chunk j of row r at chunk
+        // j ^ (r & 7), which keeps both passes free of bank conflicts) and out with 128-bit stores,
+        // four whole rows per warp instruction.  Stores issued by the warps measured 2 % faster here
+        // than TMA stores, which queue up behind the loads in the same unit.
+        __syncwarp();
+        uint8_t* dst = stage_buf + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+          *reinterpret_cast<float4*>(dst + ((j ^ (lane & 7)) << 4)) =
+              make_float4(v[j * 4 + 0], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+        __syncwarp();
+        const int rr = lane >> 3, cc = lane & 7;
+#pragma unroll
+        for (int it = 0; it < 8; it++) {
+          const int row = it * 4 + rr;
+          const float4 val = *reinterpret_cast<const float4*>(stage_buf + row * 128 + ((cc ^ (row & 7)) << 4));
+          const int gm = m0 + quarter * 32 + row;
+          if (gm < p.M) *reinterpret_cast<float4*>(p.out + (size_t)gm * p.N + c0 + cc * 4) = val;
+        }
+      }
+    }
+  }
+
+  // A wait that gave up leaves copies and MMAs in flight: give them time to land before the
+  // shared and tensor memory they target is released.
+  if (layout_ok && *abort_flag) {
+    for (int i = 0; i < 100; i++) __nanosleep(1000);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees tensor memory or exits while the other may still use it
+  if (layout_ok && warp == 9) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+bool encode_matrix(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+                   uint32_t box_cols) {
+  const uint64_t dims[2] = {cols, rows};
+  const uint64_t strides[1] = {cols * 4};
+  const uint32_t box[2] = {box_cols, box_rows};
+  return tma_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+}  // namespace
+
+int set_wait_limit_gemm_pair(long long cycles) { return set_wait_limit_here(cycles); }
+
+// The pair kernel takes whole 256-column tiles and 32-deep k-blocks, and only pays when there are
+// enough tiles to fill the pairs of the device about twice (below that the single-CTA kernel's
+// smaller tiles spread over more SMs).
+bool gemm_pair_supported(const tfjs_cuda_ctx* ctx, int64_t M, int64_t K, int64_t N) {
+  if (!(N % TILE_N == 0 && K % BLOCK_K == 0 && K >= 128 && M >= PAIR_M && M < (1ll << 31) && N < (1ll << 31)))
+    return false;
+  const int64_t tiles = ceil_div64(M, PAIR_M) * (N / TILE_N);
+  return ctx->gemm_pair >= 2 || tiles >= (int64_t)ctx->sm_count;
+}
+
+// A [M, K] must hold tf32-exact values (its producer rounded them); W is the K-major tf32 plane
+// [N, kp] of the packed weights.
+int launch_gemm_tcgen05_pair(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, const float* w_hi, int64_t kp,
+                             float* out, int64_t N, const EpilogueArgs& epi) {
+  CUtensorMap ma, mw;
+  if (!(encode_matrix(&ma, a, (uint64_t)M, (uint64_t)K, CTA_M, BLOCK_K) &&
+        encode_matrix(&mw, w_hi, (uint64_t)N, (uint64_t)kp, HALF_N, BLOCK_K)))
+    return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+  PairParams p;
+  p.M = (int)M;
+  p.N = (int)N;
+  p.K = (int)K;
+  p.num_m_tiles = (int)ceil_div64(M, PAIR_M);
+  p.num_n_tiles = (int)(N / TILE_N);
+  p.num_k_blocks = (int)(K / BLOCK_K);
+  p.status = ctx->d_status;
+  p.out = out;
+  p.epi = epi;
+  constexpr int smem_bytes = LAYOUT_BYTES + 1024 <= SMEM_LIMIT ? LAYOUT_BYTES + 1024 : SMEM_LIMIT;
+  auto kernel = gemm_tcgen05_pair_kernel;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  // per device: the dynamic shared-memory opt-in and how many pairs can be resident at once
+  static std::atomic<int> resident_pairs[64];
+  int max_pairs = resident_pairs[ctx->device & 63].load(std::memory_order_acquire);
+  if (max_pairs == 0) {
+    TFJS_CHECK_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    cfg.gridDim = dim3(2 * (unsigned)(ctx->sm_count / 2));
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    TFJS_CHECK_CUDA(ctx, cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg));
+    TFJS_REQUIRE(ctx, clusters >= 1, "no CTA pair of the pair GEMM fits on this device");
+    max_pairs = clusters < ctx->sm_count / 2 ? clusters : ctx->sm_count / 2;
+    resident_pairs[ctx->device & 63].store(max_pairs, std::memory_order_release);
+  }
+  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  cfg.gridDim = dim3(2 * (unsigned)pairs);
+  cfg.numAttrs = ctx->use_pdl ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, kernel, ma, mw, p);
+  return post_launch(ctx, "gemm_tcgen05 (TF32, CTA pairs)");
+}
