@@ -497,7 +497,8 @@ def run_cuda(args):
     if top in measured_traffic:
         mb, at_batch = measured_traffic[top]
         traffic = mb * 1e6 * per
-        traffic_from = f"ncu capture at batch {at_batch}, scaled to batch {per} (traffic grows with the batch)"
+        traffic_from = (f"ncu capture of full-size launches at batch {at_batch}" if at_batch == per else
+                        f"ncu capture at batch {at_batch}, scaled to batch {per} (traffic grows with the batch)")
     roofline = {"bound": "hbm", "kernel": top, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                 "frac": achieved / hbm_peak, "peak_source": peak_kind,
                 "launches_per_step": fam[top]["launches"] // prof_steps,

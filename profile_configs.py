@@ -6,6 +6,7 @@ operators of the unfused tf.* path.
     python profile_configs.py ops [batch] [reps]     # add / clip / exp / sum / max / pooling
     python profile_configs.py block B HW C N [stride] [key=value ...]
                                                      # one depthwise 3x3 + pointwise block on its own
+    python profile_configs.py stem B                 # the 3x3x3->32 stride-2 first convolution on its own
 
 For each config: the device time of one call launched eagerly and replayed from a CUDA graph, and
 the bandwidth / FLOP rate the algorithmic figures correspond to (parity with the CPU oracle is
@@ -126,7 +127,31 @@ def run_block(batch, hw, c, n, stride, options, reps=5):
         print(f"{name:62s} {best * 1e3:9.1f} us {nbytes[kind] / 1e6:9.1f} MB {nbytes[kind] / best / 1e6:7.0f} GB/s", flush=True)
 
 
+def run_stem(batch, reps=5):
+    """MobileNet's first layer (3x3x3 -> 32, stride 2, + bias + relu6) alone on the device."""
+    bk = tf.BackendCuda(0, "tf32")
+    tf.ENGINE.registerBackend("profile-cuda", lambda: bk, 10)
+    tf.ENGINE.setBackend("profile-cuda")
+    r = rng(22)
+    x = ops.tensor(r.uniform(-1, 1, (batch, 224, 224, 3)).astype(np.float32))
+    w = ops.tensor(r.normal(0, 0.3, (3, 3, 3, 32)).astype(np.float32))
+    b = ops.tensor(r.normal(0, 0.3, 32).astype(np.float32))
+    call = lambda: ops.fused_conv2d(x, w, 2, "same", bias=b, activation="relu6")  # noqa: E731
+    call().dispose()
+    bk.profileBegin(4 * reps)
+    for _ in range(reps):
+        call().dispose()
+    rows = bk.profileEnd()
+    per_call = len(rows) // reps
+    nbytes = 4 * (x.size + batch * 112 * 112 * 32)
+    for i in range(per_call):
+        best = min(rows[i + k * per_call][1] for k in range(reps))
+        print(f"{rows[i][0]:62s} {best * 1e3:9.1f} us {nbytes / 1e6:9.1f} MB {nbytes / best / 1e6:7.0f} GB/s", flush=True)
+
+
 def main():
+    if len(sys.argv) > 1 and sys.argv[1] == "stem":
+        return run_stem(int(sys.argv[2]) if len(sys.argv) > 2 else 64)
     if len(sys.argv) > 1 and sys.argv[1] == "block":
         nums = [int(a) for a in sys.argv[2:] if "=" not in a]
         options = {a.split("=")[0]: int(a.split("=")[1]) for a in sys.argv[2:] if "=" in a}
