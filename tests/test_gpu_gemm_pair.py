@@ -80,6 +80,30 @@ def test_pair_kernel_equals_single_cta_kernel_and_matches_the_oracle(tf, b, h, w
         bk.setMathMode("3xtf32")
 
 
+@pytest.mark.parametrize("b,h,w,c,n,act,bias", SHAPES)
+def test_pair_kernel_3xtf32_equals_single_cta_kernel_and_matches_the_oracle(tf, b, h, w, c, n, act, bias):
+    """3xTF32: each CTA's converter warps split its A stages into tf32 hi / lo, the weight halves
+    arrive as hi and lo planes, three MMAs per k-step into a main and a correction accumulator.
+    Same instruction sequence per output element as the single-CTA kernel: bit-identical, and within
+    1e-5 of the oracle."""
+    bk = tf.ENGINE.backend
+    bk.setMathMode("3xtf32")
+    bk.setOption("fuse_separable", 0)
+    try:
+        seed = b * 1000 + c + n + 1
+        x, wd, wp, bd, bp, single, _ = _block(tf, b, h, w, c, n, seed, act, bias, pair=0)
+        bk.profileBegin(16)
+        _, _, _, _, _, paired, _ = _block(tf, b, h, w, c, n, seed, act, bias, pair=2)
+        names = [name for name, _ in bk.profileEnd()]
+        assert any("3xTF32, CTA pairs" in name for name in names), names
+        assert np.array_equal(paired, single)
+        want = _oracle_block(x, wd, wp, bd, bp, act)
+        assert rel_err(paired, want) <= 1e-5   # 3xTF32 contraction tolerance
+    finally:
+        bk.setOption("gemm_pair", 1)
+        bk.setOption("fuse_separable", 1)
+
+
 def test_pair_kernel_twice_in_a_row_and_after_other_kernels(tf):
     """Tensor memory and barriers are set up per launch: back-to-back launches with different
     shapes, with a single-CTA tensor-core kernel in between, leave nothing behind."""

@@ -38,19 +38,22 @@ constexpr int HALF_N = 128;   // rows of the K-major W tile that each CTA stages
 constexpr int BLOCK_K = 32;   // 32 fp32 = 128 bytes = one swizzle row
 constexpr int A_BYTES = CTA_M * BLOCK_K * 4;   // 16 KB
 constexpr int B_BYTES = HALF_N * BLOCK_K * 4;  // 16 KB
-constexpr int STAGE_TX = A_BYTES + B_BYTES;    // bytes one CTA's loads deposit per stage
-constexpr int STAGES = 6;
+// SPLIT (3xTF32): a stage also holds the lo parts of A (written by the converter warps) and of the
+// weight half (loaded), so three stages of 64 KB instead of six of 32 KB.
+__host__ __device__ constexpr int num_stages(bool split) { return split ? 3 : 6; }
 constexpr int EPI_WARPS = 8;
 constexpr int C_CHUNK_BYTES = 32 * 32 * 4;
 constexpr int C_STAGING_BYTES = EPI_WARPS * C_CHUNK_BYTES;
 constexpr int BIAS_STAGING_BYTES = EPI_WARPS * 256;
 constexpr int BARRIER_BYTES = 1024;
-constexpr int LAYOUT_BYTES = STAGES * (A_BYTES + B_BYTES) + C_STAGING_BYTES + BIAS_STAGING_BYTES + BARRIER_BYTES;
+constexpr int LAYOUT_BYTES = 6 * (A_BYTES + B_BYTES) + C_STAGING_BYTES + BIAS_STAGING_BYTES + BARRIER_BYTES;
 constexpr int SMEM_LIMIT = 232448;  // 227 KB
 static_assert(LAYOUT_BYTES <= SMEM_LIMIT, "shared memory budget exceeded");
-constexpr int THREADS = 320;
-constexpr uint32_t ACC_COLS = TILE_N;        // tensor-memory columns per accumulator buffer
-constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;  // all 512
+// 10 warps, plus (SPLIT) four converter warps that split each A stage into tf32 hi / lo
+__host__ __device__ constexpr int cta_threads(bool split) { return split ? 448 : 320; }
+// Tensor memory, all 512 columns either way: two accumulator buffers of 256 columns, or (SPLIT) one
+// buffer made of a main tile (hi*hi) and a correction tile (lo*hi + hi*lo) that the epilogue adds.
+constexpr uint32_t TMEM_COLS = 512;
 constexpr int STATUS_SMEM_LAYOUT = 91;
 
 struct PairParams {
@@ -78,6 +81,11 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// the same with release semantics at cluster scope: the arriving thread's earlier writes are for
+// a reader in the other CTA (used once per stage and warp, never in a polling loop)
+__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
@@ -107,9 +115,15 @@ __device__ __forceinline__ void tcgen05_mma_tf32_pair(uint32_t tmem_d, uint64_t 
       : "memory");
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+template <bool SPLIT>
+__global__ void __launch_bounds__(cta_threads(SPLIT), 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                         PairParams p) {
+                         const __grid_constant__ CUtensorMap map_w_lo, PairParams p) {
+  constexpr int STAGES = num_stages(SPLIT);
+  constexpr int NUM_ACC = SPLIT ? 1 : 2;
+  constexpr uint32_t ACC_COLS = SPLIT ? 2 * TILE_N : TILE_N;  // tensor-memory columns per buffer
+  // bytes that one CTA's loads complete on the leader's full barrier per stage
+  constexpr uint32_t STAGE_TX = SPLIT ? 2 * B_BYTES : A_BYTES + B_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t align_pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
   uint32_t window;
@@ -118,14 +132,18 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   // two cluster barriers
   const bool layout_ok = align_pad + (uint32_t)LAYOUT_BYTES <= window;
   uint8_t* smem = smem_raw + align_pad;
-  uint8_t* a_st = smem;
-  uint8_t* b_st = a_st + STAGES * A_BYTES;
-  uint8_t* c_stage = b_st + STAGES * B_BYTES;
+  uint8_t* a_st = smem;                                         // [STAGES] A (SPLIT: its hi part after the split)
+  uint8_t* a_lo_st = a_st + STAGES * A_BYTES;                   // [STAGES] SPLIT only
+  uint8_t* b_st = a_lo_st + (SPLIT ? STAGES * A_BYTES : 0);     // [STAGES] this CTA's half of the weight tile
+  uint8_t* b_lo_st = b_st + STAGES * B_BYTES;                   // [STAGES] SPLIT only
+  uint8_t* c_stage = b_lo_st + (SPLIT ? STAGES * B_BYTES : 0);
   uint8_t* bias_stage = c_stage + C_STAGING_BYTES;
   uint64_t* bars = (uint64_t*)(bias_stage + BIAS_STAGING_BYTES);
   uint64_t* full_bar = bars;                     // [STAGES] leader's: both CTAs' loads -> MMA
   uint64_t* empty_bar = bars + STAGES;           // [STAGES] in each CTA: MMA -> local producer
-  uint64_t* tmem_full_bar = bars + 2 * STAGES;   // [2] in each CTA: MMA -> local epilogue
+  uint64_t* a_full_bar = bars + 2 * STAGES;      // [STAGES] SPLIT, in each CTA: its A load -> its converters
+  uint64_t* conv_bar = bars + 3 * STAGES;        // [STAGES] SPLIT, leader's: both CTAs' converters -> MMA
+  uint64_t* tmem_full_bar = bars + 4 * STAGES;   // [2] in each CTA: MMA -> local epilogue
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;  // [2] leader's: both CTAs' epilogues -> MMA
   uint32_t* tmem_ptr_holder = (uint32_t*)(tmem_empty_bar + 2);
   volatile int* abort_flag = (volatile int*)(tmem_ptr_holder + 1);
@@ -142,6 +160,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       for (int s = 0; s < STAGES; s++) {
         mbar_init(smem_u32(&full_bar[s]), 2);  // one arrive.expect_tx from the producer of each CTA
         mbar_init(smem_u32(&empty_bar[s]), 1);
+        mbar_init(smem_u32(&a_full_bar[s]), 1);
+        mbar_init(smem_u32(&conv_bar[s]), 2 * 4);  // one arrival per converter warp of each CTA
       }
       for (int a = 0; a < 2; a++) {
         mbar_init(smem_u32(&tmem_full_bar[a]), 1);
@@ -179,8 +199,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      // (No L2 prefetch cursor ahead of the loads, unlike the single-CTA kernel: with six stages in
-      // flight it measured 6-12 % slower, its requests compete with the loads.)
+      // No L2 prefetch cursor ahead of the loads, unlike the single-CTA kernel: its requests compete
+      // with the loads (TF32, six stages: 6-12 % slower with it; 3xTF32, three stages: 5 % slower).
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         const int m0 = (tile / p.num_n_tiles) * PAIR_M + (int)rank * CTA_M;
         const int n0 = (tile % p.num_n_tiles) * TILE_N + (int)rank * HALF_N;
@@ -189,8 +209,17 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           if (!ok) break;
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
           mbar_arrive_expect_tx_cluster(bar, STAGE_TX);
-          tma_load_2d_pair(smem_u32(a_st + stage * A_BYTES), &map_a, bar, kb * BLOCK_K, m0);
-          tma_load_2d_pair(smem_u32(b_st + stage * B_BYTES), &map_w, bar, kb * BLOCK_K, n0);
+          if (SPLIT) {
+            // A goes to this CTA's own converters first; the weight halves (hi and lo) to the leader
+            const uint32_t abar = smem_u32(&a_full_bar[stage]);
+            mbar_arrive_expect_tx(abar, A_BYTES);
+            tma_load_2d(smem_u32(a_st + stage * A_BYTES), &map_a, abar, kb * BLOCK_K, m0);
+            tma_load_2d_pair(smem_u32(b_st + stage * B_BYTES), &map_w, bar, kb * BLOCK_K, n0);
+            tma_load_2d_pair(smem_u32(b_lo_st + stage * B_BYTES), &map_w_lo, bar, kb * BLOCK_K, n0);
+          } else {
+            tma_load_2d_pair(smem_u32(a_st + stage * A_BYTES), &map_a, bar, kb * BLOCK_K, m0);
+            tma_load_2d_pair(smem_u32(b_st + stage * B_BYTES), &map_w, bar, kb * BLOCK_K, n0);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -204,23 +233,37 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       bool ok = true;
       int local = 0;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, local++) {
-        const int acc = local & 1;
-        const uint32_t acc_phase = (local >> 1) & 1;
+        const int acc = local % NUM_ACC;
+        const uint32_t acc_phase = (local / NUM_ACC) & 1;
         ok = mbar_wait(smem_u32(&tmem_empty_bar[acc]), acc_phase ^ 1, abort_flag, p.status, 32);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + acc * ACC_COLS;
+        const uint32_t tmem_corr = tmem_d + TILE_N;  // SPLIT only
         for (int kb = 0; kb < p.num_k_blocks; kb++) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 33);
+          if (ok && SPLIT) {
+            // (the converters of both CTAs made their stores visible to the tensor cores with
+            // fence.proxy.async and arrived with release semantics at cluster scope; this side needs
+            // the wait and the tcgen05 fence below, no cluster-scope fence of its own)
+            ok = mbar_wait(smem_u32(&conv_bar[stage]), phase, abort_flag, p.status, 35);
+          }
           if (!ok) break;
           tcgen05_fence_after();
           const uint32_t a_s = smem_u32(a_st + stage * A_BYTES);
           const uint32_t b_s = smem_u32(b_st + stage * B_BYTES);
+          const uint32_t a_lo_s = smem_u32(a_lo_st + stage * A_BYTES);
+          const uint32_t b_lo_s = smem_u32(b_lo_st + stage * B_BYTES);
 #pragma unroll
           for (int k = 0; k < BLOCK_K / 8; k++) {
             const uint32_t koff = k * 32;  // 8 tf32 = 32 bytes inside the 128-byte swizzle row
-            tcgen05_mma_tf32_pair(tmem_d, make_smem_desc(a_s + koff), make_smem_desc(b_s + koff), idesc,
-                                  (kb > 0 || k > 0) ? 1u : 0u);
+            const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+            if (SPLIT) {
+              // the small terms accumulate in their own tile, away from the large sum's alignment truncations
+              tcgen05_mma_tf32_pair(tmem_corr, make_smem_desc(a_lo_s + koff), make_smem_desc(b_s + koff), idesc, accum);
+              tcgen05_mma_tf32_pair(tmem_corr, make_smem_desc(a_s + koff), make_smem_desc(b_lo_s + koff), idesc, 1u);
+            }
+            tcgen05_mma_tf32_pair(tmem_d, make_smem_desc(a_s + koff), make_smem_desc(b_s + koff), idesc, accum);
           }
           // the stage is free in both CTAs once these MMAs have read it
           const uint32_t eb = smem_u32(&empty_bar[stage]);
@@ -232,6 +275,41 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           const uint32_t fb = smem_u32(&tmem_full_bar[acc]);
           tcgen05_commit_pair(fb);
           tcgen05_commit_pair(map_to_cta(fb, 1));
+        }
+      }
+    }
+  } else if (warp >= 10) {
+    // ---------------- converter warps (SPLIT; each CTA splits its own A stages) ----------------
+    // hi = tf32(a) in place, lo = tf32(a - hi) into the stage's lo tile; element-wise, so the
+    // swizzled placement is preserved.  A non-finite hi keeps lo at zero (inf - inf would poison
+    // the product with NaN).
+    if (SPLIT) {
+      const int t = threadIdx.x - 320;  // 0..127
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        for (int kb = 0; kb < p.num_k_blocks; kb++) {
+          ok = mbar_wait(smem_u32(&a_full_bar[stage]), phase, abort_flag, p.status, 36);
+          if (!ok) break;
+          float4* hi4 = reinterpret_cast<float4*>(a_st + stage * A_BYTES);
+          float4* lo4 = reinterpret_cast<float4*>(a_lo_st + stage * A_BYTES);
+#pragma unroll
+          for (int i = 0; i < A_BYTES / 16 / 128; i++) {
+            const int idx = t + i * 128;
+            float4 v = hi4[idx], h, l;
+            h.x = round_tf32(v.x); h.y = round_tf32(v.y); h.z = round_tf32(v.z); h.w = round_tf32(v.w);
+            l.x = (fabsf(h.x) <= 3.4028234e38f) ? round_tf32(v.x - h.x) : 0.f;
+            l.y = (fabsf(h.y) <= 3.4028234e38f) ? round_tf32(v.y - h.y) : 0.f;
+            l.z = (fabsf(h.z) <= 3.4028234e38f) ? round_tf32(v.z - h.z) : 0.f;
+            l.w = (fabsf(h.w) <= 3.4028234e38f) ? round_tf32(v.w - h.w) : 0.f;
+            hi4[idx] = h;
+            lo4[idx] = l;
+          }
+          fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor cores
+          __syncwarp();
+          if (lane == 0) mbar_arrive_release_cluster(map_to_cta(smem_u32(&conv_bar[stage]), 0));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -252,8 +330,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, local++) {
       const int m0 = (tile / p.num_n_tiles) * PAIR_M + (int)rank * CTA_M;
       const int n0 = (tile % p.num_n_tiles) * TILE_N;
-      const int acc = local & 1;
-      const uint32_t acc_phase = (local >> 1) & 1;
+      const int acc = local % NUM_ACC;
+      const uint32_t acc_phase = (local / NUM_ACC) & 1;
       float bias_l[MY_CHUNKS], alpha_l[MY_CHUNKS];
 #pragma unroll
       for (int i = 0; i < MY_CHUNKS; i++) {
@@ -282,6 +360,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         float v[32];
 #pragma unroll
         for (int k = 0; k < 32; k++) v[k] = __uint_as_float(r[k]);
+        if (SPLIT) {
+          // add the correction tile (lo*hi + hi*lo) to the hi*hi tile
+          tmem_ld_32x32b_x32(taddr + TILE_N + chunk * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int k = 0; k < 32; k++) v[k] += __uint_as_float(r[k]);
+        }
         __syncwarp();
         if (i == MY_CHUNKS - 1) {
           // this warp's last read of the accumulator: hand it back to the leader's MMA warp
@@ -354,28 +439,15 @@ bool gemm_pair_supported(const tfjs_cuda_ctx* ctx, int64_t M, int64_t K, int64_t
   return ctx->gemm_pair >= 2 || tiles >= (int64_t)ctx->sm_count;
 }
 
-// A [M, K] must hold tf32-exact values (its producer rounded them); W is the K-major tf32 plane
-// [N, kp] of the packed weights.
-int launch_gemm_tcgen05_pair(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, const float* w_hi, int64_t kp,
-                             float* out, int64_t N, const EpilogueArgs& epi) {
-  CUtensorMap ma, mw;
-  if (!(encode_matrix(&ma, a, (uint64_t)M, (uint64_t)K, CTA_M, BLOCK_K) &&
-        encode_matrix(&mw, w_hi, (uint64_t)N, (uint64_t)kp, HALF_N, BLOCK_K)))
-    return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
-  PairParams p;
-  p.M = (int)M;
-  p.N = (int)N;
-  p.K = (int)K;
-  p.num_m_tiles = (int)ceil_div64(M, PAIR_M);
-  p.num_n_tiles = (int)(N / TILE_N);
-  p.num_k_blocks = (int)(K / BLOCK_K);
-  p.status = ctx->d_status;
-  p.out = out;
-  p.epi = epi;
+namespace {
+
+template <bool SPLIT>
+int launch_pair_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mw_lo,
+                        const PairParams& p) {
   constexpr int smem_bytes = LAYOUT_BYTES + 1024 <= SMEM_LIMIT ? LAYOUT_BYTES + 1024 : SMEM_LIMIT;
-  auto kernel = gemm_tcgen05_pair_kernel;
+  auto kernel = gemm_tcgen05_pair_kernel<SPLIT>;
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(THREADS);
+  cfg.blockDim = dim3(cta_threads(SPLIT));
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute attr[2];
@@ -403,6 +475,31 @@ int launch_gemm_tcgen05_pair(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int6
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
   cfg.gridDim = dim3(2 * (unsigned)pairs);
   cfg.numAttrs = ctx->use_pdl ? 2 : 1;
-  cudaLaunchKernelEx(&cfg, kernel, ma, mw, p);
-  return post_launch(ctx, "gemm_tcgen05 (TF32, CTA pairs)");
+  cudaLaunchKernelEx(&cfg, kernel, ma, mw, mw_lo, p);
+  return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32, CTA pairs)" : "gemm_tcgen05 (TF32, CTA pairs)");
+}
+
+}  // namespace
+
+// W is the K-major tf32 plane [N, kp] of the packed weights.  w_lo == nullptr: one TF32 pass, and A
+// [M, K] must hold tf32-exact values (its producer rounded them).  With w_lo (the residual plane):
+// 3xTF32, A is split into hi / lo on chip.
+int launch_gemm_tcgen05_pair(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, const float* w_hi,
+                             const float* w_lo, int64_t kp, float* out, int64_t N, const EpilogueArgs& epi) {
+  CUtensorMap ma, mw, mw_lo;
+  if (!(encode_matrix(&ma, a, (uint64_t)M, (uint64_t)K, CTA_M, BLOCK_K) &&
+        encode_matrix(&mw, w_hi, (uint64_t)N, (uint64_t)kp, HALF_N, BLOCK_K) &&
+        encode_matrix(&mw_lo, w_lo ? w_lo : w_hi, (uint64_t)N, (uint64_t)kp, HALF_N, BLOCK_K)))
+    return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+  PairParams p;
+  p.M = (int)M;
+  p.N = (int)N;
+  p.K = (int)K;
+  p.num_m_tiles = (int)ceil_div64(M, PAIR_M);
+  p.num_n_tiles = (int)(N / TILE_N);
+  p.num_k_blocks = (int)(K / BLOCK_K);
+  p.status = ctx->d_status;
+  p.out = out;
+  p.epi = epi;
+  return w_lo ? launch_pair_variant<true>(ctx, ma, mw, mw_lo, p) : launch_pair_variant<false>(ctx, ma, mw, mw_lo, p);
 }
