@@ -104,6 +104,35 @@ def test_pair_kernel_3xtf32_equals_single_cta_kernel_and_matches_the_oracle(tf, 
         bk.setOption("fuse_separable", 1)
 
 
+@pytest.mark.parametrize("mode,tol", [("tf32", 1e-3), ("3xtf32", 1e-5)])
+def test_pair_kernel_on_a_plain_matmul(tf, mode, tol):
+    """fusedBatchMatMul on operands straight from the host: in TF32 mode nothing has rounded A, so
+    the converter warps of both CTAs round each A stage in shared memory (as the single-CTA kernel's
+    do); ragged M, relu epilogue."""
+    bk = tf.ENGINE.backend
+    bk.setMathMode(mode)
+    try:
+        rng = np.random.Generator(np.random.PCG64(99))
+        m, k, n = 1000, 256, 512
+        a = rng.uniform(-1, 1, (1, m, k)).astype(np.float32)
+        b = (rng.uniform(-1, 1, (1, k, n)) / np.sqrt(k)).astype(np.float32)
+        bias = rng.normal(0, 0.3, n).astype(np.float32)
+        outs = {}
+        for pair in (0, 2):
+            bk.setOption("gemm_pair", pair)
+            bk.profileBegin(16)
+            y = bk.fusedBatchMatMul(a=tf.ops.tensor(a), b=tf.ops.tensor(b), bias=tf.ops.tensor(bias), activation="relu")
+            outs[pair] = y.dataSync().reshape(m, n)
+            names = [name for name, _ in bk.profileEnd()]
+            assert any("CTA pairs" in name for name in names) == (pair == 2), names
+        assert np.array_equal(outs[2], outs[0])
+        want = oracle.unary("relu", oracle.fused_matmul(a, b, bias=bias)[0])
+        assert rel_err(outs[2], want) <= tol
+    finally:
+        bk.setOption("gemm_pair", 1)
+        bk.setMathMode("3xtf32")
+
+
 def test_pair_kernel_twice_in_a_row_and_after_other_kernels(tf):
     """Tensor memory and barriers are set up per launch: back-to-back launches with different
     shapes, with a single-CTA tensor-core kernel in between, leave nothing behind."""

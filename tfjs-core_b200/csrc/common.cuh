@@ -310,11 +310,12 @@ int set_wait_limit_gemm(long long cycles);
 int set_wait_limit_sepconv(long long cycles);
 int set_wait_limit_depthwise_image(long long cycles);
 int set_wait_limit_gemm_pair(long long cycles);
-// gemm_tcgen05_pair.cu: the 256 x 256 tile on a pair of CTAs (tcgen05 cta_group::2); TF32 with A
-// tf32-exact (w_lo null), or 3xTF32 (w_lo = the residual weight plane)
+// gemm_tcgen05_pair.cu: the 256 x 256 tile on a pair of CTAs (tcgen05 cta_group::2); TF32 (w_lo null;
+// A rounded on chip unless a_tf32_exact) or 3xTF32 (w_lo = the residual weight plane)
 bool gemm_pair_supported(const tfjs_cuda_ctx* ctx, int64_t M, int64_t K, int64_t N);
 int launch_gemm_tcgen05_pair(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, const float* w_hi,
-                             const float* w_lo, int64_t kp, float* out, int64_t N, const EpilogueArgs& epi);
+                             const float* w_lo, int64_t kp, float* out, int64_t N, const EpilogueArgs& epi,
+                             bool a_tf32_exact);
 // gemm_tcgen05.cu
 bool tcgen05_gemm_supported(int64_t M, int64_t N, int64_t K);
 // a_tf32_exact (TF32 mode only): every element of `a` already has its low 13 mantissa bits zero

@@ -811,11 +811,13 @@ int launch_common(tfjs_cuda_ctx* ctx, int amode, const float* a, const ConvGeom*
   // TF32: a dense A matrix is rounded to nearest in shared memory unless its producer already did
   const int prec = split ? PREC_3XTF32 : ((amode == A_MATRIX && !a_tf32_exact) ? PREC_TF32_ROUND : PREC_TF32_ASIS);
   TFJS_REQUIRE(ctx, w_q != nullptr || !split || w_lo != nullptr, "3xTF32 needs the residual weight plane");
-  // Large problems go to the CTA-pair kernel (256 x 256 tiles, half of the weight tile per SM): TF32
-  // when A is already tf32-exact, and 3xTF32.
-  if (amode == A_MATRIX && (prec == PREC_TF32_ASIS || prec == PREC_3XTF32) && !w_q && ctx->gemm_pair && kp == K &&
-      gemm_pair_supported(ctx, M, K, N))
-    return launch_gemm_tcgen05_pair(ctx, a, M, K, w_hi, split ? w_lo : nullptr, kp, out, N, epi);
+  // Large problems go to the CTA-pair kernel (256 x 256 tiles, half of the weight tile per SM).
+  // (With on-chip rounding of A the pair kernel only wins on long contractions: 203 vs 211 us at
+  // K = 512, 176 vs 187 at 1024, but 230 vs 219 at 128.)
+  if (amode == A_MATRIX && !w_q && ctx->gemm_pair && kp == K && gemm_pair_supported(ctx, M, K, N) &&
+      (prec != PREC_TF32_ROUND || K >= 512 || ctx->gemm_pair >= 2))
+    return launch_gemm_tcgen05_pair(ctx, a, M, K, w_hi, split ? w_lo : nullptr, kp, out, N, epi,
+                                    prec == PREC_TF32_ASIS);
   int block_n;
   if (N <= 32) block_n = 32;
   else if (N <= 64) block_n = 64;

@@ -38,6 +38,10 @@ constexpr int HALF_N = 128;   // rows of the K-major W tile that each CTA stages
 constexpr int BLOCK_K = 32;   // 32 fp32 = 128 bytes = one swizzle row
 constexpr int A_BYTES = CTA_M * BLOCK_K * 4;   // 16 KB
 constexpr int B_BYTES = HALF_N * BLOCK_K * 4;  // 16 KB
+// How A is prepared for the tensor core (which reads the upper 19 bits of each float32):
+constexpr int PAIR_ASIS = 0;   // one pass, A already holds tf32-exact values
+constexpr int PAIR_SPLIT = 1;  // 3xTF32: converter warps split A into hi / lo, three passes
+constexpr int PAIR_ROUND = 2;  // one pass, converter warps round A to nearest in shared memory first
 // SPLIT (3xTF32): a stage also holds the lo parts of A (written by the converter warps) and of the
 // weight half (loaded), so three stages of 64 KB instead of six of 32 KB.
 __host__ __device__ constexpr int num_stages(bool split) { return split ? 3 : 6; }
@@ -50,7 +54,7 @@ constexpr int LAYOUT_BYTES = 6 * (A_BYTES + B_BYTES) + C_STAGING_BYTES + BIAS_ST
 constexpr int SMEM_LIMIT = 232448;  // 227 KB
 static_assert(LAYOUT_BYTES <= SMEM_LIMIT, "shared memory budget exceeded");
 // 10 warps, plus (SPLIT) four converter warps that split each A stage into tf32 hi / lo
-__host__ __device__ constexpr int cta_threads(bool split) { return split ? 448 : 320; }
+__host__ __device__ constexpr int cta_threads(bool converts) { return converts ? 448 : 320; }
 // Tensor memory, all 512 columns either way: two accumulator buffers of 256 columns, or (SPLIT) one
 // buffer made of a main tile (hi*hi) and a correction tile (lo*hi + hi*lo) that the epilogue adds.
 constexpr uint32_t TMEM_COLS = 512;
@@ -82,11 +86,6 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-// the same with release semantics at cluster scope: the arriving thread's earlier writes are for
-// a reader in the other CTA (used once per stage and warp, never in a polling loop)
-__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
 __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
                "r"(bytes)
@@ -115,15 +114,17 @@ __device__ __forceinline__ void tcgen05_mma_tf32_pair(uint32_t tmem_d, uint64_t 
       : "memory");
 }
 
-template <bool SPLIT>
-__global__ void __launch_bounds__(cta_threads(SPLIT), 1)
+template <int PREC>
+__global__ void __launch_bounds__(cta_threads(PREC != PAIR_ASIS), 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                          const __grid_constant__ CUtensorMap map_w_lo, PairParams p) {
+  constexpr bool SPLIT = PREC == PAIR_SPLIT;
+  constexpr bool CONVERTS = PREC != PAIR_ASIS;  // A passes through this CTA's converter warps
   constexpr int STAGES = num_stages(SPLIT);
   constexpr int NUM_ACC = SPLIT ? 1 : 2;
   constexpr uint32_t ACC_COLS = SPLIT ? 2 * TILE_N : TILE_N;  // tensor-memory columns per buffer
   // bytes that one CTA's loads complete on the leader's full barrier per stage
-  constexpr uint32_t STAGE_TX = SPLIT ? 2 * B_BYTES : A_BYTES + B_BYTES;
+  constexpr uint32_t STAGE_TX = SPLIT ? 2 * B_BYTES : (CONVERTS ? B_BYTES : A_BYTES + B_BYTES);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t align_pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
   uint32_t window;
@@ -209,13 +210,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           if (!ok) break;
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
           mbar_arrive_expect_tx_cluster(bar, STAGE_TX);
-          if (SPLIT) {
+          if (CONVERTS) {
             // A goes to this CTA's own converters first; the weight halves (hi and lo) to the leader
             const uint32_t abar = smem_u32(&a_full_bar[stage]);
             mbar_arrive_expect_tx(abar, A_BYTES);
             tma_load_2d(smem_u32(a_st + stage * A_BYTES), &map_a, abar, kb * BLOCK_K, m0);
             tma_load_2d_pair(smem_u32(b_st + stage * B_BYTES), &map_w, bar, kb * BLOCK_K, n0);
-            tma_load_2d_pair(smem_u32(b_lo_st + stage * B_BYTES), &map_w_lo, bar, kb * BLOCK_K, n0);
+            if (SPLIT) tma_load_2d_pair(smem_u32(b_lo_st + stage * B_BYTES), &map_w_lo, bar, kb * BLOCK_K, n0);
           } else {
             tma_load_2d_pair(smem_u32(a_st + stage * A_BYTES), &map_a, bar, kb * BLOCK_K, m0);
             tma_load_2d_pair(smem_u32(b_st + stage * B_BYTES), &map_w, bar, kb * BLOCK_K, n0);
@@ -242,10 +243,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const uint32_t tmem_corr = tmem_d + TILE_N;  // SPLIT only
         for (int kb = 0; kb < p.num_k_blocks; kb++) {
           ok = mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag, p.status, 33);
-          if (ok && SPLIT) {
+          if (ok && CONVERTS) {
             // (the converters of both CTAs made their stores visible to the tensor cores with
-            // fence.proxy.async and arrived with release semantics at cluster scope; this side needs
-            // the wait and the tcgen05 fence below, no cluster-scope fence of its own)
+            // fence.proxy.async before they arrived; this side needs the wait and the tcgen05 fence
+            // below, no cluster-scope fence of its own: one per k-block in this thread cost 20 %)
             ok = mbar_wait(smem_u32(&conv_bar[stage]), phase, abort_flag, p.status, 35);
           }
           if (!ok) break;
@@ -279,11 +280,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
     }
   } else if (warp >= 10) {
-    // ---------------- converter warps (SPLIT; each CTA splits its own A stages) ----------------
-    // hi = tf32(a) in place, lo = tf32(a - hi) into the stage's lo tile; element-wise, so the
-    // swizzled placement is preserved.  A non-finite hi keeps lo at zero (inf - inf would poison
+    // ---------------- converter warps (each CTA prepares its own A stages) ----------------
+    // 3xTF32: hi = tf32(a) in place, lo = tf32(a - hi) into the stage's lo tile.  TF32 with rounding:
+    // a is rounded to nearest in place.  Element-wise, so the swizzled placement is preserved.  A non-finite hi keeps lo at zero (inf - inf would poison
     // the product with NaN).
-    if (SPLIT) {
+    if (CONVERTS) {
       const int t = threadIdx.x - 320;  // 0..127
       int stage = 0;
       uint32_t phase = 0;
@@ -298,6 +299,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           for (int i = 0; i < A_BYTES / 16 / 128; i++) {
             const int idx = t + i * 128;
             float4 v = hi4[idx], h, l;
+            if (!SPLIT) {  // TF32: round to nearest where the tensor core would truncate
+              v.x = round_tf32_for_mma(v.x); v.y = round_tf32_for_mma(v.y);
+              v.z = round_tf32_for_mma(v.z); v.w = round_tf32_for_mma(v.w);
+              hi4[idx] = v;
+              continue;
+            }
             h.x = round_tf32(v.x); h.y = round_tf32(v.y); h.z = round_tf32(v.z); h.w = round_tf32(v.w);
             l.x = (fabsf(h.x) <= 3.4028234e38f) ? round_tf32(v.x - h.x) : 0.f;
             l.y = (fabsf(h.y) <= 3.4028234e38f) ? round_tf32(v.y - h.y) : 0.f;
@@ -308,7 +315,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           }
           fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor cores
           __syncwarp();
-          if (lane == 0) mbar_arrive_release_cluster(map_to_cta(smem_u32(&conv_bar[stage]), 0));
+          // (plain remote arrive: the stores above are already performed in this SM's shared memory
+          // and ordered for its tensor core by the proxy fence; an arrive with .release.cluster
+          // costs the converters about a microsecond per stage and made them the bottleneck)
+          if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&conv_bar[stage]), 0));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -441,13 +451,14 @@ bool gemm_pair_supported(const tfjs_cuda_ctx* ctx, int64_t M, int64_t K, int64_t
 
 namespace {
 
-template <bool SPLIT>
+template <int PREC>
 int launch_pair_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mw_lo,
                         const PairParams& p) {
   constexpr int smem_bytes = LAYOUT_BYTES + 1024 <= SMEM_LIMIT ? LAYOUT_BYTES + 1024 : SMEM_LIMIT;
-  auto kernel = gemm_tcgen05_pair_kernel<SPLIT>;
+  constexpr bool SPLIT = PREC == PAIR_SPLIT;
+  auto kernel = gemm_tcgen05_pair_kernel<PREC>;
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(cta_threads(SPLIT));
+  cfg.blockDim = dim3(cta_threads(PREC != PAIR_ASIS));
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute attr[2];
@@ -481,11 +492,12 @@ int launch_pair_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtenso
 
 }  // namespace
 
-// W is the K-major tf32 plane [N, kp] of the packed weights.  w_lo == nullptr: one TF32 pass, and A
-// [M, K] must hold tf32-exact values (its producer rounded them).  With w_lo (the residual plane):
-// 3xTF32, A is split into hi / lo on chip.
+// W is the K-major tf32 plane [N, kp] of the packed weights.  With w_lo (the residual plane): 3xTF32,
+// A is split into hi / lo on chip.  Without: one TF32 pass; a_tf32_exact says that A's producer
+// already rounded it to tf32, otherwise the converter warps round it in shared memory.
 int launch_gemm_tcgen05_pair(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, const float* w_hi,
-                             const float* w_lo, int64_t kp, float* out, int64_t N, const EpilogueArgs& epi) {
+                             const float* w_lo, int64_t kp, float* out, int64_t N, const EpilogueArgs& epi,
+                             bool a_tf32_exact) {
   CUtensorMap ma, mw, mw_lo;
   if (!(encode_matrix(&ma, a, (uint64_t)M, (uint64_t)K, CTA_M, BLOCK_K) &&
         encode_matrix(&mw, w_hi, (uint64_t)N, (uint64_t)kp, HALF_N, BLOCK_K) &&
@@ -501,5 +513,7 @@ int launch_gemm_tcgen05_pair(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int6
   p.status = ctx->d_status;
   p.out = out;
   p.epi = epi;
-  return w_lo ? launch_pair_variant<true>(ctx, ma, mw, mw_lo, p) : launch_pair_variant<false>(ctx, ma, mw, mw_lo, p);
+  if (w_lo) return launch_pair_variant<PAIR_SPLIT>(ctx, ma, mw, mw_lo, p);
+  if (a_tf32_exact) return launch_pair_variant<PAIR_ASIS>(ctx, ma, mw, mw_lo, p);
+  return launch_pair_variant<PAIR_ROUND>(ctx, ma, mw, mw_lo, p);
 }
