@@ -227,6 +227,42 @@ def test_rgb_stem_conv(tf, b, h, w, n, stride, pad):
         bk.setMathMode("3xtf32")
 
 
+@pytest.mark.parametrize("b,h,w,n,stride,pad", [
+    (2, 224, 224, 32, 2, "same"),   # the network's stem
+    (1, 20, 24, 40, 1, "same"),     # pad left 1, N not a multiple of 32
+    (3, 17, 16, 8, 2, "valid"),
+    (2, 9, 12, 128, 2, "same"),     # widest N the 3xTF32 variant takes
+    (2, 9, 12, 256, 2, "same"),     # wider: the gather kernel, same tolerance
+])
+def test_rgb_stem_conv_3xtf32(tf, b, h, w, n, stride, pad):
+    """The stem in 3xTF32: the im2col threads write tf32 hi and lo tiles, the filter arrives as hi and
+    lo planes, three tensor-core products per k-step.  Within 1e-5 of the oracle, also on values
+    with large dynamic range and with a non-finite pixel (which must poison only the outputs whose
+    window holds it)."""
+    bk = tf.ENGINE.backend
+    bk.setMathMode("3xtf32")
+    rng = _rng(h * w + n + 7)
+    x = (rng.uniform(-1, 1, (b, h, w, 3)) * 10.0 ** rng.integers(-3, 3, (b, h, w, 3))).astype(np.float32)
+    wt = rng.normal(0, 0.3, (3, 3, 3, n)).astype(np.float32)
+    bias = rng.normal(0, 0.3, n).astype(np.float32)
+    ci = oracle.compute_conv2d_info(x.shape, wt.shape, stride, 1, pad)
+    want = oracle.fused_conv2d(x, wt, ci, bias=bias, activation="relu")
+    bk.profileBegin(8)
+    got = tf.ops.fused_conv2d(tf.ops.tensor(x), tf.ops.tensor(wt), stride, pad, bias=tf.ops.tensor(bias),
+                              activation="relu")
+    out = got.dataSync().reshape(want.shape)
+    names = [name for name, _ in bk.profileEnd()]
+    assert any("window TMA, 3xTF32" in name for name in names) == (n <= 128), names
+    assert rel_err(out, want) <= 1e-5
+    x[0, 3, 4, 1] = np.inf
+    want = oracle.fused_conv2d(x, wt, ci, bias=bias, activation="linear")
+    out = tf.ops.fused_conv2d(tf.ops.tensor(x), tf.ops.tensor(wt), stride, pad, bias=tf.ops.tensor(bias)
+                              ).dataSync().reshape(want.shape)
+    assert np.array_equal(np.isfinite(out), np.isfinite(want))
+    ok = np.isfinite(want)
+    assert rel_err(out[ok], want[ok]) <= 1e-5
+
+
 # ---- dense convolution fed entirely by TMA: one shifted-patch load per filter tap ----------------
 @pytest.mark.parametrize("b,h,w,cin,n,fh,fw,dil,pad", [
     (8, 56, 56, 64, 64, 3, 3, 1, "same"),     # BASELINE config 2's shape

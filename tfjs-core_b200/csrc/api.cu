@@ -352,14 +352,16 @@ extern "C" int tfjs_cuda_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_te
   // im2col rows in shared memory (TF32; other modes take the gather path below).  It can store
   // its result as half directly.
   const bool x8 = x->quant.quantized;
-  if (!x16 && ctx->use_tensor_cores &&
+  const bool split3 = ctx->math_mode == TFJS_MATH_TF32X3;  // 3xTF32: float32 image in, float32 out
+  if (!x16 && ctx->use_tensor_cores && !(split3 && (o16 || x8)) &&
       (x8 ? conv_rgb_u8_tcgen05_supported(*ci, e.activation, ctx->math_mode)
           : conv_rgb_tcgen05_supported(*ci, e.activation, ctx->math_mode))) {
     PackedWeights pw;
     bool temporary;
     rc = packed_weights(ctx, w, 0, 27, ci->outChannels, false, true, &pw, &temporary, 9, 10, 32);
     if (rc) return rc;
-    return launch_conv_rgb_tcgen05(ctx, x->ptr, *ci, pw.hi, pw.kp, o->ptr, e, o16, x8, x->quant.scale, x->quant.min);
+    return launch_conv_rgb_tcgen05(ctx, x->ptr, *ci, pw.hi, pw.kp, o->ptr, e, o16, x8, x->quant.scale, x->quant.min,
+                                   split3 ? pw.lo : nullptr);
   }
   // Every other kernel computes on float32 storage.
   F32View xv;

@@ -359,7 +359,7 @@ bool conv_rgb_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int 
 bool conv_rgb_u8_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode);
 int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const void* x, const tfjs_conv2d_info& ci, const float* w_hi,
                             int64_t kp, void* y, const EpilogueArgs& epi, bool out_half = false, bool in_u8 = false,
-                            double q_scale = 0.0, double q_min = 0.0);
+                            double q_scale = 0.0, double q_min = 0.0, const float* w_lo = nullptr);
 bool conv_tma_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode);
 int launch_conv_tma_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& ci, const float* w_hi,
                             int64_t kp, float* y, const EpilogueArgs& epi);

@@ -36,6 +36,9 @@ constexpr int PH = 8, PW = 16;                    // output patch
 constexpr int BLOCK_K = 32;
 constexpr int A_TILE_BYTES = 128 * BLOCK_K * 4;   // 16 KB
 constexpr int A_SLOTS = 2;
+// MODE_RGB in 3xTF32 (see the list of modes below): an A slot holds the hi and the lo tile, a weight
+// stage the hi and the lo plane of the filter.
+constexpr int MODE_RGB3 = 3;
 // Stride-1 depthwise blocks of 256 columns build the A tile IN PLACE: a window (10 x 18 x 128 B = 23 KB) is larger
 // than the tile made from it (16 KB), so once the threads of a group have all read their window
 // taps into registers (a named barrier) they write the tile over the start of the same stage, the
@@ -50,7 +53,7 @@ __host__ __device__ constexpr bool a_in_place(int block_n, int s, int mode, bool
   return mode == 0 && s == 1 && block_n >= 256 && !in16;
 }
 __host__ __device__ constexpr int a_slot_bytes(int block_n, int s, int mode, bool in16 = false) {
-  return a_in_place(block_n, s, mode, in16) ? 0 : A_SLOTS * A_TILE_BYTES;
+  return a_in_place(block_n, s, mode, in16) ? 0 : A_SLOTS * A_TILE_BYTES * (mode == MODE_RGB3 ? 2 : 1);
 }
 constexpr int EPI_WARPS = 8;
 constexpr int C_CHUNK_BYTES = 32 * 32 * 4;
@@ -74,6 +77,10 @@ constexpr int SMEM_LIMIT = 232448;
 constexpr int MODE_DW = 0;   // depthwise 3x3 over 32-channel k-blocks feeding the GEMM
 constexpr int MODE_RGB = 1;  // dense 3x3 convolution of a 3-channel image: the window rows are turned
                              // into im2col rows (K' = 10 * filter row + 3 * filter column + channel)
+                             // MODE_RGB3 (= 3, above) is the same in 3xTF32: the im2col threads write a
+                             // tf32 hi and a lo tile, the filter arrives as hi and lo planes, and every
+                             // k-step issues hi*hi, lo*hi and hi*lo into the one accumulator (K' is 27
+                             // terms long, so the correction terms need no accumulator of their own)
 constexpr int MODE_CONV = 2; // dense convolution, Cin a multiple of 32, stride 1: the A tile of k-block
                              // (filter row, filter column, 32-channel group) is the patch shifted by that
                              // tap, loaded by TMA straight into the swizzled layout the tensor core reads;
@@ -107,10 +114,14 @@ struct Raw {
 __host__ __device__ constexpr int w_stages(int block_n, int s, int mode) {
   return block_n >= 256 ? 2 : (block_n >= 128 ? ((mode == 0 && s == 2) ? 2 : 3) : 4);
 }
+__host__ __device__ constexpr bool is_rgb(int mode) { return mode == MODE_RGB || mode == MODE_RGB3; }
+__host__ __device__ constexpr int w_stage_bytes(int block_n, int mode) {
+  return block_n * BLOCK_K * 4 * (mode == MODE_RGB3 ? 2 : 1);
+}
 __host__ __device__ constexpr int epi_arrivals(int block_n) { return block_n >= 64 ? EPI_WARPS : 4; }
 template <int S, int MODE, bool IN16 = false, bool IN8 = false>
 __host__ __device__ constexpr int raw_stages(int block_n) {
-  int left = SMEM_LIMIT - 1024 - a_slot_bytes(block_n, S, MODE, IN16) - w_stages(block_n, S, MODE) * block_n * BLOCK_K * 4 -
+  int left = SMEM_LIMIT - 1024 - a_slot_bytes(block_n, S, MODE, IN16) - w_stages(block_n, S, MODE) * w_stage_bytes(block_n, MODE) -
              C_STAGING_BYTES - BIAS_STAGING_BYTES - DW_TABLE_BYTES - BARRIER_BYTES;
   int n = left / Raw<S, MODE, IN16, IN8>::STRIDE;
   // Window loads carry the DRAM latency: about 90 KB must be in flight per SM to keep the memory
@@ -287,7 +298,7 @@ __device__ __forceinline__ void dw_part(uint32_t raw, uint32_t a_tile, uint32_t 
 // (y0, x0): input row / column of the tile's first window element.  Byte input only: the zero fill
 // of a load outside the image is the BYTE 0, which decodes to `min`, not to the 0.0 that padding
 // means, so taps outside the image are set to zero here.
-template <int S, bool IN8>
+template <int S, bool IN8, bool SPLIT3 = false>
 __device__ __forceinline__ void rgb_part(uint32_t raw, uint32_t a_tile, int t, const SepParams& p, uint32_t lut,
                                          int y0, int x0) {
   using R = Raw<S, MODE_RGB, false, IN8>;
@@ -310,8 +321,31 @@ __device__ __forceinline__ void rgb_part(uint32_t raw, uint32_t a_tile, int t, c
     } else {
       const uint32_t row = raw + (uint32_t)(((r * S + dr) * R::ROW_FLOATS + p.rgb_off + c * S * 3) * 4);
 #pragma unroll
-      for (int j = 0; j < 9; j++) v[dr][j] = round_tf32_for_mma(lds32(row + j * 4));  // the tensor core would truncate
+      for (int j = 0; j < 9; j++)
+        v[dr][j] = SPLIT3 ? lds32(row + j * 4) : round_tf32_for_mma(lds32(row + j * 4));  // the tensor core would truncate
     }
+  }
+  if (SPLIT3) {
+    // 3xTF32: hi = tf32(x) goes to the slot's first tile, lo = tf32(x - hi) to its second (a
+    // non-finite hi keeps lo at zero: inf - inf would poison the product with NaN)
+    float lo[3][9];
+#pragma unroll
+    for (int dr = 0; dr < 3; dr++)
+#pragma unroll
+      for (int j = 0; j < 9; j++) {
+        const float h = round_tf32(v[dr][j]);
+        lo[dr][j] = (fabsf(h) <= 3.4028234e38f) ? round_tf32(v[dr][j] - h) : 0.f;
+        v[dr][j] = h;
+      }
+    const uint32_t lo_tile = a_tile + A_TILE_BYTES;
+    sts128(lo_tile + swz(t, 0), make_float4(lo[0][0], lo[0][1], lo[0][2], lo[0][3]));
+    sts128(lo_tile + swz(t, 16), make_float4(lo[0][4], lo[0][5], lo[0][6], lo[0][7]));
+    sts128(lo_tile + swz(t, 32), make_float4(lo[0][8], 0.f, lo[1][0], lo[1][1]));
+    sts128(lo_tile + swz(t, 48), make_float4(lo[1][2], lo[1][3], lo[1][4], lo[1][5]));
+    sts128(lo_tile + swz(t, 64), make_float4(lo[1][6], lo[1][7], lo[1][8], 0.f));
+    sts128(lo_tile + swz(t, 80), make_float4(lo[2][0], lo[2][1], lo[2][2], lo[2][3]));
+    sts128(lo_tile + swz(t, 96), make_float4(lo[2][4], lo[2][5], lo[2][6], lo[2][7]));
+    sts128(lo_tile + swz(t, 112), make_float4(lo[2][8], 0.f, 0.f, 0.f));
   }
   sts128(a_tile + swz(t, 0), make_float4(v[0][0], v[0][1], v[0][2], v[0][3]));
   sts128(a_tile + swz(t, 16), make_float4(v[0][4], v[0][5], v[0][6], v[0][7]));
@@ -330,8 +364,11 @@ __device__ __forceinline__ void rgb_part(uint32_t raw, uint32_t a_tile, int t, c
 template <int BLOCK_N, int S, int MODE, bool HALF = false, bool IN8 = false>
 __global__ void __launch_bounds__(THREADS, 1)
 sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                       const __grid_constant__ CUtensorMap map_y, SepParams p) {
+                       const __grid_constant__ CUtensorMap map_w_lo, const __grid_constant__ CUtensorMap map_y,
+                       SepParams p) {
   static_assert(!IN8 || MODE == MODE_RGB, "byte input is the 3-channel stem's");
+  constexpr bool SPLIT3 = MODE == MODE_RGB3;
+  constexpr int A_SLOT_STRIDE = A_TILE_BYTES * (SPLIT3 ? 2 : 1);
   constexpr bool IN16 = HALF && MODE == MODE_DW;
   constexpr bool OUT16 = HALF;
   using R = Raw<S, MODE, IN16, IN8>;
@@ -355,7 +392,8 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     index = group * per_group + turn % per_group;
     phase = (uint32_t)(turn / per_group) & 1u;
   };
-  constexpr int W_STAGE_BYTES = BLOCK_N * BLOCK_K * 4;
+  constexpr int W_STAGE_BYTES = w_stage_bytes(BLOCK_N, MODE);
+  constexpr int W_PLANE_BYTES = BLOCK_N * BLOCK_K * 4;
   // Accumulator buffers in tensor memory: two, or four when a tile is only 32 columns wide; then
   // each half of the epilogue warps drains every other tile, so two epilogues run at a time.
   constexpr int NUM_ACC = BLOCK_N == 32 ? 4 : 2;
@@ -516,6 +554,9 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
         if (w_tile < p.num_tiles && mbar_test_wait(smem_u32(&w_empty[ws]), wphase ^ 1)) {
           mbar_arrive_expect_tx(smem_u32(&w_full[ws]), W_STAGE_BYTES);
           tma_load_2d(smem_u32(w_tiles + ws * W_STAGE_BYTES), &map_w, smem_u32(&w_full[ws]), w_kb * BLOCK_K, 0);
+          if (SPLIT3)
+            tma_load_2d(smem_u32(w_tiles + ws * W_STAGE_BYTES + W_PLANE_BYTES), &map_w_lo, smem_u32(&w_full[ws]),
+                        w_kb * BLOCK_K, 0);
           if (++ws == W_STAGES) { ws = 0; wphase ^= 1; }
           if (++w_kb == p.num_k_blocks) { w_kb = 0; w_tile += gridDim.x; }
           progressed = true;
@@ -567,12 +608,17 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
           if (!ok) break;
           tcgen05_fence_after();
           const uint32_t a_s = STAGE_IS_A ? smem_u32(raw + rs * R::STRIDE)
-                                                               : smem_u32(a_tiles + slot * A_TILE_BYTES);
+                                                               : smem_u32(a_tiles + slot * A_SLOT_STRIDE);
           const uint32_t w_s = smem_u32(w_tiles + ws * W_STAGE_BYTES);
 #pragma unroll
-          for (int k = 0; k < BLOCK_K / 8; k++)
+          for (int k = 0; k < BLOCK_K / 8; k++) {
             tcgen05_mma_tf32(tmem_d, make_smem_desc(a_s + k * 32), make_smem_desc(w_s + k * 32), idesc,
                              (kb > 0 || k > 0) ? 1u : 0u);
+            if (SPLIT3) {  // lo * hi and hi * lo
+              tcgen05_mma_tf32(tmem_d, make_smem_desc(a_s + A_TILE_BYTES + k * 32), make_smem_desc(w_s + k * 32), idesc, 1u);
+              tcgen05_mma_tf32(tmem_d, make_smem_desc(a_s + k * 32), make_smem_desc(w_s + W_PLANE_BYTES + k * 32), idesc, 1u);
+            }
+          }
           tcgen05_commit(smem_u32(&w_empty[ws]));
           if (STAGE_IS_A)
             tcgen05_commit(smem_u32(&raw_empty[rs]));
@@ -631,7 +677,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
           ring_pos(n, A_SLOTS, slot, sphase);
           ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&a_empty[slot]), sphase ^ 1, abort_flag, p.status, 16));
           if (!ok) break;
-          a_s = smem_u32(a_tiles + slot * A_TILE_BYTES);
+          a_s = smem_u32(a_tiles + slot * A_SLOT_STRIDE);
         }
         for (int part = 0; part < R::PARTS; part++) {
           int rs;
@@ -644,11 +690,11 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
             a_s = raw_s;
             slot = rs;
           }
-          if (MODE == MODE_RGB) {
+          if (is_rgb(MODE)) {
             const int img = tile / tiles_per_image;
             const int rem = tile - img * tiles_per_image;
             const int ty = rem / p.tiles_x, tx = rem - ty * p.tiles_x;
-            rgb_part<S, IN8>(raw_s, a_s, t, p, table_s, ty * PH * S - p.pad_r, tx * PW * S - p.pad_c);
+            rgb_part<S, IN8, SPLIT3>(raw_s, a_s, t, p, table_s, ty * PH * S - p.pad_r, tx * PW * S - p.pad_c);
           } else {
             // in place: named barrier 1 + group over the group's threads, between reads and writes
             const int sync_id = IN_PLACE ? 1 + group : 0;
@@ -787,9 +833,9 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 
 template <int BLOCK_N, int S, int MODE, bool HALF = false, bool IN8 = false>
 int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& my,
-                   const SepParams& p) {
+                   const SepParams& p, const CUtensorMap* mw_lo = nullptr) {
   constexpr bool IN16 = HALF && MODE == MODE_DW;
-  constexpr int smem_bytes = 1024 + a_slot_bytes(BLOCK_N, S, MODE, IN16) + w_stages(BLOCK_N, S, MODE) * BLOCK_N * BLOCK_K * 4 +
+  constexpr int smem_bytes = 1024 + a_slot_bytes(BLOCK_N, S, MODE, IN16) + w_stages(BLOCK_N, S, MODE) * w_stage_bytes(BLOCK_N, MODE) +
                              C_STAGING_BYTES + raw_stages<S, MODE, IN16, IN8>(BLOCK_N) * Raw<S, MODE, IN16, IN8>::STRIDE +
                              DW_TABLE_BYTES + BIAS_STAGING_BYTES + BARRIER_BYTES;
   static_assert(smem_bytes <= SMEM_LIMIT, "shared memory budget exceeded");
@@ -802,7 +848,8 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap&
     configured[ctx->device & 63].store(true, std::memory_order_release);
   }
   const int grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
-  launch_ex(ctx, kernel, dim3(grid), dim3(THREADS), smem_bytes, mx, mw, my, p);
+  launch_ex(ctx, kernel, dim3(grid), dim3(THREADS), smem_bytes, mx, mw, mw_lo ? *mw_lo : mw, my, p);
+  if (MODE == MODE_RGB3) return post_launch(ctx, "conv2d_tcgen05 (3-channel 3x3, window TMA, 3xTF32)");
   if (MODE == MODE_RGB && IN8)
     return post_launch(ctx, HALF ? "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32, uint8 in, float16 out)"
                                  : "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32, uint8 in)");
@@ -819,15 +866,18 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap&
 
 template <int S, int MODE, bool HALF = false, bool IN8 = false>
 int launch_stride(tfjs_cuda_ctx* ctx, int block_n, const CUtensorMap& mx, const CUtensorMap& mw,
-                  const CUtensorMap& my, const SepParams& p) {
+                  const CUtensorMap& my, const SepParams& p, const CUtensorMap* mw_lo = nullptr) {
   switch (block_n) {
     case 32:
       if (MODE != MODE_DW)
-        return launch_variant<32, S, MODE == MODE_DW ? MODE_RGB : MODE, HALF, IN8>(ctx, mx, mw, my, p);
+        return launch_variant<32, S, MODE == MODE_DW ? MODE_RGB : MODE, HALF, IN8>(ctx, mx, mw, my, p, mw_lo);
       // depthwise mode has no 32-wide variant: falls through
-    case 64: return launch_variant<64, S, MODE, HALF, IN8>(ctx, mx, mw, my, p);
-    case 128: return launch_variant<128, S, MODE, HALF, IN8>(ctx, mx, mw, my, p);
-    default: return launch_variant<256, S, MODE, HALF, IN8>(ctx, mx, mw, my, p);
+    case 64: return launch_variant<64, S, MODE, HALF, IN8>(ctx, mx, mw, my, p, mw_lo);
+    case 128: return launch_variant<128, S, MODE, HALF, IN8>(ctx, mx, mw, my, p, mw_lo);
+    default:
+      // (no 256-column 3xTF32 stem: two 64 KB weight stages and the hi / lo A slots leave no room for windows)
+      if constexpr (MODE == MODE_RGB3) return set_error(ctx, TFJS_CUDA_ERR_INVALID_ARG, "3xTF32 stem takes at most 128 output channels");
+      else return launch_variant<256, S, MODE, HALF, IN8>(ctx, mx, mw, my, p, mw_lo);
   }
 }
 
@@ -908,7 +958,7 @@ int launch_sepconv_tcgen05(tfjs_cuda_ctx* ctx, const void* x, const tfjs_conv2d_
 // same kernel skeleton, the window arrives by TMA and is rearranged into im2col rows on chip.
 // `w_hi` is the filter repacked with each filter row padded to 10 floats ([N, 32]).
 bool conv_rgb_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode) {
-  return math_mode == TFJS_MATH_TF32 && ci.inChannels == 3 && ci.filterHeight == 3 && ci.filterWidth == 3 &&
+  return (math_mode == TFJS_MATH_TF32 || (math_mode == TFJS_MATH_TF32X3 && ci.outChannels <= 128)) && ci.inChannels == 3 && ci.filterHeight == 3 && ci.filterWidth == 3 &&
          ci.dilationHeight == 1 && ci.dilationWidth == 1 && ci.strideHeight == ci.strideWidth &&
          (ci.strideHeight == 1 || ci.strideHeight == 2) && ci.inWidth % 4 == 0 && ci.outChannels >= 8 &&
          ci.outChannels <= 256 && ci.outChannels % 4 == 0 && ci.batchSize >= 1 && ci.batchSize < 65536 &&
@@ -918,12 +968,12 @@ bool conv_rgb_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int 
 
 // Byte input also needs image rows of a multiple of 16 bytes (the row stride of the tensor map).
 bool conv_rgb_u8_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode) {
-  return conv_rgb_tcgen05_supported(ci, activation, math_mode) && (ci.inWidth * 3) % 16 == 0;
+  return math_mode == TFJS_MATH_TF32 && conv_rgb_tcgen05_supported(ci, activation, math_mode) && (ci.inWidth * 3) % 16 == 0;
 }
 
 int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const void* x, const tfjs_conv2d_info& ci, const float* w_hi,
                             int64_t kp, void* y, const EpilogueArgs& epi, bool out_half, bool in_u8, double q_scale,
-                            double q_min) {
+                            double q_min, const float* w_lo) {  // w_lo: 3xTF32 (float32 in and out only)
   const int S = ci.strideHeight;
   const int64_t N = ci.outChannels;
   const uint64_t el = out_half ? 2 : 4;
@@ -949,6 +999,12 @@ int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const void* x, const tfjs_conv2d
       tma_encode_tiled(&my, out_half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, y, yd, ys, yb,
                        out_half ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ok) return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+  CUtensorMap mwl;
+  if (w_lo) {
+    TFJS_REQUIRE(ctx, !out_half && !in_u8, "the 3xTF32 stem computes on float32 storage");
+    if (!tma_encode_tiled(&mwl, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, w_lo, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B))
+      return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+  }
   SepParams p;
   memset(&p, 0, sizeof(p));
   p.B = ci.batchSize;
@@ -971,6 +1027,7 @@ int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const void* x, const tfjs_conv2d
   p.rgb_off = in_u8 ? ((-3 * ci.padLeft) % 16 + 16) % 16 : ((-3 * ci.padLeft) % 4 + 4) % 4;
   p.q_scale = q_scale;
   p.q_min = q_min;
+  p.status = ctx->d_status;
   if (in_u8) {
     if (out_half)
       return S == 1 ? launch_stride<1, MODE_RGB, true, true>(ctx, block_n, mx, mw, my, p)
@@ -978,7 +1035,9 @@ int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const void* x, const tfjs_conv2d
     return S == 1 ? launch_stride<1, MODE_RGB, false, true>(ctx, block_n, mx, mw, my, p)
                   : launch_stride<2, MODE_RGB, false, true>(ctx, block_n, mx, mw, my, p);
   }
-  p.status = ctx->d_status;
+  if (w_lo)
+    return S == 1 ? launch_stride<1, MODE_RGB3>(ctx, block_n, mx, mw, my, p, &mwl)
+                  : launch_stride<2, MODE_RGB3>(ctx, block_n, mx, mw, my, p, &mwl);
   if (out_half)
     return S == 1 ? launch_stride<1, MODE_RGB, true>(ctx, block_n, mx, mw, my, p)
                   : launch_stride<2, MODE_RGB, true>(ctx, block_n, mx, mw, my, p);
