@@ -1,6 +1,8 @@
 // Tensor-core GEMM on CTA pairs (tcgen05 cta_group::2): out[M, N] = act(A[M, K] * W[K, N] + bias[N])
 // for the deep pointwise convolutions (tfjs-core/src/backends/backend.ts:414-418 fusedConv2d with a
-// 1x1 filter, :134-138 fusedBatchMatMul), float32 in and out, one TF32 pass.
+// 1x1 filter, :134-138 fusedBatchMatMul), float32 in and out.  Three precisions: one TF32 pass on an
+// A whose producer already rounded it to tf32, one TF32 pass with A rounded to nearest on chip, and
+// 3xTF32 (A split into tf32 hi / lo on chip, hi and lo weight planes, three passes).
 //
 // Why pairs.  The single-CTA kernel computes a 128 x 256 tile per SM and has to bring 128 rows of A
 // and 256 rows of W into its shared memory per k-block: 48 KB for 128 x 256 x 32 multiply-adds.  Its
@@ -19,6 +21,10 @@
 //               N = 256, K = 8) per 32-byte k-step and commits stage-release and accumulator-ready
 //               barriers in both CTAs (one tcgen05.commit per barrier; the peer's through its
 //               shared::cluster address).
+//   warps 10-13 (rounding and 3xTF32 variants) converters, in each CTA: its A load completes on a
+//               barrier of its own CTA; they round the stage in place, or split it into a hi and a lo
+//               tile, and arrive on the leader's converter barrier.  3xTF32 keeps three stages of
+//               64 KB and ONE accumulator buffer (a main and a correction tile, all 512 columns).
 //   warps 0-7   epilogue, in each CTA: its 128 rows x 256 columns of the accumulator (two buffers
 //               of 256 tensor-memory columns, so the next tile's MMAs overlap), bias, activation,
 //               swizzled staging, 128-bit row stores.  Both CTAs hand the buffer back on the leader's barrier.
