@@ -257,6 +257,11 @@ __device__ __forceinline__ float round_tf32_after_arith(float v) {
   return __int_as_float(max(t, b));
 }
 
+// Codes a kernel may leave in the context's device status word besides the number of the bounded
+// wait that gave up (1 .. 89): the host turns them into errors at the next synchronisation.
+constexpr int STATUS_CANARY = 90;       // a guard pattern behind a buffer was overwritten
+constexpr int STATUS_SMEM_LAYOUT = 91;  // a kernel's dynamic shared-memory window did not start 1024-aligned
+
 // Programmatic dependent launch.  A kernel launched through launch_ex may start while the
 // kernel before it on the stream is still running; pdl_wait() blocks until that kernel (and
 // therefore everything before it) has completed and its writes are visible, and must precede

@@ -106,8 +106,6 @@ static void release_cached(tfjs_cuda_ctx* ctx) {
 // ---- guard pattern behind every buffer (option "debug_canary") ------------------------------
 constexpr size_t CANARY_BYTES = 256;
 constexpr uint32_t CANARY_WORD = 0xA5C3F00Du;
-constexpr int STATUS_CANARY = 90;  // device status code: a guard pattern was overwritten
-constexpr int STATUS_SMEM_LAYOUT = 91;  // a kernel's dynamic shared-memory window did not start 1024-aligned
 
 __global__ void canary_fill_kernel(uint32_t* guard) { guard[threadIdx.x] = CANARY_WORD; }
 __global__ void canary_check_kernel(const uint32_t* guard, int* status) {

@@ -60,7 +60,6 @@ __host__ __device__ constexpr int layout_bytes(int block_n, bool split, bool wq)
   return wq_ring_bytes(block_n, split, wq) + num_stages(block_n, split, wq) * stage_bytes(block_n, split, wq) +
          C_STAGING_BYTES + BIAS_STAGING_BYTES + BARRIER_BYTES;
 }
-constexpr int STATUS_SMEM_LAYOUT = 91;  // device status code: the shared-memory window is not aligned as assumed
 
 // Geometry of an implicit-GEMM convolution: row m of the A matrix is output pixel
 // (b, yo, xo) = unflatten(m), column kk is filter tap (wr, wc) and input channel ci.

@@ -16,7 +16,7 @@
 // Structure (both CTAs of a pair run the same code; rank 0 is the leader):
 //   warp 8      TMA producer, in each CTA: its A tile [128 x 32] and its half of the W tile
 //               [128 x 32] per k-block into a ring of local stages.  The loads of both CTAs complete
-//               on the LEADER's full barrier (cp.async.bulk.tensor with .cta_group::2, no multicast).
+//               on the LEADER's full barrier (the .cta_group::2 form of the tensor load; every CTA fetches its own bytes).
 //   warp 9      MMA issuer, leader only: one thread issues tcgen05.mma.cta_group::2 (M = 256,
 //               N = 256, K = 8) per 32-byte k-step and commits stage-release and accumulator-ready
 //               barriers in both CTAs (one tcgen05.commit per barrier; the peer's through its
@@ -64,7 +64,6 @@ __host__ __device__ constexpr int cta_threads(bool converts) { return converts ?
 // Tensor memory, all 512 columns either way: two accumulator buffers of 256 columns, or (SPLIT) one
 // buffer made of a main tile (hi*hi) and a correction tile (lo*hi + hi*lo) that the epilogue adds.
 constexpr uint32_t TMEM_COLS = 512;
-constexpr int STATUS_SMEM_LAYOUT = 91;
 
 struct PairParams {
   int M, N, K;
