@@ -166,3 +166,32 @@ def test_default_dispatch_takes_the_pair_kernel_only_for_large_problems(tf):
         assert any("CTA pairs" in name for name in large), large
     finally:
         bk.setMathMode("3xtf32")
+
+
+def test_pair_kernel_writes_nothing_past_its_output(tf):
+    """The pair kernel stores its rows with ordinary 128-bit stores (no tensor map clips them): with
+    guard patterns behind every buffer (option debug_canary), a ragged M whose last tile is mostly
+    padding leaves the guards intact, in all three precisions."""
+    bk = tf.ENGINE.backend
+    bk.setOption("debug_canary", 1)
+    bk.setOption("fuse_separable", 0)
+    try:
+        for mode in ("tf32", "3xtf32"):
+            bk.setMathMode(mode)
+            out = _block(tf, 3, 14, 14, 512, 256, 5, "relu", True, pair=2)[5]      # M = 588
+            assert np.isfinite(out).all()
+            bk.sync()                                                               # guards checked on release
+        bk.setMathMode("tf32")
+        rng = np.random.Generator(np.random.PCG64(5))
+        a = tf.ops.tensor(rng.uniform(-1, 1, (1, 300, 512)).astype(np.float32))    # rounding variant, M = 300
+        b = tf.ops.tensor(rng.uniform(-1, 1, (1, 512, 256)).astype(np.float32))
+        bk.setOption("gemm_pair", 2)
+        y = bk.fusedBatchMatMul(a=a, b=b, bias=None, activation="linear")
+        y.dataSync()
+        y.dispose()
+        bk.sync()
+    finally:
+        bk.setOption("debug_canary", 0)
+        bk.setOption("gemm_pair", 1)
+        bk.setOption("fuse_separable", 1)
+        bk.setMathMode("3xtf32")
