@@ -122,7 +122,9 @@ const char* tfjs_cuda_last_error(const tfjs_cuda_ctx* ctx);
  * shared memory inside the GEMM main loop; the results are bit-identical), "fuse_separable"
  * (see tfjs_cuda_separable_conv2d), "gemm_pair" (TF32 matMul / 1x1 conv2d on pairs of CTAs that
  * share each weight tile: 1, the default, where the problem is large enough to pay; 0 never; 2
- * wherever the shape allows; the results are bit-identical either way), "pdl" (1 launches the main kernels with programmatic stream
+ * wherever the shape allows; the results are bit-identical either way), "gemm_block_n" (diagnostic:
+ * 32, 64, 128 or 256 fixes the tile width of the single-CTA tensor-core matMul, 0 leaves it to the
+ * cost model), "pdl" (1 launches the main kernels with programmatic stream
  * serialization, so that a kernel's prologue overlaps its predecessor's tail; default 0),
  * "wait_limit_us" (every device-side wait of the kernels is bounded; a wait that runs out makes
  * the kernel return and the next ctx_sync / tensor_read report TFJS_CUDA_ERR_TIMEOUT, the context

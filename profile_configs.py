@@ -7,6 +7,7 @@ operators of the unfused tf.* path.
     python profile_configs.py block B HW C N [stride] [key=value ...]
                                                      # one depthwise 3x3 + pointwise block on its own
     python profile_configs.py stem B                 # the 3x3x3->32 stride-2 first convolution on its own
+    python profile_configs.py matmul M K N [tf32|3xtf32] [key=value ...]   # one fused matMul + bias, graph replay
 
 For each config: the device time of one call launched eagerly and replayed from a CUDA graph, and
 the bandwidth / FLOP rate the algorithmic figures correspond to (parity with the CPU oracle is
@@ -149,7 +150,43 @@ def run_stem(batch, reps=5):
         print(f"{rows[i][0]:62s} {best * 1e3:9.1f} us {nbytes / 1e6:9.1f} MB {nbytes / best / 1e6:7.0f} GB/s", flush=True)
 
 
+def run_matmul(m, k, n, mode, options, reps=50):
+    """One fusedBatchMatMul [m, k] x [k, n] + bias on its own, replayed from a CUDA graph (device time
+    per call without host launch gaps)."""
+    bk = tf.BackendCuda(0, mode)
+    tf.ENGINE.registerBackend("profile-cuda", lambda: bk, 10)
+    tf.ENGINE.setBackend("profile-cuda")
+    for key, value in options.items():
+        bk.setOption(key, value)
+    r = rng(23)
+    a = ops.tensor(r.uniform(-1, 1, (m, k)).astype(np.float32))
+    b = ops.tensor((r.uniform(-1, 1, (k, n)) / np.sqrt(k)).astype(np.float32))
+    bias = ops.tensor(r.normal(0, 0.1, n).astype(np.float32))
+    call = lambda: ops.fused_matmul(a, b, bias=bias)  # noqa: E731
+    call().dispose()
+    bk.graphBegin()
+    call().dispose()
+    g = bk.graphEnd()
+    bk.graphLaunch(g)
+
+    def replay():
+        for _ in range(reps):
+            bk.graphLaunch(g)
+    us = bk.time(replay)["kernelMs"] * 1e3 / reps
+    bk.profileBegin(4)
+    call().dispose()
+    name = bk.profileEnd()[-1][0]
+    nbytes = 4 * (m * k + k * n + m * n + n)
+    print(f"matMul {m} x {k} x {n} {mode} {options}: {name}  {us:.1f} us  {nbytes / us / 1e3:.0f} GB/s  "
+          f"{2.0 * m * k * n / us / 1e6:.1f} TFLOP/s", flush=True)
+
+
 def main():
+    if len(sys.argv) > 1 and sys.argv[1] == "matmul":
+        nums = [int(a) for a in sys.argv[2:] if a.isdigit()]
+        mode = "3xtf32" if "3xtf32" in sys.argv else "tf32"
+        options = {a.split("=")[0]: int(a.split("=")[1]) for a in sys.argv[2:] if "=" in a}
+        return run_matmul(nums[0], nums[1], nums[2], mode, options)
     if len(sys.argv) > 1 and sys.argv[1] == "stem":
         return run_stem(int(sys.argv[2]) if len(sys.argv) > 2 else 64)
     if len(sys.argv) > 1 and sys.argv[1] == "block":

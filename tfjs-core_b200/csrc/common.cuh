@@ -105,6 +105,7 @@ struct tfjs_cuda_ctx {
   // separable_conv2d: 0 = always two kernels, 1 = one fused kernel where that is faster,
   // 2 = fused wherever the kernel takes the shape
   int fuse_separable = 1;
+  int gemm_block_n = 0;  // diagnostic: tile width of the single-CTA GEMM (32 .. 256) instead of the cost model's choice
   int gemm_pair = 1;  // 0: never use the CTA-pair GEMM, 1: where it pays, 2: wherever its shape rules allow
   // launch the kernels that support it with programmatic stream serialization (off by default:
   // with one persistent block per SM the next kernel's blocks cannot become resident before this

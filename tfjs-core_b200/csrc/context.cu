@@ -324,6 +324,10 @@ extern "C" int tfjs_cuda_ctx_set_option(tfjs_cuda_ctx* ctx, const char* key, dou
       cudaGetLastError();
       return set_error(ctx, TFJS_CUDA_ERR_CUDA, "could not set the wait limit");
     }
+  } else if (!strcmp(key, "gemm_block_n")) {
+    TFJS_REQUIRE(ctx, value == 0 || value == 32 || value == 64 || value == 128 || value == 256,
+                 "gemm_block_n must be 0 (cost model), 32, 64, 128 or 256");
+    ctx->gemm_block_n = (int)value;
   } else if (!strcmp(key, "gemm_pair")) {
     TFJS_REQUIRE(ctx, value == 0 || value == 1 || value == 2, "gemm_pair must be 0, 1 or 2");
     ctx->gemm_pair = (int)value;

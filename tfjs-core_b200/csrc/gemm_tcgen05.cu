@@ -195,10 +195,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       // would make every row wait for the slowest of its warp and measured 7 % slower)
       mbar_init(smem_u32(&full_bar[s]), AMODE == A_MATRIX ? 1 : 129);
       mbar_init(smem_u32(&empty_bar[s]), 1);
-      mbar_init(smem_u32(&conv_bar[s]), 128);
+      mbar_init(smem_u32(&conv_bar[s]), 4);  // one arrival per converter warp
     }
     for (int d = 0; d < WQ_SLOTS; d++) {
-      mbar_init(smem_u32(&slot_full_bar[d]), NCONV);
+      mbar_init(smem_u32(&slot_full_bar[d]), NCONV / 32 > 0 ? NCONV / 32 : 1);  // one arrival per converter warp
       mbar_init(smem_u32(&slot_empty_bar[d]), 1);
     }
     for (int a = 0; a < 2; a++) {
@@ -547,11 +547,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             }
           }
           fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
+          // One arrival per warp, by lane 0 once all its lanes have fenced (a hundred single-thread
+          // arrivals on one barrier queue up in the shared-memory pipe; it measured the same here).
+          __syncwarp();
           if (WQ) {
-            mbar_arrive(smem_u32(&slot_full_bar[slot]));
+            if (lane == 0) mbar_arrive(smem_u32(&slot_full_bar[slot]));
             if (++slot == WQ_SLOTS) { slot = 0; slot_phase ^= 1; }
           } else {
-            mbar_arrive(smem_u32(&conv_bar[stage]));
+            if (lane == 0) mbar_arrive(smem_u32(&conv_bar[stage]));
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -846,6 +849,7 @@ int launch_common(tfjs_cuda_ctx* ctx, int amode, const float* a, const ConvGeom*
     }
     block_n = best;
   }
+  if (ctx->gemm_block_n && !(split && ctx->gemm_block_n > 128)) block_n = ctx->gemm_block_n;
 
   CUtensorMap ma, mh, ml, mc;
   bool ok = encode_2d(&mc, out, (uint64_t)M, (uint64_t)N, 32, 32);
