@@ -99,6 +99,17 @@ def test_batch64_against_oracle_and_float64(tf, stored):
         # fused blocks change the traffic and not a single bit
         got_l, _ = _device_logits(tf, net, x, "tf32", "forward_fused")
         assert np.array_equal(got_t, got_l)
+        # and with the deep pointwise layers on CTA pairs, as at the benchmark's batch (the
+        # dispatcher leaves 64 images to the single-CTA kernel): still not a single bit, in both modes
+        bk = tf.ENGINE.backend
+        bk.setOption("gemm_pair", 2)
+        try:
+            got_p, _ = _device_logits(tf, net, x, "tf32", "forward_separable")
+            assert np.array_equal(got_p, got_t)
+            got_p3, _ = _device_logits(tf, net, x, "3xtf32", "forward_fused")
+            assert np.array_equal(got_p3, got)
+        finally:
+            bk.setOption("gemm_pair", 1)
     finally:
         net.dispose()
 
