@@ -195,3 +195,45 @@ def test_pair_kernel_writes_nothing_past_its_output(tf):
         bk.setOption("gemm_pair", 1)
         bk.setOption("fuse_separable", 1)
         bk.setMathMode("3xtf32")
+
+
+@pytest.mark.parametrize("scale,mn", [(0.0078125, -1.0), (0.013731, -1.7576)])
+def test_pair_kernel_dequantises_uint8_weights_in_the_main_loop(tf, scale, mn):
+    """Option dequant_in_gemm on CTA pairs: the pointwise filter stays uint8 in device memory, each
+    CTA loads its 128 rows x 32 bytes per k-block and its converter warps expand them into the
+    tensor cores' operand tile.  Bit-identical to the cached-plane path on pairs and on single CTAs."""
+    from tfjs_core_b200 import conv_util
+    bk = tf.ENGINE.backend
+    bk.setMathMode("tf32")
+    bk.setOption("fuse_separable", 0)
+    try:
+        rng = np.random.Generator(np.random.PCG64(77))
+        b, hw, c, n = 5, 14, 512, 512                       # M = 980: three whole pair tiles + 212 rows
+        x = rng.uniform(-1, 1, (b, hw, hw, c)).astype(np.float32)
+        wd = rng.normal(0, 0.5, (3, 3, c, 1)).astype(np.float32)
+        q = rng.integers(0, 256, (1, 1, c, n), dtype=np.uint8)
+        bd = rng.normal(0, 0.3, c).astype(np.float32)
+        bp = rng.normal(0, 0.3, n).astype(np.float32)
+        ci = conv_util.compute_conv2d_info(x.shape, wd.shape, 1, 1, "same", None, True)
+        wq = bk.registerQuantized(list(q.shape), q, scale, mn)
+        outs = {}
+        for pair, in_loop in ((0, 0), (2, 0), (0, 1), (2, 1)):
+            bk.setOption("gemm_pair", pair)
+            bk.setOption("dequant_in_gemm", in_loop)
+            bk.profileBegin(16)
+            y = bk.fusedSeparableConv2d(tf.ops.tensor(x), tf.ops.tensor(wd), wq, ci, tf.ops.tensor(bd), "relu6",
+                                        tf.ops.tensor(bp), "linear")
+            outs[(pair, in_loop)] = y.dataSync().reshape(y.shape)
+            names = [name for name, _ in bk.profileEnd()]
+            if pair == 2 and in_loop == 1:
+                assert any("uint8 weights, CTA pairs" in name for name in names), names
+        for key in outs:
+            assert np.array_equal(outs[key], outs[(0, 0)]), key
+        w = oracle.dequant_u8(q, scale, mn)
+        want = _oracle_block(x, wd, w, bd, bp, "linear")
+        assert rel_err(outs[(2, 1)], want) <= 1e-3
+    finally:
+        bk.setOption("gemm_pair", 1)
+        bk.setOption("dequant_in_gemm", 0)
+        bk.setOption("fuse_separable", 1)
+        bk.setMathMode("3xtf32")

@@ -317,11 +317,13 @@ int set_wait_limit_sepconv(long long cycles);
 int set_wait_limit_depthwise_image(long long cycles);
 int set_wait_limit_gemm_pair(long long cycles);
 // gemm_tcgen05_pair.cu: the 256 x 256 tile on a pair of CTAs (tcgen05 cta_group::2); TF32 (w_lo null;
-// A rounded on chip unless a_tf32_exact) or 3xTF32 (w_lo = the residual weight plane)
+// A rounded on chip unless a_tf32_exact), 3xTF32 (w_lo = the residual weight plane), or TF32 with the
+// weights as uint8 bytes dequantised in the main loop (w_q; A tf32-exact)
 bool gemm_pair_supported(const tfjs_cuda_ctx* ctx, int64_t M, int64_t K, int64_t N);
 int launch_gemm_tcgen05_pair(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, const float* w_hi,
                              const float* w_lo, int64_t kp, float* out, int64_t N, const EpilogueArgs& epi,
-                             bool a_tf32_exact);
+                             bool a_tf32_exact, const uint8_t* w_q = nullptr, double q_scale = 0.0,
+                             double q_min = 0.0);
 // gemm_tcgen05.cu
 bool tcgen05_gemm_supported(int64_t M, int64_t N, int64_t K);
 // a_tf32_exact (TF32 mode only): every element of `a` already has its low 13 mantissa bits zero

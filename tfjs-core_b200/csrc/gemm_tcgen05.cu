@@ -816,6 +816,9 @@ int launch_common(tfjs_cuda_ctx* ctx, int amode, const float* a, const ConvGeom*
   // Large problems go to the CTA-pair kernel (256 x 256 tiles, half of the weight tile per SM).
   // (With on-chip rounding of A the pair kernel only wins on long contractions: 203 vs 211 us at
   // K = 512, 176 vs 187 at 1024, but 230 vs 219 at 128.)
+  if (amode == A_MATRIX && w_q && prec == PREC_TF32_ASIS && ctx->gemm_pair && kp == K &&
+      gemm_pair_supported(ctx, M, K, N))
+    return launch_gemm_tcgen05_pair(ctx, a, M, K, nullptr, nullptr, kp, out, N, epi, true, w_q, q_scale, q_min);
   if (amode == A_MATRIX && !w_q && ctx->gemm_pair && kp == K && gemm_pair_supported(ctx, M, K, N) &&
       (prec != PREC_TF32_ROUND || K >= 512 || ctx->gemm_pair >= 2))
     return launch_gemm_tcgen05_pair(ctx, a, M, K, w_hi, split ? w_lo : nullptr, kp, out, N, epi,

@@ -48,6 +48,13 @@ constexpr int B_BYTES = HALF_N * BLOCK_K * 4;  // 16 KB
 constexpr int PAIR_ASIS = 0;   // one pass, A already holds tf32-exact values
 constexpr int PAIR_SPLIT = 1;  // 3xTF32: converter warps split A into hi / lo, three passes
 constexpr int PAIR_ROUND = 2;  // one pass, converter warps round A to nearest in shared memory first
+constexpr int PAIR_WQ = 3;     // one pass, A tf32-exact, weights arrive as raw uint8 affine-quantised bytes
+                               // (each CTA its 128 rows x 32 bytes per k-block) and the converter warps
+                               // dequantise them in shared memory, k-block by k-block, inside the main loop:
+                               // w = float32(float64(q) * scale + min) (io_utils.ts:139), rounded to tf32,
+                               // straight into the swizzled operand tile the tensor cores read
+constexpr int Q_BYTES = HALF_N * BLOCK_K;  // 4 KB: this CTA's half of the uint8 weight tile
+constexpr int WQ_SLOTS = 3;                // ring of dequantised weight half-tiles (16 KB each)
 // SPLIT (3xTF32): a stage also holds the lo parts of A (written by the converter warps) and of the
 // weight half (loaded), so three stages of 64 KB instead of six of 32 KB.
 __host__ __device__ constexpr int num_stages(bool split) { return split ? 3 : 6; }
@@ -60,12 +67,18 @@ constexpr int LAYOUT_BYTES = 6 * (A_BYTES + B_BYTES) + C_STAGING_BYTES + BIAS_ST
 constexpr int SMEM_LIMIT = 232448;  // 227 KB
 static_assert(LAYOUT_BYTES <= SMEM_LIMIT, "shared memory budget exceeded");
 // 10 warps, plus (SPLIT) four converter warps that split each A stage into tf32 hi / lo
-__host__ __device__ constexpr int cta_threads(bool converts) { return converts ? 448 : 320; }
+// (eight of them when they dequantise uint8 weights)
+__host__ __device__ constexpr int cta_threads(int prec) { return prec == 0 ? 320 : (prec == 3 ? 576 : 448); }
 // Tensor memory, all 512 columns either way: two accumulator buffers of 256 columns, or (SPLIT) one
 // buffer made of a main tile (hi*hi) and a correction tile (lo*hi + hi*lo) that the epilogue adds.
 constexpr uint32_t TMEM_COLS = 512;
 
 struct PairParams {
+  double q_scale, q_min;  // PAIR_WQ: w = q * q_scale + q_min, evaluated in float64
+  // set when the host has checked, for all 256 byte values, that one float32 fma followed by the
+  // tf32 rounding gives the same bits as the float64 evaluation
+  float q_scale32, q_min32;
+  int q_arith;
   int M, N, K;
   int num_m_tiles, num_n_tiles, num_k_blocks;
   float* out;
@@ -120,16 +133,17 @@ __device__ __forceinline__ void tcgen05_mma_tf32_pair(uint32_t tmem_d, uint64_t 
 }
 
 template <int PREC>
-__global__ void __launch_bounds__(cta_threads(PREC != PAIR_ASIS), 1)
+__global__ void __launch_bounds__(cta_threads(PREC), 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                          const __grid_constant__ CUtensorMap map_w_lo, PairParams p) {
   constexpr bool SPLIT = PREC == PAIR_SPLIT;
-  constexpr bool CONVERTS = PREC != PAIR_ASIS;  // A passes through this CTA's converter warps
+  constexpr bool WQ = PREC == PAIR_WQ;
+  constexpr bool CONVERTS = PREC == PAIR_SPLIT || PREC == PAIR_ROUND;  // A passes through this CTA's converter warps
   constexpr int STAGES = num_stages(SPLIT);
   constexpr int NUM_ACC = SPLIT ? 1 : 2;
   constexpr uint32_t ACC_COLS = SPLIT ? 2 * TILE_N : TILE_N;  // tensor-memory columns per buffer
   // bytes that one CTA's loads complete on the leader's full barrier per stage
-  constexpr uint32_t STAGE_TX = SPLIT ? 2 * B_BYTES : (CONVERTS ? B_BYTES : A_BYTES + B_BYTES);
+  constexpr uint32_t STAGE_TX = SPLIT ? 2 * B_BYTES : (CONVERTS ? B_BYTES : (WQ ? A_BYTES : A_BYTES + B_BYTES));
   extern __shared__ uint8_t smem_raw[];
   const uint32_t align_pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
   uint32_t window;
@@ -142,7 +156,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   uint8_t* a_lo_st = a_st + STAGES * A_BYTES;                   // [STAGES] SPLIT only
   uint8_t* b_st = a_lo_st + (SPLIT ? STAGES * A_BYTES : 0);     // [STAGES] this CTA's half of the weight tile
   uint8_t* b_lo_st = b_st + STAGES * B_BYTES;                   // [STAGES] SPLIT only
-  uint8_t* c_stage = b_lo_st + (SPLIT ? STAGES * B_BYTES : 0);
+  // PAIR_WQ: b_st is a ring of WQ_SLOTS dequantised half-tiles instead, the raw bytes of every stage follow
+  uint8_t* q_st = b_st + WQ_SLOTS * B_BYTES;                    // [STAGES] WQ only
+  float* lut = reinterpret_cast<float*>(q_st + STAGES * Q_BYTES);  // [256] WQ only
+  uint8_t* c_stage = WQ ? reinterpret_cast<uint8_t*>(lut) + 1024 : b_lo_st + (SPLIT ? STAGES * B_BYTES : 0);
   uint8_t* bias_stage = c_stage + C_STAGING_BYTES;
   uint64_t* bars = (uint64_t*)(bias_stage + BIAS_STAGING_BYTES);
   uint64_t* full_bar = bars;                     // [STAGES] leader's: both CTAs' loads -> MMA
@@ -151,7 +168,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   uint64_t* conv_bar = bars + 3 * STAGES;        // [STAGES] SPLIT, leader's: both CTAs' converters -> MMA
   uint64_t* tmem_full_bar = bars + 4 * STAGES;   // [2] in each CTA: MMA -> local epilogue
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;  // [2] leader's: both CTAs' epilogues -> MMA
-  uint32_t* tmem_ptr_holder = (uint32_t*)(tmem_empty_bar + 2);
+  uint64_t* slot_full_bar = tmem_empty_bar + 2;  // [WQ_SLOTS] WQ, leader's: both CTAs' converters -> MMA
+  uint64_t* slot_empty_bar = slot_full_bar + WQ_SLOTS;  // [WQ_SLOTS] WQ, in each CTA: MMA -> local converters
+  uint32_t* tmem_ptr_holder = (uint32_t*)(slot_empty_bar + WQ_SLOTS);
   volatile int* abort_flag = (volatile int*)(tmem_ptr_holder + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -173,6 +192,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         mbar_init(smem_u32(&tmem_full_bar[a]), 1);
         mbar_init(smem_u32(&tmem_empty_bar[a]), 2 * EPI_WARPS);
       }
+      for (int d = 0; d < WQ_SLOTS; d++) {
+        mbar_init(smem_u32(&slot_full_bar[d]), 2 * 8);  // one arrival per converter warp of each CTA
+        mbar_init(smem_u32(&slot_empty_bar[d]), 1);
+      }
       *abort_flag = 0;
       fence_barrier_init();
     }
@@ -187,6 +210,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
   } else if (threadIdx.x == 0) {
     atomicCAS(p.status, 0, STATUS_SMEM_LAYOUT);
+  }
+  if (WQ && layout_ok && threadIdx.x >= 320) {
+    // a byte has 256 values: dequantise each once per CTA; the main loop only looks bytes up
+    for (int q = threadIdx.x - 320; q < 256; q += 256)
+      lut[q] = round_tf32((float)((double)q * p.q_scale + p.q_min));
   }
   tcgen05_fence_before();
   __syncthreads();
@@ -222,6 +250,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             tma_load_2d(smem_u32(a_st + stage * A_BYTES), &map_a, abar, kb * BLOCK_K, m0);
             tma_load_2d_pair(smem_u32(b_st + stage * B_BYTES), &map_w, bar, kb * BLOCK_K, n0);
             if (SPLIT) tma_load_2d_pair(smem_u32(b_lo_st + stage * B_BYTES), &map_w_lo, bar, kb * BLOCK_K, n0);
+          } else if (WQ) {
+            // A to the leader; this CTA's 4 KB of weight bytes to its own converters
+            const uint32_t qbar = smem_u32(&a_full_bar[stage]);
+            mbar_arrive_expect_tx(qbar, Q_BYTES);
+            tma_load_2d_pair(smem_u32(a_st + stage * A_BYTES), &map_a, bar, kb * BLOCK_K, m0);
+            tma_load_2d(smem_u32(q_st + stage * Q_BYTES), &map_w, qbar, kb * BLOCK_K, n0);
           } else {
             tma_load_2d_pair(smem_u32(a_st + stage * A_BYTES), &map_a, bar, kb * BLOCK_K, m0);
             tma_load_2d_pair(smem_u32(b_st + stage * B_BYTES), &map_w, bar, kb * BLOCK_K, n0);
@@ -236,6 +270,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       constexpr uint32_t idesc = make_idesc(PAIR_M, TILE_N);
       int stage = 0;
       uint32_t phase = 0;
+      int slot = 0;  // WQ: position in the ring of dequantised weight tiles
+      uint32_t slot_phase = 0;
       bool ok = true;
       int local = 0;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, local++) {
@@ -254,10 +290,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             // below, no cluster-scope fence of its own: one per k-block in this thread cost 20 %)
             ok = mbar_wait(smem_u32(&conv_bar[stage]), phase, abort_flag, p.status, 35);
           }
+          if (ok && WQ) ok = mbar_wait(smem_u32(&slot_full_bar[slot]), slot_phase, abort_flag, p.status, 37);
           if (!ok) break;
           tcgen05_fence_after();
           const uint32_t a_s = smem_u32(a_st + stage * A_BYTES);
-          const uint32_t b_s = smem_u32(b_st + stage * B_BYTES);
+          const uint32_t b_s = smem_u32(b_st + (WQ ? slot : stage) * B_BYTES);
           const uint32_t a_lo_s = smem_u32(a_lo_st + stage * A_BYTES);
           const uint32_t b_lo_s = smem_u32(b_lo_st + stage * B_BYTES);
 #pragma unroll
@@ -275,6 +312,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           const uint32_t eb = smem_u32(&empty_bar[stage]);
           tcgen05_commit_pair(eb);
           tcgen05_commit_pair(map_to_cta(eb, 1));
+          if (WQ) {  // and so is the dequantised tile, for the converters of both CTAs
+            const uint32_t sb = smem_u32(&slot_empty_bar[slot]);
+            tcgen05_commit_pair(sb);
+            tcgen05_commit_pair(map_to_cta(sb, 1));
+            if (++slot == WQ_SLOTS) { slot = 0; slot_phase ^= 1; }
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (ok) {  // accumulator complete: wake the epilogue of both CTAs
@@ -282,6 +325,59 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           tcgen05_commit_pair(fb);
           tcgen05_commit_pair(map_to_cta(fb, 1));
         }
+      }
+    }
+  } else if (warp >= 10 && WQ) {
+    // ---------------- converter warps (each CTA dequantises its own half of the weight tile) ----------------
+    const int t = threadIdx.x - 320;  // 0..255
+    int stage = 0, slot = 0;
+    uint32_t phase = 0, slot_phase = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      for (int kb = 0; kb < p.num_k_blocks; kb++) {
+        ok = mbar_wait(smem_u32(&a_full_bar[stage]), phase, abort_flag, p.status, 38);
+        if (ok) ok = mbar_wait(smem_u32(&slot_empty_bar[slot]), slot_phase ^ 1, abort_flag, p.status, 39);
+        if (!ok) break;
+        // the uint8 tile is [128 rows][32 bytes]; thread t dequantises the 16 bytes of half t & 1 of row t >> 1
+        const uint8_t* q_tile = q_st + stage * Q_BYTES;
+        uint8_t* w_tile = b_st + slot * B_BYTES;
+        const int n = t >> 1, half = t & 1;
+        const uint4 raw = *reinterpret_cast<const uint4*>(q_tile + n * 32 + half * 16);
+        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+        if (p.q_arith) {
+          // arithmetic form: byte -> float through the 2^23 mantissa trick, one fma, then
+          // round-to-nearest (ties away) to tf32 on the bit pattern
+          const uint32_t s32 = __float_as_uint(p.q_scale32), m32 = __float_as_uint(p.q_min32);
+          const uint64_t s2 = pack_f32x2(s32, s32), m2 = pack_f32x2(m32, m32);
+          const uint64_t neg_magic2 = pack_f32x2(0xCB000000u, 0xCB000000u);  // -2^23 twice
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            uint32_t h[4];
+#pragma unroll
+            for (int e = 0; e < 4; e += 2) {
+              // 0x4B0000qq is the float 2^23 + q: subtracting 2^23 leaves q exactly
+              const uint64_t r2 = pack_f32x2(__byte_perm(words[j], 0x4B000000u, 0x7540u + e),
+                                             __byte_perm(words[j], 0x4B000000u, 0x7541u + e));
+              unpack_f32x2(fma_f32x2(add_f32x2(r2, neg_magic2), s2, m2), h[e], h[e + 1]);
+              h[e] += 0x1000u;  // the tensor core reads the upper 19 bits only: this is the rounding
+              h[e + 1] += 0x1000u;
+            }
+            *reinterpret_cast<uint4*>(w_tile + swz(n, (half * 16 + j * 4) * 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            float h[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) h[e] = lut[(words[j] >> (8 * e)) & 0xffu];
+            *reinterpret_cast<float4*>(w_tile + swz(n, (half * 16 + j * 4) * 4)) = make_float4(h[0], h[1], h[2], h[3]);
+          }
+        }
+        fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor cores
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&slot_full_bar[slot]), 0));
+        if (++slot == WQ_SLOTS) { slot = 0; slot_phase ^= 1; }
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp >= 10) {
@@ -431,6 +527,23 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   }
 }
 
+// True when, for every byte value q, tf32(fma(float(q), float(scale), float(min))) has the same
+// bits as tf32(float32(double(q) * scale + min)): the kernel may then dequantise with float32
+// arithmetic and still feed the tensor cores exactly what the float64 formula would.
+bool dequant_exact_in_float32(double scale, double min) {
+  const float s32 = (float)scale, m32 = (float)min;
+  for (int q = 0; q < 256; q++) {
+    const float want = (float)((double)q * scale + min);
+    const float got = fmaf((float)q, s32, m32);
+    uint32_t wb, gb;
+    memcpy(&wb, &want, 4);
+    memcpy(&gb, &got, 4);
+    if ((wb & 0x7f800000u) == 0x7f800000u || (gb & 0x7f800000u) == 0x7f800000u) return false;
+    if (((wb + 0x1000u) & 0xffffe000u) != ((gb + 0x1000u) & 0xffffe000u)) return false;
+  }
+  return true;
+}
+
 bool encode_matrix(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
                    uint32_t box_cols) {
   const uint64_t dims[2] = {cols, rows};
@@ -463,7 +576,7 @@ int launch_pair_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtenso
   constexpr bool SPLIT = PREC == PAIR_SPLIT;
   auto kernel = gemm_tcgen05_pair_kernel<PREC>;
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(cta_threads(PREC != PAIR_ASIS));
+  cfg.blockDim = dim3(cta_threads(PREC));
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute attr[2];
@@ -492,6 +605,7 @@ int launch_pair_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtenso
   cfg.gridDim = dim3(2 * (unsigned)pairs);
   cfg.numAttrs = ctx->use_pdl ? 2 : 1;
   cudaLaunchKernelEx(&cfg, kernel, ma, mw, mw_lo, p);
+  if (PREC == PAIR_WQ) return post_launch(ctx, "gemm_tcgen05 (TF32, uint8 weights, CTA pairs)");
   return post_launch(ctx, SPLIT ? "gemm_tcgen05 (3xTF32, CTA pairs)" : "gemm_tcgen05 (TF32, CTA pairs)");
 }
 
@@ -502,13 +616,27 @@ int launch_pair_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& ma, const CUtenso
 // already rounded it to tf32, otherwise the converter warps round it in shared memory.
 int launch_gemm_tcgen05_pair(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int64_t K, const float* w_hi,
                              const float* w_lo, int64_t kp, float* out, int64_t N, const EpilogueArgs& epi,
-                             bool a_tf32_exact) {
+                             bool a_tf32_exact, const uint8_t* w_q, double q_scale, double q_min) {
+  // w_q: the weights as K-major uint8 bytes [N, kp] (then w_hi / w_lo are unused, TF32 only, A tf32-exact)
   CUtensorMap ma, mw, mw_lo;
-  if (!(encode_matrix(&ma, a, (uint64_t)M, (uint64_t)K, CTA_M, BLOCK_K) &&
-        encode_matrix(&mw, w_hi, (uint64_t)N, (uint64_t)kp, HALF_N, BLOCK_K) &&
-        encode_matrix(&mw_lo, w_lo ? w_lo : w_hi, (uint64_t)N, (uint64_t)kp, HALF_N, BLOCK_K)))
-    return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+  bool ok = encode_matrix(&ma, a, (uint64_t)M, (uint64_t)K, CTA_M, BLOCK_K);
+  if (w_q) {
+    const uint64_t dims[2] = {(uint64_t)kp, (uint64_t)N};
+    const uint64_t strides[1] = {(uint64_t)kp};
+    const uint32_t box[2] = {BLOCK_K, HALF_N};
+    ok = ok && tma_encode_tiled(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w_q, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    mw_lo = mw;
+  } else {
+    ok = ok && encode_matrix(&mw, w_hi, (uint64_t)N, (uint64_t)kp, HALF_N, BLOCK_K) &&
+         encode_matrix(&mw_lo, w_lo ? w_lo : w_hi, (uint64_t)N, (uint64_t)kp, HALF_N, BLOCK_K);
+  }
+  if (!ok) return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
   PairParams p;
+  p.q_scale = q_scale;
+  p.q_min = q_min;
+  p.q_scale32 = (float)q_scale;
+  p.q_min32 = (float)q_min;
+  p.q_arith = (w_q && dequant_exact_in_float32(q_scale, q_min)) ? 1 : 0;
   p.M = (int)M;
   p.N = (int)N;
   p.K = (int)K;
@@ -518,6 +646,7 @@ int launch_gemm_tcgen05_pair(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int6
   p.status = ctx->d_status;
   p.out = out;
   p.epi = epi;
+  if (w_q) return launch_pair_variant<PAIR_WQ>(ctx, ma, mw, mw_lo, p);
   if (w_lo) return launch_pair_variant<PAIR_SPLIT>(ctx, ma, mw, mw_lo, p);
   if (a_tf32_exact) return launch_pair_variant<PAIR_ASIS>(ctx, ma, mw, mw_lo, p);
   return launch_pair_variant<PAIR_ROUND>(ctx, ma, mw, mw_lo, p);
