@@ -54,6 +54,42 @@ def test_bounded_wait_reports_timeout_and_context_survives(tf, mode):
     assert rel_err(good, oracle.batch_matmul(a, b)[0]) <= (1e-3 if mode == "tf32" else 1e-5)
 
 
+@pytest.mark.parametrize("mode", ["tf32", "3xtf32"])
+def test_bounded_wait_on_cta_pairs(tf, mode):
+    """The same on the CTA-pair kernel, whose two CTAs wait on each other's barriers: with the last
+    loads of both producers withheld, every role of both CTAs gives up within the limit, both take
+    part in the closing cluster barrier, the pair frees its tensor memory, and the context goes on
+    working (tf32: the variant whose converter warps round A; 3xtf32: the split variant)."""
+    bk = tf.ENGINE.backend
+    rng = np.random.Generator(np.random.PCG64(6))
+    a = rng.uniform(-1, 1, (1, 300, 512)).astype(np.float32)
+    b = (rng.uniform(-1, 1, (1, 512, 256)) / 22.0).astype(np.float32)
+    bk.setMathMode(mode)
+    bk.setOption("gemm_pair", 2)
+    try:
+        bk.profileBegin(8)
+        warm = _matmul(tf, a, b)
+        want = warm.dataSync().reshape(300, 256)
+        assert any("CTA pairs" in name for name, _ in bk.profileEnd())
+        bk.setOption("wait_limit_us", 2000)
+        bk.setOption("test_withhold_last_load", 1)
+        try:
+            broken = _matmul(tf, a, b)
+            with pytest.raises(CudaError, match=r"\[-4\].*bounded wait"):
+                bk.sync()
+            broken.dispose()
+        finally:
+            bk.setOption("test_withhold_last_load", 0)
+            bk.setOption("wait_limit_us", 2_000_000)
+        bk.sync()
+        good = _matmul(tf, a, b).dataSync().reshape(300, 256)
+        assert np.array_equal(good, want)
+        assert rel_err(good, oracle.batch_matmul(a, b)[0]) <= (1e-3 if mode == "tf32" else 1e-5)
+    finally:
+        bk.setOption("gemm_pair", 1)
+        bk.setMathMode("3xtf32")
+
+
 def test_wait_limit_bounds_are_checked(tf):
     bk = tf.ENGINE.backend
     with pytest.raises(CudaError, match="wait_limit_us"):

@@ -82,6 +82,9 @@ struct PairParams {
   int M, N, K;
   int num_m_tiles, num_n_tiles, num_k_blocks;
   float* out;
+  // diagnostic: neither producer issues the loads of its last k-block, so the consumers' bounded
+  // waits run out (nothing is left in flight, both CTAs give up cleanly)
+  int withhold_last_load;
   int* status;
   EpilogueArgs epi;
 };
@@ -241,6 +244,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         for (int kb = 0; kb < p.num_k_blocks; kb++) {
           ok = mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.status, 31);
           if (!ok) break;
+          if (p.withhold_last_load && kb + 1 == p.num_k_blocks && tile + num_pairs >= num_tiles) {
+            ok = false;  // the consumers now wait for a stage that never fills
+            break;
+          }
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
           mbar_arrive_expect_tx_cluster(bar, STAGE_TX);
           if (CONVERTS) {
@@ -645,6 +652,7 @@ int launch_gemm_tcgen05_pair(tfjs_cuda_ctx* ctx, const float* a, int64_t M, int6
   p.num_k_blocks = (int)(K / BLOCK_K);
   p.status = ctx->d_status;
   p.out = out;
+  p.withhold_last_load = ctx->test_withhold_last_load ? 1 : 0;
   p.epi = epi;
   if (w_q) return launch_pair_variant<PAIR_WQ>(ctx, ma, mw, mw_lo, p);
   if (w_lo) return launch_pair_variant<PAIR_SPLIT>(ctx, ma, mw, mw_lo, p);
