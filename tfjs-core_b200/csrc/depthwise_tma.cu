@@ -95,6 +95,7 @@ depthwise3x3_image_kernel(const __grid_constant__ CUtensorMap map_x, ImageParams
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + MAX_STAGES);
   const uint32_t stages = smem_u32(smem) + HEADER_BYTES;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == CONSUMERS) prefetch_tensormap(&map_x);  // the producer's first lane
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.num_stages; s++) {

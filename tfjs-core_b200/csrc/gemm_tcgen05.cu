@@ -187,6 +187,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  if (threadIdx.x == 32 * 8) {  // the producer warp's first lane: descriptors on their way before the set-up below
+    if (AMODE == A_MATRIX) prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_w_hi);
+    if (SPLIT) prefetch_tensormap(&map_w_lo);
+    prefetch_tensormap(&map_c);
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {

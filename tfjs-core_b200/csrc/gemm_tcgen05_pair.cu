@@ -182,6 +182,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  if (threadIdx.x == 32 * 8) {  // the producer warp's first lane: descriptors on their way before the set-up below
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_w);
+    if (SPLIT) prefetch_tensormap(&map_w_lo);
+  }
 
   if (layout_ok) {
     if (threadIdx.x == 0) {

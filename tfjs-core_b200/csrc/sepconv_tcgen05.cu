@@ -426,6 +426,12 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 32 * 8) {  // the producer warp's first lane: descriptors on their way before the set-up below
+    prefetch_tensormap(&map_x);
+    prefetch_tensormap(&map_w);
+    if (SPLIT3) prefetch_tensormap(&map_w_lo);
+    prefetch_tensormap(&map_y);
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < RAW_STAGES; s++) {

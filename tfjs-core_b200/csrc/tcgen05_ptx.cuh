@@ -87,6 +87,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// Brings a tensor map (a kernel parameter) into the descriptor cache ahead of its first use, so
+// that the first load does not wait for the fetch; issued by one thread at kernel start.
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 // Asks the TMA unit to bring a tile into L2 only (no shared memory, no barrier): issued a few
 // k-blocks ahead of the real load, it turns that load's DRAM latency into an L2 hit.
 __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
