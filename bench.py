@@ -480,6 +480,12 @@ def run_cuda(args):
         layer_bytes = mobilenet.launch_algorithmic_bytes(per, cfg["quantized"], names, half)
         if pixels:
             layer_bytes[0] -= 3 * per * 224 * 224 * 3   # the stem reads one byte per value instead of four
+    # per launch of the forward pass: the median over the profile passes (one slow pass, e.g. the
+    # first after the graph replays, must not skew a kernel's figure); every pass then counts with it
+    import statistics
+    typical = [statistics.median(rows[i + k * launches_per_step][1] for k in range(prof_steps))
+               for i in range(launches_per_step)]
+    rows = [(rows[i][0], typical[i % launches_per_step]) for i in range(launches_per_step * prof_steps)]
     fam = {}
     for i, (name, ms) in enumerate(rows):
         f = KERNEL_FAMILY.get(name, name)
