@@ -69,10 +69,11 @@ def parse_args():
     ap.add_argument("--global-batch", type=int, default=0, help="override the workload's batch")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a graph")
     ap.add_argument("--pdl", action="store_true", help="programmatic dependent launch instead of plain stream order")
-    ap.add_argument("--streams", type=int, default=2, choices=[1, 2],
-                    help="2 (default): the steps alternate between two contexts (two streams, two sets of "
-                         "activation buffers) of the same GPU, so that the CTAs of one step's kernels take the "
-                         "SMs that the tail of the other step's kernel has left; 1: one context, one stream")
+    ap.add_argument("--streams", type=int, default=0, choices=[0, 1, 2, 3, 4],
+                    help="contexts (streams, each with its own activation buffers and captured graph) of the "
+                         "GPU that the steps take in turn, so that the CTAs of one step's kernels take the SMs "
+                         "that the tail of another step's kernel has left; 0 (default): 4 up to 128 images per "
+                         "GPU, else 2; 1: one context, one stream")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample", type=int, default=12, help="images in the cpu_baseline sample")
     ap.add_argument("--ref-threads", type=int, default=0, help="host threads of --impl reference (0 = all)")
@@ -446,65 +447,73 @@ def run_cuda(args):
         for o in outs:
             o.dispose()
 
-    # ---- optional second stream: a second context on the same device with its own network, input
-    # and captured graph; steps alternate between the two, so that the CTAs of one step's kernel
-    # take the SMs that the tail of the other step's kernel has already left ----
-    bk2 = graph2 = None
-    if args.streams == 2 and graph is not None:
-        bk2 = BackendCuda(d.local_rank, args.math)
-        ENGINE.registerBackend("bench-cuda-2", lambda: bk2, 9)
-        assert ENGINE.setBackend("bench-cuda-2")
-        try:
-            bk2.setOption("dequant_in_gemm", 1 if args.dequant == "in-loop" else 0)
-            bk2.setOption("pdl", 1 if args.pdl else 0)
-            if half:
-                bk2.setActivationStorage("float16")
-            net2 = mobilenet.MobileNetV1(params, bk2)
-            x2 = (bk2.registerQuantized(list(x_host.shape), x_host, 1.0 / 127.5, -1.0) if pixels
-                  else ops.tensor(x_host))
-            lg2, pr2 = pick_forward(net2, args)(x2)
-            assert np.array_equal(pr2.dataSync(), first)     # the second context computes the same bits
-            lg2.dispose()
-            pr2.dispose()
-            bk2.graphBegin()
-            pick_forward(net2, args)(x2)
-            graph2 = bk2.graphEnd()
-        finally:
-            assert ENGINE.setBackend("bench-cuda")
+    # ---- more streams: further contexts on the same device, each with its own network, input and
+    # captured graph; the steps take them in turn, so that the CTAs of one step's kernels take the
+    # SMs that the tail of another step's kernel has already left ----
+    n_streams = args.streams if args.streams > 0 else (4 if per <= 128 else 2)
+    others = []   # (backend, graph) of the additional contexts
+    if n_streams > 1 and graph is not None:
+        for k in range(1, n_streams):
+            bk_k = BackendCuda(d.local_rank, args.math)
+            name = "bench-cuda-%d" % (k + 1)
+            ENGINE.registerBackend(name, lambda b=bk_k: b, 9)
+            assert ENGINE.setBackend(name)
+            try:
+                bk_k.setOption("dequant_in_gemm", 1 if args.dequant == "in-loop" else 0)
+                bk_k.setOption("pdl", 1 if args.pdl else 0)
+                if half:
+                    bk_k.setActivationStorage("float16")
+                net_k = mobilenet.MobileNetV1(params, bk_k)
+                x_k = (bk_k.registerQuantized(list(x_host.shape), x_host, 1.0 / 127.5, -1.0) if pixels
+                       else ops.tensor(x_host))
+                lg_k, pr_k = pick_forward(net_k, args)(x_k)
+                assert np.array_equal(pr_k.dataSync(), first)     # every context computes the same bits
+                lg_k.dispose()
+                pr_k.dispose()
+                bk_k.graphBegin()
+                pick_forward(net_k, args)(x_k)
+                others.append((bk_k, bk_k.graphEnd()))
+            finally:
+                assert ENGINE.setBackend("bench-cuda")
         plain_step = step
 
         def step(counter=[0]):  # noqa: B006 -- the counter is the point
-            counter[0] ^= 1
-            if counter[0]:
+            turn = counter[0] % (len(others) + 1)
+            counter[0] += 1
+            if turn == 0:
                 return plain_step()
-            bk2.graphLaunch(graph2)
+            bk_k, graph_k = others[turn - 1]
+            bk_k.graphLaunch(graph_k)
             return None
 
     def timed(fn):
-        """Device time of fn's launches: CUDA events on the launching stream; with two streams both
-        are bracketed (their start events are recorded back to back on idle streams) and the
-        longer span counts."""
-        if bk2 is None:
-            return bk.time(fn)["kernelMs"]
-        spans = {}
+        """Device time of fn's launches: CUDA events on the launching stream; with several streams
+        all are bracketed (their start events are recorded back to back on idle streams) and the
+        longest span counts."""
+        spans = []
 
-        def inner():
-            spans["second"] = bk2.time(fn)["kernelMs"]
-        spans["first"] = bk.time(inner)["kernelMs"]
-        return max(spans.values())
+        def nest(k):
+            if k == len(others):
+                return fn()
+            spans.append(others[k][0].time(lambda: nest(k + 1))["kernelMs"])
+        spans.append(bk.time(lambda: nest(0))["kernelMs"])
+        return max(spans)
+
+    def all_launches():
+        return bk.launchCount() + sum(b.launchCount() for b, _ in others)
 
     # ---- device-resident throughput ----
     run_steps(args.warmup)
     bk.sync()
-    if bk2 is not None:
-        bk2.sync()
+    for bk_k, _ in others:
+        bk_k.sync()
     d.barrier()
     sampler = ClockSampler(d.local_rank)
     sampler.start()
-    launches_before = bk.launchCount() + (bk2.launchCount() if bk2 is not None else 0)
+    launches_before = all_launches()
     t = {"kernelMs": timed(lambda: run_steps(args.steps))}
     clocks = sampler.stop()
-    gpu_launches = bk.launchCount() + (bk2.launchCount() if bk2 is not None else 0) - launches_before
+    gpu_launches = all_launches() - launches_before
     d.barrier()
     ms_total = d.max(t["kernelMs"])
     ms_per_step = ms_total / args.steps
@@ -707,7 +716,7 @@ def run_cuda(args):
                        "activation_storage": "float16" if half else "float32", "input": args.input,
                        "launches_per_step": int(launches_per_step),
                        "launch": "eager" if graph is None else "cuda-graph replay",
-                       "streams": 2 if bk2 is not None else 1,
+                       "streams": len(others) + 1,
                        "l2": "every step streams %.1f GB of activations per GPU (> 126 MB L2) between reuses"
                              % (step_bytes / 1e9)},
             "parity_check": parity,
