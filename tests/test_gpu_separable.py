@@ -298,6 +298,34 @@ def test_conv2d_shifted_patch_tma(tf, b, h, w, cin, n, fh, fw, dil, pad):
         bk.setMathMode("3xtf32")
 
 
+@pytest.mark.parametrize("b,h,w,cin,n,fh,fw,dil,pad", [
+    (8, 56, 56, 64, 64, 3, 3, 1, "same"),     # BASELINE config 2's shape
+    (2, 20, 23, 32, 40, 3, 3, 1, "same"),     # overhanging patches, N not a multiple of 32
+    (1, 9, 9, 64, 8, 5, 5, 2, "same"),        # dilation 2
+    (3, 16, 16, 96, 128, 1, 3, 1, "valid"),   # widest N the 3xTF32 variant takes
+    (3, 16, 16, 96, 256, 1, 3, 1, "valid"),   # wider: the gather kernel, same tolerance
+])
+def test_conv2d_shifted_patch_tma_3xtf32(tf, b, h, w, cin, n, fh, fw, dil, pad):
+    """The same convolution in 3xTF32: the helper warps split each TMA-loaded A tile into tf32 hi (in
+    place) and lo (behind it), the filter arrives as hi and lo planes, three products per k-step.
+    Within 1e-5 of the oracle on values spread over several orders of magnitude."""
+    bk = tf.ENGINE.backend
+    bk.setMathMode("3xtf32")
+    rng = _rng(h * 31 + cin + n + 3)
+    x = (rng.uniform(-1, 1, (b, h, w, cin)) * 10.0 ** rng.integers(-2, 2, (b, h, w, cin))).astype(np.float32)
+    wt = rng.normal(0, 0.2, (fh, fw, cin, n)).astype(np.float32)
+    bias = rng.normal(0, 0.3, n).astype(np.float32)
+    ci = oracle.compute_conv2d_info(x.shape, wt.shape, 1, dil, pad)
+    want = oracle.fused_conv2d(x, wt, ci, bias=bias, activation="relu")
+    bk.profileBegin(8)
+    got = tf.ops.fused_conv2d(tf.ops.tensor(x), tf.ops.tensor(wt), 1, pad, dilations=dil,
+                              bias=tf.ops.tensor(bias), activation="relu")
+    out = got.dataSync().reshape(want.shape)
+    names = [name for name, _ in bk.profileEnd()]
+    assert (names[-1] == "conv2d_tcgen05 (shifted-patch TMA, 3xTF32)") == (n <= 128), names
+    assert rel_err(out, want) <= 1e-5
+
+
 @pytest.mark.parametrize("c,h,stride", [(32, 16, 1), (64, 28, 2), (256, 28, 1)])
 def test_non_finite_filter_taps_at_the_border(tf, c, h, stride):
     """The reference skips filter taps that fall outside the image (backend_cpu.ts:2002-2014);

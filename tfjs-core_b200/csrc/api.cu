@@ -390,7 +390,7 @@ extern "C" int tfjs_cuda_conv2d(tfjs_cuda_ctx* ctx, tfjs_tensor_id x_id, tfjs_te
     rc = packed_weights(ctx, w, 0, (int64_t)ci->filterHeight * ci->filterWidth * ci->inChannels,
                         ci->outChannels, false, true, &pw, &temporary);
     if (rc) return done(rc);
-    return done(launch_conv_tma_tcgen05(ctx, xv.ptr, *ci, pw.hi, pw.kp, ov.ptr, e));
+    return done(launch_conv_tma_tcgen05(ctx, xv.ptr, *ci, pw.hi, pw.kp, ov.ptr, e, split3 ? pw.lo : nullptr));
   }
   // Everything else with Cin % 4 == 0 (or a 3-channel, 3-wide filter) is an implicit GEMM: the
   // A tile is gathered from the image by the kernel itself, K = fH * fW * Cin.

@@ -370,7 +370,7 @@ int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const void* x, const tfjs_conv2d
                             double q_scale = 0.0, double q_min = 0.0, const float* w_lo = nullptr);
 bool conv_tma_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode);
 int launch_conv_tma_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& ci, const float* w_hi,
-                            int64_t kp, float* y, const EpilogueArgs& epi);
+                            int64_t kp, float* y, const EpilogueArgs& epi, const float* w_lo = nullptr);
 // conv.cu
 int launch_conv2d_direct(tfjs_cuda_ctx* ctx, const float* x, const float* w, float* y,
                          const tfjs_conv2d_info& ci, const EpilogueArgs& epi);

@@ -39,6 +39,11 @@ constexpr int A_SLOTS = 2;
 // MODE_RGB in 3xTF32 (see the list of modes below): an A slot holds the hi and the lo tile, a weight
 // stage the hi and the lo plane of the filter.
 constexpr int MODE_RGB3 = 3;
+// MODE_CONV in 3xTF32: the stage the TMA load filled becomes the hi tile, the helper warps write the
+// lo tile behind it (a stage is 32 KB), the filter arrives as hi and lo planes.
+constexpr int MODE_CONV3 = 5;
+__host__ __device__ constexpr bool is_conv(int mode) { return mode == 2 || mode == MODE_CONV3; }
+__host__ __device__ constexpr bool is_split3(int mode) { return mode == MODE_RGB3 || mode == MODE_CONV3; }
 // Stride-1 depthwise blocks of 256 columns build the A tile IN PLACE: a window (10 x 18 x 128 B = 23 KB) is larger
 // than the tile made from it (16 KB), so once the threads of a group have all read their window
 // taps into registers (a named barrier) they write the tile over the start of the same stage, the
@@ -53,7 +58,7 @@ __host__ __device__ constexpr bool a_in_place(int block_n, int s, int mode, bool
   return mode == 0 && s == 1 && block_n >= 256 && !in16;
 }
 __host__ __device__ constexpr int a_slot_bytes(int block_n, int s, int mode, bool in16 = false) {
-  return a_in_place(block_n, s, mode, in16) ? 0 : A_SLOTS * A_TILE_BYTES * (mode == MODE_RGB3 ? 2 : 1);
+  return (a_in_place(block_n, s, mode, in16) || is_conv(mode)) ? 0 : A_SLOTS * A_TILE_BYTES * (mode == MODE_RGB3 ? 2 : 1);
 }
 constexpr int EPI_WARPS = 8;
 constexpr int C_CHUNK_BYTES = 32 * 32 * 4;
@@ -64,7 +69,7 @@ constexpr int DW_THREADS = 256;
 // two groups of 128 on alternate k-blocks.  With two groups every A slot, raw stage and barrier
 // belongs to one group only: a parity wait is only safe for a thread that watches every phase of
 // its barrier, and a group does not see the phases of the k-blocks it skips.
-__host__ __device__ constexpr int dw_groups(int s, int mode) { return (mode == 2 || (mode == 0 && s == 2)) ? 1 : 2; }
+__host__ __device__ constexpr int dw_groups(int s, int mode) { return (is_conv(mode) || (mode == 0 && s == 2)) ? 1 : 2; }
 constexpr int THREADS = 320 + DW_THREADS;
 constexpr int MAX_C = 256;                        // depthwise channels (= K of the GEMM)
 constexpr int DW_TABLE_BYTES = 10 * MAX_C * 4;    // 9 filter taps + bias per channel
@@ -102,8 +107,8 @@ struct Raw {
   // slack in front so that the copy can start on a 16-byte boundary, rounded up to 16 bytes
   static constexpr int ROW_FLOATS = MODE == MODE_DW ? COLS * BLOCK_K
                                     : (IN8 ? (COLS * 3 + 15 + 15) / 16 * 16 : (COLS * 3 + 3 + 3) / 4 * 4);
-  static constexpr int BYTES = MODE == MODE_CONV ? A_TILE_BYTES : ROWS * ROW_FLOATS * ELEM;
-  static constexpr int STRIDE = (BYTES + 1023) / 1024 * 1024;
+  static constexpr int BYTES = is_conv(MODE) ? A_TILE_BYTES : ROWS * ROW_FLOATS * ELEM;   // what the load deposits
+  static constexpr int STRIDE = MODE == MODE_CONV3 ? 2 * A_TILE_BYTES : (BYTES + 1023) / 1024 * 1024;
   static constexpr int GROUP_THREADS = DW_THREADS / dw_groups(S, MODE);
   static constexpr int TR = S == 1 ? 2 : 1;                            // a thread's block of outputs: rows
   static constexpr int TC = PW * PART_ROWS * 8 / (TR * GROUP_THREADS);  // and columns (4 / 2)
@@ -116,7 +121,7 @@ __host__ __device__ constexpr int w_stages(int block_n, int s, int mode) {
 }
 __host__ __device__ constexpr bool is_rgb(int mode) { return mode == MODE_RGB || mode == MODE_RGB3; }
 __host__ __device__ constexpr int w_stage_bytes(int block_n, int mode) {
-  return block_n * BLOCK_K * 4 * (mode == MODE_RGB3 ? 2 : 1);
+  return block_n * BLOCK_K * 4 * (is_split3(mode) ? 2 : 1);
 }
 __host__ __device__ constexpr int epi_arrivals(int block_n) { return block_n >= 64 ? EPI_WARPS : 4; }
 template <int S, int MODE, bool IN16 = false, bool IN8 = false>
@@ -367,7 +372,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
                        const __grid_constant__ CUtensorMap map_w_lo, const __grid_constant__ CUtensorMap map_y,
                        SepParams p) {
   static_assert(!IN8 || MODE == MODE_RGB, "byte input is the 3-channel stem's");
-  constexpr bool SPLIT3 = MODE == MODE_RGB3;
+  constexpr bool SPLIT3 = is_split3(MODE);
   constexpr int A_SLOT_STRIDE = A_TILE_BYTES * (SPLIT3 ? 2 : 1);
   constexpr bool IN16 = HALF && MODE == MODE_DW;
   constexpr bool OUT16 = HALF;
@@ -380,7 +385,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   constexpr bool IN_PLACE = a_in_place(BLOCK_N, S, MODE, IN16);
   // MODE_CONV: the stage the TMA load filled IS the A tile; the helper warps only round it to tf32
   // in place before the tensor core reads it
-  constexpr bool STAGE_IS_A = IN_PLACE || MODE == MODE_CONV;
+  constexpr bool STAGE_IS_A = IN_PLACE || is_conv(MODE);
   constexpr int NUM_A = STAGE_IS_A ? RAW_STAGES : A_SLOTS;  // A tiles (and their full barriers)
   static_assert(!IN_PLACE || (R::BYTES >= A_TILE_BYTES && R::STRIDE % 1024 == 0), "the tile fits its window's stage");
   static_assert(GROUPS == 1 || R::PARTS == 1, "two groups take whole k-blocks of one raw stage each");
@@ -402,7 +407,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
   // stage is the A operand itself) the commit of the MMAs that read it
   // (one arrival per warp, by lane 0 after __syncwarp: 256 single-thread arrivals on one barrier
   // serialise in the shared-memory pipe, which is the busiest unit of this kernel)
-  constexpr int RAW_READERS = MODE == MODE_CONV ? 1 : GROUP_THREADS / 32;
+  constexpr int RAW_READERS = is_conv(MODE) ? 1 : GROUP_THREADS / 32;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -505,6 +510,9 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
           if (!ok) break;
           mbar_arrive_expect_tx(smem_u32(&w_full[ws]), W_STAGE_BYTES);
           tma_load_2d(smem_u32(w_tiles + ws * W_STAGE_BYTES), &map_w, smem_u32(&w_full[ws]), kb * BLOCK_K, 0);
+          if (SPLIT3)
+            tma_load_2d(smem_u32(w_tiles + ws * W_STAGE_BYTES + W_PLANE_BYTES), &map_w_lo, smem_u32(&w_full[ws]),
+                        kb * BLOCK_K, 0);
           if (++ws == W_STAGES) { ws = 0; wphase ^= 1; }
           for (int part = 0; part < R::PARTS; part++, rn++) {
             int rs;
@@ -513,7 +521,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
             ok = mbar_wait(smem_u32(&raw_empty[rs]), rphase ^ 1, abort_flag, p.status, 12);
             if (!ok) break;
             mbar_arrive_expect_tx(smem_u32(&raw_full[rs]), R::BYTES);
-            if (MODE == MODE_CONV) {
+            if (is_conv(MODE)) {
               const int tap = kb / p.cin_groups, cg = kb - tap * p.cin_groups;
               const int wr = tap / p.fw, wc = tap - wr * p.fw;
               tma_load_4d(smem_u32(raw + rs * R::STRIDE), &map_x, smem_u32(&raw_full[rs]), cg * BLOCK_K,
@@ -609,8 +617,8 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
             ring_pos(n, A_SLOTS, slot, sphase);
           }
           ok = mbar_wait(smem_u32(&w_full[ws]), wphase, abort_flag, p.status, 14);
-          if (ok && MODE == MODE_CONV) ok = mbar_wait(smem_u32(&a_full[rs]), rphase, abort_flag, p.status, 15);
-          if (ok && MODE != MODE_CONV) ok = mbar_wait(smem_u32(&a_full[slot]), sphase, abort_flag, p.status, 15);
+          if (ok && is_conv(MODE)) ok = mbar_wait(smem_u32(&a_full[rs]), rphase, abort_flag, p.status, 15);
+          if (ok && !is_conv(MODE)) ok = mbar_wait(smem_u32(&a_full[slot]), sphase, abort_flag, p.status, 15);
           if (!ok) break;
           tcgen05_fence_after();
           const uint32_t a_s = STAGE_IS_A ? smem_u32(raw + rs * R::STRIDE)
@@ -635,7 +643,7 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
         if (ok) tcgen05_commit(smem_u32(&tmem_full_bar[acc]));
       }
     }
-  } else if (warp >= 10 && MODE == MODE_CONV) {
+  } else if (warp >= 10 && is_conv(MODE)) {
     // ---------------- rounding warps ----------------
     // The A tile arrives from TMA in the layout the tensor core reads, as raw float32.  The tensor
     // core would truncate it to tf32; these 256 threads round it to nearest in place (element-wise,
@@ -654,6 +662,19 @@ sepconv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
 #pragma unroll
         for (int i = 0; i < A_TILE_BYTES / 16 / DW_THREADS; i++) {
           float4 v = tile4[t + i * DW_THREADS];
+          if (SPLIT3) {
+            // 3xTF32: hi = tf32(a) in place, lo = tf32(a - hi) into the tile behind it (a non-finite
+            // hi keeps lo at zero: inf - inf would poison the product with NaN)
+            float4 h, l;
+            h.x = round_tf32(v.x); h.y = round_tf32(v.y); h.z = round_tf32(v.z); h.w = round_tf32(v.w);
+            l.x = (fabsf(h.x) <= 3.4028234e38f) ? round_tf32(v.x - h.x) : 0.f;
+            l.y = (fabsf(h.y) <= 3.4028234e38f) ? round_tf32(v.y - h.y) : 0.f;
+            l.z = (fabsf(h.z) <= 3.4028234e38f) ? round_tf32(v.z - h.z) : 0.f;
+            l.w = (fabsf(h.w) <= 3.4028234e38f) ? round_tf32(v.w - h.w) : 0.f;
+            tile4[t + i * DW_THREADS] = h;
+            tile4[A_TILE_BYTES / 16 + t + i * DW_THREADS] = l;
+            continue;
+          }
           v.x = round_tf32_for_mma(v.x); v.y = round_tf32_for_mma(v.y);
           v.z = round_tf32_for_mma(v.z); v.w = round_tf32_for_mma(v.w);
           tile4[t + i * DW_THREADS] = v;
@@ -862,6 +883,7 @@ int launch_variant(tfjs_cuda_ctx* ctx, const CUtensorMap& mx, const CUtensorMap&
   if (MODE == MODE_RGB)
     return post_launch(ctx, HALF ? "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32, float16 out)"
                                  : "conv2d_tcgen05 (3-channel 3x3, window TMA, TF32)");
+  if (MODE == MODE_CONV3) return post_launch(ctx, "conv2d_tcgen05 (shifted-patch TMA, 3xTF32)");
   if (MODE == MODE_CONV) return post_launch(ctx, "conv2d_tcgen05 (shifted-patch TMA, TF32)");
   if (HALF)
     return post_launch(ctx, S == 1 ? "separableConv2d (fused dw3x3 s1 + pw, TF32, float16)"
@@ -882,7 +904,7 @@ int launch_stride(tfjs_cuda_ctx* ctx, int block_n, const CUtensorMap& mx, const 
     case 128: return launch_variant<128, S, MODE, HALF, IN8>(ctx, mx, mw, my, p, mw_lo);
     default:
       // (no 256-column 3xTF32 stem: two 64 KB weight stages and the hi / lo A slots leave no room for windows)
-      if constexpr (MODE == MODE_RGB3) return set_error(ctx, TFJS_CUDA_ERR_INVALID_ARG, "3xTF32 stem takes at most 128 output channels");
+      if constexpr (is_split3(MODE)) return set_error(ctx, TFJS_CUDA_ERR_INVALID_ARG, "the 3xTF32 variants take at most 128 output channels");
       else return launch_variant<256, S, MODE, HALF, IN8>(ctx, mx, mw, my, p, mw_lo);
   }
 }
@@ -1054,7 +1076,7 @@ int launch_conv_rgb_tcgen05(tfjs_cuda_ctx* ctx, const void* x, const tfjs_conv2d
 // Dense convolution with Cin a multiple of 32 and stride 1 (any filter size and dilation), TF32:
 // every k-block's A tile is the output patch shifted by one filter tap, fetched by one TMA load.
 bool conv_tma_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int math_mode) {
-  return math_mode == TFJS_MATH_TF32 && ci.inChannels >= 32 && ci.inChannels % 32 == 0 && ci.strideHeight == 1 &&
+  return (math_mode == TFJS_MATH_TF32 || (math_mode == TFJS_MATH_TF32X3 && ci.outChannels <= 128)) && ci.inChannels >= 32 && ci.inChannels % 32 == 0 && ci.strideHeight == 1 &&
          ci.strideWidth == 1 && ci.outChannels >= 8 && ci.outChannels <= 256 && ci.outChannels % 4 == 0 &&
          ci.batchSize >= 1 && ci.batchSize < 65536 && ci.outHeight >= 1 && ci.outWidth >= 1 &&
          (int64_t)ci.filterHeight * ci.filterWidth * ci.inChannels < (1ll << 24) && activation != TFJS_ACT_PRELU &&
@@ -1062,7 +1084,7 @@ bool conv_tma_tcgen05_supported(const tfjs_conv2d_info& ci, int activation, int 
 }
 
 int launch_conv_tma_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2d_info& ci, const float* w_hi,
-                            int64_t kp, float* y, const EpilogueArgs& epi) {
+                            int64_t kp, float* y, const EpilogueArgs& epi, const float* w_lo) {  // w_lo: 3xTF32
   const int64_t N = ci.outChannels;
   const int C = ci.inChannels;
   const int block_n = N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256));
@@ -1103,5 +1125,11 @@ int launch_conv_tma_tcgen05(tfjs_cuda_ctx* ctx, const float* x, const tfjs_conv2
   p.num_k_blocks = ci.filterHeight * ci.filterWidth * p.cin_groups;
   p.epi = epi;
   p.status = ctx->d_status;
+  if (w_lo) {
+    CUtensorMap mwl;
+    if (!tma_encode_tiled(&mwl, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, w_lo, wd, ws, wb, CU_TENSOR_MAP_SWIZZLE_128B))
+      return set_error(ctx, TFJS_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+    return launch_stride<1, MODE_CONV3>(ctx, block_n, mx, mw, my, p, &mwl);
+  }
   return launch_stride<1, MODE_CONV>(ctx, block_n, mx, mw, my, p);
 }
