@@ -304,6 +304,10 @@ KERNEL_FAMILY = {"separableConv2d (fused dw3x3 s1 + pw, TF32, float16)": "separa
                  "separableConv2d (fused dw3x3 s2 + pw, TF32)": "separable_fused",
                  "gemm_tcgen05 (TF32)": "gemm_tcgen05", "gemm_tcgen05 (3xTF32)": "gemm_tcgen05",
                  "gemm_tcgen05 (TF32, CTA pairs)": "gemm_tcgen05",
+                 "gemm_tcgen05 (3xTF32, CTA pairs)": "gemm_tcgen05",
+                 "gemm_tcgen05 (TF32, uint8 weights, CTA pairs)": "gemm_tcgen05",
+                 "conv2d_tcgen05 (3-channel 3x3, window TMA, 3xTF32)": "conv2d_tcgen05",
+                 "conv2d_tcgen05 (shifted-patch TMA, 3xTF32)": "conv2d_tcgen05",
                  "gemm_tcgen05 (TF32, uint8 weights)": "gemm_tcgen05",
                  "gemm_tcgen05 (3xTF32, uint8 weights)": "gemm_tcgen05",
                  "conv2d_tcgen05 (TF32)": "conv2d_tcgen05", "conv2d_tcgen05 (3xTF32)": "conv2d_tcgen05",
