@@ -200,3 +200,23 @@ def test_context_creation_reports_errors_without_a_gpu():
     rc = lib.tfjs_cuda_ctx_create(0, ctypes.byref(ctx))
     assert rc == _ffi.ERR_CUDA and not ctx.value
     assert b"CUDA device" in lib.tfjs_cuda_last_error(None)
+
+
+def test_bench_groups_every_hot_path_kernel_name_into_a_family():
+    """bench.py reports per-family times (`kernels{}`, `roofline.kernel`) by the names the library
+    gives its launches: every name of a kernel on the inference path that the sources can report
+    must be in its table, or a new variant would show up as a family of its own."""
+    import importlib.util
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_for_test", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    names = set()
+    csrc = os.path.join(root, "tfjs-core_b200", "csrc")
+    for fn in os.listdir(csrc):
+        text = open(os.path.join(csrc, fn)).read()
+        names.update(re.findall(r'"((?:gemm_tcgen05|conv2d_tcgen05|separableConv2d|depthwiseConv2D \(3x3|avgPool \(global|softmax_last)[^"]*)"', text))
+    names = {n for n in names if "(" in n}   # kernel names carry their variant in parentheses; error texts do not
+    assert len(names) >= 20, names
+    missing = sorted(n for n in names if n not in bench.KERNEL_FAMILY)
+    assert not missing, missing
